@@ -1,0 +1,85 @@
+"""ctypes loader of `libb200backend.so`.
+
+The shared library is the product; nothing in this package computes on the CPU.
+Loading fails loudly when the library has not been built (`python -m fandhe_ai_b200.build`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libb200backend.so"
+
+_lib = None
+
+
+class BackendError(RuntimeError):
+    """Mirror of the reference's `BackendError` (crates/tensor-core/src/device.rs:225-371):
+    `kind` is the variant name, `status` the C-ABI code."""
+
+    def __init__(self, status: int, kind: str, message: str):
+        super().__init__(f"{kind}: {message}")
+        self.status = status
+        self.kind = kind
+        self.message = message
+
+
+def lib() -> C.CDLL:
+    """Returns the loaded library, loading it on first use."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m fandhe_ai_b200.build` "
+                "(this backend has no CPU or PyTorch fallback)"
+            )
+        _lib = C.CDLL(str(LIB_PATH))
+        _declare(_lib)
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        l = lib()
+        raise BackendError(status, l.b200_status_name(status).decode(), l.b200_last_error().decode())
+
+
+_P = C.c_void_p
+_SZ = C.c_size_t
+_I32 = C.c_int32
+_I64 = C.c_int64
+
+# name -> (restype, argtypes); every symbol declared in include/b200_backend.h
+SIGNATURES = {
+    "b200_last_error": (C.c_char_p, []),
+    "b200_status_name": (C.c_char_p, [_I32]),
+    "b200_ctx_create": (_I32, [_I32, C.POINTER(_P)]),
+    "b200_ctx_destroy": (_I32, [_P]),
+    "b200_synchronize": (_I32, [_P]),
+    "b200_ctx_is_poisoned": (_I32, [_P]),
+    "b200_ctx_generation": (C.c_uint64, [_P]),
+    "b200_ctx_stream": (_P, [_P]),
+    "b200_gemm_tuning": (_I32, [_P, _I32, _I32]),
+    "b200_alloc_zeroed": (_I32, [_P, _SZ, C.POINTER(_P)]),
+    "b200_upload": (_I32, [_P, _P, _SZ, C.POINTER(_P)]),
+    "b200_upload_into": (_I32, [_P, _P, _SZ, _P, _SZ]),
+    "b200_download": (_I32, [_P, _P, _SZ, _P, _SZ]),
+    "b200_release": (_I32, [_P, _P]),
+    "b200_buf_bytes": (_SZ, [_P]),
+    "b200_buf_device_ptr": (_P, [_P]),
+    "b200_quantize_i8_per_row": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ]),
+    "b200_dequantize_i8_per_row": (_I32, [_P, _P, _SZ, _P, _SZ, _I64, _I64, _P, _SZ]),
+    "b200_quantize_fp8_e4m3_per_tensor": (_I32, [_P, _P, _SZ, _I64, _P, _SZ, _P, _SZ]),
+    "b200_gemm_i8_s32": (_I32, [_P, _P, _SZ, _P, _SZ, _I64, _I64, _I64, _P, _SZ]),
+    "b200_gemm_q8_scaled": (_I32, [_P, _I32, _P, _SZ, _P, _SZ, _I32, _P, _SZ, _P, _SZ, _I32, _P, _SZ, _I32,
+                                   _P, _SZ, _I64, _I64, _I64, _I32, _P, _SZ]),
+    "b200_linear_w8a8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _P, _SZ]),
+}
+
+
+def _declare(l: C.CDLL) -> None:
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(l, name)
+        fn.restype = res
+        fn.argtypes = args

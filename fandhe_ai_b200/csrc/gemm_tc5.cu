@@ -1,0 +1,466 @@
+// tcgen05 / TMEM quantized GEMM for sm_100a.
+//
+// One CTA computes a 128 x BN accumulator tile (optionally over a slice of K).
+// Warp roles: warp 0 = TMA producer (one elected lane), warp 1 = TMEM owner and
+// MMA issuer (one elected lane), warps 2..5 = epilogue (each reads the 32 TMEM
+// lanes of its quarter).  Operand tiles are K-major with 128-byte rows, written
+// by TMA with the 128-byte swizzle and consumed by tcgen05.mma through
+// shared-memory descriptors; a ring of `stages` buffers is handed back and forth
+// with full/empty mbarriers; the accumulator lives in TMEM until the epilogue
+// pulls it out with tcgen05.ld.
+//
+// Replaces, for the quantized path, the reference's fused GEMM kernels
+// gemm_tiled_bias_act_f32 (crates/backend-cuda/src/kernels.rs:368-477) and
+// gemm_mma_f16 (crates/backend-cuda/src/kernels_mma.rs:227-375).
+#include "gemm_tc5.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kBM = 128;       // accumulator rows per CTA = TMEM lanes
+constexpr int kBK = 128;       // operand bytes along K per stage (one swizzle row)
+constexpr int kUmmaK = 32;     // K per tcgen05.mma for 8-bit operands
+constexpr int kThreads = 192;
+constexpr int kABytes = kBM * kBK;
+
+struct KernelArgs {
+    int M, N, K;
+    int stages;
+    int kb_total;        // ceil(K / kBK)
+    int kb_per_split;
+    int gate;            // B tile = bn/2 gate rows + bn/2 up rows
+    int n_half;          // N / 2 in the gate form
+    GemmEpilogue ep;
+    uint32_t* err;
+};
+
+template <bool kInt8>
+__device__ __forceinline__ float acc_to_f32(uint32_t v) {
+    if constexpr (kInt8) return static_cast<float>(static_cast<int32_t>(v));
+    return __uint_as_float(v);
+}
+
+__device__ __forceinline__ void store_out4(const GemmEpilogue& ep, size_t idx, float y0, float y1, float y2, float y3) {
+    if (ep.residual) {
+        const float4 r = *reinterpret_cast<const float4*>(ep.residual + idx);
+        y0 += r.x; y1 += r.y; y2 += r.z; y3 += r.w;
+    }
+    if (ep.out_bf16) {
+        uint2 o;
+        o.x = f32_to_bf16_bits(y0) | (f32_to_bf16_bits(y1) << 16);
+        o.y = f32_to_bf16_bits(y2) | (f32_to_bf16_bits(y3) << 16);
+        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(ep.out) + idx) = o;
+    } else {
+        *reinterpret_cast<float4*>(static_cast<float*>(ep.out) + idx) = make_float4(y0, y1, y2, y3);
+    }
+}
+
+template <int BN, bool kInt8>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, KernelArgs p) {
+    constexpr int kBBytes = BN * kBK;
+    constexpr int kStageBytes = kABytes + kBBytes;
+    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kIdesc = kInt8 ? umma_idesc(1, 2, kBM, BN) : umma_idesc(0, 1, kBM, BN);
+
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + p.stages * kStageBytes;   // full[s], empty[s], tmem_full, tmem slot
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (p.stages + s); };
+    const uint32_t tmem_full_bar = bar_base + 8u * (2 * p.stages);
+    const uint32_t tmem_slot = tmem_full_bar + 8u;
+    // generic pointer to the TMEM-address slot
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_dyn + (tmem_slot - smem_u32(smem_dyn)));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tma_a);
+        tma_prefetch_desc(&tma_b);
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tmem_full_bar, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc5_fence_before();
+    __syncthreads();
+    tc5_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    const int out_cols = p.gate ? BN / 2 : BN;          // output columns per CTA
+    const int n0 = blockIdx.x * out_cols;               // first output column
+    const int m0 = blockIdx.y * kBM;
+    const int split = blockIdx.z;
+    const int kb_begin = split * p.kb_per_split;
+    int kb_end = kb_begin + p.kb_per_split;
+    if (kb_end > p.kb_total) kb_end = p.kb_total;
+    const int num_kb = kb_end > kb_begin ? kb_end - kb_begin : 0;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            for (int i = 0; i < num_kb; ++i) {
+                const int s = i % p.stages;
+                const uint32_t ph = (i / p.stages) & 1;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, p.err, kErrProducerWait)) break;
+                mbar_arrive_expect_tx(full_bar(s), kStageBytes);
+                const uint32_t a_dst = smem_base + s * kStageBytes;
+                const uint32_t b_dst = a_dst + kABytes;
+                const int kx = (kb_begin + i) * kBK;
+                tma_load_2d(a_dst, &tma_a, full_bar(s), kx, m0);
+                if (p.gate) {
+                    tma_load_2d(b_dst, &tma_b, full_bar(s), kx, n0);
+                    tma_load_2d(b_dst + (BN / 2) * kBK, &tma_b, full_bar(s), kx, p.n_half + n0);
+                } else {
+                    tma_load_2d(b_dst, &tma_b, full_bar(s), kx, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            bool ok = true;
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % p.stages;
+                const uint32_t ph = (i / p.stages) & 1;
+                ok = mbar_wait(full_bar(s), ph, p.err, kErrMmaWait);
+                if (!ok) break;
+                tc5_fence_after();
+                const uint32_t a_src = smem_base + s * kStageBytes;
+                const uint64_t adesc = umma_desc_k128(a_src);
+                const uint64_t bdesc = umma_desc_k128(a_src + kABytes);
+#pragma unroll
+                for (int k = 0; k < kBK / kUmmaK; ++k) {
+                    // advance both descriptors by 32 bytes along K inside the swizzle row
+                    umma_ss<kInt8>(tmem_base, adesc + 2u * k, bdesc + 2u * k, kIdesc, (i | k) != 0 ? 1u : 0u);
+                }
+                tc5_commit(empty_bar(s));
+            }
+            tc5_commit(tmem_full_bar);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4
+        const int q = warp & 3;
+        const int row = m0 + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        bool ready = num_kb > 0 && mbar_wait(tmem_full_bar, 0, p.err, kErrEpilogueWait);
+        tc5_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        const GemmEpilogue& ep = p.ep;
+        if (ready) {
+            if (!ep.fused) {
+                uint32_t* raw = static_cast<uint32_t*>(ep.raw) +
+                                (static_cast<size_t>(split) * p.M + (row_ok ? row : 0)) * p.N;
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (n0 + c0 >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + c0, v);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const int n = n0 + c0 + j;
+                            if (n < p.N) *reinterpret_cast<uint4*>(raw + n) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        }
+                    }
+                }
+            } else if (!p.gate) {
+                const float sa = ep.a_scale[ep.a_per_row ? (row_ok ? row : 0) : 0];
+                const size_t row_off = static_cast<size_t>(row_ok ? row : 0) * p.N;
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (n0 + c0 >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + c0, v);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const int n = n0 + c0 + j;
+                            if (n >= p.N) break;
+                            float y[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                const float sb = ep.b_scale[ep.b_per_col ? n + t : 0];
+                                const float b = ep.bias ? ep.bias[n + t] : 0.0f;
+                                float x = fmaf(acc_to_f32<kInt8>(v[j + t]), sa * sb, b);
+                                if (ep.act == kActSilu) x = silu(x);
+                                else if (ep.act == kActRelu) x = fmaxf(x, 0.0f);
+                                y[t] = x;
+                            }
+                            store_out4(ep, row_off + n, y[0], y[1], y[2], y[3]);
+                        }
+                    }
+                }
+            } else {
+                // gate form: columns [0, BN/2) hold gate, [BN/2, BN) hold up, for outputs n0 .. n0 + BN/2
+                const float sa = ep.a_scale[ep.a_per_row ? (row_ok ? row : 0) : 0];
+                const size_t row_off = static_cast<size_t>(row_ok ? row : 0) * p.n_half;
+                constexpr int kHalf = BN / 2;
+                constexpr int kStep = kHalf < 32 ? kHalf : 32;
+                for (int c0 = 0; c0 < kHalf; c0 += 32) {
+                    if (n0 + c0 >= p.n_half) break;
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(t_row + c0, g);
+                    tmem_ld_32x32(t_row + kHalf + c0, u);
+                    tmem_ld_wait();
+                    if (row_ok) {
+#pragma unroll
+                        for (int j = 0; j < kStep; j += 4) {
+                            const int n = n0 + c0 + j;
+                            if (n >= p.n_half) break;
+                            float y[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                const float sg = ep.b_scale[ep.b_per_col ? n + t : 0];
+                                const float su = ep.b_scale[ep.b_per_col ? p.n_half + n + t : 0];
+                                const float bg = ep.bias ? ep.bias[n + t] : 0.0f;
+                                const float bu = ep.bias ? ep.bias[p.n_half + n + t] : 0.0f;
+                                const float gv = fmaf(acc_to_f32<kInt8>(g[j + t]), sa * sg, bg);
+                                const float uv = fmaf(acc_to_f32<kInt8>(u[j + t]), sa * su, bu);
+                                y[t] = silu(gv) * uv;
+                            }
+                            store_out4(ep, row_off + n, y[0], y[1], y[2], y[3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc5_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc5_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// Sums the split-K partial planes in plane order and applies the same epilogue as the
+// fused path.  One thread per four output columns.
+template <bool kInt8>
+__global__ void splitk_epilogue_kernel(const uint32_t* __restrict__ raw, int splits, int M, int N, int gate,
+                                       GemmEpilogue ep) {
+    const int n_out = gate ? N / 2 : N;
+    const int64_t groups = static_cast<int64_t>(M) * (n_out / 4);
+    const size_t plane = static_cast<size_t>(M) * N;
+    for (int64_t g = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; g < groups; g += int64_t(gridDim.x) * blockDim.x) {
+        const int m = static_cast<int>(g / (n_out / 4));
+        const int n = static_cast<int>(g % (n_out / 4)) * 4;
+        const float sa = ep.a_scale[ep.a_per_row ? m : 0];
+        float y[4];
+        auto total = [&](int col, float* out4) {
+            const uint32_t* src = raw + static_cast<size_t>(m) * N + col;
+            if constexpr (kInt8) {
+                int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+                for (int s = 0; s < splits; ++s) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(src + s * plane);
+                    a0 += static_cast<int>(v.x); a1 += static_cast<int>(v.y);
+                    a2 += static_cast<int>(v.z); a3 += static_cast<int>(v.w);
+                }
+                out4[0] = static_cast<float>(a0); out4[1] = static_cast<float>(a1);
+                out4[2] = static_cast<float>(a2); out4[3] = static_cast<float>(a3);
+            } else {
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                for (int s = 0; s < splits; ++s) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(src + s * plane);
+                    a0 += __uint_as_float(v.x); a1 += __uint_as_float(v.y);
+                    a2 += __uint_as_float(v.z); a3 += __uint_as_float(v.w);
+                }
+                out4[0] = a0; out4[1] = a1; out4[2] = a2; out4[3] = a3;
+            }
+        };
+        if (!gate) {
+            float t[4];
+            total(n, t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float sb = ep.b_scale[ep.b_per_col ? n + i : 0];
+                const float b = ep.bias ? ep.bias[n + i] : 0.0f;
+                float x = fmaf(t[i], sa * sb, b);
+                if (ep.act == kActSilu) x = silu(x);
+                else if (ep.act == kActRelu) x = fmaxf(x, 0.0f);
+                y[i] = x;
+            }
+        } else {
+            float tg[4], tu[4];
+            total(n, tg);
+            total(n_out + n, tu);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float sg = ep.b_scale[ep.b_per_col ? n + i : 0];
+                const float su = ep.b_scale[ep.b_per_col ? n_out + n + i : 0];
+                const float bg = ep.bias ? ep.bias[n + i] : 0.0f;
+                const float bu = ep.bias ? ep.bias[n_out + n + i] : 0.0f;
+                y[i] = silu(fmaf(tg[i], sa * sg, bg)) * fmaf(tu[i], sa * su, bu);
+            }
+        }
+        store_out4(ep, static_cast<size_t>(m) * n_out + n, y[0], y[1], y[2], y[3]);
+    }
+}
+
+// Sums int32 partial planes in plane order (integer addition: exact, order-free).
+__global__ void sum_planes_i32_kernel(const int* __restrict__ raw, int splits, int64_t elems, int* __restrict__ out) {
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < elems; i += int64_t(gridDim.x) * blockDim.x) {
+        int a = 0;
+        for (int s = 0; s < splits; ++s) a += raw[s * elems + i];
+        out[i] = a;
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess) {
+            sym = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// 2-D map over a row-major [rows, cols] matrix of bytes, box = [box_rows, 128 bytes], 128-byte swizzle.
+bool make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool kInt8>
+cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t stream) {
+    const int stage_bytes = kABytes + BN * kBK;
+    const int smem = plan.stages * stage_bytes + 1024 + 8 * (2 * plan.stages + 2);
+    static int configured = 0;
+    if (configured < smem) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, kInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    const int out_cols = plan.gate ? BN / 2 : BN;
+    const int n_out = plan.gate ? plan.N / 2 : plan.N;
+    dim3 grid((n_out + out_cols - 1) / out_cols, (plan.M + kBM - 1) / kBM, plan.splits);
+    gemm_tc5_kernel<BN, kInt8><<<grid, kThreads, smem, stream>>>(plan.tma_a, plan.tma_b, args);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* b, int M, int N, int K, int gate,
+                           int want_splits, int want_bn, const char** why) {
+    static const char* kNone = "";
+    if (why) *why = kNone;
+    auto fail = [&](const char* msg) {
+        if (why) *why = msg;
+        return cudaErrorInvalidValue;
+    };
+    if (M <= 0 || N <= 0 || K <= 0) return fail("gemm: m, n, k must be positive");
+    if (K % 16 != 0) return fail("gemm: k must be a multiple of 16 (TMA row stride)");
+    if (N % 16 != 0) return fail("gemm: n must be a multiple of 16");
+    if (gate && (N % 32 != 0)) return fail("gemm: gated n must be a multiple of 32");
+    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
+        return fail("gemm: operand base addresses must be 16-byte aligned");
+    plan->kind = kind;
+    plan->M = M; plan->N = N; plan->K = K; plan->gate = gate;
+    const int m_tiles = (M + kBM - 1) / kBM;
+    const int kb_total = (K + kBK - 1) / kBK;
+    int bn = want_bn;
+    if (bn <= 0) bn = (M >= 512) ? 256 : 128;
+    if (bn != 64 && bn != 128 && bn != 256) return fail("gemm: tile width must be 64, 128 or 256");
+    const int n_out = gate ? N / 2 : N;
+    const int out_cols = gate ? bn / 2 : bn;
+    const int tiles = m_tiles * ((n_out + out_cols - 1) / out_cols);
+    int splits = want_splits;
+    if (splits <= 0) {
+        splits = 1;
+        if (tiles < 148) {
+            splits = 296 / tiles;
+            if (splits > kb_total / 2) splits = kb_total / 2;
+            if (splits > 16) splits = 16;
+            if (splits < 1) splits = 1;
+        }
+    }
+    if (splits > kb_total) splits = kb_total;
+    {   // every split must own at least one K block
+        const int per = (kb_total + splits - 1) / splits;
+        splits = (kb_total + per - 1) / per;
+    }
+    plan->bn = bn;
+    plan->splits = splits;
+    const int stage_bytes = kABytes + bn * kBK;
+    // Small grids keep two CTAs per SM resident (about 100 KB each); big ones take the whole SM.
+    int stages = (m_tiles * 1 >= 4 || bn == 256) ? (200 * 1024) / stage_bytes : (100 * 1024) / stage_bytes;
+    if (stages > 8) stages = 8;
+    if (stages < 2) stages = 2;
+    plan->stages = stages;
+    if (!make_operand_map(&plan->tma_a, a, M, K, kBM)) return fail("gemm: cuTensorMapEncodeTiled failed for A");
+    if (!make_operand_map(&plan->tma_b, b, N, K, gate ? bn / 2 : bn)) return fail("gemm: cuTensorMapEncodeTiled failed for B");
+    return cudaSuccess;
+}
+
+cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* err, cudaStream_t stream) {
+    KernelArgs args;
+    args.M = plan.M; args.N = plan.N; args.K = plan.K;
+    args.stages = plan.stages;
+    args.kb_total = (plan.K + kBK - 1) / kBK;
+    args.kb_per_split = (args.kb_total + plan.splits - 1) / plan.splits;
+    args.gate = plan.gate;
+    args.n_half = plan.N / 2;
+    args.ep = ep;
+    args.err = err;
+    if (ep.fused && plan.splits != 1) return cudaErrorInvalidValue;
+    if (!ep.fused && plan.gate) return cudaErrorInvalidValue;   // raw planes always use the plain column layout
+    const bool i8 = plan.kind == kGemmI8;
+    switch (plan.bn) {
+        case 64: return i8 ? launch_t<64, true>(plan, args, stream) : launch_t<64, false>(plan, args, stream);
+        case 128: return i8 ? launch_t<128, true>(plan, args, stream) : launch_t<128, false>(plan, args, stream);
+        case 256: return i8 ? launch_t<256, true>(plan, args, stream) : launch_t<256, false>(plan, args, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t gemm_splitk_epilogue(int kind, int splits, int M, int N, int gate, const void* raw,
+                                 const GemmEpilogue& ep, cudaStream_t stream) {
+    const int n_out = gate ? N / 2 : N;
+    int64_t groups = static_cast<int64_t>(M) * (n_out / 4);
+    int64_t grid = (groups + 255) / 256;
+    if (grid > 148 * 8) grid = 148 * 8;
+    if (grid < 1) grid = 1;
+    if (kind == kGemmI8)
+        splitk_epilogue_kernel<true><<<static_cast<int>(grid), 256, 0, stream>>>(
+            static_cast<const uint32_t*>(raw), splits, M, N, gate, ep);
+    else
+        splitk_epilogue_kernel<false><<<static_cast<int>(grid), 256, 0, stream>>>(
+            static_cast<const uint32_t*>(raw), splits, M, N, gate, ep);
+    return cudaGetLastError();
+}
+
+cudaError_t gemm_sum_planes_i32(const int* raw, int splits, int64_t elems, int* out, cudaStream_t stream) {
+    int64_t grid = (elems + 255) / 256;
+    if (grid > 148 * 8) grid = 148 * 8;
+    if (grid < 1) grid = 1;
+    sum_planes_i32_kernel<<<static_cast<int>(grid), 256, 0, stream>>>(raw, splits, elems, out);
+    return cudaGetLastError();
+}
+
+}  // namespace b200

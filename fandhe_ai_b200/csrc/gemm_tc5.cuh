@@ -1,0 +1,64 @@
+// Interface of the tcgen05 quantized GEMM (defined in gemm_tc5.cu).
+//
+//   acc[m, n] = sum_k A[m, k] * B[n, k]      A: [M, K] row-major, B: [N, K] row-major (both K-major)
+//
+// 8-bit operands (signed int8 -> s32 accumulator, or FP8 E4M3 -> f32 accumulator).
+// Output is either the raw accumulators, optionally split along K into `splits`
+// partial planes [splits][M][N] that a later row-wise kernel sums in plane order,
+// or the fused epilogue  y = act(acc * sa[m] * sb[n] + bias[n]) (+ residual).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+enum GemmKind : int { kGemmI8 = 0, kGemmFp8 = 1 };
+enum GemmAct : int { kActNone = 0, kActRelu = 1, kActSilu = 2, kActSiluGate = 3 };
+
+struct GemmEpilogue {
+    int fused = 0;                 // 0: write raw accumulators to `raw`; 1: fused epilogue to `out`
+    void* raw = nullptr;           // [splits][M][N] int32 (i8) or f32 (fp8)
+    const float* a_scale = nullptr;  // [M] when a_per_row else [1]
+    int a_per_row = 0;
+    const float* b_scale = nullptr;  // [N] when b_per_col else [1]
+    int b_per_col = 0;
+    const float* bias = nullptr;     // [N] (for the gate form: [N], gate half then up half) or null
+    const float* residual = nullptr; // [M][N_out] f32 or null
+    void* out = nullptr;             // [M][N_out] f32 or bf16
+    int out_bf16 = 0;
+    int act = kActNone;              // kActSiluGate: B rows [0, N/2) are gate, [N/2, N) are up, N_out = N/2
+};
+
+struct GemmPlan {
+    CUtensorMap tma_a;
+    CUtensorMap tma_b;
+    int kind = kGemmI8;
+    int M = 0, N = 0, K = 0;
+    int bn = 128;      // CTA tile width (output columns; for the gate form bn/2 gate + bn/2 up rows of B)
+    int stages = 3;
+    int splits = 1;
+    int gate = 0;
+};
+
+// Picks tile width / stage count / split count for a shape.  `want_splits` <= 0
+// lets the heuristic choose (it only splits when the tile grid alone would leave
+// most of the 148 SMs idle); the fused epilogue requires splits == 1.
+// Returns cudaSuccess or an error; `why` receives a static message on failure.
+cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* b, int M, int N, int K,
+                           int gate, int want_splits, int want_bn, const char** why);
+
+// Enqueues the GEMM on `stream`.  `err` is the context's device error word.
+cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* err, cudaStream_t stream);
+
+// Finish for raw planes: sums the `splits` planes [splits][M][N] in plane order and applies
+// the epilogue (same arithmetic as the fused path).  With `gate` the planes come from a
+// plain (gate = 0) plan over all N = 2F weight rows: gate columns [0, N/2), up columns [N/2, N).
+cudaError_t gemm_splitk_epilogue(int kind, int splits, int M, int N, int gate, const void* raw,
+                                 const GemmEpilogue& ep, cudaStream_t stream);
+cudaError_t gemm_sum_planes_i32(const int* raw, int splits, int64_t elems, int* out, cudaStream_t stream);
+
+// Required raw-output elements for a plan: splits * M * N.
+inline size_t gemm_raw_elems(const GemmPlan& p) { return size_t(p.splits) * size_t(p.M) * size_t(p.N); }
+
+}  // namespace b200
