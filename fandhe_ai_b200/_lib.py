@@ -45,10 +45,29 @@ def check(status: int) -> None:
         raise BackendError(status, l.b200_status_name(status).decode(), l.b200_last_error().decode())
 
 
+class PagedKvLayoutC(C.Structure):
+    """b200_paged_kv_layout"""
+    _fields_ = [("num_blocks", C.c_uint64), ("block_size", C.c_uint64), ("embed_dim", C.c_uint64),
+                ("dtype", C.c_int32)]
+
+
+class PagedAttentionArgsC(C.Structure):
+    """b200_paged_attention_args"""
+    _fields_ = [("layout", PagedKvLayoutC), ("batch", C.c_uint64), ("l_new", C.c_uint64), ("num_heads", C.c_uint64),
+                ("num_kv_heads", C.c_uint64), ("max_blocks_per_seq", C.c_uint64), ("scale", C.c_float)]
+
+
+class PagedAttentionPlanC(C.Structure):
+    """b200_paged_attention_plan"""
+    _fields_ = [("out_numel", C.c_uint64), ("s_max", C.c_uint64), ("query_rows", C.c_uint64),
+                ("workspace_elems", C.c_uint64)]
+
+
 _P = C.c_void_p
 _SZ = C.c_size_t
 _I32 = C.c_int32
 _I64 = C.c_int64
+_U64 = C.c_uint64
 
 # name -> (restype, argtypes); every symbol declared in include/b200_backend.h
 SIGNATURES = {
@@ -74,6 +93,16 @@ SIGNATURES = {
     "b200_gemm_i8_s32": (_I32, [_P, _P, _SZ, _P, _SZ, _I64, _I64, _I64, _P, _SZ]),
     "b200_gemm_q8_scaled": (_I32, [_P, _I32, _P, _SZ, _P, _SZ, _I32, _P, _SZ, _P, _SZ, _I32, _P, _SZ, _I32,
                                    _P, _SZ, _I64, _I64, _I64, _I32, _P, _SZ]),
+    "b200_validate_paged_kv_append": (_I32, [_U64, _U64, _U64, _U64, _P, _U64, C.POINTER(PagedKvLayoutC),
+                                             C.POINTER(_U64)]),
+    "b200_validate_paged_attention": (_I32, [_U64, _U64, _U64, _P, _U64, _P, _U64, C.POINTER(PagedAttentionArgsC),
+                                             C.POINTER(PagedAttentionPlanC)]),
+    "b200_paged_kv_append": (_I32, [_P, _P, _SZ, _P, _SZ, _P, _P, _P, _U64, C.POINTER(PagedKvLayoutC)]),
+    "b200_paged_attention_forward": (_I32, [_P, _P, _SZ, _P, _P, _P, _U64, _P, _U64, C.POINTER(PagedAttentionArgsC),
+                                            _P, _SZ]),
+    "b200_paged_attention_forward_resident": (_I32, [_P, _P, _SZ, _P, _P, _P, _P, _U64,
+                                                     C.POINTER(PagedAttentionArgsC), _P, _SZ]),
+    "b200_paged_attention_tuning": (_I32, [_P, _I32]),
     "b200_linear_w8a8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _P, _SZ]),
 }
 

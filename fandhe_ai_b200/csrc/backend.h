@@ -20,6 +20,7 @@ struct b200_ctx {
     bool ws_locked = false;             // set while a composite call lends out part of the scratch
     int tune_bn = 0;                    // 0 = heuristic
     int tune_splits = 0;                // 0 = heuristic
+    int tune_attn_chunk_blocks = 0;     // 0 = default
     int sm_count = 0;
 };
 

@@ -1,6 +1,7 @@
 // Host-callable launchers of the non-GEMM kernels (quantisers, paged KV, decoder glue).
 // All of them only enqueue work on the given stream.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -13,5 +14,31 @@ cudaError_t dequantize_i8_per_row(const int8_t* q, const float* scale, int64_t r
 // `amax_scratch` is one uint32 of device memory owned by the context.
 cudaError_t quantize_fp8_per_tensor(const float* x, int64_t n, uint8_t* q, float* scale, uint32_t* amax_scratch,
                                     cudaStream_t s);
+
+// ---- paged_kv.cu
+struct PagedAttnShape {
+    int batch, l_new, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks, max_blocks_per_seq;
+    float scale;
+};
+struct PagedAttnPlan {
+    PagedAttnShape shape;
+    int kv_bf16;
+    int fast;           // TMA split-K path (head_dim 128, bf16, block 16, 1/2/4/8 q heads per kv head)
+    int chunk_blocks;   // blocks per split
+    int max_chunks;     // splits reserved per query row
+    CUtensorMap tma_k, tma_v;
+};
+// Copies row r of k_new / v_new [rows, e] (f32) to pool row slots_dev[r], rounding to bf16 when kv_bf16.
+cudaError_t paged_kv_append(const float* k_new, const float* v_new, void* k_pool, void* v_pool, const uint32_t* slots_dev,
+                            int64_t rows, int64_t e, int64_t pool_rows, int kv_bf16, uint32_t* err, cudaStream_t s);
+bool paged_attention_fast_path(const PagedAttnShape& sh, int kv_bf16);
+// max_seq_len bounds the number of splits a row can need; want_chunk_blocks <= 0 picks the default.
+cudaError_t paged_attention_make_plan(PagedAttnPlan* plan, const PagedAttnShape& sh, int kv_bf16, const void* k_pool,
+                                      const void* v_pool, int max_seq_len, int want_chunk_blocks);
+size_t paged_attention_scratch_bytes(const PagedAttnPlan& plan);
+// q, out: [batch, l_new, num_q_heads * head_dim] f32.  tables/seq_lens are device arrays.
+cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,
+                                   const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
+                                   uint32_t* err, cudaStream_t stream);
 
 }  // namespace b200

@@ -1,0 +1,576 @@
+// Paged KV cache kernels: append and decode attention.
+//
+// Pool layout (unchanged from the reference, crates/tensor-core/src/paged_kv.rs:17-21):
+// K and V pools are [num_blocks, block_size, E_kv] row-major; the token at logical position
+// pos of a sequence lives in pool row  block_table[pos / block_size] * block_size + pos % block_size.
+// Here E_kv = num_kv_heads * head_dim and the element type is bf16 (or f32, the reference's type).
+//
+// Replaces paged_kv_append_f32 and paged_attention_f32
+// (crates/backend-cuda/src/kernels_paged_kv.rs:55-83, 86-228).  The reference kernel walks the
+// keys with one CTA per query row and lets thread 0 do max and sum alone; here the key range of
+// a query row is cut into chunks (flash-decoding split-K), each chunk is one CTA fed by a TMA
+// ring of 4 KB tiles gathered through the block table, and a second kernel merges the chunks.
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+namespace {
+
+// ------------------------------------------------------------------------------------ append
+template <typename KvT>
+__device__ __forceinline__ KvT to_kv(float v);
+template <>
+__device__ __forceinline__ float to_kv<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ uint16_t to_kv<uint16_t>(float v) { return static_cast<uint16_t>(f32_to_bf16_bits(v)); }
+
+template <typename KvT>
+__global__ void paged_kv_append_kernel(const float* __restrict__ k_new, const float* __restrict__ v_new,
+                                       KvT* __restrict__ k_pool, KvT* __restrict__ v_pool,
+                                       const uint32_t* __restrict__ slots, int64_t rows, int64_t e, int64_t pool_rows,
+                                       uint32_t* err) {
+    // one thread per 4 consecutive elements of a row (e % 4 == 0 is checked on the host)
+    const int64_t groups_per_row = e / 4;
+    const int64_t total = rows * groups_per_row;
+    for (int64_t g = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; g < total; g += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t r = g / groups_per_row;
+        const int64_t c = (g % groups_per_row) * 4;
+        const int64_t slot = slots[r];
+        if (slot >= pool_rows) {   // never write out of range; flag it instead
+            atomicCAS(err, 0u, static_cast<uint32_t>(kErrAppendSlot));
+            continue;
+        }
+        const float4 kv = *reinterpret_cast<const float4*>(k_new + r * e + c);
+        const float4 vv = *reinterpret_cast<const float4*>(v_new + r * e + c);
+        KvT* kd = k_pool + slot * e + c;
+        KvT* vd = v_pool + slot * e + c;
+        if constexpr (sizeof(KvT) == 4) {
+            *reinterpret_cast<float4*>(kd) = kv;
+            *reinterpret_cast<float4*>(vd) = vv;
+        } else {
+            uint2 ko, vo;
+            ko.x = f32_to_bf16_bits(kv.x) | (f32_to_bf16_bits(kv.y) << 16);
+            ko.y = f32_to_bf16_bits(kv.z) | (f32_to_bf16_bits(kv.w) << 16);
+            vo.x = f32_to_bf16_bits(vv.x) | (f32_to_bf16_bits(vv.y) << 16);
+            vo.y = f32_to_bf16_bits(vv.z) | (f32_to_bf16_bits(vv.w) << 16);
+            *reinterpret_cast<uint2*>(kd) = ko;
+            *reinterpret_cast<uint2*>(vd) = vo;
+        }
+    }
+}
+
+// scalar variant for e % 4 != 0
+template <typename KvT>
+__global__ void paged_kv_append_scalar_kernel(const float* __restrict__ k_new, const float* __restrict__ v_new,
+                                              KvT* __restrict__ k_pool, KvT* __restrict__ v_pool,
+                                              const uint32_t* __restrict__ slots, int64_t rows, int64_t e,
+                                              int64_t pool_rows, uint32_t* err) {
+    const int64_t total = rows * e;
+    for (int64_t g = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; g < total; g += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t r = g / e, c = g % e;
+        const int64_t slot = slots[r];
+        if (slot >= pool_rows) {
+            atomicCAS(err, 0u, static_cast<uint32_t>(kErrAppendSlot));
+            continue;
+        }
+        k_pool[slot * e + c] = to_kv<KvT>(k_new[g]);
+        v_pool[slot * e + c] = to_kv<KvT>(v_new[g]);
+    }
+}
+
+// ------------------------------------------------------------------------------------ attention, generic
+template <typename KvT>
+__device__ __forceinline__ float kv_to_f32(KvT v);
+template <>
+__device__ __forceinline__ float kv_to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float kv_to_f32<uint16_t>(uint16_t v) { return bf16_bits_to_f32(v); }
+
+constexpr int kGenThreads = 128;
+constexpr int kGenMaxDimsPerLane = 8;   // head_dim <= 256
+
+// Any head_dim <= 256, any block size, any q:kv head ratio, f32 or bf16 pools.  One CTA per
+// (query row, q head); each warp walks tokens warp, warp + 4, ... with an online softmax, lanes
+// stride the head dimension; the four warps are merged at the end.  Writes NaN when it meets an
+// out-of-range block id (the reference kernel's reaction, kernels_paged_kv.rs:86-228).
+template <typename KvT>
+__global__ void __launch_bounds__(kGenThreads)
+paged_attention_generic_kernel(const float* __restrict__ q, const KvT* __restrict__ k_pool, const KvT* __restrict__ v_pool,
+                               const uint32_t* __restrict__ block_tables, const uint32_t* __restrict__ seq_lens,
+                               PagedAttnShape sh, float* __restrict__ out, uint32_t* err) {
+    __shared__ float red_m[4], red_l[4];
+    __shared__ float red_o[4][256];
+    const int row = blockIdx.x;              // b * l_new + i
+    const int h = blockIdx.y;
+    const int b = row / sh.l_new, i = row % sh.l_new;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int dh = sh.head_dim;
+    const int kvh = h / (sh.num_q_heads / sh.num_kv_heads);
+    const int64_t ekv = int64_t(sh.num_kv_heads) * dh;
+    const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
+    const float* q_row = q + (int64_t(row) * sh.num_q_heads + h) * dh;
+    float qs[kGenMaxDimsPerLane];
+#pragma unroll
+    for (int t = 0; t < kGenMaxDimsPerLane; ++t) {
+        const int d = lane + 32 * t;
+        qs[t] = d < dh ? q_row[d] * sh.scale : 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    float acc[kGenMaxDimsPerLane];
+#pragma unroll
+    for (int t = 0; t < kGenMaxDimsPerLane; ++t) acc[t] = 0.0f;
+    bool bad = false;
+    for (int j = warp; j < limit; j += 4) {
+        const uint32_t blk = block_tables[int64_t(b) * sh.max_blocks_per_seq + j / sh.block_size];
+        if (blk >= uint32_t(sh.num_blocks)) { bad = true; break; }
+        const int64_t off = (int64_t(blk) * sh.block_size + j % sh.block_size) * ekv + int64_t(kvh) * dh;
+        float s = 0.0f;
+#pragma unroll
+        for (int t = 0; t < kGenMaxDimsPerLane; ++t) {
+            const int d = lane + 32 * t;
+            if (d < dh) s = fmaf(qs[t], kv_to_f32<KvT>(k_pool[off + d]), s);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float m_new = fmaxf(m, s);
+        const float corr = expf(m - m_new);      // exp(-inf) = 0 on the first token
+        const float p = expf(s - m_new);
+        l = l * corr + p;
+#pragma unroll
+        for (int t = 0; t < kGenMaxDimsPerLane; ++t) {
+            const int d = lane + 32 * t;
+            if (d < dh) acc[t] = fmaf(p, kv_to_f32<KvT>(v_pool[off + d]), acc[t] * corr);
+        }
+        m = m_new;
+    }
+    if (lane == 0) { red_m[warp] = m; red_l[warp] = l; }
+#pragma unroll
+    for (int t = 0; t < kGenMaxDimsPerLane; ++t) {
+        const int d = lane + 32 * t;
+        if (d < dh) red_o[warp][d] = acc[t];
+    }
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    float* o_row = out + (int64_t(row) * sh.num_q_heads + h) * dh;
+    if (any_bad) {
+        if (threadIdx.x == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrAttnBlockId));
+        for (int d = threadIdx.x; d < dh; d += kGenThreads) o_row[d] = __int_as_float(0x7FC00000);
+        return;
+    }
+    float mm = fmaxf(fmaxf(red_m[0], red_m[1]), fmaxf(red_m[2], red_m[3]));
+    float w[4], ll = 0.0f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        w[t] = red_m[t] == -INFINITY ? 0.0f : expf(red_m[t] - mm);
+        ll += red_l[t] * w[t];
+    }
+    for (int d = threadIdx.x; d < dh; d += kGenThreads) {
+        float o = 0.0f;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) o += red_o[t][d] * w[t];
+        o_row[d] = limit > 0 ? o / ll : 0.0f;
+    }
+}
+
+// ------------------------------------------------------------------------------------ attention, fast path
+// head_dim 128, bf16 pools, block_size 16, G = q heads per kv head in {1, 2, 4}.
+constexpr int kD = 128;
+constexpr int kBS = 16;                 // tokens per block = tokens per tile
+constexpr int kTileBytes = kBS * kD * 2;  // 4096
+constexpr int kStages = 8;
+constexpr int kConsumerWarps = 4;
+constexpr int kFastThreads = 32 * (kConsumerWarps + 1);
+constexpr int kMaxChunkBlocks = 32;     // producer lanes prefetch one block id each
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int G>
+__global__ void __launch_bounds__(kFastThreads)
+paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
+                              const float* __restrict__ q, const uint32_t* __restrict__ block_tables,
+                              const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_blocks,
+                              int max_chunks, float* __restrict__ part_o, float* __restrict__ part_ml, uint32_t* err) {
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t ring = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    uint8_t* ring_ptr = smem_dyn + (ring - smem_u32(smem_dyn));
+    const int chunk_tokens = chunk_blocks * kBS;
+    float* scores = reinterpret_cast<float*>(ring_ptr + kStages * kTileBytes);            // [chunk_tokens][G]
+    float* red = scores + kMaxChunkBlocks * kBS * G;                                      // [4][G][128]
+    float* stat = red + kConsumerWarps * G * kD;                                          // [4][G] scratch, then m[G], l[G]
+    const uint32_t bars = smem_u32(stat + 8 * G + 8);
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
+
+    const int chunk = blockIdx.x;
+    const int kv_slot = blockIdx.y;                 // kv head (times sub-group when the group is wider than G)
+    const int row = blockIdx.z;                     // b * l_new + i
+    const int b = row / sh.l_new, i = row % sh.l_new;
+    const int group = sh.num_q_heads / sh.num_kv_heads;
+    const int subs = group / G;                     // 1, or 2 when 8 q heads share a kv head and G = 4
+    const int kvh = kv_slot / subs;
+    const int h0 = kvh * group + (kv_slot % subs) * G;   // first q head of this CTA
+    const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
+    const int tok0 = chunk * chunk_tokens;
+    if (tok0 >= limit) return;                      // whole CTA leaves together, nothing allocated yet
+    int ntok = limit - tok0;
+    if (ntok > chunk_tokens) ntok = chunk_tokens;
+    const int nb = (ntok + kBS - 1) / kBS;          // tiles of K, and as many of V
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ---------------- producer warp: block ids are fetched by the lanes in one go, lane 0 issues TMA
+        if (lane == 0) { tma_prefetch_desc(&tma_k); tma_prefetch_desc(&tma_v); }
+        uint32_t my_blk = 0;
+        if (lane < nb) {
+            my_blk = block_tables[int64_t(b) * sh.max_blocks_per_seq + chunk * chunk_blocks + lane];
+            if (my_blk >= uint32_t(sh.num_blocks)) {
+                atomicCAS(err, 0u, static_cast<uint32_t>(kErrAttnBlockId));
+                my_blk = 0;
+            }
+        }
+        bool ok = true;
+        for (int t = 0; t < 2 * nb; ++t) {
+            const int s = t % kStages;
+            const uint32_t ph = (t / kStages) & 1;
+            const uint32_t blk = __shfl_sync(0xffffffffu, my_blk, t < nb ? t : t - nb);
+            if (lane == 0 && ok) {
+                ok = mbar_wait(empty_bar(s), ph ^ 1u, err, kErrProducerWait);
+                if (ok) {
+                    mbar_arrive_expect_tx(full_bar(s), kTileBytes);
+                    tma_load_2d(ring + s * kTileBytes, t < nb ? &tma_k : &tma_v, full_bar(s), kvh * kD,
+                                int(blk) * kBS);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers
+    // Phase 1: scores.  Lane = (token-in-step t4 = lane >> 3, slice sl = lane & 7); a lane owns the two
+    // 16-byte pieces sl and sl + 8 of a 256-byte K row, i.e. dims [8 sl, 8 sl + 8) and [64 + 8 sl, 64 + 8 sl + 8).
+    const int t4 = lane >> 3, sl = lane & 7;
+    float qr[G][16];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float* qp = q + (int64_t(row) * sh.num_q_heads + h0 + g) * kD;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) {
+            qr[g][d] = qp[8 * sl + d] * sh.scale;
+            qr[g][8 + d] = qp[64 + 8 * sl + d] * sh.scale;
+        }
+    }
+    bool ok = true;
+    for (int kt = warp; kt < nb; kt += kConsumerWarps) {
+        const int s = kt % kStages;
+        const uint32_t ph = (kt / kStages) & 1;
+        ok = ok && mbar_wait(full_bar(s), ph, err, kErrAttnLoadWait);
+        const uint8_t* tile = ring_ptr + s * kTileBytes;
+#pragma unroll
+        for (int step = 0; step < 4; ++step) {
+            const int tok = step * 4 + t4;                      // token inside the tile
+            const uint4 lo = *reinterpret_cast<const uint4*>(tile + tok * 256 + sl * 16);
+            const uint4 hi = *reinterpret_cast<const uint4*>(tile + tok * 256 + 128 + sl * 16);
+            float kf[16];
+            kf[0] = bf16_bits_to_f32(lo.x & 0xFFFFu); kf[1] = __uint_as_float(lo.x & 0xFFFF0000u);
+            kf[2] = bf16_bits_to_f32(lo.y & 0xFFFFu); kf[3] = __uint_as_float(lo.y & 0xFFFF0000u);
+            kf[4] = bf16_bits_to_f32(lo.z & 0xFFFFu); kf[5] = __uint_as_float(lo.z & 0xFFFF0000u);
+            kf[6] = bf16_bits_to_f32(lo.w & 0xFFFFu); kf[7] = __uint_as_float(lo.w & 0xFFFF0000u);
+            kf[8] = bf16_bits_to_f32(hi.x & 0xFFFFu); kf[9] = __uint_as_float(hi.x & 0xFFFF0000u);
+            kf[10] = bf16_bits_to_f32(hi.y & 0xFFFFu); kf[11] = __uint_as_float(hi.y & 0xFFFF0000u);
+            kf[12] = bf16_bits_to_f32(hi.z & 0xFFFFu); kf[13] = __uint_as_float(hi.z & 0xFFFF0000u);
+            kf[14] = bf16_bits_to_f32(hi.w & 0xFFFFu); kf[15] = __uint_as_float(hi.w & 0xFFFF0000u);
+            float sc[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float a = 0.0f;
+#pragma unroll
+                for (int d = 0; d < 16; ++d) a = fmaf(qr[g][d], kf[d], a);
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                a += __shfl_xor_sync(0xffffffffu, a, 4);
+                sc[g] = a;
+            }
+            if (sl == 0) {
+                const int ct = kt * kBS + tok;                  // token inside the chunk
+                const bool valid = ct < ntok;
+#pragma unroll
+                for (int g = 0; g < G; ++g) scores[ct * G + g] = valid ? sc[g] : -INFINITY;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+    }
+    consumer_sync();
+
+    // chunk max and sum of exp per head (128 consumer threads stride the tokens)
+    const int ctid = threadIdx.x;                    // 0..127
+    const int ntile_tok = nb * kBS;
+    float mx[G], sm[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) mx[g] = -INFINITY;
+    for (int t = ctid; t < ntile_tok; t += 128)
+#pragma unroll
+        for (int g = 0; g < G; ++g) mx[g] = fmaxf(mx[g], scores[t * G + g]);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
+        if (lane == 0) stat[warp * G + g] = mx[g];
+    }
+    consumer_sync();
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+        mx[g] = fmaxf(fmaxf(stat[g], stat[G + g]), fmaxf(stat[2 * G + g], stat[3 * G + g]));
+    consumer_sync();
+#pragma unroll
+    for (int g = 0; g < G; ++g) sm[g] = 0.0f;
+    for (int t = ctid; t < ntile_tok; t += 128)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float p = expf(scores[t * G + g] - mx[g]);   // masked tokens: exp(-inf) = 0
+            scores[t * G + g] = p;
+            sm[g] += p;
+        }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sm[g] += __shfl_xor_sync(0xffffffffu, sm[g], o);
+        if (lane == 0) stat[warp * G + g] = sm[g];
+    }
+    consumer_sync();
+#pragma unroll
+    for (int g = 0; g < G; ++g) sm[g] = (stat[g] + stat[G + g]) + (stat[2 * G + g] + stat[3 * G + g]);
+
+    // Phase 2: weighted sum of V.  Lane owns dims [4 lane, 4 lane + 4).
+    float acc[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+    for (int vt = warp; vt < nb; vt += kConsumerWarps) {
+        const int t = nb + vt;
+        const int s = t % kStages;
+        const uint32_t ph = (t / kStages) & 1;
+        ok = ok && mbar_wait(full_bar(s), ph, err, kErrAttnLoadWait);
+        const uint8_t* tile = ring_ptr + s * kTileBytes;
+        int valid = ntok - vt * kBS;
+        if (valid > kBS) valid = kBS;
+        for (int tok = 0; tok < valid; ++tok) {      // rows past the sequence end may hold anything: never read them
+            const uint2 vv = *reinterpret_cast<const uint2*>(tile + tok * 256 + lane * 8);
+            const float v0 = bf16_bits_to_f32(vv.x & 0xFFFFu), v1 = __uint_as_float(vv.x & 0xFFFF0000u);
+            const float v2 = bf16_bits_to_f32(vv.y & 0xFFFFu), v3 = __uint_as_float(vv.y & 0xFFFF0000u);
+            const float* pr = scores + (vt * kBS + tok) * G;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float p = pr[g];
+                acc[g][0] = fmaf(p, v0, acc[g][0]);
+                acc[g][1] = fmaf(p, v1, acc[g][1]);
+                acc[g][2] = fmaf(p, v2, acc[g][2]);
+                acc[g][3] = fmaf(p, v3, acc[g][3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+        *reinterpret_cast<float4*>(red + (warp * G + g) * kD + lane * 4) =
+            make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    consumer_sync();
+    // partial of this chunk: unnormalised sum relative to the chunk max, plus (max, sum)
+    for (int idx = ctid; idx < G * kD; idx += 128) {
+        const int g = idx / kD, d = idx % kD;
+        const float o = (red[(0 * G + g) * kD + d] + red[(1 * G + g) * kD + d]) +
+                        (red[(2 * G + g) * kD + d] + red[(3 * G + g) * kD + d]);
+        part_o[((int64_t(row) * sh.num_q_heads + h0 + g) * max_chunks + chunk) * kD + d] = ok ? o : __int_as_float(0x7FC00000);
+    }
+    if (ctid < G) {
+        float* ml = part_ml + ((int64_t(row) * sh.num_q_heads + h0 + ctid) * max_chunks + chunk) * 2;
+        ml[0] = mx[ctid];
+        ml[1] = sm[ctid];
+    }
+}
+
+// Merges the chunk partials of one (query row, q head): one warp each, lanes own 4 dims.
+__global__ void __launch_bounds__(128)
+paged_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_tokens, int max_chunks,
+                               float* __restrict__ out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t pair = int64_t(blockIdx.x) * 4 + warp;          // row * Hq + h
+    const int64_t pairs = int64_t(sh.batch) * sh.l_new * sh.num_q_heads;
+    if (pair >= pairs) return;
+    const int row = int(pair / sh.num_q_heads);
+    const int b = row / sh.l_new, i = row % sh.l_new;
+    const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
+    const int nchunks = limit > 0 ? (limit + chunk_tokens - 1) / chunk_tokens : 0;
+    const float* ml = part_ml + pair * max_chunks * 2;
+    float m = -INFINITY;
+    for (int c = 0; c < nchunks; ++c) m = fmaxf(m, ml[2 * c]);
+    float l = 0.0f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < nchunks; ++c) {
+        const float w = expf(ml[2 * c] - m);
+        l = fmaf(ml[2 * c + 1], w, l);
+        const float4 po = *reinterpret_cast<const float4*>(part_o + (pair * max_chunks + c) * kD + lane * 4);
+        o.x = fmaf(po.x, w, o.x); o.y = fmaf(po.y, w, o.y); o.z = fmaf(po.z, w, o.z); o.w = fmaf(po.w, w, o.w);
+    }
+    if (nchunks == 0) l = 1.0f;
+    *reinterpret_cast<float4*>(out + pair * kD + lane * 4) = make_float4(o.x / l, o.y / l, o.z / l, o.w / l);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// [pool_rows, E_kv] bf16, box = one block of one kv head: [16 rows, 128 elements]
+bool make_pool_map(CUtensorMap* map, const void* pool, int64_t pool_rows, int64_t ekv) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(ekv), static_cast<cuuint64_t>(pool_rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ekv) * 2};
+    cuuint32_t box[2] = {kD, kBS};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int fast_smem_bytes(int g) {
+    return 1024 + kStages * kTileBytes + (kMaxChunkBlocks * kBS * g + kConsumerWarps * g * kD + 8 * g + 8) * 4 +
+           2 * kStages * 8 + 16;
+}
+
+template <int G>
+cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_t* tables, const uint32_t* seq_lens,
+                        float* part_o, float* part_ml, uint32_t* err, cudaStream_t stream) {
+    const int smem = fast_smem_bytes(G);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const PagedAttnShape& sh = plan.shape;
+    const int group = sh.num_q_heads / sh.num_kv_heads;
+    dim3 grid(plan.max_chunks, sh.num_kv_heads * (group / G), sh.batch * sh.l_new);
+    paged_attention_decode_kernel<G><<<grid, kFastThreads, smem, stream>>>(
+        plan.tma_k, plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml, err);
+    return cudaGetLastError();
+}
+
+int grid_for(int64_t n, int threads) {
+    int64_t g = (n + threads - 1) / threads;
+    if (g > 148 * 16) g = 148 * 16;
+    if (g < 1) g = 1;
+    return static_cast<int>(g);
+}
+
+}  // namespace
+
+cudaError_t paged_kv_append(const float* k_new, const float* v_new, void* k_pool, void* v_pool, const uint32_t* slots_dev,
+                            int64_t rows, int64_t e, int64_t pool_rows, int kv_bf16, uint32_t* err, cudaStream_t s) {
+    if (rows == 0 || e == 0) return cudaSuccess;
+    const bool vec = (e % 4) == 0;
+    const int grid = grid_for(vec ? rows * (e / 4) : rows * e, 256);
+    if (kv_bf16) {
+        if (vec)
+            paged_kv_append_kernel<uint16_t><<<grid, 256, 0, s>>>(k_new, v_new, static_cast<uint16_t*>(k_pool),
+                                                                 static_cast<uint16_t*>(v_pool), slots_dev, rows, e, pool_rows, err);
+        else
+            paged_kv_append_scalar_kernel<uint16_t><<<grid, 256, 0, s>>>(k_new, v_new, static_cast<uint16_t*>(k_pool),
+                                                                        static_cast<uint16_t*>(v_pool), slots_dev, rows, e, pool_rows, err);
+    } else {
+        if (vec)
+            paged_kv_append_kernel<float><<<grid, 256, 0, s>>>(k_new, v_new, static_cast<float*>(k_pool),
+                                                              static_cast<float*>(v_pool), slots_dev, rows, e, pool_rows, err);
+        else
+            paged_kv_append_scalar_kernel<float><<<grid, 256, 0, s>>>(k_new, v_new, static_cast<float*>(k_pool),
+                                                                     static_cast<float*>(v_pool), slots_dev, rows, e, pool_rows, err);
+    }
+    return cudaGetLastError();
+}
+
+bool paged_attention_fast_path(const PagedAttnShape& sh, int kv_bf16) {
+    if (!kv_bf16 || sh.head_dim != kD || sh.block_size != kBS) return false;
+    if (sh.num_kv_heads <= 0 || sh.num_q_heads % sh.num_kv_heads != 0) return false;
+    const int group = sh.num_q_heads / sh.num_kv_heads;
+    return group == 1 || group == 2 || group == 4 || group == 8;
+}
+
+cudaError_t paged_attention_make_plan(PagedAttnPlan* plan, const PagedAttnShape& sh, int kv_bf16, const void* k_pool,
+                                      const void* v_pool, int max_seq_len, int want_chunk_blocks) {
+    plan->shape = sh;
+    plan->kv_bf16 = kv_bf16;
+    plan->fast = paged_attention_fast_path(sh, kv_bf16) && ((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0) &&
+                 ((reinterpret_cast<uintptr_t>(v_pool) & 15) == 0);
+    plan->chunk_blocks = 0;
+    plan->max_chunks = 0;
+    if (!plan->fast) return cudaSuccess;
+    int cb = want_chunk_blocks > 0 ? want_chunk_blocks : 16;
+    if (cb > kMaxChunkBlocks) cb = kMaxChunkBlocks;
+    plan->chunk_blocks = cb;
+    const int chunk_tokens = cb * kBS;
+    plan->max_chunks = max_seq_len > 0 ? (max_seq_len + chunk_tokens - 1) / chunk_tokens : 1;
+    const int64_t pool_rows = int64_t(sh.num_blocks) * sh.block_size;
+    const int64_t ekv = int64_t(sh.num_kv_heads) * sh.head_dim;
+    if (!make_pool_map(&plan->tma_k, k_pool, pool_rows, ekv) || !make_pool_map(&plan->tma_v, v_pool, pool_rows, ekv))
+        return cudaErrorInvalidValue;
+    return cudaSuccess;
+}
+
+size_t paged_attention_scratch_bytes(const PagedAttnPlan& plan) {
+    if (!plan.fast) return 0;
+    const size_t pairs = size_t(plan.shape.batch) * plan.shape.l_new * plan.shape.num_q_heads;
+    return pairs * plan.max_chunks * (kD + 2) * sizeof(float);
+}
+
+cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,
+                                   const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
+                                   uint32_t* err, cudaStream_t stream) {
+    const PagedAttnShape& sh = plan.shape;
+    const int64_t rows = int64_t(sh.batch) * sh.l_new;
+    if (rows == 0) return cudaSuccess;
+    if (!plan.fast) {
+        dim3 grid(static_cast<unsigned>(rows), sh.num_q_heads);
+        if (plan.kv_bf16)
+            paged_attention_generic_kernel<uint16_t><<<grid, kGenThreads, 0, stream>>>(
+                q, static_cast<const uint16_t*>(k_pool), static_cast<const uint16_t*>(v_pool), tables_dev, seq_lens_dev, sh, out, err);
+        else
+            paged_attention_generic_kernel<float><<<grid, kGenThreads, 0, stream>>>(
+                q, static_cast<const float*>(k_pool), static_cast<const float*>(v_pool), tables_dev, seq_lens_dev, sh, out, err);
+        return cudaGetLastError();
+    }
+    const size_t pairs = size_t(rows) * sh.num_q_heads;
+    float* part_o = static_cast<float*>(scratch);
+    float* part_ml = part_o + pairs * plan.max_chunks * kD;
+    const int group = sh.num_q_heads / sh.num_kv_heads;
+    cudaError_t e;
+    if (group == 1) e = launch_fast<1>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, err, stream);
+    else if (group == 2) e = launch_fast<2>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, err, stream);
+    else e = launch_fast<4>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, err, stream);
+    if (e != cudaSuccess) return e;
+    const int blocks = static_cast<int>((pairs + 3) / 4);
+    paged_attention_combine_kernel<<<blocks, 128, 0, stream>>>(part_o, part_ml, seq_lens_dev, sh, plan.chunk_blocks * kBS,
+                                                              plan.max_chunks, out);
+    return cudaGetLastError();
+}
+
+}  // namespace b200

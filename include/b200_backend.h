@@ -154,6 +154,79 @@ int32_t b200_linear_w8a8(b200_ctx* ctx, const b200_buf* a_f32, size_t a_off, int
                          const b200_buf* bias, size_t bias_off, int64_t n, int32_t activation,
                          const b200_buf* residual, size_t residual_off, b200_buf* out, size_t out_off);
 
+/* ------------------------------------------------------------------ paged KV cache
+ * PagedKvLayout / PagedAttentionArgs / PagedAttentionPlan of the reference
+ * (crates/tensor-core/src/paged_kv.rs:47-123, 130-200, 204-213), extended with the pool
+ * element type and the number of KV heads.  K and V pools are [num_blocks, block_size,
+ * embed_dim] row-major with embed_dim = num_kv_heads * head_dim; a token row is
+ * block_id * block_size + pos % block_size.  q and out are f32 [batch, l_new, num_heads * head_dim]. */
+typedef struct b200_paged_kv_layout {
+    uint64_t num_blocks;   /* 1 .. u32::MAX - 1 */
+    uint64_t block_size;   /* power of two, 1 .. 256 */
+    uint64_t embed_dim;    /* E of the pools, 1 .. i32::MAX */
+    int32_t dtype;         /* B200_BF16 or B200_F32 */
+} b200_paged_kv_layout;
+
+typedef struct b200_paged_attention_args {
+    b200_paged_kv_layout layout;
+    uint64_t batch;
+    uint64_t l_new;
+    uint64_t num_heads;            /* query heads; a multiple of num_kv_heads */
+    uint64_t num_kv_heads;         /* divides embed_dim; equal to num_heads for the reference's MHA */
+    uint64_t max_blocks_per_seq;
+    float scale;                   /* multiplied into q before the dot product; finite */
+} b200_paged_attention_args;
+
+typedef struct b200_paged_attention_plan {
+    uint64_t out_numel;        /* batch * l_new * num_heads * head_dim */
+    uint64_t s_max;            /* max(seq_lens) */
+    uint64_t query_rows;       /* batch * num_heads * l_new */
+    uint64_t workspace_elems;  /* query_rows * s_max, capped at 2^30 as in the reference */
+} b200_paged_attention_plan;
+
+/* validate_paged_kv_append (crates/tensor-core/src/paged_kv.rs:220-267): element counts, slots
+ * below num_blocks * block_size, no duplicate slot.  Pure host function, needs no device. */
+int32_t b200_validate_paged_kv_append(uint64_t k_new_numel, uint64_t v_new_numel, uint64_t k_pool_numel,
+                                      uint64_t v_pool_numel, const uint32_t* slot_mapping, uint64_t n_slots,
+                                      const b200_paged_kv_layout* layout, uint64_t* rows_out);
+/* validate_paged_attention (crates/tensor-core/src/paged_kv.rs:276-373): l_new <= seq_len <=
+ * max_blocks_per_seq * block_size, used block ids < num_blocks (the sentinel 0xFFFFFFFF only in
+ * unused slots), workspace cap.  Pure host function, needs no device. */
+int32_t b200_validate_paged_attention(uint64_t q_numel, uint64_t k_pool_numel, uint64_t v_pool_numel,
+                                      const uint32_t* block_tables, uint64_t n_tables, const uint32_t* seq_lens,
+                                      uint64_t n_seq_lens, const b200_paged_attention_args* args,
+                                      b200_paged_attention_plan* plan_out);
+
+/* BackendOps::paged_kv_append (crates/tensor-core/src/backend_ops.rs:4709-4722): row r of k_new / v_new
+ * (f32 [rows, embed_dim]) goes to pool row slot_mapping[r] (host array), rounded to the pool dtype.
+ * Validates first, then enqueues; no sync. */
+int32_t b200_paged_kv_append(b200_ctx* ctx, const b200_buf* k_new, size_t k_new_off, const b200_buf* v_new,
+                             size_t v_new_off, b200_buf* k_pool, b200_buf* v_pool, const uint32_t* slot_mapping,
+                             uint64_t n_slots, const b200_paged_kv_layout* layout);
+
+/* BackendOps::paged_attention_forward (crates/tensor-core/src/backend_ops.rs:4755-4769):
+ * out[b, i, h, :] = softmax_j((q * scale) . k_j) . v_j over j <= seq_len[b] - l_new + i.
+ * block_tables is the host array [batch, max_blocks_per_seq] (unused slots 0xFFFFFFFF), seq_lens the
+ * host array [batch]; both are validated and uploaded on every call, as the reference does. */
+int32_t b200_paged_attention_forward(b200_ctx* ctx, const b200_buf* q, size_t q_off, const b200_buf* k_pool,
+                                     const b200_buf* v_pool, const uint32_t* block_tables, uint64_t n_tables,
+                                     const uint32_t* seq_lens, uint64_t n_seq_lens,
+                                     const b200_paged_attention_args* args, b200_buf* out, size_t out_off);
+
+/* Same computation with block tables and seq_lens already resident on the device (u32 buffers kept
+ * and updated incrementally by the decode loop); `max_seq_len` is an upper bound of seq_lens that
+ * sizes the split grid.  The host cannot check the table contents here: a used slot holding an id
+ * >= num_blocks makes the kernel set the device error word (reported by the next download /
+ * synchronize) instead of touching memory.  No counterpart in the reference, which re-uploads the
+ * tables on each call (crates/backend-cuda/src/paged_kv.rs:222-310). */
+int32_t b200_paged_attention_forward_resident(b200_ctx* ctx, const b200_buf* q, size_t q_off, const b200_buf* k_pool,
+                                              const b200_buf* v_pool, const b200_buf* block_tables,
+                                              const b200_buf* seq_lens, uint64_t max_seq_len,
+                                              const b200_paged_attention_args* args, b200_buf* out, size_t out_off);
+
+/* Blocks per split of the decode-attention kernel (1..32; 0 restores the default), for tuning. */
+int32_t b200_paged_attention_tuning(b200_ctx* ctx, int32_t chunk_blocks);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,301 @@
+"""Pins the CPU oracle against the known-answer vectors that the reference's own tests hold
+for this path (no GPU).  Each test names the reference test it takes its vector from."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+
+def test_fma_reference_hand_computed_2x2():
+    # crates/backend-cpu/tests/fma_contract.rs: hand-computed 2x2 product = [19, 22, 43, 50]
+    c = O.matmul_reference_fma(np.array([[1, 2], [3, 4]], np.float32), np.array([[5, 6], [7, 8]], np.float32))
+    assert c.ravel().tolist() == [19.0, 22.0, 43.0, 50.0]
+
+
+def test_fma_reference_is_k_ascending_fma_chain():
+    # crates/backend-cpu/src/parity.rs:340-361: c = fma(a_ip, b_pj, c) for p ascending; a non-fused
+    # accumulation must be detectable at K = 4096 (the falsification test of fma_contract.rs).
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((2, 4096)).astype(np.float32)
+    b = rng.standard_normal((4096, 3)).astype(np.float32)
+    got = O.matmul_reference_fma(a, b)
+    fused = np.zeros((2, 3), np.float32)
+    plain = np.zeros((2, 3), np.float32)
+    for i in range(2):
+        for j in range(3):
+            acc_f = np.float32(0)
+            acc_p = np.float32(0)
+            for p in range(4096):
+                # fma in f64 is exact for f32 operands, then one rounding
+                acc_f = np.float32(np.float64(a[i, p]) * np.float64(b[p, j]) + np.float64(acc_f))
+                acc_p = np.float32(np.float32(a[i, p] * b[p, j]) + acc_p)
+            fused[i, j], plain[i, j] = acc_f, acc_p
+    assert np.array_equal(got, fused)
+    assert not np.array_equal(got, plain)
+
+
+def _pattern_a(r, k):
+    # crates/backend-cuda/tests/int8_mma_probe_real_device.rs:143-149
+    if (r, k) == (0, 0):
+        return -128
+    if (r, k) == (1, 1):
+        return 127
+    return (r * 37 + k * 91 + 11) % 251 - 125
+
+
+def _pattern_b(k, c):
+    # int8_mma_probe_real_device.rs:151-157
+    if (k, c) == (0, 0):
+        return -128
+    if (k, c) == (31, 7):
+        return 127
+    return (k * 53 + c * 29 + 7) % 247 - 123
+
+
+def test_int8_accumulate_matches_probe_host_model():
+    # model_is_consistent_with_naive_gemm (int8_mma_probe_real_device.rs:490-515): 16x32 by 32x8,
+    # edge values -128 / 127 included, i64 reference truncated to i32
+    a = np.array([[_pattern_a(r, k) for k in range(32)] for r in range(16)], np.int8)
+    b = np.array([[_pattern_b(k, c) for c in range(8)] for k in range(32)], np.int8)
+    acc = O.gemm_i8_s32(a, np.ascontiguousarray(b.T))
+    ref = a.astype(np.int64) @ b.astype(np.int64)
+    assert np.array_equal(acc.astype(np.int64), ref)
+    assert a[0, 0] == -128 and a[1, 1] == 127 and b[0, 0] == -128 and b[31, 7] == 127
+
+
+def test_int8_k128_chain_and_k_safe():
+    # tier1_and_k128_expectations_are_arithmetically_exact: A = B = 127 over K = 128 -> 2 064 512
+    a = np.full((1, 128), 127, np.int8)
+    acc = O.gemm_i8_s32(a, a)
+    assert acc[0, 0] == 2_064_512 == 4 * 32 * 127 * 127
+    # k_safe_boundary_arithmetic: K_safe = floor(i32::MAX / 127^2) = 133 144
+    k_safe = (2**31 - 1) // (127 * 127)
+    assert k_safe == 133_144
+    a = np.full((1, k_safe), 127, np.int8)
+    assert int(O.gemm_i8_s32(a, a)[0, 0]) == k_safe * 127 * 127
+    # one more term wraps around in two's complement, as a wrapping i32 add does
+    a = np.full((1, k_safe + 1), 127, np.int8)
+    assert int(O.gemm_i8_s32(a, a)[0, 0]) == (k_safe + 1) * 127 * 127 - 2**32
+
+
+def test_bf16_round_to_nearest_even():
+    # crates/backend-cpu/src/typed_bf16.rs:359-380: 1 + 2^-8 is a tie and goes to 1.0 (even)
+    assert O.bf16_to_f32(O.f32_to_bf16(np.float32(1.0 + 2.0**-8))) == 1.0
+    assert O.bf16_to_f32(O.f32_to_bf16(np.float32(1.0 + 3 * 2.0**-8))) == np.float32(1.0 + 2.0**-6)
+    # crates/facade/tests/low_precision_ops_backend_parity.rs:132-167: overflow to inf, NaN stays NaN
+    assert np.isinf(O.bf16_to_f32(O.f32_to_bf16(np.float32(3.4e38))))
+    assert np.isnan(O.bf16_to_f32(O.f32_to_bf16(np.float32("nan"))))
+    # against an independent implementation
+    import torch
+
+    x = torch.randn(100000) * 37.0
+    want = x.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(O.f32_to_bf16(x.numpy()), want)
+
+
+def test_composite_tolerance_boundary_table():
+    # crates/tensor-core/src/tolerance.rs:43-87
+    assert O.composite_close(1.001_000_5, 1.0) and O.composite_close(1.0, 1.001_000_5)
+    assert not O.composite_close(1.01, 1.0)
+    assert O.composite_close(0.0, 0.0)
+    assert O.composite_close(5e-6, 0.0)
+    assert not O.composite_close(2e-5, 0.0)
+    assert not O.composite_close(float("nan"), 1.0)
+    assert not O.composite_close(float("inf"), 1.0)
+    assert not O.composite_close(float("inf"), float("inf"))
+    vals = [0.0, 1e-12, 5e-6, 2e-5, 0.5, 1.0, 1.0005, 1.001_000_5, 1.002, -1.0, -1.001_000_5, 1e20, 1.0011e20]
+    for a in vals:
+        for b in vals:
+            x, y = float(np.float32(a)), float(np.float32(b))
+            diff = abs(x - y)
+            rel = diff / max(abs(x), abs(y), 1e-12)
+            assert O.composite_close(a, b) == (rel < 1e-3 or diff < 1e-5), (a, b)
+
+
+def test_rmsnorm_basic_and_nan():
+    # crates/backend-cpu/src/rmsnorm.rs:431-441: x = [1,2,3,4], mean(x^2) = 7.5
+    x = np.array([[1, 2, 3, 4]], np.float32)
+    out = O.rmsnorm(x, None, 0.0)
+    rstd = np.float32(1.0) / np.sqrt(np.float32(7.5))
+    assert np.all(np.abs(out - x * rstd) < 1e-5)
+    # rmsnorm.rs:451-462: one NaN element makes the whole row NaN
+    for hidden in (4, 5):
+        x = np.ones((1, hidden), np.float32)
+        x[0, 0] = np.nan
+        assert np.all(np.isnan(O.rmsnorm(x, None, 1e-5)))
+    # f64 sum of squares: a row whose f32 sum of squares would overflow stays finite
+    big = np.full((1, 8), 1e20, np.float32)
+    assert np.all(np.isfinite(O.rmsnorm(big, None, 0.0)))
+
+
+def test_sigmoid_is_the_two_branch_form():
+    # crates/tensor-core/src/scalar_op.rs:666-673: never exponentiates a positive argument
+    assert O.sigmoid_stable(0.0) == 0.5
+    assert O.sigmoid_stable(200.0) == 1.0
+    assert O.sigmoid_stable(-200.0) == 0.0
+    assert O.silu(-200.0) == 0.0 and O.silu(200.0) == 200.0
+    for x in (-3.0, -0.5, 0.25, 4.0):
+        assert abs(O.sigmoid_stable(x) - 1.0 / (1.0 + np.exp(-x))) < 1e-6
+
+
+def test_greedy_argmax_takes_the_first_maximum():
+    # crates/autodiff/src/generate/mod.rs:333-343: strict '>' keeps the smallest index on ties
+    assert O.greedy_argmax([1.0, 3.0, 3.0, 2.0]) == 1
+    assert O.greedy_argmax([5.0, 5.0, 5.0]) == 0
+    assert O.greedy_argmax([-2.0, -1.0]) == 1
+
+
+def _paged_case(block_size, batch, embed, heads, steps, scale_in=1.0, seed=3):
+    """Runs the append/attention step sequence of one reference case on the oracle in f32 MHA mode
+    and returns the outputs per step together with a dense (unpaged) recomputation."""
+    rng = np.random.default_rng(seed)
+    total = sum(steps)
+    nblk = batch * -(-total // block_size) + 2
+    k_pool = np.zeros((nblk * block_size, embed), np.float32)
+    v_pool = np.zeros_like(k_pool)
+    # physical block ids handed out in reverse so that physical order != logical order
+    # (crates/backend-cuda/tests/paged_kv_real_device.rs:228-245)
+    free = list(range(nblk))
+    tables = [[] for _ in range(batch)]
+    dense_k = [np.zeros((0, embed), np.float32) for _ in range(batch)]
+    dense_v = [np.zeros((0, embed), np.float32) for _ in range(batch)]
+    seq = 0
+    mbps = -(-total // block_size)
+    outs = []
+    dh = embed // heads
+    for l_new in steps:
+        k_new = (rng.standard_normal((batch, l_new, embed)) * scale_in).astype(np.float32)
+        v_new = (rng.standard_normal((batch, l_new, embed)) * scale_in).astype(np.float32)
+        q = (rng.standard_normal((batch, l_new, embed)) * scale_in).astype(np.float32)
+        slots = []
+        for b in range(batch):
+            for i in range(l_new):
+                pos = seq + i
+                if pos % block_size == 0:
+                    tables[b].append(free.pop())
+                slots.append(tables[b][pos // block_size] * block_size + pos % block_size)
+            dense_k[b] = np.concatenate([dense_k[b], k_new[b]])
+            dense_v[b] = np.concatenate([dense_v[b], v_new[b]])
+        O.paged_kv_append(k_new.reshape(-1, embed), v_new.reshape(-1, embed), k_pool, v_pool, slots, embed, False)
+        seq += l_new
+        flat = np.full((batch, mbps), 0xFFFFFFFF, np.uint32)
+        for b in range(batch):
+            flat[b, : len(tables[b])] = tables[b]
+        scale = 1.0 / np.sqrt(dh)
+        out = O.paged_attention(q, k_pool, v_pool, flat, [seq] * batch, batch=batch, l_new=l_new, num_q_heads=heads,
+                                num_kv_heads=heads, head_dim=dh, block_size=block_size, num_blocks=nblk,
+                                max_blocks_per_seq=mbps, scale=scale, kv_bf16=False)
+        # dense recomputation with the mask j <= s_prev + i
+        dense = np.zeros_like(out)
+        for b in range(batch):
+            for h in range(heads):
+                kk = dense_k[b][:, h * dh:(h + 1) * dh].astype(np.float64)
+                vv = dense_v[b][:, h * dh:(h + 1) * dh].astype(np.float64)
+                for i in range(l_new):
+                    lim = seq - l_new + i + 1
+                    s = (q[b, i, h * dh:(h + 1) * dh].astype(np.float64) * scale) @ kk[:lim].T
+                    p = np.exp(s - s.max())
+                    p /= p.sum()
+                    dense[b, i, h * dh:(h + 1) * dh] = p @ vv[:lim]
+        outs.append((out, dense))
+    return outs
+
+
+# a subset of the reference's shape matrix (crates/backend-cuda/tests/common/paged_attention_judgement.rs:58-97):
+# (name, block_size, batch, embed, heads, steps)
+PAGED_CASES = [
+    ("legacy_bs1_b1", 1, 1, 8, 2, [3, 1, 1]),
+    ("legacy_bs4_b2", 4, 2, 16, 2, [5, 1, 1, 4]),
+    ("legacy_bs16_b3", 16, 3, 48, 3, [16, 1, 15]),
+    ("bs2_prefill3", 2, 2, 16, 2, [3, 1, 1]),
+    ("bs16_prefill15", 16, 2, 16, 2, [15, 1, 1]),
+    ("bs16_prefill16", 16, 2, 16, 2, [16, 1, 1]),
+    ("bs16_prefill17", 16, 2, 16, 2, [17, 1, 1]),
+    ("long_bs16_s301", 16, 2, 32, 2, [100, 100, 100, 1]),
+    ("dh160_h1", 16, 1, 160, 1, [5, 1, 1]),
+    ("dh1_e4_h4", 4, 2, 4, 4, [6, 1, 1]),
+    ("multi_prefill_bs4", 4, 2, 16, 2, [3, 4, 5, 1]),
+]
+
+
+@pytest.mark.parametrize("case", PAGED_CASES, ids=[c[0] for c in PAGED_CASES])
+def test_paged_attention_oracle_equals_dense_attention(case):
+    # The reference pins its paged attention by comparing it with the unpaged K-1 cache path
+    # (crates/facade/tests/paged_attention_facade.rs:93-197); the same cross-check pins the oracle.
+    _, bs, batch, embed, heads, steps = case
+    for out, dense in _paged_case(bs, batch, embed, heads, steps):
+        fails, max_abs, max_rel = O.compare(out, dense)
+        assert fails == 0, (max_abs, max_rel)
+
+
+def test_paged_attention_seq_len_one_returns_the_v_row():
+    # smoke vector of crates/backend-cuda/tests/paged_kv_real_device.rs:177-189
+    (out, _), = _paged_case(4, 2, 16, 2, [1])
+    rng = np.random.default_rng(3)
+    _k = rng.standard_normal((2, 1, 16))
+    v = rng.standard_normal((2, 1, 16)).astype(np.float32)
+    assert np.array_equal(out, v)
+
+
+def test_paged_attention_large_amplitude_is_finite():
+    # case "large_amplitude" (input_scale 4.0)
+    for out, dense in _paged_case(16, 2, 32, 2, [17, 1, 1], scale_in=4.0):
+        assert np.all(np.isfinite(out))
+        assert O.compare(out, dense)[0] == 0
+
+
+def test_gqa_bf16_generalisation_reduces_to_the_pinned_case():
+    # The GQA / bf16 extension is unpinned by the reference; with one q head per kv head and values that
+    # are exactly representable in bf16 it must reproduce the f32 multi-head result bit for bit.
+    rng = np.random.default_rng(11)
+    bs, nblk, heads, dh, seq = 4, 6, 2, 8, 9
+    e = heads * dh
+    k = O.bf16_to_f32(O.f32_to_bf16(rng.standard_normal((nblk * bs, e)).astype(np.float32)))
+    v = O.bf16_to_f32(O.f32_to_bf16(rng.standard_normal((nblk * bs, e)).astype(np.float32)))
+    q = rng.standard_normal((1, 1, e)).astype(np.float32)
+    tables = np.array([[5, 2, 0]], np.uint32)
+    kw = dict(batch=1, l_new=1, num_q_heads=heads, num_kv_heads=heads, head_dim=dh, block_size=bs, num_blocks=nblk,
+              max_blocks_per_seq=3, scale=0.35)
+    a = O.paged_attention(q, k, v, tables, [seq], kv_bf16=False, **kw)
+    b = O.paged_attention(q, O.f32_to_bf16(k), O.f32_to_bf16(v), tables, [seq], kv_bf16=True, **kw)
+    assert np.array_equal(a, b)
+    # grouped: 4 q heads on 2 kv heads == MHA over the kv heads repeated per group
+    q4 = rng.standard_normal((1, 1, 4 * dh)).astype(np.float32)
+    kw4 = dict(kw, num_q_heads=4)
+    g = O.paged_attention(q4, k, v, tables, [seq], kv_bf16=False, **kw4)
+    k_rep = np.repeat(k.reshape(-1, heads, dh), 2, axis=1).reshape(-1, 4 * dh)
+    v_rep = np.repeat(v.reshape(-1, heads, dh), 2, axis=1).reshape(-1, 4 * dh)
+    kw_rep = dict(kw, num_q_heads=4, num_kv_heads=4)
+    m = O.paged_attention(q4, k_rep, v_rep, tables, [seq], kv_bf16=False, **kw_rep)
+    assert np.array_equal(g, m)
+
+
+def test_e4m3_encode_against_independent_implementation():
+    # unpinned by the reference; checked against torch's float8_e4m3fn cast (RNE, finite range)
+    import torch
+
+    codes = np.arange(256, dtype=np.uint8)
+    vals = O.e4m3_to_f32(codes)
+    want = torch.from_numpy(codes).view(torch.float8_e4m3fn).float().numpy()
+    assert np.array_equal(np.nan_to_num(vals, nan=-1.0), np.nan_to_num(want, nan=-1.0))
+    for scale in (50.0, 1.0, 0.01):
+        x = torch.randn(50000) * scale
+        x = x[x.abs() <= 448]
+        want = x.to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+        got = np.array([O.f32_to_e4m3_scalar(float(v)) for v in x.numpy()], np.uint8)
+        assert np.array_equal(got, want)
+    assert O.f32_to_e4m3_scalar(1e9) == 0x7E and O.f32_to_e4m3_scalar(-1e9) == 0xFE  # saturation to +-448
+
+
+def test_int8_quantiser_rule():
+    # unpinned by the reference; the rule of the benchmark text: scale = max|row| / 127, round half even
+    x = np.array([[127.0, -63.5, 62.5, 0.4, -0.6, 1.5, 2.5, -127.0], [0, 0, 0, 0, 0, 0, 0, 0]], np.float32)
+    q, s = O.quantize_i8_per_row(x)
+    assert s[0] == 1.0 and s[1] == 0.0
+    assert q[0].tolist() == [127, -64, 62, 0, -1, 2, 2, -127]   # ties to even: 63.5 -> 64, 62.5 -> 62, 2.5 -> 2
+    assert q[1].tolist() == [0] * 8
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((64, 256)) * 0.02).astype(np.float32)
+    q, s = O.quantize_i8_per_row(w)
+    assert np.all(np.abs(q).max(axis=1) == 127)
+    assert np.allclose(O.dequantize_i8_per_row(q, s), w, atol=float(s.max()) * 0.5 + 1e-9)

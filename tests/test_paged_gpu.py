@@ -1,0 +1,256 @@
+"""GPU parity of the paged KV cache (append + attention) against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from fandhe_ai_b200 import BF16, F32, BackendError
+from fandhe_ai_b200 import paged_kv as P
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(be, block_size, batch, embed, heads, steps, scale_in=1.0, kv_heads=0, dtype=F32, seed=3, rewind=None):
+    """The reference's case driver (crates/backend-cuda/tests/paged_kv_real_device.rs:44-145): a sequence of
+    appends of steps[i] tokens, each followed by attention over everything cached; physical block ids are
+    handed out in reverse.  Every step is compared with the oracle under the strict composite judgement."""
+    rng = np.random.default_rng(seed)
+    kvh = kv_heads or heads
+    dh = embed // heads
+    ekv = kvh * dh
+    total = sum(steps)
+    nblk = batch * -(-total // block_size) + 2
+    layout = P.PagedKvLayout(nblk, block_size, ekv, dtype)
+    npdt = layout.np_dtype
+    k_pool_h = np.zeros((nblk * block_size, ekv), npdt)
+    v_pool_h = np.zeros_like(k_pool_h)
+    k_pool = be.alloc_zeroed(k_pool_h.shape, npdt)
+    v_pool = be.alloc_zeroed(k_pool_h.shape, npdt)
+    free = list(range(nblk))
+    tables = [[] for _ in range(batch)]
+    seq = 0
+    mbps = -(-total // block_size)
+    for step, l_new in enumerate(steps):
+        if rewind is not None and rewind[0] == step:
+            seq = rewind[1]
+            keep = -(-seq // block_size)
+            for b in range(batch):
+                while len(tables[b]) > keep:
+                    free.append(tables[b].pop())
+        k_new = (rng.standard_normal((batch, l_new, ekv)) * scale_in).astype(np.float32)
+        v_new = (rng.standard_normal((batch, l_new, ekv)) * scale_in).astype(np.float32)
+        q = (rng.standard_normal((batch, l_new, embed)) * scale_in).astype(np.float32)
+        slots = []
+        for b in range(batch):
+            for i in range(l_new):
+                pos = seq + i
+                if pos % block_size == 0:
+                    tables[b].append(free.pop())
+                slots.append(tables[b][pos // block_size] * block_size + pos % block_size)
+        P.paged_kv_append(be, be.upload(k_new), be.upload(v_new), k_pool, v_pool, slots, layout)
+        O.paged_kv_append(k_new.reshape(-1, ekv), v_new.reshape(-1, ekv), k_pool_h, v_pool_h, slots, ekv, dtype == BF16)
+        seq += l_new
+        flat = np.full((batch, mbps), P.SENTINEL, np.uint32)
+        for b in range(batch):
+            flat[b, : len(tables[b])] = tables[b]
+        args = P.PagedAttentionArgs(layout, batch, l_new, heads, mbps, float(1.0 / np.sqrt(dh)), kvh)
+        out = P.paged_attention_forward(be, be.upload(q), k_pool, v_pool, flat, [seq] * batch, args).numpy()
+        ref = O.paged_attention(q, k_pool_h, v_pool_h, flat, [seq] * batch, batch=batch, l_new=l_new, num_q_heads=heads,
+                                num_kv_heads=kvh, head_dim=dh, block_size=block_size, num_blocks=nblk,
+                                max_blocks_per_seq=mbps, scale=args.scale, kv_bf16=dtype == BF16)
+        fails, max_abs, max_rel = O.compare(out, ref)
+        assert fails == 0, (step, max_abs, max_rel)
+    assert np.array_equal(k_pool.numpy(), k_pool_h) and np.array_equal(v_pool.numpy(), v_pool_h)
+
+
+# the reference's 23-case shape matrix (crates/backend-cuda/tests/common/paged_attention_judgement.rs:58-97)
+CASES = [
+    ("legacy_bs1_b1", 1, 1, 8, 2, [3, 1, 1], {}),
+    ("legacy_bs4_b2", 4, 2, 16, 2, [5, 1, 1, 4], {}),
+    ("legacy_bs16_b1", 16, 1, 64, 4, [17, 1, 1], {}),
+    ("legacy_bs16_b3", 16, 3, 48, 3, [16, 1, 15], {}),
+    ("bs1_prefill1", 1, 2, 16, 2, [1, 1, 1], {}),
+    ("bs1_prefill2", 1, 2, 16, 2, [2, 1, 1], {}),
+    ("bs2_prefill1", 2, 2, 16, 2, [1, 1, 1], {}),
+    ("bs2_prefill2", 2, 2, 16, 2, [2, 1, 1], {}),
+    ("bs2_prefill3", 2, 2, 16, 2, [3, 1, 1], {}),
+    ("bs16_prefill15", 16, 2, 16, 2, [15, 1, 1], {}),
+    ("bs16_prefill16", 16, 2, 16, 2, [16, 1, 1], {}),
+    ("bs16_prefill17", 16, 2, 16, 2, [17, 1, 1], {}),
+    ("bs256_prefill255", 256, 2, 16, 2, [255, 1, 1], {}),
+    ("bs256_prefill256", 256, 2, 16, 2, [256, 1, 1], {}),
+    ("bs256_prefill257", 256, 2, 16, 2, [257, 1, 1], {}),
+    ("long_bs16_s301", 16, 2, 32, 2, [100, 100, 100, 1], {}),
+    ("dh160_h1", 16, 1, 160, 1, [5, 1, 1], {}),
+    ("dh1_e4_h4", 4, 2, 4, 4, [6, 1, 1], {}),
+    ("multi_prefill_bs4", 4, 2, 16, 2, [3, 4, 5, 1], {}),
+    ("rewind_mid_block", 4, 2, 16, 2, [9, 1, 5], {"rewind": (1, 6)}),
+    ("rewind_to_boundary", 4, 2, 16, 2, [9, 2], {"rewind": (0 + 1, 4)}),
+    ("large_amplitude", 16, 2, 32, 2, [17, 1, 1], {"scale_in": 4.0}),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_reference_shape_matrix_f32_mha(be, case):
+    _, bs, batch, embed, heads, steps, kw = case
+    run_case(be, bs, batch, embed, heads, steps, dtype=F32, **kw)
+
+
+@pytest.mark.parametrize("case", CASES[:6] + CASES[15:17], ids=[c[0] for c in CASES[:6] + CASES[15:17]])
+def test_reference_shape_matrix_bf16_pools(be, case):
+    _, bs, batch, embed, heads, steps, kw = case
+    run_case(be, bs, batch, embed, heads, steps, dtype=BF16, **kw)
+
+
+# the split-K fast path: head_dim 128, bf16, block 16, grouped heads
+@pytest.mark.parametrize("heads,kv_heads,batch,steps", [
+    (4, 1, 2, [15, 1, 1]), (4, 1, 2, [16, 1, 1]), (4, 1, 2, [17, 1, 1]),
+    (8, 2, 3, [255, 1, 1]), (8, 2, 3, [256, 1]), (8, 2, 3, [257, 1]),     # the split boundary (256 tokens) +- 1
+    (32, 8, 2, [700, 1, 1]), (2, 2, 2, [300, 1]), (4, 2, 2, [300, 1]), (8, 1, 1, [530, 1]),
+    (4, 1, 2, [40, 3, 2]),                                                  # l_new > 1 with cached tokens
+])
+def test_split_k_fast_path(be, heads, kv_heads, batch, steps):
+    run_case(be, 16, batch, heads * 128, heads, steps, kv_heads=kv_heads, dtype=BF16, seed=heads + batch)
+
+
+def test_fast_path_large_amplitude_and_split_sizes(be):
+    for chunk_blocks in (1, 4, 32):
+        P.paged_attention_tuning(be, chunk_blocks)
+        try:
+            run_case(be, 16, 2, 4 * 128, 4, [600, 1], kv_heads=1, dtype=BF16, scale_in=3.0)
+        finally:
+            P.paged_attention_tuning(be, 0)
+
+
+def ragged_problem(batch, heads, kv_heads, lo, hi, nblk, seed):
+    """Config-3-shaped problem: per-sequence context lengths ~ U[lo, hi], block tables = consecutive slices
+    of a seeded permutation of the block pool, q/k/v ~ N(0,1)."""
+    rng = np.random.default_rng(seed)
+    dh, bs = 128, 16
+    ekv = kv_heads * dh
+    ctx = rng.integers(lo, hi + 1, batch)
+    mbps = -(-hi // bs)
+    perm = rng.permutation(nblk).astype(np.uint32)
+    tables = np.full((batch, mbps), P.SENTINEL, np.uint32)
+    at = 0
+    for b in range(batch):
+        used = -(-int(ctx[b]) // bs)
+        tables[b, :used] = perm[at:at + used]
+        at += used
+    assert at <= nblk
+    pool_rows = nblk * bs
+    k = O.f32_to_bf16(rng.standard_normal((pool_rows, ekv), dtype=np.float32))
+    v = O.f32_to_bf16(rng.standard_normal((pool_rows, ekv), dtype=np.float32))
+    q = rng.standard_normal((batch, 1, heads * dh), dtype=np.float32)
+    layout = P.PagedKvLayout(nblk, bs, ekv, BF16)
+    args = P.PagedAttentionArgs(layout, batch, 1, heads, mbps, float(1.0 / np.sqrt(dh)), kv_heads)
+    return q, k, v, tables, ctx.astype(np.uint32), args
+
+
+def test_config3_shape_ragged_contexts(be):
+    # batch 8 of the 64, same head geometry (32 q heads / 8 kv heads), contexts U[512, 8192]
+    q, k, v, tables, ctx, args = ragged_problem(8, 32, 8, 512, 8192, 5000, seed=0)
+    out = P.paged_attention_forward(be, be.upload(q), be.upload(k), be.upload(v), tables, ctx, args).numpy()
+    ref = O.paged_attention(q, k, v, tables, ctx, batch=8, l_new=1, num_q_heads=32, num_kv_heads=8, head_dim=128,
+                            block_size=16, num_blocks=5000, max_blocks_per_seq=args.max_blocks_per_seq, scale=args.scale,
+                            kv_bf16=True)
+    fails, max_abs, max_rel = O.compare(out, ref)
+    assert fails == 0, (max_abs, max_rel)
+
+
+def test_resident_tables_entry_matches_host_tables_entry(be):
+    q, k, v, tables, ctx, args = ragged_problem(4, 8, 2, 100, 1500, 600, seed=1)
+    qd, kd, vd = be.upload(q), be.upload(k), be.upload(v)
+    a = P.paged_attention_forward(be, qd, kd, vd, tables, ctx, args).numpy()
+    out = be.alloc_zeroed(a.shape, np.float32)
+    P.paged_attention_forward_resident(be, qd, kd, vd, be.upload(tables), be.upload(ctx), int(ctx.max()), args, out)
+    assert np.array_equal(out.numpy(), a)
+
+
+def test_full_size_properties_config3(be):
+    """Config 3 at full size (batch 64, 200k-block pool): properties that need no oracle pass.
+    (a) V rows all equal to one vector -> the output is that vector whatever the scores are;
+    (b) permuting the physical blocks (and the tables with them) leaves the output unchanged bit for bit."""
+    rng = np.random.default_rng(5)
+    batch, heads, kvh, dh, bs, nblk = 64, 32, 8, 128, 16, 200_000
+    ekv = kvh * dh
+    ctx = rng.integers(512, 8193, batch).astype(np.uint32)
+    mbps = 512
+    used_total = int(sum(-(-int(c) // bs) for c in ctx))
+    perm = rng.permutation(nblk).astype(np.uint32)
+    tables = np.full((batch, mbps), P.SENTINEL, np.uint32)
+    at = 0
+    for b in range(batch):
+        used = -(-int(ctx[b]) // bs)
+        tables[b, :used] = perm[at:at + used]
+        at += used
+    layout = P.PagedKvLayout(nblk, bs, ekv, BF16)
+    args = P.PagedAttentionArgs(layout, batch, 1, heads, mbps, float(1.0 / np.sqrt(dh)), kvh)
+    q = rng.standard_normal((batch, 1, heads * dh), dtype=np.float32)
+    # (a) constant V
+    vec = O.bf16_to_f32(O.f32_to_bf16(rng.standard_normal(ekv, dtype=np.float32)))
+    k_pool = be.alloc_zeroed((nblk * bs, ekv), np.uint16)
+    v_pool = be.alloc_zeroed((nblk * bs, ekv), np.uint16)
+    used_blocks = perm[:used_total]
+    k_rows = O.f32_to_bf16(rng.standard_normal((used_total * bs, ekv), dtype=np.float32))
+    v_rows = np.tile(O.f32_to_bf16(vec), (used_total * bs, 1))
+    # upload block by block into the scattered physical positions (contiguous runs of the permutation are rare,
+    # so stage through a host image of the used rows only)
+    order = np.argsort(used_blocks)
+    for idx in order:
+        blk = int(used_blocks[idx])
+        be.upload_into(k_rows[idx * bs:(idx + 1) * bs], k_pool, blk * bs * ekv * 2)
+        be.upload_into(v_rows[idx * bs:(idx + 1) * bs], v_pool, blk * bs * ekv * 2)
+    qd = be.upload(q)
+    out = P.paged_attention_forward(be, qd, k_pool, v_pool, tables, ctx, args).numpy()
+    want = np.tile(vec.reshape(kvh, 1, dh), (1, heads // kvh, 1)).reshape(-1)
+    err = np.abs(out - want[None, None, :])
+    assert np.all(err <= 1e-3 * np.abs(want)[None, None, :] + 1e-5)
+    # (b) the same logical content behind different physical blocks: shift every used block id by a fixed
+    # rotation inside the used set
+    rot = np.roll(used_blocks, 1)
+    remap = {int(a): int(b) for a, b in zip(used_blocks, rot)}
+    tables2 = tables.copy()
+    for b in range(batch):
+        used = -(-int(ctx[b]) // bs)
+        tables2[b, :used] = [remap[int(x)] for x in tables[b, :used]]
+    k_pool2 = be.alloc_zeroed((nblk * bs, ekv), np.uint16)
+    for idx in order:
+        blk = remap[int(used_blocks[idx])]
+        be.upload_into(k_rows[idx * bs:(idx + 1) * bs], k_pool2, blk * bs * ekv * 2)
+    out2 = P.paged_attention_forward(be, qd, k_pool2, v_pool, tables2, ctx, args).numpy()
+    # V is constant everywhere it is read, so only K moved
+    v_pool2 = be.alloc_zeroed((nblk * bs, ekv), np.uint16)
+    for idx in order:
+        blk = remap[int(used_blocks[idx])]
+        be.upload_into(v_rows[idx * bs:(idx + 1) * bs], v_pool2, blk * bs * ekv * 2)
+    out3 = P.paged_attention_forward(be, qd, k_pool2, v_pool2, tables2, ctx, args).numpy()
+    assert np.array_equal(out3, out)
+    for b_ in (k_pool, v_pool, k_pool2, v_pool2):
+        b_.release()
+
+
+def test_invalid_arguments_are_rejected_before_any_launch(be):
+    layout = P.PagedKvLayout(4, 2, 4, F32)
+    pool = be.alloc_zeroed((8, 4), np.float32)
+    pool2 = be.alloc_zeroed((8, 4), np.float32)
+    rows = be.upload(np.ones((2, 4), np.float32))
+    with pytest.raises(BackendError) as e:
+        P.paged_kv_append(be, rows, rows, pool, pool2, [3, 3], layout)          # duplicate slot
+    assert e.value.kind == "InvalidArgument"
+    with pytest.raises(BackendError):
+        P.paged_kv_append(be, rows, rows, pool, pool2, [0, 8], layout)          # slot out of range
+    args = P.PagedAttentionArgs(layout, 1, 1, 2, 2, 0.5)
+    q = be.upload(np.ones((1, 1, 4), np.float32))
+    with pytest.raises(BackendError):
+        P.paged_attention_forward(be, q, pool, pool2, [0, P.SENTINEL], [3], args)   # sentinel in a used slot
+    with pytest.raises(BackendError):
+        P.paged_attention_forward(be, q, pool, pool2, [0, 1], [5], args)            # seq_len above capacity
+    assert not be.poisoned
+    assert not pool.numpy().any()
+
+
+def test_stale_and_foreign_buffers_are_errors(be, fresh_be):
+    other = fresh_be.upload(np.ones(16, np.float32))
+    with pytest.raises(BackendError) as e:
+        be.download(other)
+    assert e.value.kind == "DeviceMismatch"

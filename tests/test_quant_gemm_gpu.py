@@ -1,0 +1,232 @@
+"""GPU parity of the quantized linear path against the CPU oracle, through the C ABI.
+Bit-exact for integer / byte work (quantised codes, int32 accumulators, FP8 codes); the composite
+tolerance rel < 1e-3 or abs < 1e-5 (crates/tensor-core/src/tolerance.rs:15-37) for dequantised f32."""
+import numpy as np
+import pytest
+
+from fandhe_ai_b200 import ACT_NONE, ACT_RELU, ACT_SILU, ACT_SILU_GATE, BF16, F32, FP8_E4M3, I8, BackendError
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def normal(seed, shape, std=1.0):
+    return (np.random.default_rng(seed).standard_normal(shape) * std).astype(np.float32)
+
+
+# ---------------------------------------------------------------- quantisers: byte-identical
+@pytest.mark.parametrize("rows,cols", [(128, 4096), (1, 64), (7, 1000), (33, 14336), (5, 3)])
+def test_quantize_i8_per_row_is_byte_identical(be, rows, cols):
+    x = normal(rows * 1000 + cols, (rows, cols))
+    x[0, 0] = 0.0
+    q, s = be.quantize_i8_per_row(be.upload(x), rows, cols)
+    q_ref, s_ref = O.quantize_i8_per_row(x)
+    assert np.array_equal(s.numpy(), s_ref)
+    assert np.array_equal(q.numpy(), q_ref)
+
+
+def test_quantize_i8_zero_row_and_ties(be):
+    x = np.zeros((3, 8), np.float32)
+    x[1] = [127.0, -63.5, 62.5, 0.4, -0.6, 1.5, 2.5, -127.0]
+    q, s = be.quantize_i8_per_row(be.upload(x), 3, 8)
+    assert s.numpy().tolist() == [0.0, 1.0, 0.0]
+    assert q.numpy()[1].tolist() == [127, -64, 62, 0, -1, 2, 2, -127]
+    assert not q.numpy()[0].any() and not q.numpy()[2].any()
+
+
+def test_dequantize_round_trip(be):
+    w = normal(5, (64, 512), 0.02)
+    q, s = be.quantize_i8_per_row(be.upload(w), 64, 512)
+    back = be.dequantize_i8_per_row(q, s, 64, 512).numpy()
+    assert np.array_equal(back, O.dequantize_i8_per_row(*O.quantize_i8_per_row(w)))
+
+
+@pytest.mark.parametrize("n,std", [(128 * 4096, 1.0), (1000, 30.0), (17, 0.001), (1, 2.0)])
+def test_quantize_fp8_is_byte_identical(be, n, std):
+    x = normal(n, (n,), std)
+    q, s = be.quantize_fp8_e4m3_per_tensor(be.upload(x), n)
+    q_ref, s_ref = O.quantize_fp8_per_tensor(x)
+    assert np.array_equal(s.numpy(), s_ref)
+    assert np.array_equal(q.numpy(), q_ref)
+    assert int(q_ref.view(np.uint8).max() & 0x7F) == 0x7E   # amax lands on +-448
+
+
+def test_quantize_fp8_all_zero(be):
+    q, s = be.quantize_fp8_e4m3_per_tensor(be.upload(np.zeros(64, np.float32)), 64)
+    assert s.numpy()[0] == 0.0 and not q.numpy().any()
+
+
+# ---------------------------------------------------------------- int8 GEMM: int32 accumulators bit-exact
+def rand_i8(seed, shape):
+    return np.random.default_rng(seed).integers(-127, 128, size=shape, dtype=np.int8)
+
+
+@pytest.mark.parametrize("m,n,k,tile,splits", [
+    (128, 128, 128, 0, 0), (128, 4096, 4096, 0, 0), (1, 4096, 4096, 0, 0), (16, 1024, 4096, 64, 0),
+    (100, 272, 2064, 0, 0), (300, 1040, 528, 128, 1), (128, 512, 4096, 128, 8), (128, 512, 1024, 256, 3),
+    (257, 256, 384, 256, 1), (1024, 512, 512, 256, 1), (128, 256, 16, 0, 0),
+])
+def test_gemm_i8_s32_is_bit_exact(be, m, n, k, tile, splits):
+    a, w = rand_i8(m + n, (m, k)), rand_i8(k + 1, (n, k))
+    be.gemm_tuning(tile, splits)
+    try:
+        acc = be.gemm_i8_s32(be.upload(a), be.upload(w), m, n, k).numpy()
+    finally:
+        be.gemm_tuning(0, 0)
+    assert np.array_equal(acc, O.gemm_i8_s32(a, w))
+
+
+def test_gemm_i8_extreme_values_and_k128_chain(be):
+    # the edge values of the reference's MMA probe (crates/backend-cuda/tests/int8_mma_probe_real_device.rs):
+    # -128 and 127 operands, and the K = 128 chain of 127 * 127 = 2 064 512
+    a = np.full((128, 128), 127, np.int8)
+    acc = be.gemm_i8_s32(be.upload(a), be.upload(a), 128, 128, 128).numpy()
+    assert np.all(acc == 2_064_512)
+    a = np.full((16, 256), -128, np.int8)
+    w = np.full((32, 256), -128, np.int8)
+    acc = be.gemm_i8_s32(be.upload(a), be.upload(w), 16, 32, 256).numpy()
+    assert np.all(acc == 128 * 128 * 256)
+    w[:] = 127
+    acc = be.gemm_i8_s32(be.upload(a), be.upload(w), 16, 32, 256).numpy()
+    assert np.all(acc == -128 * 127 * 256)
+
+
+def test_gemm_rejects_unaligned_shapes_without_fallback(be):
+    a, w = rand_i8(1, (8, 24)), rand_i8(2, (16, 24))
+    with pytest.raises(BackendError) as e:
+        be.gemm_i8_s32(be.upload(a), be.upload(w), 8, 16, 24)
+    assert e.value.kind == "Unsupported"
+    assert not be.poisoned
+
+
+# ---------------------------------------------------------------- config 1: INT8 quantized linear
+def test_config1_int8_linear(be):
+    # X [128, 4096] ~ N(0,1) seed 0, W [4096, 4096] ~ N(0, 0.02^2), bias ~ U(-0.1, 0.1)
+    m, k, n = 128, 4096, 4096
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    bias = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+    wq_d, ws_d = be.quantize_i8_per_row(be.upload(w), n, k)
+    xq_d, xs_d = be.quantize_i8_per_row(be.upload(x), m, k)
+    wq, ws = O.quantize_i8_per_row(w)
+    xq, xs = O.quantize_i8_per_row(x)
+    assert np.array_equal(wq_d.numpy(), wq) and np.array_equal(ws_d.numpy(), ws)
+    assert np.array_equal(xq_d.numpy(), xq) and np.array_equal(xs_d.numpy(), xs)
+    acc = be.gemm_i8_s32(xq_d, wq_d, m, n, k).numpy()
+    acc_ref = O.gemm_i8_s32(xq, wq)
+    assert np.array_equal(acc, acc_ref)                         # int32 accumulators: bit-exact
+    y = be.linear_forward_device(be.upload(x), m, k, wq_d, ws_d, be.upload(bias), n).numpy()
+    y_ref = O.linear_w8a8(x, wq, ws, bias)
+    fails, max_abs, max_rel = O.compare(y, y_ref)
+    assert fails == 0, (max_abs, max_rel)
+    assert np.array_equal(y, y_ref)                             # same fma on the same integers
+
+
+@pytest.mark.parametrize("act", [ACT_NONE, ACT_RELU, ACT_SILU, ACT_SILU_GATE])
+@pytest.mark.parametrize("m,splits", [(128, 0), (16, 1), (200, 1), (128, 4)])
+def test_linear_epilogues(be, act, m, splits):
+    k, n = 1024, 512
+    x = normal(m, (m, k))
+    w = normal(2, (n, k), 0.02)
+    bias = normal(3, (n,), 0.05)
+    n_out = n // 2 if act == ACT_SILU_GATE else n
+    res = normal(4, (m, n_out))
+    wq, ws = O.quantize_i8_per_row(w)
+    be.gemm_tuning(0, splits)
+    try:
+        y = be.linear_forward_device(be.upload(x), m, k, be.upload(wq), be.upload(ws), be.upload(bias), n, act,
+                                     be.upload(res)).numpy()
+    finally:
+        be.gemm_tuning(0, 0)
+    y_ref = O.linear_w8a8(x, wq, ws, bias, act, res)
+    assert y.shape == y_ref.shape
+    fails, max_abs, max_rel = O.compare(y, y_ref)
+    assert fails == 0, (max_abs, max_rel)
+
+
+def test_linear_into_overwrites_every_output_and_views_into_flat_buffers(be):
+    # DeviceParamStore addressing: weights, scales and biases of two layers live in flat buffers and are
+    # handed over as (buffer, offset) views (crates/autodiff/src/optim/device_store.rs:429-445)
+    m, k, n1, n2 = 32, 256, 128, 64
+    x = normal(1, (m, k))
+    w1, w2 = normal(2, (n1, k), 0.02), normal(3, (n2, n1), 0.02)
+    b1, b2 = normal(4, (n1,), 0.1), normal(5, (n2,), 0.1)
+    (q1, s1), (q2, s2) = O.quantize_i8_per_row(w1), O.quantize_i8_per_row(w2)
+    payload = be.upload(np.concatenate([q1.ravel(), q2.ravel()]))
+    scales = be.upload(np.concatenate([s1, s2]))
+    biases = be.upload(np.concatenate([b1, b2]))
+    h = be.upload(np.full((m, n1), np.nan, np.float32))
+    out = be.upload(np.full((m, n2), np.nan, np.float32))
+    be.linear_forward_device_into(be.upload(x), m, k, payload, 0, scales, 0, biases, 0, n1, ACT_RELU, h)
+    be.linear_forward_device_into(h, m, n1, payload, q1.size, scales, 4 * n1, biases, 4 * n1, n2, ACT_NONE, out)
+    h_ref = O.linear_w8a8(x, q1, s1, b1, ACT_RELU)
+    out_ref = O.linear_w8a8(h_ref, q2, s2, b2, ACT_NONE)
+    got = out.numpy()
+    assert np.all(np.isfinite(got))
+    assert O.compare(got, out_ref)[0] == 0
+
+
+# ---------------------------------------------------------------- config 2: FP8 E4M3 GEMM
+def fp8_operands(seed, m, n, k):
+    a = normal(seed, (m, k))
+    b = normal(seed + 1, (n, k))
+    (aq, sa), (bq, sb) = O.quantize_fp8_per_tensor(a), O.quantize_fp8_per_tensor(b)
+    return aq, sa, bq, sb
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 4096, 4096), (128, 4096, 4096), (128, 1024, 8192),
+                                   (16, 512, 14336), (300, 272, 528)])
+def test_fp8_gemm_bf16_out(be, m, n, k):
+    aq, sa, bq, sb = fp8_operands(m + k, m, n, k)
+    aq_d, sa_d = be.quantize_fp8_e4m3_per_tensor(be.upload(np.zeros(1, np.float32)), 1)  # shapes only
+    y = be.gemm_q8_scaled(FP8_E4M3, be.upload(aq), be.upload(sa), False, be.upload(bq), be.upload(sb), False, m, n, k,
+                          out_dtype=BF16).numpy()
+    acc = O.gemm_fp8_f32(aq, bq)
+    y_ref = O.epilogue_scaled(acc, sa, False, sb, False, out_bf16=True)
+    # the accumulation order inside the tensor core differs from the oracle's k-ascending chain, and the
+    # result is rounded to bf16 (relative step 2^-8): compare the bf16 values within one bf16 step
+    got, ref = O.bf16_to_f32(y), O.bf16_to_f32(y_ref)
+    denom = np.maximum(np.maximum(np.abs(got), np.abs(ref)), 1e-12)
+    assert np.all((np.abs(got - ref) / denom < 2.0**-7) | (np.abs(got - ref) < 1e-5))
+    # and the f32 output within the composite tolerance
+    y32 = be.gemm_q8_scaled(FP8_E4M3, be.upload(aq), be.upload(sa), False, be.upload(bq), be.upload(sb), False, m, n, k,
+                            out_dtype=F32).numpy()
+    fails, max_abs, max_rel = O.compare(y32, O.epilogue_scaled(acc, sa, False, sb, False))
+    assert fails == 0, (max_abs, max_rel)
+
+
+def test_fp8_operands_quantised_on_device_are_identical_and_gated_epilogue(be):
+    m, f, k = 64, 256, 1024        # gate/up concatenated: N = 2 * f
+    a = normal(10, (m, k))
+    b = normal(11, (2 * f, k))
+    aq_d, sa_d = be.quantize_fp8_e4m3_per_tensor(be.upload(a), a.size)
+    bq_d, sb_d = be.quantize_fp8_e4m3_per_tensor(be.upload(b), b.size)
+    (aq, sa), (bq, sb) = O.quantize_fp8_per_tensor(a), O.quantize_fp8_per_tensor(b)
+    assert np.array_equal(aq_d.numpy().reshape(a.shape), aq) and np.array_equal(bq_d.numpy().reshape(b.shape), bq)
+    assert sa_d.numpy()[0] == sa[0] and sb_d.numpy()[0] == sb[0]
+    y = be.gemm_q8_scaled(FP8_E4M3, aq_d, sa_d, False, bq_d, sb_d, False, m, 2 * f, k, activation=ACT_SILU_GATE).numpy()
+    ref = O.epilogue_scaled(O.gemm_fp8_f32(aq, bq), sa, False, sb, False, act=O.ACT_SILU_GATE)
+    assert y.shape == (m, f)
+    fails, max_abs, max_rel = O.compare(y, ref)
+    assert fails == 0, (max_abs, max_rel)
+
+
+# ---------------------------------------------------------------- size-independent properties at full size
+def test_gemm_i8_linearity_and_identity_at_large_size(be):
+    # acc(A, W1 + W2) == acc(A, W1) + acc(A, W2) in exact integers; W = identity copies A
+    m, n, k = 1024, 4096, 4096
+    rng = np.random.default_rng(42)
+    a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    w1 = rng.integers(-60, 61, (n, k), dtype=np.int8)
+    w2 = rng.integers(-60, 61, (n, k), dtype=np.int8)
+    a_d = be.upload(a)
+    s1 = be.gemm_i8_s32(a_d, be.upload(w1), m, n, k).numpy()
+    s2 = be.gemm_i8_s32(a_d, be.upload(w2), m, n, k).numpy()
+    s12 = be.gemm_i8_s32(a_d, be.upload((w1 + w2).astype(np.int8)), m, n, k).numpy()
+    assert np.array_equal(s12, s1 + s2)
+    eye = np.eye(k, dtype=np.int8)
+    assert np.array_equal(be.gemm_i8_s32(a_d, be.upload(eye), m, k, k).numpy(), a.astype(np.int32))
+    # spot-check 64 random rows of the big product against the oracle
+    rows = rng.choice(m, 64, replace=False)
+    assert np.array_equal(s1[rows], O.gemm_i8_s32(a[rows], w1))
