@@ -175,25 +175,51 @@ def fp8_operands(seed, m, n, k):
     return aq, sa, bq, sb
 
 
+def fp8_truth(aq, bq, sa, sb):
+    """f64 product of the decoded operands: the value every f32 accumulation order approximates."""
+    a = O.e4m3_to_f32(aq).astype(np.float64)
+    b = O.e4m3_to_f32(bq).astype(np.float64)
+    return (a @ b.T) * (float(sa[0]) * float(sb[0]))
+
+
+def judge_vs_truth(got, seq, truth, label):
+    """The tensor core sums K in its own order, so outputs that nearly cancel (|y| << sqrt(K)) cannot meet
+    rel < 1e-3 against a sequential f32 chain - the sequential chain itself misses it against the exact
+    value.  Following the reference's treatment of tensor-core kernels (baseline non-regression instead of
+    loosened tolerances, crates/backend-cuda/tests/common/parity_baseline.rs), the kernel's error against
+    the f64 ground truth must not exceed the sequential f32 FMA chain's."""
+    err_gpu = np.abs(got.astype(np.float64) - truth)
+    err_seq = np.abs(seq.astype(np.float64) - truth)
+    assert np.all(np.isfinite(got)), label
+    assert err_gpu.max() <= 2.0 * err_seq.max() + 1e-7, (label, err_gpu.max(), err_seq.max())
+    assert err_gpu.mean() <= 1.5 * err_seq.mean() + 1e-9, (label, err_gpu.mean(), err_seq.mean())
+    # and wherever the result is not a near-cancellation, the composite tolerance holds outright
+    big = np.abs(truth) > 1e3 * err_seq.max()
+    fails, max_abs, max_rel = O.compare(got[big], seq[big])
+    assert fails == 0, (label, max_abs, max_rel)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 4096, 4096), (128, 4096, 4096), (128, 1024, 8192),
-                                   (16, 512, 14336), (300, 272, 528)])
-def test_fp8_gemm_bf16_out(be, m, n, k):
+                                   (16, 512, 14336), (300, 272, 528), (1024, 512, 4096)])
+def test_fp8_gemm(be, m, n, k):
     aq, sa, bq, sb = fp8_operands(m + k, m, n, k)
-    aq_d, sa_d = be.quantize_fp8_e4m3_per_tensor(be.upload(np.zeros(1, np.float32)), 1)  # shapes only
-    y = be.gemm_q8_scaled(FP8_E4M3, be.upload(aq), be.upload(sa), False, be.upload(bq), be.upload(sb), False, m, n, k,
-                          out_dtype=BF16).numpy()
+    truth = fp8_truth(aq, bq, sa, sb)
     acc = O.gemm_fp8_f32(aq, bq)
-    y_ref = O.epilogue_scaled(acc, sa, False, sb, False, out_bf16=True)
-    # the accumulation order inside the tensor core differs from the oracle's k-ascending chain, and the
-    # result is rounded to bf16 (relative step 2^-8): compare the bf16 values within one bf16 step
-    got, ref = O.bf16_to_f32(y), O.bf16_to_f32(y_ref)
-    denom = np.maximum(np.maximum(np.abs(got), np.abs(ref)), 1e-12)
-    assert np.all((np.abs(got - ref) / denom < 2.0**-7) | (np.abs(got - ref) < 1e-5))
-    # and the f32 output within the composite tolerance
-    y32 = be.gemm_q8_scaled(FP8_E4M3, be.upload(aq), be.upload(sa), False, be.upload(bq), be.upload(sb), False, m, n, k,
-                            out_dtype=F32).numpy()
-    fails, max_abs, max_rel = O.compare(y32, O.epilogue_scaled(acc, sa, False, sb, False))
-    assert fails == 0, (max_abs, max_rel)
+    seq = O.epilogue_scaled(acc, sa, False, sb, False)
+    a_d, sa_d, b_d, sb_d = be.upload(aq), be.upload(sa), be.upload(bq), be.upload(sb)
+    y32 = be.gemm_q8_scaled(FP8_E4M3, a_d, sa_d, False, b_d, sb_d, False, m, n, k, out_dtype=F32).numpy()
+    judge_vs_truth(y32, seq, truth, "f32 out")
+    # bf16 output = the f32 result rounded once (RNE): byte-identical to rounding the f32 output on the host
+    y16 = be.gemm_q8_scaled(FP8_E4M3, a_d, sa_d, False, b_d, sb_d, False, m, n, k, out_dtype=BF16).numpy()
+    assert np.array_equal(y16, O.f32_to_bf16(y32))
+    # the split-K path (f32 planes summed in plane order) obeys the same bound
+    if k >= 1024:
+        be.gemm_tuning(0, 4)
+        try:
+            ys = be.gemm_q8_scaled(FP8_E4M3, a_d, sa_d, False, b_d, sb_d, False, m, n, k, out_dtype=F32).numpy()
+        finally:
+            be.gemm_tuning(0, 0)
+        judge_vs_truth(ys, seq, truth, "split-K")
 
 
 def test_fp8_operands_quantised_on_device_are_identical_and_gated_epilogue(be):
@@ -208,8 +234,11 @@ def test_fp8_operands_quantised_on_device_are_identical_and_gated_epilogue(be):
     y = be.gemm_q8_scaled(FP8_E4M3, aq_d, sa_d, False, bq_d, sb_d, False, m, 2 * f, k, activation=ACT_SILU_GATE).numpy()
     ref = O.epilogue_scaled(O.gemm_fp8_f32(aq, bq), sa, False, sb, False, act=O.ACT_SILU_GATE)
     assert y.shape == (m, f)
-    fails, max_abs, max_rel = O.compare(y, ref)
-    assert fails == 0, (max_abs, max_rel)
+    a64, b64 = O.e4m3_to_f32(aq).astype(np.float64), O.e4m3_to_f32(bq).astype(np.float64)
+    lin = (a64 @ b64.T) * (float(sa[0]) * float(sb[0]))
+    g, u = lin[:, :f], lin[:, f:]
+    truth = g / (1.0 + np.exp(-g)) * u
+    judge_vs_truth(y, ref, truth, "gated")
 
 
 # ---------------------------------------------------------------- size-independent properties at full size
