@@ -63,6 +63,15 @@ class PagedAttentionPlanC(C.Structure):
                 ("workspace_elems", C.c_uint64)]
 
 
+class DecoderConfigC(C.Structure):
+    """b200_decoder_config"""
+    _fields_ = [("n_layers", C.c_int32), ("d_model", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("d_ff", C.c_int32), ("vocab", C.c_int32), ("rms_eps", C.c_float),
+                ("rope_theta", C.c_float), ("max_batch", C.c_int32), ("max_seq_len", C.c_int32),
+                ("block_size", C.c_int32), ("num_blocks", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32),
+                ("use_graph", C.c_int32)]
+
+
 _P = C.c_void_p
 _SZ = C.c_size_t
 _I32 = C.c_int32
@@ -103,6 +112,30 @@ SIGNATURES = {
     "b200_paged_attention_forward_resident": (_I32, [_P, _P, _SZ, _P, _P, _P, _P, _U64,
                                                      C.POINTER(PagedAttentionArgsC), _P, _SZ]),
     "b200_paged_attention_tuning": (_I32, [_P, _I32]),
+    "b200_block_table_create": (_I32, [_U64, _U64, C.POINTER(_P)]),
+    "b200_block_table_destroy": (None, [_P]),
+    "b200_block_table_extend_for_append": (_I32, [_P, _U64, _U64, _P, _U64, C.POINTER(_U64)]),
+    "b200_block_table_flatten": (_I32, [_P, _U64, _P, _U64]),
+    "b200_block_table_rewind_to": (_I32, [_P, _U64]),
+    "b200_block_table_clear": (None, [_P]),
+    "b200_block_table_seq_len": (_U64, [_P]),
+    "b200_block_table_free_blocks": (_U64, [_P]),
+    "b200_block_table_used_blocks": (_U64, [_P]),
+    "b200_block_table_batch": (_I64, [_P]),
+    "b200_decoder_create": (_I32, [_P, C.POINTER(DecoderConfigC), C.POINTER(_P)]),
+    "b200_decoder_destroy": (_I32, [_P]),
+    "b200_decoder_load_tensor": (_I32, [_P, _I32, _I32, _P, _I64, _I64]),
+    "b200_decoder_init_random": (_I32, [_P, _U64, C.c_float]),
+    "b200_nccl_unique_id": (_I32, [_P]),
+    "b200_decoder_init_tp": (_I32, [_P, _P]),
+    "b200_decoder_begin": (_I32, [_P, _I32, _P, _P]),
+    "b200_decoder_fill_cache_random": (_I32, [_P, _U64, C.c_float]),
+    "b200_decoder_step": (_I32, [_P, _P, _P]),
+    "b200_decoder_logits": (_I32, [_P, _P, _U64]),
+    "b200_decoder_generate": (_I32, [_P, _P, _I32, _I32, _I32, _P]),
+    "b200_decoder_launches_per_step": (_U64, [_P]),
+    "b200_decoder_weight_bytes": (_U64, [_P]),
+    "b200_decoder_plan_info": (_I32, [_P, _P]),
     "b200_linear_w8a8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _P, _SZ]),
 }
 

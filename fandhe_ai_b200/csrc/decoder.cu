@@ -1,0 +1,904 @@
+// C-ABI implementation, part 3: the decode driver.
+//
+//  - BlockTable: the host page table of the reference (crates/autodiff/src/nn/paged_kv.rs:158-364):
+//    LIFO stack of returned blocks, then fresh ids counted up from 0; row-major slot mapping
+//    block_id * block_size + pos % block_size; flattened [B, max_blocks_per_seq] padded with
+//    0xFFFFFFFF; rewind returns tail blocks.  Extension: per-row reservation for ragged batches.
+//  - ParamStore: flat device buffers (int8 payload, f32 scales, f32 vectors) addressed by
+//    offset, the addressing model of DeviceParamStore
+//    (crates/autodiff/src/optim/device_store.rs:1288-1364).
+//  - Decoder: a Llama-style stack (RMSNorm, RoPE, GQA paged attention, SwiGLU) run as one CUDA
+//    graph per decode step; greedy sampling on the device; only token ids cross to the host
+//    (the reference's generate() loop, crates/autodiff/src/generate/mod.rs:500-613, pulls full
+//    logits to the host each step).
+//  - Tensor parallelism: QKV / gate / up column-parallel, O / down row-parallel, KV cache sharded
+//    by KV head; the row-parallel outputs are summed across ranks with ncclAllReduce on the
+//    context's stream.  NCCL is loaded with dlopen so that single-GPU use has no such dependency.
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "backend.h"
+#include "gemm_tc5.cuh"
+#include "kernels.cuh"
+
+using namespace b200;
+
+// ------------------------------------------------------------------------------------ BlockTable
+struct b200_block_table {
+    uint64_t max_blocks = 0;
+    uint64_t block_size = 1;
+    std::vector<uint32_t> returned;
+    uint64_t next_unused = 0;
+    std::vector<std::vector<uint32_t>> tables;
+    std::vector<uint64_t> seq_lens;
+    bool has_batch = false;
+
+    uint64_t free_blocks() const { return returned.size() + (max_blocks > next_unused ? max_blocks - next_unused : 0); }
+    bool alloc(uint32_t* out) {
+        if (!returned.empty()) {
+            *out = returned.back();
+            returned.pop_back();
+            return true;
+        }
+        if (next_unused < max_blocks) {
+            *out = static_cast<uint32_t>(next_unused++);
+            return true;
+        }
+        return false;
+    }
+    void reset() {
+        returned.clear();
+        next_unused = 0;
+        tables.clear();
+        seq_lens.clear();
+        has_batch = false;
+    }
+    uint64_t seq_len() const { return seq_lens.empty() ? 0 : seq_lens[0]; }
+};
+
+namespace {
+
+int32_t bt_invalid(const std::string& m) { return fail(B200_INVALID_ARGUMENT, "block_table: " + m); }
+
+// Grows row `row` so that it can hold `total` tokens.  Returns false when the pool runs out.
+bool bt_reserve_row(b200_block_table* t, size_t row, uint64_t total) {
+    const uint64_t need = (total + t->block_size - 1) / t->block_size;
+    while (t->tables[row].size() < need) {
+        uint32_t id;
+        if (!t->alloc(&id)) return false;
+        t->tables[row].push_back(id);
+    }
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t b200_block_table_create(uint64_t max_blocks, uint64_t block_size, b200_block_table** out) {
+    if (!out) return bt_invalid("out is null");
+    *out = nullptr;
+    if (block_size == 0 || block_size > 256 || (block_size & (block_size - 1)) != 0)
+        return bt_invalid("block_size must be a power of two in 1..256");
+    if (max_blocks == 0 || max_blocks >= 0xFFFFFFFFull) return bt_invalid("max_blocks must be in 1..u32::MAX-1");
+    b200_block_table* t = new (std::nothrow) b200_block_table();
+    if (!t) return fail(B200_DEVICE_ALLOCATION_FAILED, "block_table: host allocation failed");
+    t->max_blocks = max_blocks;
+    t->block_size = block_size;
+    *out = t;
+    return B200_OK;
+}
+
+void b200_block_table_destroy(b200_block_table* t) { delete t; }
+
+// BlockTable::extend_for_append (paged_kv.rs:206-297): all rows advance by l_new; slots are row-major.
+// State is left unchanged on failure.
+int32_t b200_block_table_extend_for_append(b200_block_table* t, uint64_t batch, uint64_t l_new, uint32_t* slots_out,
+                                           uint64_t slots_capacity, uint64_t* n_slots) {
+    if (!t) return bt_invalid("table is null");
+    if (n_slots) *n_slots = 0;
+    if (batch == 0) return bt_invalid("batch size 0 cannot be appended");
+    if (t->has_batch && t->tables.size() != batch)
+        return bt_invalid("batch " + std::to_string(batch) + " differs from the cache's " + std::to_string(t->tables.size()));
+    if (l_new == 0) return B200_OK;
+    const uint64_t s_prev = t->seq_len();
+    uint64_t s_total, extra_total, rows;
+    if (__builtin_add_overflow(s_prev, l_new, &s_total)) return bt_invalid("sequence length overflows");
+    const uint64_t held = (s_prev + t->block_size - 1) / t->block_size;
+    const uint64_t extra_per_row = (s_total + t->block_size - 1) / t->block_size - held;
+    if (__builtin_mul_overflow(extra_per_row, batch, &extra_total)) return bt_invalid("needed block count overflows");
+    if (extra_total > t->free_blocks())
+        return bt_invalid("not enough free blocks (needed " + std::to_string(extra_total) + ", free " +
+                          std::to_string(t->free_blocks()) + ")");
+    if (__builtin_mul_overflow(batch, l_new, &rows)) return bt_invalid("append row count overflows");
+    if (rows > slots_capacity || !slots_out) return bt_invalid("slot buffer too small");
+    if ((t->max_blocks * t->block_size) > 0xFFFFFFFFull) return bt_invalid("slot number does not fit u32");
+    if (!t->has_batch) {
+        t->tables.assign(batch, {});
+        t->seq_lens.assign(batch, 0);
+        t->has_batch = true;
+    }
+    uint64_t at = 0;
+    for (uint64_t row = 0; row < batch; ++row) {
+        for (uint64_t i = 0; i < l_new; ++i) {
+            const uint64_t pos = s_prev + i;
+            if (pos % t->block_size == 0) {
+                uint32_t id = 0;
+                t->alloc(&id);   // cannot fail: checked above
+                t->tables[row].push_back(id);
+            }
+            const uint32_t blk = t->tables[row][pos / t->block_size];
+            slots_out[at++] = static_cast<uint32_t>(uint64_t(blk) * t->block_size + pos % t->block_size);
+        }
+    }
+    for (auto& l : t->seq_lens) l = s_total;
+    if (n_slots) *n_slots = rows;
+    return B200_OK;
+}
+
+// BlockTable::flatten_tables (paged_kv.rs:299-322)
+int32_t b200_block_table_flatten(const b200_block_table* t, uint64_t max_blocks_per_seq, uint32_t* out, uint64_t capacity) {
+    if (!t) return bt_invalid("table is null");
+    uint64_t n;
+    if (__builtin_mul_overflow(uint64_t(t->tables.size()), max_blocks_per_seq, &n)) return bt_invalid("flattened size overflows");
+    if (n > capacity || (n > 0 && !out)) return bt_invalid("output buffer too small");
+    uint64_t at = 0;
+    for (const auto& row : t->tables) {
+        if (row.size() > max_blocks_per_seq) return bt_invalid("a row holds more blocks than max_blocks_per_seq");
+        for (uint32_t id : row) out[at++] = id;
+        for (uint64_t i = row.size(); i < max_blocks_per_seq; ++i) out[at++] = 0xFFFFFFFFu;
+    }
+    return B200_OK;
+}
+
+// BlockTable::rewind_to (paged_kv.rs:324-364)
+int32_t b200_block_table_rewind_to(b200_block_table* t, uint64_t new_len) {
+    if (!t) return bt_invalid("table is null");
+    const uint64_t cur = t->seq_len();
+    if (new_len > cur) return bt_invalid("rewind target " + std::to_string(new_len) + " exceeds the length " + std::to_string(cur));
+    if (!t->has_batch || new_len == cur) return B200_OK;
+    if (new_len == 0) {
+        t->reset();
+        return B200_OK;
+    }
+    const uint64_t keep = (new_len + t->block_size - 1) / t->block_size;
+    for (auto& row : t->tables)
+        while (row.size() > keep) {
+            t->returned.push_back(row.back());
+            row.pop_back();
+        }
+    for (auto& l : t->seq_lens) l = new_len;
+    return B200_OK;
+}
+
+void b200_block_table_clear(b200_block_table* t) {
+    if (t) t->reset();
+}
+uint64_t b200_block_table_seq_len(const b200_block_table* t) { return t ? t->seq_len() : 0; }
+uint64_t b200_block_table_free_blocks(const b200_block_table* t) { return t ? t->free_blocks() : 0; }
+uint64_t b200_block_table_used_blocks(const b200_block_table* t) {
+    if (!t) return 0;
+    uint64_t n = 0;
+    for (const auto& r : t->tables) n += r.size();
+    return n;
+}
+int64_t b200_block_table_batch(const b200_block_table* t) { return (t && t->has_batch) ? int64_t(t->tables.size()) : -1; }
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------ NCCL (dlopen)
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+struct NcclUniqueId { char internal[128]; };
+enum { kNcclInt32 = 2, kNcclFloat32 = 7 };
+enum { kNcclSum = 0, kNcclMax = 2 };
+
+struct NcclApi {
+    void* handle = nullptr;
+    int (*GetUniqueId)(NcclUniqueId*) = nullptr;
+    int (*CommInitRank)(ncclComm_t*, int, NcclUniqueId, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+
+NcclApi& nccl() {
+    static NcclApi api = [] {
+        NcclApi a;
+        a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!a.handle) return a;
+        a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(a.handle, "ncclGetUniqueId"));
+        a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(a.handle, "ncclCommInitRank"));
+        a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(a.handle, "ncclCommDestroy"));
+        a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(a.handle, "ncclAllReduce"));
+        a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(a.handle, "ncclGetErrorString"));
+        a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce;
+        return a;
+    }();
+    return api;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------ Decoder
+struct LayerParams {
+    size_t wqkv = 0, wo = 0, wgu = 0, wdown = 0;                  // byte offsets into the int8 payload
+    size_t s_qkv = 0, s_o = 0, s_gu = 0, s_down = 0;              // element offsets into the scale buffer
+    size_t attn_norm = 0, mlp_norm = 0;                           // element offsets into the vector buffer
+    void* k_pool = nullptr;
+    void* v_pool = nullptr;
+    GemmPlan p_qkv, p_o, p_gu, p_down;
+    PagedAttnPlan attn;
+};
+
+struct b200_decoder {
+    b200_ctx* ctx = nullptr;
+    b200_decoder_config cfg{};
+    int hq_l = 0, hkv_l = 0, f_l = 0;           // per-rank head counts and d_ff
+    int n_qkv = 0;                              // (hq_l + 2 hkv_l) * head_dim
+    // ParamStore
+    int8_t* payload = nullptr;
+    float* scales = nullptr;
+    float* vectors = nullptr;                   // norm weights
+    float* embed = nullptr;                     // [vocab, d] f32
+    size_t payload_bytes = 0, scales_elems = 0, vectors_elems = 0;
+    std::vector<LayerParams> layers;
+    size_t w_lm = 0, s_lm = 0, final_norm = 0;
+    GemmPlan p_lm;
+    // rope
+    float* cos_t = nullptr;
+    float* sin_t = nullptr;
+    // step state
+    int batch = 0;
+    int max_total_len = 0;
+    bool planned = false;
+    b200_block_table* table = nullptr;
+    uint32_t* tables_dev = nullptr;
+    uint32_t* seq_lens_dev = nullptr;
+    uint32_t* pos_dev = nullptr;                // position of the token being added, per row
+    int max_blocks_per_seq = 0;
+    int* ids_dev = nullptr;
+    int* next_ids_dev = nullptr;
+    float* h = nullptr;
+    int8_t* xq = nullptr;
+    float* sx = nullptr;
+    int* raw = nullptr;
+    size_t raw_elems = 0;
+    float* q = nullptr;
+    float* attn_out = nullptr;
+    float* part = nullptr;                      // [M, d] f32 addend of the cross-rank sum
+    float* logits = nullptr;
+    void* attn_scratch = nullptr;
+    int* ids_pinned = nullptr;
+    int* next_pinned = nullptr;
+    // graph
+    cudaGraphExec_t graph = nullptr;
+    int eager_steps_done = 0;
+    uint64_t steps = 0;
+    bool store_poisoned = false;
+    // tensor parallel
+    ncclComm_t comm = nullptr;
+    uint64_t launches_per_step = 0;
+};
+
+namespace {
+
+int32_t dec_fail(b200_decoder* d, int32_t st, const std::string& msg) {
+    if (d) d->store_poisoned = true;
+    return fail_runtime(d ? d->ctx : nullptr, st, msg);
+}
+
+#define CU_TRY(expr)                                                                                         \
+    do {                                                                                                     \
+        cudaError_t _e = (expr);                                                                             \
+        if (_e != cudaSuccess)                                                                               \
+            return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+    } while (0)
+
+template <typename T>
+cudaError_t dmalloc(T** p, size_t elems) {
+    return cudaMalloc(reinterpret_cast<void**>(p), elems * sizeof(T) > 0 ? elems * sizeof(T) : 16);
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int32_t check_config(const b200_decoder_config& c) {
+    auto bad = [](const char* m) { return fail(B200_INVALID_ARGUMENT, std::string("decoder config: ") + m); };
+    if (c.n_layers <= 0 || c.d_model <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.d_ff <= 0 ||
+        c.vocab <= 0)
+        return bad("all sizes must be positive");
+    if (c.n_heads % c.n_kv_heads != 0) return bad("n_heads must be a multiple of n_kv_heads");
+    if (c.head_dim % 2 != 0) return bad("head_dim must be even (rotary pairs)");
+    if (c.tp_size <= 0 || c.tp_rank < 0 || c.tp_rank >= c.tp_size) return bad("tp_rank / tp_size out of range");
+    if (c.n_kv_heads % c.tp_size != 0 || c.d_ff % c.tp_size != 0) return bad("n_kv_heads and d_ff must divide by tp_size");
+    if (c.d_model % 16 != 0 || (c.d_ff / c.tp_size) % 16 != 0 || (c.n_heads / c.tp_size * c.head_dim) % 16 != 0 ||
+        c.vocab % 16 != 0 || (c.head_dim * (c.n_heads + 2 * c.n_kv_heads) / c.tp_size) % 16 != 0)
+        return fail(B200_UNSUPPORTED, "decoder config: GEMM dimensions must be multiples of 16");
+    if (c.max_batch <= 0 || c.max_seq_len <= 0) return bad("max_batch / max_seq_len must be positive");
+    if (c.block_size <= 0 || c.block_size > 256 || (c.block_size & (c.block_size - 1))) return bad("block_size must be a power of two <= 256");
+    if (c.num_blocks <= 0) return bad("num_blocks must be positive");
+    if (!(c.rms_eps >= 0.0f) || !std::isfinite(c.rms_eps)) return bad("rms_eps must be finite and non-negative");
+    if (!(c.rope_theta > 0.0f)) return bad("rope_theta must be positive");
+    return B200_OK;
+}
+
+int32_t dec_check(b200_decoder* d) {
+    if (!d) return fail(B200_INVALID_ARGUMENT, "decoder is null");
+    if (d->store_poisoned) return fail(B200_STORE_POISONED, "the decoder's device state is poisoned by an earlier runtime failure; re-create it");
+    if (int32_t st = check_ctx(d->ctx)) return st;
+    return set_device(d->ctx);
+}
+
+void drop_graph(b200_decoder* d) {
+    if (d->graph) {
+        cudaGraphExecDestroy(d->graph);
+        d->graph = nullptr;
+    }
+    d->eager_steps_done = 0;
+}
+
+// Quantises a full f32 matrix [rows, cols] (device, temporary) per row and stores either a row subset
+// or a column slice into the payload; scales follow.
+int32_t store_weight(b200_decoder* d, const float* w_full, int64_t rows, int64_t cols, const std::vector<std::pair<int64_t, int64_t>>& row_ranges,
+                     int64_t c0, int64_t ccount, size_t payload_off, size_t scale_off) {
+    cudaStream_t s = d->ctx->stream;
+    int8_t* q_full = nullptr;
+    float* s_full = nullptr;
+    CU_TRY(dmalloc(&q_full, size_t(rows) * cols));
+    CU_TRY(dmalloc(&s_full, size_t(rows)));
+    CU_TRY(quantize_i8_per_row(w_full, rows, cols, q_full, s_full, s));
+    size_t out_row = 0;
+    for (auto rr : row_ranges) {
+        const int64_t r0 = rr.first, rn = rr.second;
+        CU_TRY(slice_cols_i8(q_full + r0 * cols, rn, cols, c0, ccount, d->payload + payload_off + out_row * ccount, s));
+        CU_TRY(cudaMemcpyAsync(d->scales + scale_off + out_row, s_full + r0, rn * sizeof(float), cudaMemcpyDeviceToDevice, s));
+        out_row += rn;
+    }
+    CU_TRY(cudaStreamSynchronize(s));
+    cudaFree(q_full);
+    cudaFree(s_full);
+    return B200_OK;
+}
+
+struct TensorShape {
+    int64_t rows, cols;                                        // full (unsharded) shape
+    std::vector<std::pair<int64_t, int64_t>> row_ranges;       // rows kept by this rank
+    int64_t c0, ccount;                                        // columns kept by this rank
+    size_t payload_off, scale_off;
+};
+
+bool tensor_shape(const b200_decoder* d, int which, int layer, TensorShape* t) {
+    const auto& c = d->cfg;
+    const int tp = c.tp_size, r = c.tp_rank;
+    const int64_t dh = c.head_dim, dm = c.d_model;
+    if (which == B200_W_LM_HEAD) {
+        *t = {c.vocab, dm, {{0, c.vocab}}, 0, dm, d->w_lm, d->s_lm};
+        return true;
+    }
+    if (layer < 0 || layer >= c.n_layers) return false;
+    const LayerParams& L = d->layers[layer];
+    const int64_t hq = c.n_heads, hkv = c.n_kv_heads, F = c.d_ff;
+    switch (which) {
+        case B200_W_QKV:
+            *t = {(hq + 2 * hkv) * dh, dm,
+                  {{r * (hq / tp) * dh, (hq / tp) * dh}, {hq * dh + r * (hkv / tp) * dh, (hkv / tp) * dh},
+                   {(hq + hkv) * dh + r * (hkv / tp) * dh, (hkv / tp) * dh}},
+                  0, dm, L.wqkv, L.s_qkv};
+            return true;
+        case B200_W_O:
+            *t = {dm, hq * dh, {{0, dm}}, r * (hq / tp) * dh, (hq / tp) * dh, L.wo, L.s_o};
+            return true;
+        case B200_W_GATE_UP:
+            *t = {2 * F, dm, {{r * (F / tp), F / tp}, {F + r * (F / tp), F / tp}}, 0, dm, L.wgu, L.s_gu};
+            return true;
+        case B200_W_DOWN:
+            *t = {dm, F, {{0, dm}}, r * (F / tp), F / tp, L.wdown, L.s_down};
+            return true;
+        default: return false;
+    }
+}
+
+int32_t all_reduce_sum_f32(b200_decoder* d, float* buf, size_t n) {
+    int rc = nccl().AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, d->comm, d->ctx->stream);
+    if (rc != 0) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, "ncclAllReduce failed");
+    return B200_OK;
+}
+
+// Enqueues one decode step for the current batch on the context's stream.
+int32_t enqueue_step(b200_decoder* d) {
+    const auto& c = d->cfg;
+    cudaStream_t s = d->ctx->stream;
+    uint32_t* err = d->ctx->err_dev;
+    const int M = d->batch, dm = c.d_model, dh = c.head_dim;
+    const bool tp = c.tp_size > 1;
+    uint64_t launches = 0;
+    GemmEpilogue ep;
+    ep.raw = d->raw;
+    CU_TRY(begin_step(d->seq_lens_dev, d->pos_dev, M, s));
+    ++launches;
+    CU_TRY(embed_norm_quant(d->ids_dev, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, d->h,
+                            d->xq, d->sx, err, s));
+    ++launches;
+    for (int l = 0; l < c.n_layers; ++l) {
+        LayerParams& L = d->layers[l];
+        // QKV projection -> RoPE -> append to the paged cache
+        CU_TRY(gemm_launch(L.p_qkv, ep, err, s));
+        CU_TRY(qkv_rope_append(d->raw, L.p_qkv.splits, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv, d->cos_t,
+                               d->sin_t, c.max_seq_len, d->pos_dev, d->tables_dev, d->max_blocks_per_seq,
+                               c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
+                               static_cast<uint16_t*>(L.v_pool), err, s));
+        // attention over the cache (this rank's KV heads), then per-token quantisation
+        CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
+                                      d->attn_scratch, err, s));
+        CU_TRY(quantize_i8_per_row(d->attn_out, M, int64_t(d->hq_l) * dh, d->xq, d->sx, s));
+        // O projection (row-parallel) -> residual -> norm -> quant
+        CU_TRY(gemm_launch(L.p_o, ep, err, s));
+        launches += 6;
+        if (tp) {
+            CU_TRY(dequant_planes(d->raw, L.p_o.splits, M, dm, d->sx, d->scales + L.s_o, d->part, s));
+            if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
+            launches += 2;
+        }
+        CU_TRY(resid_norm_quant(d->raw, L.p_o.splits, M, dm, d->sx, d->scales + L.s_o, tp ? d->part : nullptr,
+                                d->vectors + L.mlp_norm, c.rms_eps, d->h, d->xq, d->sx, s));
+        // gate / up (column-parallel) -> SiLU gate -> quant
+        CU_TRY(gemm_launch(L.p_gu, ep, err, s));
+        CU_TRY(gate_quant(d->raw, L.p_gu.splits, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
+        // down (row-parallel) -> residual -> next norm -> quant
+        CU_TRY(gemm_launch(L.p_down, ep, err, s));
+        launches += 4;
+        if (tp) {
+            CU_TRY(dequant_planes(d->raw, L.p_down.splits, M, dm, d->sx, d->scales + L.s_down, d->part, s));
+            if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
+            launches += 2;
+        }
+        const float* next_norm = d->vectors + (l + 1 < c.n_layers ? d->layers[l + 1].attn_norm : d->final_norm);
+        CU_TRY(resid_norm_quant(d->raw, L.p_down.splits, M, dm, d->sx, d->scales + L.s_down, tp ? d->part : nullptr,
+                                next_norm, c.rms_eps, d->h, d->xq, d->sx, s));
+        ++launches;
+    }
+    // lm_head with the dequant epilogue fused into the GEMM, then greedy argmax on the device
+    GemmEpilogue lm;
+    lm.fused = 1;
+    lm.a_scale = d->sx;
+    lm.a_per_row = 1;
+    lm.b_scale = d->scales + d->s_lm;
+    lm.b_per_col = 1;
+    lm.out = d->logits;
+    CU_TRY(gemm_launch(d->p_lm, lm, err, s));
+    CU_TRY(argmax_rows(d->logits, M, c.vocab, d->next_ids_dev, s));
+    launches += 2;
+    d->launches_per_step = launches;
+    return B200_OK;
+}
+
+void free_step_state(b200_decoder* d) {
+    drop_graph(d);
+    d->planned = false;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_decoder** out) {
+    if (!out) return fail(B200_INVALID_ARGUMENT, "decoder_create: out is null");
+    *out = nullptr;
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (!cfg) return fail(B200_INVALID_ARGUMENT, "decoder_create: config is null");
+    if (int32_t st = check_config(*cfg)) return st;
+    if (int32_t st = set_device(ctx)) return st;
+    b200_decoder* d = new (std::nothrow) b200_decoder();
+    if (!d) return fail(B200_DEVICE_ALLOCATION_FAILED, "decoder_create: host allocation failed");
+    d->ctx = ctx;
+    d->cfg = *cfg;
+    const auto& c = d->cfg;
+    const int tp = c.tp_size;
+    d->hq_l = c.n_heads / tp;
+    d->hkv_l = c.n_kv_heads / tp;
+    d->f_l = c.d_ff / tp;
+    d->n_qkv = (d->hq_l + 2 * d->hkv_l) * c.head_dim;
+    const size_t dm = c.d_model, dh = c.head_dim;
+    // ---- ParamStore layout: registration order = layer by layer, qkv, o, gate_up, down; then lm_head
+    size_t pay = 0, sc = 0, vec = 0;
+    d->layers.resize(c.n_layers);
+    for (auto& L : d->layers) {
+        L.wqkv = pay; pay += align_up(size_t(d->n_qkv) * dm, 256);
+        L.wo = pay; pay += align_up(dm * d->hq_l * dh, 256);
+        L.wgu = pay; pay += align_up(size_t(2) * d->f_l * dm, 256);
+        L.wdown = pay; pay += align_up(dm * d->f_l, 256);
+        L.s_qkv = sc; sc += align_up(d->n_qkv, 64);
+        L.s_o = sc; sc += align_up(dm, 64);
+        L.s_gu = sc; sc += align_up(size_t(2) * d->f_l, 64);
+        L.s_down = sc; sc += align_up(dm, 64);
+        L.attn_norm = vec; vec += align_up(dm, 64);
+        L.mlp_norm = vec; vec += align_up(dm, 64);
+    }
+    d->w_lm = pay; pay += align_up(size_t(c.vocab) * dm, 256);
+    d->s_lm = sc; sc += align_up(c.vocab, 64);
+    d->final_norm = vec; vec += align_up(dm, 64);
+    d->payload_bytes = pay; d->scales_elems = sc; d->vectors_elems = vec;
+    const size_t M = c.max_batch;
+    const size_t pool_elems = size_t(c.num_blocks) * c.block_size * d->hkv_l * dh;
+    const size_t widest = std::max<size_t>(std::max<size_t>(dm, d->f_l), size_t(d->hq_l) * dh);
+    cudaError_t e = cudaSuccess;
+    auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+    A(dmalloc(&d->payload, pay));
+    A(dmalloc(&d->scales, sc));
+    A(dmalloc(&d->vectors, vec));
+    A(dmalloc(&d->embed, size_t(c.vocab) * dm));
+    A(dmalloc(&d->cos_t, size_t(c.max_seq_len) * dh / 2));
+    A(dmalloc(&d->sin_t, size_t(c.max_seq_len) * dh / 2));
+    for (auto& L : d->layers) {
+        A(cudaMalloc(&L.k_pool, pool_elems * 2));
+        A(cudaMalloc(&L.v_pool, pool_elems * 2));
+    }
+    d->max_blocks_per_seq = (c.max_seq_len + c.block_size - 1) / c.block_size;
+    A(dmalloc(&d->tables_dev, M * d->max_blocks_per_seq));
+    A(dmalloc(&d->seq_lens_dev, M));
+    A(dmalloc(&d->pos_dev, M));
+    A(dmalloc(&d->ids_dev, M));
+    A(dmalloc(&d->next_ids_dev, M));
+    A(dmalloc(&d->h, M * dm));
+    A(dmalloc(&d->xq, M * widest));
+    A(dmalloc(&d->sx, M));
+    A(dmalloc(&d->q, M * d->hq_l * dh));
+    A(dmalloc(&d->attn_out, M * d->hq_l * dh));
+    A(dmalloc(&d->part, M * dm));
+    A(dmalloc(&d->logits, M * size_t(c.vocab)));
+    A(cudaMallocHost(reinterpret_cast<void**>(&d->ids_pinned), M * sizeof(int)));
+    A(cudaMallocHost(reinterpret_cast<void**>(&d->next_pinned), M * sizeof(int)));
+    if (e == cudaSuccess) e = cudaMemsetAsync(d->vectors, 0, vec * sizeof(float), ctx->stream);
+    if (e != cudaSuccess) {
+        std::string msg = std::string("decoder_create: allocation failed: ") + cudaGetErrorString(e);
+        cudaGetLastError();
+        b200_decoder_destroy(d);
+        return fail(B200_DEVICE_ALLOCATION_FAILED, msg);
+    }
+    // rope table in f64 on the host: angle = pos * theta^(-2i/dh)
+    {
+        const size_t half = dh / 2;
+        std::vector<float> ct(size_t(c.max_seq_len) * half), stv(ct.size());
+        for (int p = 0; p < c.max_seq_len; ++p)
+            for (size_t i = 0; i < half; ++i) {
+                const double inv = std::pow(double(c.rope_theta), -2.0 * double(i) / double(dh));
+                const double ang = double(p) * inv;
+                ct[p * half + i] = float(std::cos(ang));
+                stv[p * half + i] = float(std::sin(ang));
+            }
+        e = cudaMemcpyAsync(d->cos_t, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d->sin_t, stv.data(), stv.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) {
+            b200_decoder_destroy(d);
+            return fail_runtime(ctx, B200_TRANSFER_FAILED, std::string("decoder_create: ") + cudaGetErrorString(e));
+        }
+    }
+    if (int32_t st = b200_block_table_create(uint64_t(c.num_blocks), uint64_t(c.block_size), &d->table)) {
+        b200_decoder_destroy(d);
+        return st;
+    }
+    *out = d;
+    return B200_OK;
+}
+
+int32_t b200_decoder_destroy(b200_decoder* d) {
+    if (!d) return B200_OK;
+    cudaSetDevice(d->ctx->ordinal);
+    cudaStreamSynchronize(d->ctx->stream);
+    drop_graph(d);
+    if (d->comm && nccl().ok) nccl().CommDestroy(d->comm);
+    for (auto& L : d->layers) {
+        cudaFree(L.k_pool);
+        cudaFree(L.v_pool);
+    }
+    void* ptrs[] = {d->payload, d->scales, d->vectors, d->embed, d->cos_t, d->sin_t, d->tables_dev, d->seq_lens_dev, d->pos_dev,
+                    d->ids_dev, d->next_ids_dev, d->h, d->xq, d->sx, d->raw, d->q, d->attn_out, d->part, d->logits,
+                    d->attn_scratch};
+    for (void* p : ptrs) cudaFree(p);
+    if (d->ids_pinned) cudaFreeHost(d->ids_pinned);
+    if (d->next_pinned) cudaFreeHost(d->next_pinned);
+    b200_block_table_destroy(d->table);
+    cudaGetLastError();
+    delete d;
+    return B200_OK;
+}
+
+int32_t b200_decoder_load_tensor(b200_decoder* d, int32_t which, int32_t layer, const float* host, int64_t rows, int64_t cols) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!host) return fail(B200_INVALID_ARGUMENT, "decoder_load_tensor: host pointer is null");
+    const auto& c = d->cfg;
+    cudaStream_t s = d->ctx->stream;
+    const size_t dm = c.d_model;
+    if (which == B200_W_EMBED || which == B200_W_ATTN_NORM || which == B200_W_MLP_NORM || which == B200_W_FINAL_NORM) {
+        float* dst = nullptr;
+        int64_t want_rows = 1, want_cols = int64_t(dm);
+        if (which == B200_W_EMBED) { dst = d->embed; want_rows = c.vocab; }
+        else if (which == B200_W_FINAL_NORM) dst = d->vectors + d->final_norm;
+        else {
+            if (layer < 0 || layer >= c.n_layers) return fail(B200_INVALID_ARGUMENT, "decoder_load_tensor: layer out of range");
+            dst = d->vectors + (which == B200_W_ATTN_NORM ? d->layers[layer].attn_norm : d->layers[layer].mlp_norm);
+        }
+        if (rows != want_rows || cols != want_cols) return fail(B200_SHAPE_MISMATCH, "decoder_load_tensor: shape differs from the config");
+        CU_TRY(cudaMemcpyAsync(dst, host, size_t(rows) * cols * 4, cudaMemcpyHostToDevice, s));
+        CU_TRY(cudaStreamSynchronize(s));
+        return B200_OK;
+    }
+    TensorShape t;
+    if (!tensor_shape(d, which, layer, &t)) return fail(B200_INVALID_ARGUMENT, "decoder_load_tensor: unknown tensor or layer");
+    if (rows != t.rows || cols != t.cols) {
+        char msg[160];
+        std::snprintf(msg, sizeof msg, "decoder_load_tensor: shape [%lld, %lld] differs from the expected [%lld, %lld]",
+                      (long long)rows, (long long)cols, (long long)t.rows, (long long)t.cols);
+        return fail(B200_SHAPE_MISMATCH, msg);
+    }
+    float* tmp = nullptr;
+    CU_TRY(dmalloc(&tmp, size_t(rows) * cols));
+    CU_TRY(cudaMemcpyAsync(tmp, host, size_t(rows) * cols * 4, cudaMemcpyHostToDevice, s));
+    int32_t st = store_weight(d, tmp, rows, cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off);
+    cudaFree(tmp);
+    return st;
+}
+
+int32_t b200_decoder_init_random(b200_decoder* d, uint64_t seed, float std) {
+    if (int32_t st = dec_check(d)) return st;
+    const auto& c = d->cfg;
+    cudaStream_t s = d->ctx->stream;
+    const size_t dm = c.d_model;
+    CU_TRY(fill_normal(d->embed, int64_t(c.vocab) * dm, seed, 1, std, s));
+    {
+        std::vector<float> ones(d->vectors_elems, 1.0f);
+        CU_TRY(cudaMemcpyAsync(d->vectors, ones.data(), ones.size() * 4, cudaMemcpyHostToDevice, s));
+        CU_TRY(cudaStreamSynchronize(s));
+    }
+    size_t max_elems = size_t(c.vocab) * dm;
+    max_elems = std::max(max_elems, size_t(2) * c.d_ff * dm);
+    max_elems = std::max(max_elems, size_t(c.n_heads + 2 * c.n_kv_heads) * c.head_dim * dm);
+    float* tmp = nullptr;
+    CU_TRY(dmalloc(&tmp, max_elems));
+    int32_t st = B200_OK;
+    const int kinds[4] = {B200_W_QKV, B200_W_O, B200_W_GATE_UP, B200_W_DOWN};
+    for (int l = 0; l < c.n_layers && st == B200_OK; ++l)
+        for (int k = 0; k < 4 && st == B200_OK; ++k) {
+            TensorShape t;
+            tensor_shape(d, kinds[k], l, &t);
+            cudaError_t e = fill_normal(tmp, t.rows * t.cols, seed, 16 + uint64_t(l) * 8 + k, std, s);
+            if (e != cudaSuccess) { st = dec_fail(d, B200_KERNEL_LAUNCH_FAILED, cudaGetErrorString(e)); break; }
+            st = store_weight(d, tmp, t.rows, t.cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off);
+        }
+    if (st == B200_OK) {
+        TensorShape t;
+        tensor_shape(d, B200_W_LM_HEAD, 0, &t);
+        cudaError_t e = fill_normal(tmp, t.rows * t.cols, seed, 2, std, s);
+        if (e != cudaSuccess) st = dec_fail(d, B200_KERNEL_LAUNCH_FAILED, cudaGetErrorString(e));
+        else st = store_weight(d, tmp, t.rows, t.cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off);
+    }
+    cudaStreamSynchronize(s);
+    cudaFree(tmp);
+    return st;
+}
+
+int32_t b200_nccl_unique_id(uint8_t* out128) {
+    if (!out128) return fail(B200_INVALID_ARGUMENT, "nccl_unique_id: out is null");
+    if (!nccl().ok) return fail(B200_UNSUPPORTED, "nccl_unique_id: libnccl.so.2 could not be loaded");
+    NcclUniqueId id;
+    if (nccl().GetUniqueId(&id) != 0) return fail(B200_DEVICE_UNAVAILABLE, "ncclGetUniqueId failed");
+    std::memcpy(out128, id.internal, 128);
+    return B200_OK;
+}
+
+int32_t b200_decoder_init_tp(b200_decoder* d, const uint8_t* unique_id128) {
+    if (int32_t st = dec_check(d)) return st;
+    if (d->cfg.tp_size == 1) return B200_OK;
+    if (!unique_id128) return fail(B200_INVALID_ARGUMENT, "decoder_init_tp: unique id is null");
+    if (!nccl().ok) return fail(B200_UNSUPPORTED, "decoder_init_tp: libnccl.so.2 could not be loaded");
+    NcclUniqueId id;
+    std::memcpy(id.internal, unique_id128, 128);
+    int rc = nccl().CommInitRank(&d->comm, d->cfg.tp_size, id, d->cfg.tp_rank);
+    if (rc != 0) return fail(B200_DEVICE_UNAVAILABLE, "ncclCommInitRank failed");
+    return B200_OK;
+}
+
+// Starts a generation: clears the page table, reserves blocks for `max_total_len[b]` tokens per row
+// (the reference's generate() always runs to max_length, so the final length is known up front), uploads
+// the flattened tables once, and sets seq_lens to `start_lens` (0 for a fresh cache).
+int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_lens, const int32_t* max_total_lens) {
+    if (int32_t st = dec_check(d)) return st;
+    const auto& c = d->cfg;
+    if (batch <= 0 || batch > c.max_batch) return fail(B200_INVALID_ARGUMENT, "decoder_begin: batch out of range");
+    if (!max_total_lens) return fail(B200_INVALID_ARGUMENT, "decoder_begin: max_total_lens is null");
+    int mx = 0;
+    for (int b = 0; b < batch; ++b) {
+        const int s0 = start_lens ? start_lens[b] : 0;
+        if (s0 < 0 || max_total_lens[b] < s0 || max_total_lens[b] > c.max_seq_len || max_total_lens[b] <= 0)
+            return fail(B200_INVALID_ARGUMENT, "decoder_begin: lengths out of range for row " + std::to_string(b));
+        mx = std::max(mx, max_total_lens[b]);
+    }
+    free_step_state(d);
+    b200_block_table* t = d->table;
+    t->reset();
+    t->tables.assign(batch, {});
+    t->seq_lens.assign(batch, 0);
+    t->has_batch = true;
+    for (int b = 0; b < batch; ++b) {
+        if (!bt_reserve_row(t, b, uint64_t(max_total_lens[b]))) {
+            t->reset();
+            return fail(B200_INVALID_ARGUMENT, "decoder_begin: not enough free blocks in the pool");
+        }
+        t->seq_lens[b] = start_lens ? start_lens[b] : 0;
+    }
+    std::vector<uint32_t> flat(size_t(batch) * d->max_blocks_per_seq), lens(batch);
+    if (int32_t st = b200_block_table_flatten(t, d->max_blocks_per_seq, flat.data(), flat.size())) return st;
+    for (int b = 0; b < batch; ++b) lens[b] = uint32_t(t->seq_lens[b]);
+    cudaStream_t s = d->ctx->stream;
+    CU_TRY(cudaMemcpyAsync(d->tables_dev, flat.data(), flat.size() * 4, cudaMemcpyHostToDevice, s));
+    CU_TRY(cudaMemcpyAsync(d->seq_lens_dev, lens.data(), lens.size() * 4, cudaMemcpyHostToDevice, s));
+    CU_TRY(cudaStreamSynchronize(s));
+    d->batch = batch;
+    d->max_total_len = mx;
+    // ---- plans for this batch size
+    const int M = batch, dm = c.d_model, dh = c.head_dim;
+    const char* why = "";
+    size_t raw_need = 0;
+    auto plan = [&](GemmPlan* p, size_t w_off, int N, int K) -> cudaError_t {
+        cudaError_t e = gemm_make_plan(p, kGemmI8, d->xq, d->payload + w_off, M, N, K, 0, d->ctx->tune_splits, d->ctx->tune_bn, &why);
+        if (e == cudaSuccess) raw_need = std::max(raw_need, gemm_raw_elems(*p));
+        return e;
+    };
+    PagedAttnShape sh{M, 1, d->hq_l, d->hkv_l, dh, c.block_size, c.num_blocks, d->max_blocks_per_seq, 1.0f / std::sqrt(float(dh))};
+    if (!paged_attention_fast_path(sh, 1) && dh > 256) return fail(B200_UNSUPPORTED, "decoder_begin: head_dim above 256");
+    size_t attn_need = 0;
+    for (auto& L : d->layers) {
+        cudaError_t e = plan(&L.p_qkv, L.wqkv, d->n_qkv, dm);
+        if (e == cudaSuccess) e = plan(&L.p_o, L.wo, dm, d->hq_l * dh);
+        if (e == cudaSuccess) e = plan(&L.p_gu, L.wgu, 2 * d->f_l, dm);
+        if (e == cudaSuccess) e = plan(&L.p_down, L.wdown, dm, d->f_l);
+        if (e != cudaSuccess) return fail(B200_UNSUPPORTED, std::string("decoder_begin: ") + why);
+        e = paged_attention_make_plan(&L.attn, sh, 1, L.k_pool, L.v_pool, mx, d->ctx->tune_attn_chunk_blocks);
+        if (e != cudaSuccess) return fail(B200_KERNEL_LAUNCH_FAILED, "decoder_begin: attention plan failed");
+        attn_need = std::max(attn_need, paged_attention_scratch_bytes(L.attn));
+    }
+    {
+        cudaError_t e = gemm_make_plan(&d->p_lm, kGemmI8, d->xq, d->payload + d->w_lm, M, c.vocab, dm, 0, 1, d->ctx->tune_bn, &why);
+        if (e != cudaSuccess) return fail(B200_UNSUPPORTED, std::string("decoder_begin: ") + why);
+    }
+    if (raw_need > d->raw_elems) {
+        cudaFree(d->raw);
+        d->raw = nullptr;
+        CU_TRY(dmalloc(&d->raw, raw_need));
+        d->raw_elems = raw_need;
+    }
+    cudaFree(d->attn_scratch);
+    d->attn_scratch = nullptr;
+    CU_TRY(cudaMalloc(&d->attn_scratch, attn_need > 0 ? attn_need : 16));
+    d->planned = true;
+    d->steps = 0;
+    return B200_OK;
+}
+
+// Fills this rank's KV pools with synthetic bf16 N(0, std^2) values (benchmark set-up: stands in for a
+// prefill whose results the timed decode steps only read).
+int32_t b200_decoder_fill_cache_random(b200_decoder* d, uint64_t seed, float std) {
+    if (int32_t st = dec_check(d)) return st;
+    const auto& c = d->cfg;
+    const int64_t pool_elems = int64_t(c.num_blocks) * c.block_size * d->hkv_l * c.head_dim;
+    for (int l = 0; l < c.n_layers; ++l) {
+        CU_TRY(fill_normal_bf16(static_cast<uint16_t*>(d->layers[l].k_pool), pool_elems, seed, 1000 + 2 * l, std, d->ctx->stream));
+        CU_TRY(fill_normal_bf16(static_cast<uint16_t*>(d->layers[l].v_pool), pool_elems, seed, 1001 + 2 * l, std, d->ctx->stream));
+    }
+    return B200_OK;
+}
+
+// One decode step for every row of the batch.  ids_host != NULL: the step's input ids are copied from
+// the host (pinned staging) first; otherwise the ids produced by the previous step are used in place.
+// next_ids_host != NULL: the sampled ids are copied back and the call returns when they are final.
+int32_t b200_decoder_step(b200_decoder* d, const int32_t* ids_host, int32_t* next_ids_host) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!d->planned) return fail(B200_INVALID_ARGUMENT, "decoder_step: call decoder_begin first");
+    cudaStream_t s = d->ctx->stream;
+    const int M = d->batch;
+    for (int b = 0; b < M; ++b)
+        if (d->table->seq_lens[b] + 1 > uint64_t(d->table->tables[b].size()) * d->cfg.block_size)
+            return fail(B200_INVALID_ARGUMENT, "decoder_step: row " + std::to_string(b) + " is past its reserved length");
+    if (ids_host) {
+        std::memcpy(d->ids_pinned, ids_host, size_t(M) * sizeof(int));
+        CU_TRY(cudaMemcpyAsync(d->ids_dev, d->ids_pinned, size_t(M) * sizeof(int), cudaMemcpyHostToDevice, s));
+    } else if (d->steps > 0) {
+        CU_TRY(cudaMemcpyAsync(d->ids_dev, d->next_ids_dev, size_t(M) * sizeof(int), cudaMemcpyDeviceToDevice, s));
+    }
+    if (d->graph) {
+        CU_TRY(cudaGraphLaunch(d->graph, s));
+    } else if (d->eager_steps_done < 1 || d->cfg.use_graph == 0) {
+        // the first step runs eagerly (it also sets the kernels' shared-memory attributes)
+        if (int32_t st = enqueue_step(d)) return st;
+        d->eager_steps_done++;
+    } else {
+        cudaGraph_t g = nullptr;
+        CU_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        int32_t st = enqueue_step(d);
+        cudaError_t e = cudaStreamEndCapture(s, &g);
+        if (st != B200_OK) {
+            if (g) cudaGraphDestroy(g);
+            return st;
+        }
+        if (e != cudaSuccess) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, std::string("graph capture: ") + cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&d->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, std::string("graph instantiate: ") + cudaGetErrorString(e));
+        CU_TRY(cudaGraphLaunch(d->graph, s));
+    }
+    for (int b = 0; b < M; ++b) d->table->seq_lens[b] += 1;     // commit the logical state after the enqueue succeeded
+    d->steps++;
+    if (next_ids_host) {
+        CU_TRY(cudaMemcpyAsync(d->next_pinned, d->next_ids_dev, size_t(M) * sizeof(int), cudaMemcpyDeviceToHost, s));
+        CU_TRY(cudaStreamSynchronize(s));
+        std::memcpy(next_ids_host, d->next_pinned, size_t(M) * sizeof(int));
+        if (int32_t st = b200_synchronize(d->ctx)) {
+            d->store_poisoned = true;
+            return st;
+        }
+    }
+    return B200_OK;
+}
+
+// Copies the logits [batch, vocab] of the last step to the host (synchronises).
+int32_t b200_decoder_logits(b200_decoder* d, float* host, uint64_t capacity_elems) {
+    if (int32_t st = dec_check(d)) return st;
+    const size_t n = size_t(d->batch) * d->cfg.vocab;
+    if (!host || capacity_elems < n) return fail(B200_INVALID_ARGUMENT, "decoder_logits: host buffer too small");
+    CU_TRY(cudaMemcpyAsync(host, d->logits, n * 4, cudaMemcpyDeviceToHost, d->ctx->stream));
+    return b200_synchronize(d->ctx);
+}
+
+// generate() of the reference (crates/autodiff/src/generate/mod.rs:500-613) with greedy sampling: the
+// prompt [batch, prompt_len] is consumed token by token through the same decode step (teacher forcing),
+// then the model's own tokens are fed back until max_length; out is [batch, max_length] (prompt included).
+// There is no end-of-sequence stop, as in the reference.
+int32_t b200_decoder_generate(b200_decoder* d, const int32_t* prompt, int32_t batch, int32_t prompt_len, int32_t max_length,
+                              int32_t* out) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!prompt || !out) return fail(B200_INVALID_ARGUMENT, "decoder_generate: null pointer");
+    if (prompt_len <= 0 || max_length <= prompt_len) return fail(B200_INVALID_ARGUMENT, "decoder_generate: need 0 < prompt_len < max_length");
+    for (int64_t i = 0; i < int64_t(batch) * prompt_len; ++i)
+        if (prompt[i] < 0 || prompt[i] >= d->cfg.vocab) return fail(B200_INVALID_ARGUMENT, "decoder_generate: token id outside the vocabulary");
+    std::vector<int32_t> lens(batch, max_length - 1);   // the last generated token is never fed back
+    if (int32_t st = b200_decoder_begin(d, batch, nullptr, lens.data())) return st;
+    std::vector<int32_t> ids(batch), next(batch);
+    for (int b = 0; b < batch; ++b)
+        for (int t = 0; t < prompt_len; ++t) out[size_t(b) * max_length + t] = prompt[size_t(b) * prompt_len + t];
+    for (int t = 0; t < max_length - 1; ++t) {
+        const bool in_prompt = t < prompt_len;
+        if (in_prompt)
+            for (int b = 0; b < batch; ++b) ids[b] = prompt[size_t(b) * prompt_len + t];
+        const bool need_out = t >= prompt_len - 1;
+        if (int32_t st = b200_decoder_step(d, in_prompt ? ids.data() : nullptr, need_out ? next.data() : nullptr)) return st;
+        if (need_out)
+            for (int b = 0; b < batch; ++b) out[size_t(b) * max_length + t + 1] = next[b];
+    }
+    return B200_OK;
+}
+
+uint64_t b200_decoder_launches_per_step(const b200_decoder* d) { return d ? d->launches_per_step : 0; }
+uint64_t b200_decoder_weight_bytes(const b200_decoder* d) { return d ? d->payload_bytes : 0; }
+
+// Plan summary for benchmarks: tile width and split count of the four per-layer GEMMs and the split
+// size of the attention kernel.  out[0..9] = {qkv.bn, qkv.splits, o.bn, o.splits, gu.bn, gu.splits,
+// down.bn, down.splits, attn.chunk_blocks, attn.max_chunks}.
+int32_t b200_decoder_plan_info(const b200_decoder* d, int32_t* out10) {
+    if (!d || !out10 || !d->planned) return fail(B200_INVALID_ARGUMENT, "decoder_plan_info: no plan");
+    const LayerParams& L = d->layers[0];
+    const int v[10] = {L.p_qkv.bn, L.p_qkv.splits, L.p_o.bn, L.p_o.splits, L.p_gu.bn, L.p_gu.splits,
+                       L.p_down.bn, L.p_down.splits, L.attn.chunk_blocks, L.attn.max_chunks};
+    for (int i = 0; i < 10; ++i) out10[i] = v[i];
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -41,4 +41,30 @@ cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, co
                                    const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
                                    uint32_t* err, cudaStream_t stream);
 
+// ---- decode_kernels.cu (one CTA per token row; `raw` = split-K planes [splits][M][N] of int32)
+cudaError_t embed_norm_quant(const int* ids, const float* table, int vocab, int M, int d, const float* norm_w, float eps,
+                             float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s);
+// `pre` != nullptr: the already dequantised (and, under tensor parallelism, all-reduced) GEMM output
+// [M, d] is used instead of raw / sx_in / sw.
+cudaError_t resid_norm_quant(const int* raw, int splits, int M, int d, const float* sx_in, const float* sw,
+                             const float* pre, const float* norm_w, float eps, float* h, int8_t* xq, float* sx_out,
+                             cudaStream_t s);
+cudaError_t gate_quant(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
+                       float* sx_out, cudaStream_t s);
+cudaError_t qkv_rope_append(const int* raw, int splits, int M, int hq, int hkv, int dh, const float* sx_in,
+                            const float* sw, const float* cos_t, const float* sin_t, int max_pos,
+                            const uint32_t* positions, const uint32_t* block_tables, int max_blocks_per_seq,
+                            int block_size, int num_blocks, float* q_out, uint16_t* k_pool, uint16_t* v_pool,
+                            uint32_t* err, cudaStream_t s);
+// y[m, n] = sum_planes(raw)[m, n] * (sx[m] * sw[n]) as f32 (the addend of a cross-rank sum)
+cudaError_t dequant_planes(const int* raw, int splits, int M, int N, const float* sx, const float* sw, float* y,
+                           cudaStream_t s);
+// positions[i] = seq_lens[i]; seq_lens[i] += 1
+cudaError_t begin_step(uint32_t* seq_lens, uint32_t* positions, int n, cudaStream_t s);
+cudaError_t argmax_rows(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s);
+cudaError_t fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id, float std, cudaStream_t s);
+cudaError_t fill_normal_bf16(uint16_t* out, int64_t n, uint64_t seed, uint64_t stream_id, float std, cudaStream_t s);
+cudaError_t slice_cols_i8(const int8_t* src, int64_t rows, int64_t ld, int64_t c0, int64_t cols, int8_t* dst,
+                          cudaStream_t s);
+
 }  // namespace b200

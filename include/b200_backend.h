@@ -227,6 +227,89 @@ int32_t b200_paged_attention_forward_resident(b200_ctx* ctx, const b200_buf* q, 
 /* Blocks per split of the decode-attention kernel (1..32; 0 restores the default), for tuning. */
 int32_t b200_paged_attention_tuning(b200_ctx* ctx, int32_t chunk_blocks);
 
+/* ------------------------------------------------------------------ host page table
+ * BlockTable of the reference (crates/autodiff/src/nn/paged_kv.rs:158-364), host only: blocks are
+ * taken from a LIFO stack of returned ids first, then from a counter starting at 0, so the order is
+ * deterministic.  All rows have the same length (the reference's invariant). */
+typedef struct b200_block_table b200_block_table;
+int32_t b200_block_table_create(uint64_t max_blocks, uint64_t block_size, b200_block_table** out);
+void b200_block_table_destroy(b200_block_table* table);
+/* extend_for_append (paged_kv.rs:206-297): every one of the `batch` rows grows by l_new tokens; writes the
+ * row-major slot mapping (row b, token i) into slots_out.  Fails without changing the table when the
+ * batch differs from the cached one or the pool has too few free blocks. */
+int32_t b200_block_table_extend_for_append(b200_block_table* table, uint64_t batch, uint64_t l_new,
+                                           uint32_t* slots_out, uint64_t slots_capacity, uint64_t* n_slots);
+/* flatten_tables (paged_kv.rs:299-322): [batch, max_blocks_per_seq], unused slots 0xFFFFFFFF. */
+int32_t b200_block_table_flatten(const b200_block_table* table, uint64_t max_blocks_per_seq, uint32_t* out,
+                                 uint64_t capacity);
+/* rewind_to (paged_kv.rs:324-364): shrink to new_len, hand the tail blocks back; 0 resets the table. */
+int32_t b200_block_table_rewind_to(b200_block_table* table, uint64_t new_len);
+void b200_block_table_clear(b200_block_table* table);
+uint64_t b200_block_table_seq_len(const b200_block_table* table);
+uint64_t b200_block_table_free_blocks(const b200_block_table* table);
+uint64_t b200_block_table_used_blocks(const b200_block_table* table);
+int64_t b200_block_table_batch(const b200_block_table* table);   /* -1 while no batch is fixed */
+
+/* ------------------------------------------------------------------ decode driver
+ * The caller of the two kernels families above: a Llama-style decoder stack (RMSNorm eps, rotate-half
+ * RoPE, grouped-query paged attention with a bf16 cache, SwiGLU) with INT8 per-output-channel
+ * weights and per-token INT8 activations, resident in flat parameter buffers in the manner of
+ * DeviceParamStore (crates/autodiff/src/optim/device_store.rs:27-52, 1288-1364), driven like the
+ * reference's generate() (crates/autodiff/src/generate/mod.rs:500-613) but with sampling on the
+ * device.  The reference has no such model; the wiring is defined here and in the CPU oracle. */
+typedef struct b200_decoder b200_decoder;
+
+typedef struct b200_decoder_config {
+    int32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ff, vocab;
+    float rms_eps;
+    float rope_theta;
+    int32_t max_batch;      /* rows a step may hold */
+    int32_t max_seq_len;    /* positions per row (rope table, block table width) */
+    int32_t block_size;     /* tokens per KV block (16 selects the TMA attention path) */
+    int32_t num_blocks;     /* blocks per K / V pool per layer */
+    int32_t tp_rank, tp_size;   /* tensor parallel: this process's rank and the number of ranks */
+    int32_t use_graph;      /* replay each step as a CUDA graph after the first (eager) one */
+} b200_decoder_config;
+
+typedef enum b200_weight {
+    B200_W_EMBED = 0,       /* [vocab, d_model] f32, kept f32 */
+    B200_W_ATTN_NORM = 1,   /* [1, d_model] per layer */
+    B200_W_QKV = 2,         /* [(n_heads + 2 n_kv_heads) head_dim, d_model]: q rows, then k rows, then v rows */
+    B200_W_O = 3,           /* [d_model, n_heads head_dim] */
+    B200_W_MLP_NORM = 4,    /* [1, d_model] per layer */
+    B200_W_GATE_UP = 5,     /* [2 d_ff, d_model]: gate rows then up rows */
+    B200_W_DOWN = 6,        /* [d_model, d_ff] */
+    B200_W_FINAL_NORM = 7,  /* [1, d_model] */
+    B200_W_LM_HEAD = 8      /* [vocab, d_model] */
+} b200_weight;
+
+int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_decoder** out);
+int32_t b200_decoder_destroy(b200_decoder* dec);
+/* Loads one full (unsharded) f32 tensor [rows, cols] from the host; matrices are quantised on the
+ * device (one scale per full row) and this rank's shard is kept. */
+int32_t b200_decoder_load_tensor(b200_decoder* dec, int32_t which, int32_t layer, const float* host, int64_t rows,
+                                 int64_t cols);
+/* Synthetic weights N(0, std^2) from a counter-based generator (norm weights 1), identical on every rank. */
+int32_t b200_decoder_init_random(b200_decoder* dec, uint64_t seed, float std);
+/* 128-byte NCCL unique id (rank 0 makes it, the launcher hands it to every rank) and communicator set-up. */
+int32_t b200_nccl_unique_id(uint8_t* out128);
+int32_t b200_decoder_init_tp(b200_decoder* dec, const uint8_t* unique_id128);
+/* Starts a generation of `batch` rows: row b starts at start_lens[b] cached tokens (NULL: 0) and may grow
+ * to max_total_lens[b]; blocks for the final length are reserved now and the tables uploaded once. */
+int32_t b200_decoder_begin(b200_decoder* dec, int32_t batch, const int32_t* start_lens, const int32_t* max_total_lens);
+/* Benchmark set-up: fills this rank's KV pools with synthetic bf16 values. */
+int32_t b200_decoder_fill_cache_random(b200_decoder* dec, uint64_t seed, float std);
+/* One decode step.  ids_host != NULL: input ids come from the host; else the previous step's samples.
+ * next_ids_host != NULL: the greedy samples are copied back (this synchronises). */
+int32_t b200_decoder_step(b200_decoder* dec, const int32_t* ids_host, int32_t* next_ids_host);
+int32_t b200_decoder_logits(b200_decoder* dec, float* host, uint64_t capacity_elems);
+/* generate() with greedy sampling: out is [batch, max_length] and begins with the prompt. */
+int32_t b200_decoder_generate(b200_decoder* dec, const int32_t* prompt, int32_t batch, int32_t prompt_len,
+                              int32_t max_length, int32_t* out);
+uint64_t b200_decoder_launches_per_step(const b200_decoder* dec);
+uint64_t b200_decoder_weight_bytes(const b200_decoder* dec);
+int32_t b200_decoder_plan_info(const b200_decoder* dec, int32_t* out10);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,125 @@
+"""CPU restatement of the quantized Llama-style decoder (TEST INFRASTRUCTURE ONLY, like oracle.py).
+
+PARITY UNPINNED: the reference has no RoPE, SwiGLU layer, Llama model, int8 path or tensor parallelism;
+the wiring below is this project's definition, built from the pieces the reference does pin (RMSNorm
+with an f64 sum of squares, the two-branch SiLU, the sequential paged attention, first-max greedy
+sampling) and the quantisation rule of the benchmark text.  One token row at a time goes through
+
+    h = embed[id]
+    per layer:  xq, sx = quant(rmsnorm(h) * attn_norm)
+                qkv    = acc(xq, Wqkv) * (sx * s_w)            -> RoPE on q, k -> k, v appended as bf16
+                a      = paged_attention(q, cache)              (f32 math on bf16 K/V)
+                h     += sum_r acc(quant_r(a_r), Wo_r) * (sa_r * s_w)     (r: tensor-parallel rank, ascending)
+                xq, sx = quant(rmsnorm(h) * mlp_norm)
+                f      = silu(gate) * up,   gate/up = acc(xq, Wgu) * (sx * s_w)
+                h     += sum_r acc(quant_r(f_r), Wdown_r) * (sf_r * s_w)
+    logits = acc(quant(rmsnorm(h) * final_norm), Wlm) * (sx * s_w);  next = first argmax
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import oracle as O
+
+
+def make_weights(cfg: dict, seed: int = 0, std: float = 0.02) -> dict:
+    """Random-init weights N(0, std^2) (norm weights 1), f32, full (unsharded) shapes."""
+    rng = np.random.default_rng(seed)
+    d, dh, hq, hkv, f, v = cfg["d_model"], cfg["head_dim"], cfg["n_heads"], cfg["n_kv_heads"], cfg["d_ff"], cfg["vocab"]
+
+    def n(*shape):
+        return (rng.standard_normal(shape) * std).astype(np.float32)
+
+    w = {"embed": n(v, d), "final_norm": np.ones(d, np.float32), "lm_head": n(v, d), "layers": []}
+    for _ in range(cfg["n_layers"]):
+        w["layers"].append({"attn_norm": np.ones(d, np.float32), "wqkv": n((hq + 2 * hkv) * dh, d), "wo": n(d, hq * dh),
+                            "mlp_norm": np.ones(d, np.float32), "wgu": n(2 * f, d), "wdown": n(d, f)})
+    return w
+
+
+class DecoderRef:
+    def __init__(self, cfg: dict, weights: dict, tp: int = 1):
+        self.cfg = cfg
+        self.tp = tp
+        self.w = weights
+        self.q = {"lm_head": O.quantize_i8_per_row(weights["lm_head"]), "layers": []}
+        for lw in weights["layers"]:
+            self.q["layers"].append({k: O.quantize_i8_per_row(lw[k]) for k in ("wqkv", "wo", "wgu", "wdown")})
+        self.cos, self.sin = O.rope_table(cfg["max_seq_len"], cfg["head_dim"], cfg.get("rope_theta", 10000.0))
+        self.k = None
+
+    def begin(self, batch: int):
+        c = self.cfg
+        ekv = c["n_kv_heads"] * c["head_dim"]
+        self.bs = c.get("block_size", 16)
+        self.mbps = -(-c["max_seq_len"] // self.bs)
+        nblk = batch * self.mbps
+        self.nblk = nblk
+        self.k = [np.zeros((nblk * self.bs, ekv), np.uint16) for _ in range(c["n_layers"])]
+        self.v = [np.zeros((nblk * self.bs, ekv), np.uint16) for _ in range(c["n_layers"])]
+        self.tables = np.arange(nblk, dtype=np.uint32).reshape(batch, self.mbps)
+        self.seq = np.zeros(batch, np.int64)
+        self.batch = batch
+
+    def _row_parallel(self, x, wq, ws, h):
+        """h + sum over ranks (ascending) of acc(quant_r(x_r), W_r) * (s_r * s_w); x: [M, K]."""
+        tp = self.tp
+        k = x.shape[1] // tp
+        total = None
+        for r in range(tp):
+            xq, sx = O.quantize_i8_per_row(x[:, r * k:(r + 1) * k])
+            acc = O.gemm_i8_s32(xq, np.ascontiguousarray(wq[:, r * k:(r + 1) * k]))
+            y = O.epilogue_scaled(acc, sx, True, ws, True)
+            total = y if total is None else (total + y).astype(np.float32)
+        return (total + h).astype(np.float32)
+
+    def step(self, ids):
+        """One token per row; returns (logits [B, V], next ids [B])."""
+        c = self.cfg
+        d, dh, hq, hkv, f = c["d_model"], c["head_dim"], c["n_heads"], c["n_kv_heads"], c["d_ff"]
+        eps = c.get("rms_eps", 1e-5)
+        b = self.batch
+        ids = np.asarray(ids)
+        h = self.w["embed"][ids].astype(np.float32)
+        pos = self.seq.copy()
+        for l, (lw, lq) in enumerate(zip(self.w["layers"], self.q["layers"])):
+            xn = O.rmsnorm(h, lw["attn_norm"], eps)
+            qkv = O.linear_w8a8(xn, *lq["wqkv"])
+            q = np.empty((b, hq * dh), np.float32)
+            k_new = np.empty((b, hkv * dh), np.float32)
+            for r in range(b):
+                q[r] = O.rope_apply(qkv[r, : hq * dh], hq, dh, self.cos[pos[r]], self.sin[pos[r]])
+                k_new[r] = O.rope_apply(qkv[r, hq * dh:(hq + hkv) * dh], hkv, dh, self.cos[pos[r]], self.sin[pos[r]])
+            v_new = np.ascontiguousarray(qkv[:, (hq + hkv) * dh:])
+            slots = [int(self.tables[r, pos[r] // self.bs]) * self.bs + int(pos[r] % self.bs) for r in range(b)]
+            O.paged_kv_append(k_new, v_new, self.k[l], self.v[l], slots, hkv * dh, True)
+            a = O.paged_attention(q.reshape(b, 1, -1), self.k[l], self.v[l], self.tables, pos + 1, batch=b, l_new=1,
+                                  num_q_heads=hq, num_kv_heads=hkv, head_dim=dh, block_size=self.bs,
+                                  num_blocks=self.nblk, max_blocks_per_seq=self.mbps,
+                                  scale=float(np.float32(1.0) / np.sqrt(np.float32(dh))), kv_bf16=True).reshape(b, -1)
+            h = self._row_parallel(a, *lq["wo"], h)
+            xn = O.rmsnorm(h, lw["mlp_norm"], eps)
+            xq, sx = O.quantize_i8_per_row(xn)
+            acc = O.gemm_i8_s32(xq, lq["wgu"][0])
+            act = O.epilogue_scaled(acc, sx, True, lq["wgu"][1], True, act=O.ACT_SILU_GATE)
+            h = self._row_parallel(act, *lq["wdown"], h)
+        self.seq += 1
+        xn = O.rmsnorm(h, self.w["final_norm"], eps)
+        logits = O.linear_w8a8(xn, *self.q["lm_head"])
+        nxt = np.array([O.greedy_argmax(logits[r]) for r in range(b)], np.int32)
+        return logits, nxt
+
+    def generate(self, prompt, max_length: int):
+        """Greedy generate: returns (ids [B, max_length], logits of every step that sampled a token)."""
+        prompt = np.asarray(prompt, np.int32)
+        b, t = prompt.shape
+        self.begin(b)
+        out = np.zeros((b, max_length), np.int32)
+        out[:, :t] = prompt
+        all_logits = []
+        for step in range(max_length - 1):
+            logits, nxt = self.step(out[:, step])
+            if step >= t - 1:
+                out[:, step + 1] = nxt
+                all_logits.append(logits)
+        return out, all_logits

@@ -1,0 +1,85 @@
+"""GPU parity of the decode driver against the CPU decoder restatement (oracle/decoder_ref.py):
+greedy token ids must be identical, logits within the composite tolerance."""
+import numpy as np
+import pytest
+
+from fandhe_ai_b200.decoder import Decoder, DecoderConfig
+from oracle import oracle as O
+from oracle.decoder_ref import DecoderRef, make_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def run_generate(be, cfg: dict, batch: int, prompt_len: int, max_length: int, seed: int, use_graph: int = 1):
+    weights = make_weights(cfg, seed=seed)
+    rng = np.random.default_rng(seed + 1)
+    prompt = rng.integers(0, cfg["vocab"], (batch, prompt_len)).astype(np.int32)
+    ref = DecoderRef(cfg, weights)
+    ids_ref, logits_ref = ref.generate(prompt, max_length)
+    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
+                       cfg["vocab"], cfg.get("rms_eps", 1e-5), cfg.get("rope_theta", 10000.0), max_batch=batch,
+                       max_seq_len=cfg["max_seq_len"], block_size=cfg.get("block_size", 16), use_graph=use_graph)
+    dec = Decoder(be, dc)
+    try:
+        dec.load_weights(weights)
+        ids = dec.generate(prompt, max_length)
+        last_logits = dec.logits()
+    finally:
+        dec.close()
+    return ids, ids_ref, last_logits, logits_ref
+
+
+SMALL = dict(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ff=1024, vocab=2048, max_seq_len=64)
+
+
+@pytest.mark.parametrize("use_graph", [0, 1])
+def test_small_decoder_token_ids_are_identical(be, use_graph):
+    ids, ids_ref, logits, logits_ref = run_generate(be, SMALL, batch=4, prompt_len=20, max_length=40, seed=0,
+                                                    use_graph=use_graph)
+    assert np.array_equal(ids[:, :20], ids_ref[:, :20])
+    assert np.array_equal(ids, ids_ref)
+    fails, max_abs, max_rel = O.compare(logits, logits_ref[-1])
+    assert fails == 0, (max_abs, max_rel)
+
+
+def test_generic_attention_path_head_dim_64(be):
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=4, head_dim=64, d_ff=512, vocab=1024, max_seq_len=48)
+    ids, ids_ref, logits, logits_ref = run_generate(be, cfg, batch=3, prompt_len=10, max_length=30, seed=3)
+    assert np.array_equal(ids, ids_ref)
+    assert O.compare(logits, logits_ref[-1])[0] == 0
+
+
+def test_config4_shape_reduced_steps(be):
+    # the small Llama-style decoder of the benchmark list (12 layers, d_model 768, 12 heads, d_ff 3072,
+    # vocab 32000, RMSNorm eps 1e-5, RoPE theta 10000) with a shorter prompt and fewer generated tokens
+    cfg = dict(n_layers=12, d_model=768, n_heads=12, n_kv_heads=12, head_dim=64, d_ff=3072, vocab=32000,
+               max_seq_len=64, rms_eps=1e-5, rope_theta=10000.0)
+    ids, ids_ref, logits, logits_ref = run_generate(be, cfg, batch=8, prompt_len=16, max_length=40, seed=4)
+    assert np.array_equal(ids, ids_ref)
+    fails, max_abs, max_rel = O.compare(logits, logits_ref[-1])
+    assert fails == 0, (max_abs, max_rel)
+
+
+def test_step_api_matches_generate_and_feeds_ids_from_the_host(be):
+    cfg = SMALL
+    weights = make_weights(cfg, seed=7)
+    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
+                       cfg["vocab"], max_batch=2, max_seq_len=cfg["max_seq_len"])
+    dec = Decoder(be, dc)
+    try:
+        dec.load_weights(weights)
+        prompt = np.array([[5, 9, 100, 7], [1, 2, 3, 4]], np.int32)
+        want = dec.generate(prompt, 12)
+        dec.begin(2, [11, 11])
+        got = np.zeros((2, 12), np.int32)
+        got[:, :4] = prompt
+        for t in range(11):
+            nxt = dec.step(got[:, t])           # every step's ids come from the host, every result goes back
+            if t >= 3:
+                got[:, t + 1] = nxt
+        assert np.array_equal(got, want)
+        with pytest.raises(Exception):          # the reserved length is used up
+            dec.step(got[:, 11])
+        assert dec.launches_per_step == 2 + cfg["n_layers"] * 11 + 2
+    finally:
+        dec.close()
