@@ -136,6 +136,9 @@ SIGNATURES = {
     "b200_decoder_launches_per_step": (_U64, [_P]),
     "b200_decoder_weight_bytes": (_U64, [_P]),
     "b200_decoder_plan_info": (_I32, [_P, _P]),
+    "b200_timer_start": (_I32, [_P]),
+    "b200_timer_stop": (_I32, [_P, C.POINTER(C.c_float)]),
+    "b200_decoder_time_attention": (_I32, [_P, _I32, C.POINTER(C.c_float), C.POINTER(_U64)]),
     "b200_linear_w8a8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _P, _SZ]),
 }
 

@@ -101,6 +101,16 @@ class Backend:
     def stream(self) -> int:
         return lib().b200_ctx_stream(self._ctx) or 0
 
+    def timer_start(self) -> None:
+        """Starts the CUDA-event stopwatch on this context's stream."""
+        check(lib().b200_timer_start(self._ctx))
+
+    def timer_stop(self) -> float:
+        """Waits for the stream and returns the device milliseconds since timer_start()."""
+        ms = C.c_float()
+        check(lib().b200_timer_stop(self._ctx, C.byref(ms)))
+        return float(ms.value)
+
     def gemm_tuning(self, tile_n: int = 0, splits: int = 0) -> None:
         check(lib().b200_gemm_tuning(self._ctx, tile_n, splits))
 

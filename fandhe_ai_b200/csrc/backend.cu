@@ -182,6 +182,8 @@ int32_t b200_ctx_destroy(b200_ctx* ctx) {
         cudaStreamSynchronize(ctx->stream);
         cudaStreamDestroy(ctx->stream);
     }
+    if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+    if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->err_dev) cudaFree(ctx->err_dev);
     if (ctx->err_host) cudaFreeHost(ctx->err_host);

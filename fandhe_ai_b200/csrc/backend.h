@@ -22,6 +22,8 @@ struct b200_ctx {
     int tune_splits = 0;                // 0 = heuristic
     int tune_attn_chunk_blocks = 0;     // 0 = default
     int sm_count = 0;
+    cudaEvent_t ev_start = nullptr;     // stopwatch of b200_timer_start / b200_timer_stop
+    cudaEvent_t ev_stop = nullptr;
 };
 
 struct b200_buf {

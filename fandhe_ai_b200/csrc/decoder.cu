@@ -278,6 +278,8 @@ struct b200_decoder {
     float* logits = nullptr;
     void* attn_scratch = nullptr;
     int* ids_pinned = nullptr;
+    cudaEvent_t ids_copied = nullptr;           // the staged ids of the previous step have reached the device
+    bool ids_copy_pending = false;
     int* next_pinned = nullptr;
     // graph
     cudaGraphExec_t graph = nullptr;
@@ -555,6 +557,7 @@ int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_
     A(dmalloc(&d->part, M * dm));
     A(dmalloc(&d->logits, M * size_t(c.vocab)));
     A(cudaMallocHost(reinterpret_cast<void**>(&d->ids_pinned), M * sizeof(int)));
+    A(cudaEventCreateWithFlags(&d->ids_copied, cudaEventDisableTiming));
     A(cudaMallocHost(reinterpret_cast<void**>(&d->next_pinned), M * sizeof(int)));
     if (e == cudaSuccess) e = cudaMemsetAsync(d->vectors, 0, vec * sizeof(float), ctx->stream);
     if (e != cudaSuccess) {
@@ -605,6 +608,7 @@ int32_t b200_decoder_destroy(b200_decoder* d) {
                     d->attn_scratch};
     for (void* p : ptrs) cudaFree(p);
     if (d->ids_pinned) cudaFreeHost(d->ids_pinned);
+    if (d->ids_copied) cudaEventDestroy(d->ids_copied);
     if (d->next_pinned) cudaFreeHost(d->next_pinned);
     b200_block_table_destroy(d->table);
     cudaGetLastError();
@@ -809,8 +813,12 @@ int32_t b200_decoder_step(b200_decoder* d, const int32_t* ids_host, int32_t* nex
         if (d->table->seq_lens[b] + 1 > uint64_t(d->table->tables[b].size()) * d->cfg.block_size)
             return fail(B200_INVALID_ARGUMENT, "decoder_step: row " + std::to_string(b) + " is past its reserved length");
     if (ids_host) {
+        // the staging buffer is read when the copy executes, not when it is enqueued
+        if (d->ids_copy_pending) CU_TRY(cudaEventSynchronize(d->ids_copied));
         std::memcpy(d->ids_pinned, ids_host, size_t(M) * sizeof(int));
         CU_TRY(cudaMemcpyAsync(d->ids_dev, d->ids_pinned, size_t(M) * sizeof(int), cudaMemcpyHostToDevice, s));
+        CU_TRY(cudaEventRecord(d->ids_copied, s));
+        d->ids_copy_pending = true;
     } else if (d->steps > 0) {
         CU_TRY(cudaMemcpyAsync(d->ids_dev, d->next_ids_dev, size_t(M) * sizeof(int), cudaMemcpyDeviceToDevice, s));
     }
@@ -898,6 +906,68 @@ int32_t b200_decoder_plan_info(const b200_decoder* d, int32_t* out10) {
     const int v[10] = {L.p_qkv.bn, L.p_qkv.splits, L.p_o.bn, L.p_o.splits, L.p_gu.bn, L.p_gu.splits,
                        L.p_down.bn, L.p_down.splits, L.attn.chunk_blocks, L.attn.max_chunks};
     for (int i = 0; i < 10; ++i) out10[i] = v[i];
+    return B200_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------ measurement aids
+extern "C" {
+
+// CUDA-event stopwatch on the context's stream (device time of the work enqueued between the two
+// calls).  The reference's bench harness waits for completion without a transfer
+// (crates/bench-harness/src/lib.rs, module doc); this is the same wait made with events.
+int32_t b200_timer_start(b200_ctx* ctx) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (int32_t st = set_device(ctx)) return st;
+    if (!ctx->ev_start) {
+        cudaError_t e = cudaEventCreate(&ctx->ev_start);
+        if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_stop);
+        if (e != cudaSuccess) return fail(B200_KERNEL_LAUNCH_FAILED, std::string("timer: ") + cudaGetErrorString(e));
+    }
+    cudaError_t e = cudaEventRecord(ctx->ev_start, ctx->stream);
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("timer: ") + cudaGetErrorString(e));
+    return B200_OK;
+}
+
+int32_t b200_timer_stop(b200_ctx* ctx, float* elapsed_ms) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (!ctx->ev_start || !elapsed_ms) return fail(B200_INVALID_ARGUMENT, "timer_stop: timer not started");
+    cudaError_t e = cudaEventRecord(ctx->ev_stop, ctx->stream);
+    if (e == cudaSuccess) e = cudaEventSynchronize(ctx->ev_stop);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(elapsed_ms, ctx->ev_start, ctx->ev_stop);
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("timer: ") + cudaGetErrorString(e));
+    return b200_synchronize(ctx);
+}
+
+// Times the decode-attention launch (split kernel + combine) alone on the decoder's current caches:
+// `iters` launches cycling over the layers, so consecutive launches read different pools (each far
+// larger than L2).  Reports the mean device time per launch and the algorithmic bytes of one launch:
+// K and V rows of every cached token of this rank's KV heads, q and out rows, and the used table entries.
+int32_t b200_decoder_time_attention(b200_decoder* d, int32_t iters, float* ms_per_launch, uint64_t* bytes_per_launch) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!d->planned || iters <= 0 || !ms_per_launch) return fail(B200_INVALID_ARGUMENT, "decoder_time_attention: no plan or bad arguments");
+    cudaStream_t s = d->ctx->stream;
+    const auto& c = d->cfg;
+    uint64_t bytes = 0;
+    for (int b = 0; b < d->batch; ++b) {
+        const uint64_t n = d->table->seq_lens[b];
+        bytes += n * uint64_t(d->hkv_l) * c.head_dim * 2 * 2;
+        bytes += (n + c.block_size - 1) / c.block_size * 4;
+    }
+    bytes += uint64_t(d->batch) * d->hq_l * c.head_dim * 4 * 2;
+    if (bytes_per_launch) *bytes_per_launch = bytes;
+    auto run = [&](int l) {
+        LayerParams& L = d->layers[l % c.n_layers];
+        return paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
+                                      d->attn_scratch, d->ctx->err_dev, s);
+    };
+    for (int w = 0; w < 3; ++w) CU_TRY(run(w));
+    if (int32_t st = b200_timer_start(d->ctx)) return st;
+    for (int i = 0; i < iters; ++i) CU_TRY(run(i + 3));
+    float ms = 0.0f;
+    if (int32_t st = b200_timer_stop(d->ctx, &ms)) return st;
+    *ms_per_launch = ms / float(iters);
     return B200_OK;
 }
 

@@ -172,6 +172,13 @@ class Decoder:
         self._batch = batch
         return out
 
+    def time_attention(self, iters: int = 32):
+        """(mean ms of one decode-attention launch alone, its algorithmic bytes)."""
+        ms = C.c_float()
+        nbytes = C.c_uint64()
+        check(lib().b200_decoder_time_attention(self._h, iters, C.byref(ms), C.byref(nbytes)))
+        return float(ms.value), int(nbytes.value)
+
     @property
     def launches_per_step(self) -> int:
         return int(lib().b200_decoder_launches_per_step(self._h))

@@ -310,6 +310,16 @@ uint64_t b200_decoder_launches_per_step(const b200_decoder* dec);
 uint64_t b200_decoder_weight_bytes(const b200_decoder* dec);
 int32_t b200_decoder_plan_info(const b200_decoder* dec, int32_t* out10);
 
+/* ------------------------------------------------------------------ measurement aids
+ * CUDA-event stopwatch on the context's stream: device time of everything enqueued between start and
+ * stop (stop waits for it, without a transfer, like the completion wait of the reference's bench
+ * harness, crates/bench-harness/src/lib.rs module doc). */
+int32_t b200_timer_start(b200_ctx* ctx);
+int32_t b200_timer_stop(b200_ctx* ctx, float* elapsed_ms);
+/* Mean device time of one decode-attention launch on the decoder's current caches (cycling over the
+ * layers so that each launch reads a different pool) and the algorithmic bytes of one launch. */
+int32_t b200_decoder_time_attention(b200_decoder* dec, int32_t iters, float* ms_per_launch, uint64_t* bytes_per_launch);
+
 #ifdef __cplusplus
 }
 #endif
