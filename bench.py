@@ -31,6 +31,10 @@ CONFIGS = {
     # the configuration the metric is quoted on
     "llama8b": dict(n_layers=32, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128, d_ff=14336, vocab=128256,
                     batch=128, prompt_lo=256, prompt_hi=2048),
+    # the same layer shape with 4 layers, half the batch and a small vocabulary: small enough for an ncu
+    # capture (about 1 GB of weights, 0.3 GB of KV per layer, both above the L2 size)
+    "mid": dict(n_layers=4, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128, d_ff=14336, vocab=32000, batch=64,
+                prompt_lo=256, prompt_hi=2048),
     # a small shape for quick functional runs of this script
     "tiny": dict(n_layers=2, d_model=512, n_heads=8, n_kv_heads=8, head_dim=128, d_ff=1024, vocab=2048, batch=16,
                  prompt_lo=32, prompt_hi=128),
