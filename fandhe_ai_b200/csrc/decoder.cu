@@ -259,6 +259,7 @@ struct b200_decoder {
     // step state
     int batch = 0;
     int max_total_len = 0;
+    std::vector<int> row_limits;                // tokens each row may hold in this generation
     bool planned = false;
     b200_block_table* table = nullptr;
     uint32_t* tables_dev = nullptr;
@@ -732,12 +733,14 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     t->tables.assign(batch, {});
     t->seq_lens.assign(batch, 0);
     t->has_batch = true;
+    d->row_limits.assign(batch, 0);
     for (int b = 0; b < batch; ++b) {
         if (!bt_reserve_row(t, b, uint64_t(max_total_lens[b]))) {
             t->reset();
             return fail(B200_INVALID_ARGUMENT, "decoder_begin: not enough free blocks in the pool");
         }
         t->seq_lens[b] = start_lens ? start_lens[b] : 0;
+        d->row_limits[b] = max_total_lens[b];
     }
     std::vector<uint32_t> flat(size_t(batch) * d->max_blocks_per_seq), lens(batch);
     if (int32_t st = b200_block_table_flatten(t, d->max_blocks_per_seq, flat.data(), flat.size())) return st;
@@ -810,7 +813,7 @@ int32_t b200_decoder_step(b200_decoder* d, const int32_t* ids_host, int32_t* nex
     cudaStream_t s = d->ctx->stream;
     const int M = d->batch;
     for (int b = 0; b < M; ++b)
-        if (d->table->seq_lens[b] + 1 > uint64_t(d->table->tables[b].size()) * d->cfg.block_size)
+        if (d->table->seq_lens[b] + 1 > uint64_t(d->row_limits[b]))
             return fail(B200_INVALID_ARGUMENT, "decoder_step: row " + std::to_string(b) + " is past its reserved length");
     if (ids_host) {
         // the staging buffer is read when the copy executes, not when it is enqueued
