@@ -111,6 +111,8 @@ SIGNATURES = {
                                             _P, _SZ]),
     "b200_paged_attention_forward_resident": (_I32, [_P, _P, _SZ, _P, _P, _P, _P, _U64,
                                                      C.POINTER(PagedAttentionArgsC), _P, _SZ]),
+    "b200_paged_attention_forward_noalloc": (_I32, [_P, _P, _SZ, _P, _P, _P, _P, _U64,
+                                                    C.POINTER(PagedAttentionArgsC), _P, _SZ]),
     "b200_paged_attention_tuning": (_I32, [_P, _I32]),
     "b200_block_table_create": (_I32, [_U64, _U64, C.POINTER(_P)]),
     "b200_block_table_destroy": (None, [_P]),

@@ -303,4 +303,65 @@ int32_t b200_paged_attention_forward_resident(b200_ctx* ctx, const b200_buf* q, 
                          int(max_seq_len), buf_ptr<float>(out, out_off));
 }
 
+// Decode attention for callers that cannot allocate device memory at call time - a host thread that
+// drives the GPU from inside a latency-critical serving loop or a callback where cudaMalloc (which may
+// synchronise the whole device and take a driver lock) is forbidden, or a process whose memory budget was
+// handed out in full at start-up.  Same computation and same arguments as
+// b200_paged_attention_forward_resident; the split partials go to a fixed 32 MiB array that is part of
+// the library image on every GPU that loads it, instead of the context's growable scratch.
+//  - Sizes whose partials would not fit (query rows * heads * splits * 520 bytes > 32 MiB) are refused
+//    with B200_UNSUPPORTED; nothing is launched.
+//  - The first call on a device looks up the array's device address; make that call before any stream
+//    capture begins on the device.
+//  - The array is shared by every context of the process on that GPU and keeps the previous call's
+//    contents; each launch overwrites every partial it later reads, so nothing needs clearing, but two
+//    calls whose kernels overlap on the GPU (different streams or contexts) race on it.
+int32_t b200_paged_attention_forward_noalloc(b200_ctx* ctx, const b200_buf* q, size_t q_off, const b200_buf* k_pool,
+                                             const b200_buf* v_pool, const b200_buf* block_tables,
+                                             const b200_buf* seq_lens, uint64_t max_seq_len,
+                                             const b200_paged_attention_args* args, b200_buf* out, size_t out_off) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (int32_t st = args_recheck(args)) return st;
+    const size_t es = elem_size(args->layout.dtype);
+    const uint64_t eq = args->num_heads * head_dim(args);
+    uint64_t out_numel;
+    if (!cmul(args->batch, args->l_new, &out_numel) || !cmul(out_numel, eq, &out_numel)) return invalid("output element count overflows");
+    uint64_t max_seq;
+    if (!cmul(args->max_blocks_per_seq, args->layout.block_size, &max_seq)) return invalid("max_blocks_per_seq * block_size overflows");
+    if (max_seq_len > max_seq || max_seq_len > kI32Max) return invalid("max_seq_len exceeds max_blocks_per_seq * block_size");
+    if (int32_t st = check_buf(ctx, q, q_off, out_numel * 4, "paged_attention_forward_noalloc q")) return st;
+    if (int32_t st = check_buf(ctx, out, out_off, out_numel * 4, "paged_attention_forward_noalloc out")) return st;
+    if (int32_t st = check_buf(ctx, k_pool, 0, pool_elems(&args->layout) * es, "paged_attention_forward_noalloc k_pool")) return st;
+    if (int32_t st = check_buf(ctx, v_pool, 0, pool_elems(&args->layout) * es, "paged_attention_forward_noalloc v_pool")) return st;
+    if (int32_t st = check_buf(ctx, block_tables, 0, args->batch * args->max_blocks_per_seq * 4, "paged_attention_forward_noalloc block_tables")) return st;
+    if (int32_t st = check_buf(ctx, seq_lens, 0, args->batch * 4, "paged_attention_forward_noalloc seq_lens")) return st;
+    if ((q_off & 15) || (out_off & 15)) return fail(B200_INVALID_ARGUMENT, "paged_attention_forward_noalloc: offsets must be multiples of 16 bytes");
+    if (out_numel == 0) return B200_OK;
+    PagedAttnShape sh;
+    if (int32_t st = shape_from_args(args, &sh)) return st;
+    if (int32_t st = set_device(ctx)) return st;
+    PagedAttnPlan plan;
+    cudaError_t e = paged_attention_make_plan(&plan, sh, args->layout.dtype == B200_BF16, k_pool->ptr, v_pool->ptr,
+                                              int(max_seq_len), ctx->tune_attn_chunk_blocks);
+    if (e != cudaSuccess) return fail(B200_KERNEL_LAUNCH_FAILED, "paged_attention_forward_noalloc: tensor map creation failed");
+    const size_t need = paged_attention_scratch_bytes(plan);
+    if (need > paged_attention_static_scratch_capacity()) {
+        char msg[200];
+        std::snprintf(msg, sizeof msg,
+                      "paged_attention_forward_noalloc: the split partials need %zu bytes, the static scratch holds %zu; "
+                      "use b200_paged_attention_forward_resident for this size",
+                      need, paged_attention_static_scratch_capacity());
+        return fail(B200_UNSUPPORTED, msg);
+    }
+    void* scratch = nullptr;
+    e = paged_attention_static_scratch(ctx->ordinal, &scratch);
+    if (e != cudaSuccess)
+        return fail(B200_KERNEL_LAUNCH_FAILED, std::string("paged_attention_forward_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+    e = paged_attention_launch(plan, buf_ptr<const float>(q, q_off), k_pool->ptr, v_pool->ptr,
+                               buf_ptr<const uint32_t>(block_tables, 0), buf_ptr<const uint32_t>(seq_lens, 0),
+                               buf_ptr<float>(out, out_off), scratch, ctx->err_dev, ctx->stream);
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("paged_attention_forward_noalloc: ") + cudaGetErrorString(e));
+    return B200_OK;
+}
+
 }  // extern "C"

@@ -41,6 +41,12 @@ cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, co
                                    const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
                                    uint32_t* err, cudaStream_t stream);
 
+// Device address (for the given, current device) and size of the file-scope static scratch array that
+// stands in for `scratch` when the caller must not allocate.  The first call on a device looks the address
+// up with cudaGetSymbolAddress; it allocates nothing.
+cudaError_t paged_attention_static_scratch(int device, void** out);
+size_t paged_attention_static_scratch_capacity();
+
 // ---- decode_kernels.cu (one CTA per token row; `raw` = split-K planes [splits][M][N] of int32)
 cudaError_t embed_norm_quant(const int* ids, const float* table, int vocab, int M, int d, const float* norm_w, float eps,
                              float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s);

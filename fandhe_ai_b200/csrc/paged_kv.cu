@@ -10,6 +10,8 @@
 // keys with one CTA per query row and lets thread 0 do max and sum alone; here the key range of
 // a query row is cut into chunks (flash-decoding split-K), each chunk is one CTA fed by a TMA
 // ring of 4 KB tiles gathered through the block table, and a second kernel merges the chunks.
+#include <mutex>
+
 #include "kernels.cuh"
 #include "ptx.cuh"
 
@@ -540,6 +542,36 @@ size_t paged_attention_scratch_bytes(const PagedAttnPlan& plan) {
     if (!plan.fast) return 0;
     const size_t pairs = size_t(plan.shape.batch) * plan.shape.l_new * plan.shape.num_q_heads;
     return pairs * plan.max_chunks * (kD + 2) * sizeof(float);
+}
+
+// ------------------------------------------------------------------------------------ static scratch
+// Scratch for callers that must not allocate: the split partials of the decode-attention kernel live
+// in this file-scope array instead of a cudaMalloc'ed buffer.  Every GPU that loads the library holds
+// these 32 MiB until the process exits.  In host code the symbol below is only a stand-in: the device
+// address has to be asked for with cudaGetSymbolAddress, once per device, with that device current.
+constexpr size_t kStaticScratchBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_attention_static_scratch[kStaticScratchBytes];
+
+size_t paged_attention_static_scratch_capacity() { return kStaticScratchBytes; }
+
+cudaError_t paged_attention_static_scratch(int device, void** out) {
+    constexpr int kMaxDevices = 64;
+    static void* ptrs[kMaxDevices] = {};
+    static std::mutex mu;
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[device]) {
+        int current = -1;
+        cudaError_t e = cudaGetDevice(&current);
+        if (e != cudaSuccess) return e;
+        if (current != device) return cudaErrorInvalidDevice;   // the caller makes `device` current first
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_attention_static_scratch);
+        if (e != cudaSuccess) return e;
+        ptrs[device] = p;
+    }
+    *out = ptrs[device];
+    return cudaSuccess;
 }
 
 cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,

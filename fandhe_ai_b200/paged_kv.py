@@ -133,5 +133,20 @@ def paged_attention_forward_resident(be: Backend, q: DeviceBuffer, k_pool: Devic
     return out
 
 
+def paged_attention_forward_noalloc(be: Backend, q: DeviceBuffer, k_pool: DeviceBuffer, v_pool: DeviceBuffer,
+                                    block_tables: DeviceBuffer, seq_lens: DeviceBuffer, max_seq_len: int,
+                                    args: PagedAttentionArgs, out: DeviceBuffer) -> DeviceBuffer:
+    """`paged_attention_forward_resident` for callers that must not allocate device memory during the
+    call (a serving loop where cudaMalloc is forbidden, a process with a fixed memory budget): the split
+    partials use a fixed 32 MiB array inside the library.  Larger requests raise Unsupported.  The first
+    call per device resolves the array's address and should precede any stream capture; overlapping calls
+    on one GPU race on the array."""
+    ac = args.to_c()
+    check(lib().b200_paged_attention_forward_noalloc(be._ctx, q.handle, 0, k_pool.handle, v_pool.handle,
+                                                     block_tables.handle, seq_lens.handle, max_seq_len, C.byref(ac),
+                                                     out.handle, 0))
+    return out
+
+
 def paged_attention_tuning(be: Backend, chunk_blocks: int = 0) -> None:
     check(lib().b200_paged_attention_tuning(be._ctx, chunk_blocks))

@@ -224,6 +224,22 @@ int32_t b200_paged_attention_forward_resident(b200_ctx* ctx, const b200_buf* q, 
                                               const b200_buf* seq_lens, uint64_t max_seq_len,
                                               const b200_paged_attention_args* args, b200_buf* out, size_t out_off);
 
+/* No counterpart in the reference.  b200_paged_attention_forward_resident for callers that may not
+ * allocate device memory when they call: a serving loop or callback in which cudaMalloc is off limits
+ * (it can stall the whole device behind a driver lock), or a process that gave away its whole memory
+ * budget at start-up.  This entry point calls no cudaMalloc / cudaFree and no allocating library routine:
+ * the per-split partial results go to a fixed 32 MiB array inside the library image (held by every GPU
+ * that loads the library until the process exits).  Requests whose partials need more - query rows x
+ * heads x splits x 520 bytes - are refused with B200_UNSUPPORTED before anything is launched.  The first
+ * call on a device resolves the array's device address; issue it before starting any stream capture on
+ * that device.  All contexts of the process share the array on a given GPU, and it keeps whatever the
+ * last call left; a call rewrites every partial it reads, so nothing has to be cleared, but calls whose
+ * kernels overlap on the GPU race on it. */
+int32_t b200_paged_attention_forward_noalloc(b200_ctx* ctx, const b200_buf* q, size_t q_off, const b200_buf* k_pool,
+                                             const b200_buf* v_pool, const b200_buf* block_tables,
+                                             const b200_buf* seq_lens, uint64_t max_seq_len,
+                                             const b200_paged_attention_args* args, b200_buf* out, size_t out_off);
+
 /* Blocks per split of the decode-attention kernel (1..32; 0 restores the default), for tuning. */
 int32_t b200_paged_attention_tuning(b200_ctx* ctx, int32_t chunk_blocks);
 
