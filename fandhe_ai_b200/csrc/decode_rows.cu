@@ -1,0 +1,434 @@
+// Cluster versions of the row-wise decode kernels.  A token row is cut into CL column chunks, one CTA
+// each, launched as one thread-block cluster per row; the two row-wide reductions (f64 sum of squares for
+// RMSNorm, |max| for the per-token int8 scale) are exchanged through distributed shared memory and summed
+// in cluster-rank order, so the result does not depend on scheduling.  With 128 rows this puts 512..1024
+// CTAs with 16-byte loads on the machine instead of 128 CTAs with scalar loads.
+//
+// The per-element arithmetic is the same as in decode_kernels.cu (and as in the CPU restatement):
+// y = fma(float(sum of planes), sx * sw, 0); h += y; xn = (h * rstd) * w; q = rne(xn / (amax / 127)).
+#include <cooperative_groups.h>
+
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxChunk = 2048;   // columns a CTA may hold (shared-memory row chunk)
+
+struct RowShared {
+    double part_sum;      // this CTA's sum of squares
+    float part_max;       // this CTA's |max|
+    double warp_d[8];
+    float warp_f[8];
+    int warp_i[8];
+    float chunk[kMaxChunk];
+};
+
+__device__ __forceinline__ double block_sum(double v, RowShared& sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) sh.warp_d[warp] = v;
+    __syncthreads();
+    double r = 0.0;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) r += sh.warp_d[w];
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, RowShared& sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) sh.warp_f[warp] = v;
+    __syncthreads();
+    float r = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) r = fmaxf(r, sh.warp_f[w]);
+    return r;
+}
+
+__device__ __forceinline__ int quant_i8(float x, float scale) {
+    if (scale == 0.0f) return 0;
+    float r = rintf(x / scale);
+    r = fminf(fmaxf(r, -127.0f), 127.0f);
+    return static_cast<int>(r);
+}
+
+// Row-wide sum over the cluster in rank order.
+__device__ __forceinline__ double cluster_sum(cg::cluster_group& cl, RowShared& sh, double mine) {
+    if (threadIdx.x == 0) sh.part_sum = mine;
+    cl.sync();
+    double total = 0.0;
+    const unsigned n = cl.num_blocks();
+    for (unsigned r = 0; r < n; ++r) total += *cl.map_shared_rank(&sh.part_sum, r);
+    return total;
+}
+__device__ __forceinline__ float cluster_max(cg::cluster_group& cl, RowShared& sh, float mine) {
+    if (threadIdx.x == 0) sh.part_max = mine;
+    cl.sync();
+    float total = 0.0f;
+    const unsigned n = cl.num_blocks();
+    for (unsigned r = 0; r < n; ++r) total = fmaxf(total, *cl.map_shared_rank(&sh.part_max, r));
+    return total;
+}
+
+// RMSNorm + per-token int8 quantisation of the row whose chunk [c0, c0 + nc) sits in sh.chunk.
+// `n` is the full row width.  Ends with a cluster barrier so that no CTA leaves while a peer still reads it.
+__device__ __forceinline__ void norm_quant_chunk(cg::cluster_group& cl, RowShared& sh, int n, int c0, int nc,
+                                                 const float* __restrict__ norm_w, float eps, int8_t* __restrict__ q_row,
+                                                 float* __restrict__ scale_out) {
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < nc; i += kThreads) {
+        const double v = static_cast<double>(sh.chunk[i]);
+        acc = fma(v, v, acc);
+    }
+    acc = cluster_sum(cl, sh, block_sum(acc, sh));
+    const float inv_n = 1.0f / static_cast<float>(n);
+    const float rstd = static_cast<float>(1.0 / sqrt(fma(acc, static_cast<double>(inv_n), static_cast<double>(eps))));
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < nc; i += kThreads) {
+        const float v = __fmul_rn(__fmul_rn(sh.chunk[i], rstd), norm_w[c0 + i]);
+        sh.chunk[i] = v;
+        amax = fmaxf(amax, fabsf(v));
+    }
+    amax = cluster_max(cl, sh, block_max(amax, sh));
+    const float s = amax / 127.0f;
+    if (cl.block_rank() == 0 && threadIdx.x == 0) *scale_out = s;
+    uint32_t* q4 = reinterpret_cast<uint32_t*>(q_row + c0);
+    for (int i = threadIdx.x; i < nc / 4; i += kThreads) {
+        const uint32_t b0 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 0], s)) & 0xFFu;
+        const uint32_t b1 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 1], s)) & 0xFFu;
+        const uint32_t b2 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 2], s)) & 0xFFu;
+        const uint32_t b3 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 3], s)) & 0xFFu;
+        q4[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    }
+    cl.sync();
+}
+
+// Quantisation only (no norm) of the chunk in sh.chunk.
+__device__ __forceinline__ void quant_chunk(cg::cluster_group& cl, RowShared& sh, int c0, int nc,
+                                            int8_t* __restrict__ q_row, float* __restrict__ scale_out) {
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < nc; i += kThreads) amax = fmaxf(amax, fabsf(sh.chunk[i]));
+    amax = cluster_max(cl, sh, block_max(amax, sh));
+    const float s = amax / 127.0f;
+    if (cl.block_rank() == 0 && threadIdx.x == 0) *scale_out = s;
+    uint32_t* q4 = reinterpret_cast<uint32_t*>(q_row + c0);
+    for (int i = threadIdx.x; i < nc / 4; i += kThreads) {
+        const uint32_t b0 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 0], s)) & 0xFFu;
+        const uint32_t b1 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 1], s)) & 0xFFu;
+        const uint32_t b2 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 2], s)) & 0xFFu;
+        const uint32_t b3 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 3], s)) & 0xFFu;
+        q4[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    }
+    cl.sync();
+}
+
+// Sum of the split-K planes of four consecutive elements (16-byte loads).
+__device__ __forceinline__ int4 sum_planes4(const int* __restrict__ raw, int splits, size_t plane, size_t idx) {
+    int4 a = make_int4(0, 0, 0, 0);
+    for (int s = 0; s < splits; ++s) {
+        const int4 v = *reinterpret_cast<const int4*>(raw + s * plane + idx);
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    }
+    return a;
+}
+
+// grid = (CL, M), cluster = (CL, 1, 1): blockIdx.x = column chunk (= cluster rank), blockIdx.y = row.
+
+__global__ void __launch_bounds__(kThreads)
+embed_norm_quant_cl_kernel(const int* __restrict__ ids, const float* __restrict__ table, int vocab, int d, int nc,
+                           const float* __restrict__ norm_w, float eps, float* __restrict__ h, int8_t* __restrict__ xq,
+                           float* __restrict__ sx, uint32_t* err) {
+    __shared__ RowShared sh;
+    cg::cluster_group cl = cg::this_cluster();
+    const int m = blockIdx.y, c0 = blockIdx.x * nc;
+    int id = ids[m];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrTokenId));
+        id = 0;
+    }
+    const float* src = table + static_cast<size_t>(id) * d + c0;
+    float* hdst = h + static_cast<size_t>(m) * d + c0;
+    for (int g = threadIdx.x; g < nc / 4; g += kThreads) {
+        const float4 v = *reinterpret_cast<const float4*>(src + 4 * g);
+        *reinterpret_cast<float4*>(hdst + 4 * g) = v;
+        *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = v;
+    }
+    __syncthreads();
+    norm_quant_chunk(cl, sh, d, c0, nc, norm_w, eps, xq + static_cast<size_t>(m) * d, sx + m);
+}
+
+__global__ void __launch_bounds__(kThreads)
+resid_norm_quant_cl_kernel(const int* __restrict__ raw, int splits, int M, int d, int nc,
+                           const float* __restrict__ sx_in, const float* __restrict__ sw, const float* __restrict__ pre,
+                           const float* __restrict__ norm_w, float eps, float* __restrict__ h, int8_t* __restrict__ xq,
+                           float* __restrict__ sx_out) {
+    __shared__ RowShared sh;
+    cg::cluster_group cl = cg::this_cluster();
+    const int m = blockIdx.y, c0 = blockIdx.x * nc;
+    const size_t plane = static_cast<size_t>(M) * d;
+    const size_t base = static_cast<size_t>(m) * d + c0;
+    const float sa = pre ? 0.0f : sx_in[m];
+    for (int g = threadIdx.x; g < nc / 4; g += kThreads) {
+        float4 y;
+        if (pre) {
+            y = *reinterpret_cast<const float4*>(pre + base + 4 * g);
+        } else {
+            const int4 a = sum_planes4(raw, splits, plane, base + 4 * g);
+            const float4 w4 = *reinterpret_cast<const float4*>(sw + c0 + 4 * g);
+            y.x = fmaf(static_cast<float>(a.x), sa * w4.x, 0.0f);
+            y.y = fmaf(static_cast<float>(a.y), sa * w4.y, 0.0f);
+            y.z = fmaf(static_cast<float>(a.z), sa * w4.z, 0.0f);
+            y.w = fmaf(static_cast<float>(a.w), sa * w4.w, 0.0f);
+        }
+        float4 hv = *reinterpret_cast<const float4*>(h + base + 4 * g);
+        hv.x = y.x + hv.x; hv.y = y.y + hv.y; hv.z = y.z + hv.z; hv.w = y.w + hv.w;
+        *reinterpret_cast<float4*>(h + base + 4 * g) = hv;
+        *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = hv;
+    }
+    __syncthreads();
+    norm_quant_chunk(cl, sh, d, c0, nc, norm_w, eps, xq + static_cast<size_t>(m) * d, sx_out + m);
+}
+
+__global__ void __launch_bounds__(kThreads)
+gate_quant_cl_kernel(const int* __restrict__ raw, int splits, int M, int F, int nc, const float* __restrict__ sx_in,
+                     const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+    __shared__ RowShared sh;
+    cg::cluster_group cl = cg::this_cluster();
+    const int m = blockIdx.y, c0 = blockIdx.x * nc;
+    const size_t plane = static_cast<size_t>(M) * 2 * F;
+    const size_t base = static_cast<size_t>(m) * 2 * F + c0;
+    const float sa = sx_in[m];
+    for (int g = threadIdx.x; g < nc / 4; g += kThreads) {
+        const int4 ag = sum_planes4(raw, splits, plane, base + 4 * g);
+        const int4 au = sum_planes4(raw, splits, plane, base + F + 4 * g);
+        const float4 wg = *reinterpret_cast<const float4*>(sw + c0 + 4 * g);
+        const float4 wu = *reinterpret_cast<const float4*>(sw + F + c0 + 4 * g);
+        float4 o;
+        o.x = __fmul_rn(silu(fmaf(static_cast<float>(ag.x), sa * wg.x, 0.0f)), fmaf(static_cast<float>(au.x), sa * wu.x, 0.0f));
+        o.y = __fmul_rn(silu(fmaf(static_cast<float>(ag.y), sa * wg.y, 0.0f)), fmaf(static_cast<float>(au.y), sa * wu.y, 0.0f));
+        o.z = __fmul_rn(silu(fmaf(static_cast<float>(ag.z), sa * wg.z, 0.0f)), fmaf(static_cast<float>(au.z), sa * wu.z, 0.0f));
+        o.w = __fmul_rn(silu(fmaf(static_cast<float>(ag.w), sa * wg.w, 0.0f)), fmaf(static_cast<float>(au.w), sa * wu.w, 0.0f));
+        *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = o;
+    }
+    __syncthreads();
+    quant_chunk(cl, sh, c0, nc, xq + static_cast<size_t>(m) * F, sx_out + m);
+}
+
+// Per-token int8 quantisation of an f32 matrix row (the attention output before the O projection).
+__global__ void __launch_bounds__(kThreads)
+quant_rows_cl_kernel(const float* __restrict__ x, int n, int nc, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+    __shared__ RowShared sh;
+    cg::cluster_group cl = cg::this_cluster();
+    const int m = blockIdx.y, c0 = blockIdx.x * nc;
+    const float* src = x + static_cast<size_t>(m) * n + c0;
+    for (int g = threadIdx.x; g < nc / 4; g += kThreads)
+        *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = *reinterpret_cast<const float4*>(src + 4 * g);
+    __syncthreads();
+    quant_chunk(cl, sh, c0, nc, xq + static_cast<size_t>(m) * n, sx_out + m);
+}
+
+// First index of the row maximum; chunk = columns per CTA (a multiple of 4).
+__global__ void __launch_bounds__(kThreads)
+argmax_cl_kernel(const float* __restrict__ logits, int vocab, int chunk, int* __restrict__ out_ids) {
+    __shared__ RowShared sh;
+    __shared__ float part_v;
+    __shared__ int part_i;
+    cg::cluster_group cl = cg::this_cluster();
+    const int m = blockIdx.y;
+    const int c0 = blockIdx.x * chunk;
+    int c1 = c0 + chunk;
+    if (c1 > vocab) c1 = vocab;
+    const float* row = logits + static_cast<size_t>(m) * vocab;
+    float best = -INFINITY;
+    int bi = 0x7FFFFFFF;
+    auto better = [](float v, int i, float bv, int bidx) { return v > bv || (v == bv && i < bidx); };
+    for (int i = c0 + 4 * threadIdx.x; i < c1; i += 4 * kThreads) {     // vocab % 4 == 0 (checked on the host)
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        if (v.x > best) { best = v.x; bi = i; }
+        if (v.y > best) { best = v.y; bi = i + 1; }
+        if (v.z > best) { best = v.z; bi = i + 2; }
+        if (v.w > best) { best = v.w; bi = i + 3; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sh.warp_f[warp] = best; sh.warp_i[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kThreads / 32; ++w)
+            if (better(sh.warp_f[w], sh.warp_i[w], best, bi)) { best = sh.warp_f[w]; bi = sh.warp_i[w]; }
+        part_v = best;
+        part_i = bi;
+    }
+    cl.sync();
+    if (cl.block_rank() == 0 && threadIdx.x == 0) {
+        best = part_v; bi = part_i;
+        for (unsigned r = 1; r < cl.num_blocks(); ++r) {
+            const float ov = *cl.map_shared_rank(&part_v, r);
+            const int oi = *cl.map_shared_rank(&part_i, r);
+            if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+        }
+        out_ids[m] = bi == 0x7FFFFFFF ? 0 : bi;
+    }
+    cl.sync();
+}
+
+// Finishes the QKV GEMM: one CTA per (row, group of heads); no row-wide reduction is needed.
+// q and k heads are rotated (rotate-half pairs (i, i + dh/2)), v heads are only dequantised.
+__global__ void __launch_bounds__(kThreads)
+qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int hq, int hkv, int dh, int heads_per_cta,
+                           const float* __restrict__ sx_in, const float* __restrict__ sw,
+                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                           const uint32_t* __restrict__ positions, const uint32_t* __restrict__ block_tables,
+                           int max_blocks_per_seq, int block_size, int num_blocks, float* __restrict__ q_out,
+                           uint16_t* __restrict__ k_pool, uint16_t* __restrict__ v_pool, uint32_t* err) {
+    const int m = blockIdx.y;
+    const int n = (hq + 2 * hkv) * dh;
+    const int half = dh / 2;
+    const size_t plane = static_cast<size_t>(M) * n;
+    const float sa = sx_in[m];
+    const int pos = static_cast<int>(positions[m]);
+    bool ok = pos < max_pos;
+    uint32_t blk = 0;
+    if (ok) {
+        blk = block_tables[static_cast<size_t>(m) * max_blocks_per_seq + pos / block_size];
+        ok = blk < static_cast<uint32_t>(num_blocks);
+    }
+    if (!ok) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrAppendSlot));
+        return;
+    }
+    const float* cr = cos_t + static_cast<size_t>(pos) * half;
+    const float* sr = sin_t + static_cast<size_t>(pos) * half;
+    const size_t slot = static_cast<size_t>(blk) * block_size + pos % block_size;
+    const int ekv = hkv * dh;
+    const int head0 = blockIdx.x * heads_per_cta;
+    for (int t = threadIdx.x; t < heads_per_cta * half; t += kThreads) {
+        const int head = head0 + t / half, i = t % half;
+        if (head >= hq + 2 * hkv) break;
+        const size_t idx = static_cast<size_t>(m) * n + head * dh + i;
+        int a1 = 0, a2 = 0;
+        for (int s = 0; s < splits; ++s) {
+            a1 += raw[s * plane + idx];
+            a2 += raw[s * plane + idx + half];
+        }
+        const float x1 = fmaf(static_cast<float>(a1), sa * sw[head * dh + i], 0.0f);
+        const float x2 = fmaf(static_cast<float>(a2), sa * sw[head * dh + i + half], 0.0f);
+        if (head < hq + hkv) {
+            const float c = cr[i], s = sr[i];
+            const float o1 = fmaf(x1, c, -__fmul_rn(x2, s));
+            const float o2 = fmaf(x2, c, __fmul_rn(x1, s));
+            if (head < hq) {
+                q_out[(static_cast<size_t>(m) * hq + head) * dh + i] = o1;
+                q_out[(static_cast<size_t>(m) * hq + head) * dh + i + half] = o2;
+            } else {
+                const int kh = head - hq;
+                k_pool[slot * ekv + kh * dh + i] = static_cast<uint16_t>(f32_to_bf16_bits(o1));
+                k_pool[slot * ekv + kh * dh + i + half] = static_cast<uint16_t>(f32_to_bf16_bits(o2));
+            }
+        } else {
+            const int vh = head - hq - hkv;
+            v_pool[slot * ekv + vh * dh + i] = static_cast<uint16_t>(f32_to_bf16_bits(x1));
+            v_pool[slot * ekv + vh * dh + i + half] = static_cast<uint16_t>(f32_to_bf16_bits(x2));
+        }
+    }
+}
+
+// Largest power-of-two cluster size <= 8 whose chunks are multiples of 4 columns, fit the shared chunk and
+// keep every thread busy; 0 when the row cannot be chunked that way.
+int pick_cluster(int n) {
+    for (int cl = 8; cl >= 1; cl >>= 1) {
+        if (n % (cl * 4) != 0) continue;
+        const int nc = n / cl;
+        if (nc > kMaxChunk) continue;
+        if (cl > 1 && nc < kThreads * 2) continue;   // too little work per CTA: use fewer, larger chunks
+        return cl;
+    }
+    return 0;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_cluster(void (*kernel)(KArgs...), int cl, int rows, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cl, rows, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+}  // namespace
+
+// Dispatchers: the cluster kernel when the row width allows it, else the one-CTA-per-row kernel.
+cudaError_t embed_norm_quant_auto(const int* ids, const float* table, int vocab, int M, int d, const float* norm_w,
+                                  float eps, float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s) {
+    const int cl = pick_cluster(d);
+    if (cl == 0) return embed_norm_quant(ids, table, vocab, M, d, norm_w, eps, h, xq, sx, err, s);
+    return launch_cluster(embed_norm_quant_cl_kernel, cl, M, s, ids, table, vocab, d, d / cl, norm_w, eps, h, xq, sx, err);
+}
+
+cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, const float* sx_in, const float* sw,
+                                  const float* pre, const float* norm_w, float eps, float* h, int8_t* xq, float* sx_out,
+                                  cudaStream_t s) {
+    const int cl = pick_cluster(d);
+    if (cl == 0) return resid_norm_quant(raw, splits, M, d, sx_in, sw, pre, norm_w, eps, h, xq, sx_out, s);
+    return launch_cluster(resid_norm_quant_cl_kernel, cl, M, s, raw, splits, M, d, d / cl, sx_in, sw, pre, norm_w, eps, h,
+                          xq, sx_out);
+}
+
+cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
+                            float* sx_out, cudaStream_t s) {
+    const int cl = pick_cluster(F);
+    if (cl == 0) return gate_quant(raw, splits, M, F, sx_in, sw, xq, sx_out, s);
+    return launch_cluster(gate_quant_cl_kernel, cl, M, s, raw, splits, M, F, F / cl, sx_in, sw, xq, sx_out);
+}
+
+cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s) {
+    const int cl = pick_cluster(n);
+    if (cl == 0) return quantize_i8_per_row(x, M, n, xq, sx_out, s);
+    return launch_cluster(quant_rows_cl_kernel, cl, M, s, x, n, n / cl, xq, sx_out);
+}
+
+cudaError_t argmax_rows_auto(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s) {
+    if (vocab % 4 != 0 || vocab < 8 * 4 * kThreads) return argmax_rows(logits, M, vocab, out_ids, s);
+    const int cl = 8;
+    int chunk = (vocab + cl - 1) / cl;
+    chunk = (chunk + 3) / 4 * 4;
+    return launch_cluster(argmax_cl_kernel, cl, M, s, logits, vocab, chunk, out_ids);
+}
+
+cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int hkv, int dh, const float* sx_in,
+                                 const float* sw, const float* cos_t, const float* sin_t, int max_pos,
+                                 const uint32_t* positions, const uint32_t* block_tables, int max_blocks_per_seq,
+                                 int block_size, int num_blocks, float* q_out, uint16_t* k_pool, uint16_t* v_pool,
+                                 uint32_t* err, cudaStream_t s) {
+    const int heads = hq + 2 * hkv;
+    int hpc = (2 * kThreads) / (dh / 2);      // two rotary pairs per thread
+    if (hpc < 1) hpc = 1;
+    dim3 grid((heads + hpc - 1) / hpc, M);
+    qkv_rope_append_par_kernel<<<grid, kThreads, 0, s>>>(raw, splits, M, hq, hkv, dh, hpc, sx_in, sw, cos_t, sin_t, max_pos,
+                                                        positions, block_tables, max_blocks_per_seq, block_size, num_blocks,
+                                                        q_out, k_pool, v_pool, err);
+    return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -427,21 +427,21 @@ int32_t enqueue_step(b200_decoder* d) {
     ep.raw = d->raw;
     CU_TRY(begin_step(d->seq_lens_dev, d->pos_dev, M, s));
     ++launches;
-    CU_TRY(embed_norm_quant(d->ids_dev, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, d->h,
+    CU_TRY(embed_norm_quant_auto(d->ids_dev, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, d->h,
                             d->xq, d->sx, err, s));
     ++launches;
     for (int l = 0; l < c.n_layers; ++l) {
         LayerParams& L = d->layers[l];
         // QKV projection -> RoPE -> append to the paged cache
         CU_TRY(gemm_launch(L.p_qkv, ep, err, s));
-        CU_TRY(qkv_rope_append(d->raw, L.p_qkv.splits, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv, d->cos_t,
+        CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.splits, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv, d->cos_t,
                                d->sin_t, c.max_seq_len, d->pos_dev, d->tables_dev, d->max_blocks_per_seq,
                                c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
                                static_cast<uint16_t*>(L.v_pool), err, s));
         // attention over the cache (this rank's KV heads), then per-token quantisation
         CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
                                       d->attn_scratch, err, s));
-        CU_TRY(quantize_i8_per_row(d->attn_out, M, int64_t(d->hq_l) * dh, d->xq, d->sx, s));
+        CU_TRY(quantize_rows_auto(d->attn_out, M, d->hq_l * dh, d->xq, d->sx, s));
         // O projection (row-parallel) -> residual -> norm -> quant
         CU_TRY(gemm_launch(L.p_o, ep, err, s));
         launches += 6;
@@ -450,11 +450,11 @@ int32_t enqueue_step(b200_decoder* d) {
             if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
             launches += 2;
         }
-        CU_TRY(resid_norm_quant(d->raw, L.p_o.splits, M, dm, d->sx, d->scales + L.s_o, tp ? d->part : nullptr,
+        CU_TRY(resid_norm_quant_auto(d->raw, L.p_o.splits, M, dm, d->sx, d->scales + L.s_o, tp ? d->part : nullptr,
                                 d->vectors + L.mlp_norm, c.rms_eps, d->h, d->xq, d->sx, s));
         // gate / up (column-parallel) -> SiLU gate -> quant
         CU_TRY(gemm_launch(L.p_gu, ep, err, s));
-        CU_TRY(gate_quant(d->raw, L.p_gu.splits, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
+        CU_TRY(gate_quant_auto(d->raw, L.p_gu.splits, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
         // down (row-parallel) -> residual -> next norm -> quant
         CU_TRY(gemm_launch(L.p_down, ep, err, s));
         launches += 4;
@@ -464,7 +464,7 @@ int32_t enqueue_step(b200_decoder* d) {
             launches += 2;
         }
         const float* next_norm = d->vectors + (l + 1 < c.n_layers ? d->layers[l + 1].attn_norm : d->final_norm);
-        CU_TRY(resid_norm_quant(d->raw, L.p_down.splits, M, dm, d->sx, d->scales + L.s_down, tp ? d->part : nullptr,
+        CU_TRY(resid_norm_quant_auto(d->raw, L.p_down.splits, M, dm, d->sx, d->scales + L.s_down, tp ? d->part : nullptr,
                                 next_norm, c.rms_eps, d->h, d->xq, d->sx, s));
         ++launches;
     }
@@ -477,7 +477,7 @@ int32_t enqueue_step(b200_decoder* d) {
     lm.b_per_col = 1;
     lm.out = d->logits;
     CU_TRY(gemm_launch(d->p_lm, lm, err, s));
-    CU_TRY(argmax_rows(d->logits, M, c.vocab, d->next_ids_dev, s));
+    CU_TRY(argmax_rows_auto(d->logits, M, c.vocab, d->next_ids_dev, s));
     launches += 2;
     d->launches_per_step = launches;
     return B200_OK;
