@@ -35,6 +35,10 @@ CONFIGS = {
     # capture (about 1 GB of weights, 0.3 GB of KV per layer, both above the L2 size)
     "mid": dict(n_layers=4, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128, d_ff=14336, vocab=32000, batch=64,
                 prompt_lo=256, prompt_hi=2048),
+    # one KV head per GPU (what each rank of an 8-way tensor-parallel run sees): token rows of the pools are
+    # 256 bytes, so every KV block is one contiguous 4 KB piece; same KV bytes per layer as llama8b
+    "kv1": dict(n_layers=2, d_model=512, n_heads=4, n_kv_heads=1, head_dim=128, d_ff=1024, vocab=2048, batch=1024,
+                prompt_lo=256, prompt_hi=2048),
     # a small shape for quick functional runs of this script
     "tiny": dict(n_layers=2, d_model=512, n_heads=8, n_kv_heads=8, head_dim=128, d_ff=1024, vocab=2048, batch=16,
                  prompt_lo=32, prompt_hi=128),
@@ -258,6 +262,12 @@ def run_gpu(args, cfg, rank, world, local_rank):
     dec.init_random(seed=0, std=0.02)
     dec.fill_cache_random(seed=1, std=1.0)
     batch = cfg["batch"]
+    if args.attn_chunk_blocks:
+        from fandhe_ai_b200 import paged_kv as _pk
+
+        _pk.paged_attention_tuning(be, args.attn_chunk_blocks)
+    if args.gemm_splits or args.gemm_tile:
+        be.gemm_tuning(args.gemm_tile, args.gemm_splits)
     dec.begin(batch, (lens + total_steps).tolist(), start_lens=lens.tolist())
     ids = np.random.default_rng(3).integers(0, cfg["vocab"], batch).astype(np.int32)
     nxt = np.empty(batch, np.int32)
@@ -346,6 +356,9 @@ def main():
     ap.add_argument("--cpu-layers", type=int, default=2, help="full-size layers in the CPU sample")
     ap.add_argument("--cpu-vocab", type=int, default=8016, help="lm_head rows in the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--attn-chunk-blocks", type=int, default=0, help="KV blocks per attention split (0: default)")
+    ap.add_argument("--gemm-splits", type=int, default=0, help="force the split-K count of the layer GEMMs (0: heuristic)")
+    ap.add_argument("--gemm-tile", type=int, default=0, help="force the GEMM tile width (0: heuristic)")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     rank = int(os.environ.get("RANK", "0"))

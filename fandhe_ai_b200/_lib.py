@@ -135,6 +135,8 @@ SIGNATURES = {
     "b200_decoder_step": (_I32, [_P, _P, _P]),
     "b200_decoder_logits": (_I32, [_P, _P, _U64]),
     "b200_decoder_generate": (_I32, [_P, _P, _I32, _I32, _I32, _P]),
+    "b200_decoder_shard_plan": (_I32, [C.POINTER(DecoderConfigC), _I32, C.POINTER(_I64), C.POINTER(_I64), _P,
+                                       C.POINTER(_I32), C.POINTER(_I64), C.POINTER(_I64)]),
     "b200_decoder_launches_per_step": (_U64, [_P]),
     "b200_decoder_weight_bytes": (_U64, [_P]),
     "b200_decoder_plan_info": (_I32, [_P, _P]),

@@ -213,7 +213,7 @@ int32_t b200_validate_paged_attention(uint64_t q_numel, uint64_t k_pool_numel, u
 
 int32_t b200_paged_attention_tuning(b200_ctx* ctx, int32_t chunk_blocks) {
     if (!ctx) return fail(B200_INVALID_ARGUMENT, "paged_attention_tuning: context is null");
-    if (chunk_blocks < 0 || chunk_blocks > 32) return fail(B200_INVALID_ARGUMENT, "paged_attention_tuning: chunk_blocks must be in 0..32");
+    if (chunk_blocks < 0 || chunk_blocks > 256) return fail(B200_INVALID_ARGUMENT, "paged_attention_tuning: chunk_blocks must be in 0..256");
     ctx->tune_attn_chunk_blocks = chunk_blocks;
     return B200_OK;
 }

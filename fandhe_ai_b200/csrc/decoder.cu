@@ -378,35 +378,51 @@ struct TensorShape {
     size_t payload_off, scale_off;
 };
 
-bool tensor_shape(const b200_decoder* d, int which, int layer, TensorShape* t) {
-    const auto& c = d->cfg;
+// Which rows and columns of a full weight matrix rank `tp_rank` keeps (pure host arithmetic):
+// column-parallel matrices (QKV, gate/up) keep row ranges, row-parallel ones (O, down) keep a column range.
+bool shard_of(const b200_decoder_config& c, int which, TensorShape* t) {
     const int tp = c.tp_size, r = c.tp_rank;
     const int64_t dh = c.head_dim, dm = c.d_model;
-    if (which == B200_W_LM_HEAD) {
-        *t = {c.vocab, dm, {{0, c.vocab}}, 0, dm, d->w_lm, d->s_lm};
-        return true;
-    }
-    if (layer < 0 || layer >= c.n_layers) return false;
-    const LayerParams& L = d->layers[layer];
     const int64_t hq = c.n_heads, hkv = c.n_kv_heads, F = c.d_ff;
     switch (which) {
+        case B200_W_LM_HEAD:
+            *t = {c.vocab, dm, {{0, c.vocab}}, 0, dm, 0, 0};
+            return true;
         case B200_W_QKV:
             *t = {(hq + 2 * hkv) * dh, dm,
                   {{r * (hq / tp) * dh, (hq / tp) * dh}, {hq * dh + r * (hkv / tp) * dh, (hkv / tp) * dh},
                    {(hq + hkv) * dh + r * (hkv / tp) * dh, (hkv / tp) * dh}},
-                  0, dm, L.wqkv, L.s_qkv};
+                  0, dm, 0, 0};
             return true;
         case B200_W_O:
-            *t = {dm, hq * dh, {{0, dm}}, r * (hq / tp) * dh, (hq / tp) * dh, L.wo, L.s_o};
+            *t = {dm, hq * dh, {{0, dm}}, r * (hq / tp) * dh, (hq / tp) * dh, 0, 0};
             return true;
         case B200_W_GATE_UP:
-            *t = {2 * F, dm, {{r * (F / tp), F / tp}, {F + r * (F / tp), F / tp}}, 0, dm, L.wgu, L.s_gu};
+            *t = {2 * F, dm, {{r * (F / tp), F / tp}, {F + r * (F / tp), F / tp}}, 0, dm, 0, 0};
             return true;
         case B200_W_DOWN:
-            *t = {dm, F, {{0, dm}}, r * (F / tp), F / tp, L.wdown, L.s_down};
+            *t = {dm, F, {{0, dm}}, r * (F / tp), F / tp, 0, 0};
             return true;
         default: return false;
     }
+}
+
+bool tensor_shape(const b200_decoder* d, int which, int layer, TensorShape* t) {
+    if (!shard_of(d->cfg, which, t)) return false;
+    if (which == B200_W_LM_HEAD) {
+        t->payload_off = d->w_lm;
+        t->scale_off = d->s_lm;
+        return true;
+    }
+    if (layer < 0 || layer >= d->cfg.n_layers) return false;
+    const LayerParams& L = d->layers[layer];
+    switch (which) {
+        case B200_W_QKV: t->payload_off = L.wqkv; t->scale_off = L.s_qkv; break;
+        case B200_W_O: t->payload_off = L.wo; t->scale_off = L.s_o; break;
+        case B200_W_GATE_UP: t->payload_off = L.wgu; t->scale_off = L.s_gu; break;
+        default: t->payload_off = L.wdown; t->scale_off = L.s_down; break;
+    }
+    return true;
 }
 
 int32_t all_reduce_sum_f32(b200_decoder* d, float* buf, size_t n) {
@@ -894,6 +910,27 @@ int32_t b200_decoder_generate(b200_decoder* d, const int32_t* prompt, int32_t ba
         if (need_out)
             for (int b = 0; b < batch; ++b) out[size_t(b) * max_length + t + 1] = next[b];
     }
+    return B200_OK;
+}
+
+// Tensor-parallel shard of one weight matrix, without a device: validates the configuration and reports
+// the full shape, up to three kept row ranges (start, count pairs) and the kept column range.
+int32_t b200_decoder_shard_plan(const b200_decoder_config* cfg, int32_t which, int64_t* rows, int64_t* cols,
+                                int64_t* row_ranges6, int32_t* n_ranges, int64_t* col_start, int64_t* col_count) {
+    if (!cfg || !rows || !cols || !row_ranges6 || !n_ranges || !col_start || !col_count)
+        return fail(B200_INVALID_ARGUMENT, "decoder_shard_plan: null pointer");
+    if (int32_t st = check_config(*cfg)) return st;
+    TensorShape t;
+    if (!shard_of(*cfg, which, &t)) return fail(B200_INVALID_ARGUMENT, "decoder_shard_plan: not a sharded matrix");
+    *rows = t.rows;
+    *cols = t.cols;
+    *n_ranges = int32_t(t.row_ranges.size());
+    for (size_t i = 0; i < t.row_ranges.size() && i < 3; ++i) {
+        row_ranges6[2 * i] = t.row_ranges[i].first;
+        row_ranges6[2 * i + 1] = t.row_ranges[i].second;
+    }
+    *col_start = t.c0;
+    *col_count = t.ccount;
     return B200_OK;
 }
 

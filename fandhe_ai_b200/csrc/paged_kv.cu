@@ -178,226 +178,14 @@ paged_attention_generic_kernel(const float* __restrict__ q, const KvT* __restric
 constexpr int kD = 128;
 constexpr int kBS = 16;                 // tokens per block = tokens per tile
 constexpr int kTileBytes = kBS * kD * 2;  // 4096
-constexpr int kStages = 8;
 constexpr int kConsumerWarps = 4;
+constexpr int kStagesPerWarp = 3;       // K, V and the next K of one warp's blocks in flight
+constexpr int kStages = kConsumerWarps * kStagesPerWarp;
 constexpr int kFastThreads = 32 * (kConsumerWarps + 1);
-constexpr int kMaxChunkBlocks = 32;     // producer lanes prefetch one block id each
+constexpr int kMaxChunkBlocks = 256;    // upper bound of blocks per split (tuning range)
+constexpr int kDefaultChunkBlocks = 32;
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-template <int G>
-__global__ void __launch_bounds__(kFastThreads)
-paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
-                              const float* __restrict__ q, const uint32_t* __restrict__ block_tables,
-                              const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_blocks,
-                              int max_chunks, float* __restrict__ part_o, float* __restrict__ part_ml, uint32_t* err) {
-    extern __shared__ uint8_t smem_dyn[];
-    const uint32_t ring = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-    uint8_t* ring_ptr = smem_dyn + (ring - smem_u32(smem_dyn));
-    const int chunk_tokens = chunk_blocks * kBS;
-    float* scores = reinterpret_cast<float*>(ring_ptr + kStages * kTileBytes);            // [chunk_tokens][G]
-    float* red = scores + kMaxChunkBlocks * kBS * G;                                      // [4][G][128]
-    float* stat = red + kConsumerWarps * G * kD;                                          // [4][G] scratch, then m[G], l[G]
-    const uint32_t bars = smem_u32(stat + 8 * G + 8);
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
-
-    const int chunk = blockIdx.x;
-    const int kv_slot = blockIdx.y;                 // kv head (times sub-group when the group is wider than G)
-    const int row = blockIdx.z;                     // b * l_new + i
-    const int b = row / sh.l_new, i = row % sh.l_new;
-    const int group = sh.num_q_heads / sh.num_kv_heads;
-    const int subs = group / G;                     // 1, or 2 when 8 q heads share a kv head and G = 4
-    const int kvh = kv_slot / subs;
-    const int h0 = kvh * group + (kv_slot % subs) * G;   // first q head of this CTA
-    const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
-    const int tok0 = chunk * chunk_tokens;
-    if (tok0 >= limit) return;                      // whole CTA leaves together, nothing allocated yet
-    int ntok = limit - tok0;
-    if (ntok > chunk_tokens) ntok = chunk_tokens;
-    const int nb = (ntok + kBS - 1) / kBS;          // tiles of K, and as many of V
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
-        }
-        fence_barrier_init();
-    }
-    __syncthreads();
-
-    if (warp == kConsumerWarps) {
-        // ---------------- producer warp: block ids are fetched by the lanes in one go, lane 0 issues TMA
-        if (lane == 0) { tma_prefetch_desc(&tma_k); tma_prefetch_desc(&tma_v); }
-        uint32_t my_blk = 0;
-        if (lane < nb) {
-            my_blk = block_tables[int64_t(b) * sh.max_blocks_per_seq + chunk * chunk_blocks + lane];
-            if (my_blk >= uint32_t(sh.num_blocks)) {
-                atomicCAS(err, 0u, static_cast<uint32_t>(kErrAttnBlockId));
-                my_blk = 0;
-            }
-        }
-        bool ok = true;
-        for (int t = 0; t < 2 * nb; ++t) {
-            const int s = t % kStages;
-            const uint32_t ph = (t / kStages) & 1;
-            const uint32_t blk = __shfl_sync(0xffffffffu, my_blk, t < nb ? t : t - nb);
-            if (lane == 0 && ok) {
-                ok = mbar_wait(empty_bar(s), ph ^ 1u, err, kErrProducerWait);
-                if (ok) {
-                    mbar_arrive_expect_tx(full_bar(s), kTileBytes);
-                    tma_load_2d(ring + s * kTileBytes, t < nb ? &tma_k : &tma_v, full_bar(s), kvh * kD,
-                                int(blk) * kBS);
-                }
-            }
-        }
-        return;
-    }
-
-    // ---------------- consumers
-    // Phase 1: scores.  Lane = (token-in-step t4 = lane >> 3, slice sl = lane & 7); a lane owns the two
-    // 16-byte pieces sl and sl + 8 of a 256-byte K row, i.e. dims [8 sl, 8 sl + 8) and [64 + 8 sl, 64 + 8 sl + 8).
-    const int t4 = lane >> 3, sl = lane & 7;
-    float qr[G][16];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const float* qp = q + (int64_t(row) * sh.num_q_heads + h0 + g) * kD;
-#pragma unroll
-        for (int d = 0; d < 8; ++d) {
-            qr[g][d] = qp[8 * sl + d] * sh.scale;
-            qr[g][8 + d] = qp[64 + 8 * sl + d] * sh.scale;
-        }
-    }
-    bool ok = true;
-    for (int kt = warp; kt < nb; kt += kConsumerWarps) {
-        const int s = kt % kStages;
-        const uint32_t ph = (kt / kStages) & 1;
-        ok = ok && mbar_wait(full_bar(s), ph, err, kErrAttnLoadWait);
-        const uint8_t* tile = ring_ptr + s * kTileBytes;
-#pragma unroll
-        for (int step = 0; step < 4; ++step) {
-            const int tok = step * 4 + t4;                      // token inside the tile
-            const uint4 lo = *reinterpret_cast<const uint4*>(tile + tok * 256 + sl * 16);
-            const uint4 hi = *reinterpret_cast<const uint4*>(tile + tok * 256 + 128 + sl * 16);
-            float kf[16];
-            kf[0] = bf16_bits_to_f32(lo.x & 0xFFFFu); kf[1] = __uint_as_float(lo.x & 0xFFFF0000u);
-            kf[2] = bf16_bits_to_f32(lo.y & 0xFFFFu); kf[3] = __uint_as_float(lo.y & 0xFFFF0000u);
-            kf[4] = bf16_bits_to_f32(lo.z & 0xFFFFu); kf[5] = __uint_as_float(lo.z & 0xFFFF0000u);
-            kf[6] = bf16_bits_to_f32(lo.w & 0xFFFFu); kf[7] = __uint_as_float(lo.w & 0xFFFF0000u);
-            kf[8] = bf16_bits_to_f32(hi.x & 0xFFFFu); kf[9] = __uint_as_float(hi.x & 0xFFFF0000u);
-            kf[10] = bf16_bits_to_f32(hi.y & 0xFFFFu); kf[11] = __uint_as_float(hi.y & 0xFFFF0000u);
-            kf[12] = bf16_bits_to_f32(hi.z & 0xFFFFu); kf[13] = __uint_as_float(hi.z & 0xFFFF0000u);
-            kf[14] = bf16_bits_to_f32(hi.w & 0xFFFFu); kf[15] = __uint_as_float(hi.w & 0xFFFF0000u);
-            float sc[G];
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float a = 0.0f;
-#pragma unroll
-                for (int d = 0; d < 16; ++d) a = fmaf(qr[g][d], kf[d], a);
-                a += __shfl_xor_sync(0xffffffffu, a, 1);
-                a += __shfl_xor_sync(0xffffffffu, a, 2);
-                a += __shfl_xor_sync(0xffffffffu, a, 4);
-                sc[g] = a;
-            }
-            if (sl == 0) {
-                const int ct = kt * kBS + tok;                  // token inside the chunk
-                const bool valid = ct < ntok;
-#pragma unroll
-                for (int g = 0; g < G; ++g) scores[ct * G + g] = valid ? sc[g] : -INFINITY;
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(s));
-    }
-    consumer_sync();
-
-    // chunk max and sum of exp per head (128 consumer threads stride the tokens)
-    const int ctid = threadIdx.x;                    // 0..127
-    const int ntile_tok = nb * kBS;
-    float mx[G], sm[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) mx[g] = -INFINITY;
-    for (int t = ctid; t < ntile_tok; t += 128)
-#pragma unroll
-        for (int g = 0; g < G; ++g) mx[g] = fmaxf(mx[g], scores[t * G + g]);
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
-        if (lane == 0) stat[warp * G + g] = mx[g];
-    }
-    consumer_sync();
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-        mx[g] = fmaxf(fmaxf(stat[g], stat[G + g]), fmaxf(stat[2 * G + g], stat[3 * G + g]));
-    consumer_sync();
-#pragma unroll
-    for (int g = 0; g < G; ++g) sm[g] = 0.0f;
-    for (int t = ctid; t < ntile_tok; t += 128)
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float p = expf(scores[t * G + g] - mx[g]);   // masked tokens: exp(-inf) = 0
-            scores[t * G + g] = p;
-            sm[g] += p;
-        }
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sm[g] += __shfl_xor_sync(0xffffffffu, sm[g], o);
-        if (lane == 0) stat[warp * G + g] = sm[g];
-    }
-    consumer_sync();
-#pragma unroll
-    for (int g = 0; g < G; ++g) sm[g] = (stat[g] + stat[G + g]) + (stat[2 * G + g] + stat[3 * G + g]);
-
-    // Phase 2: weighted sum of V.  Lane owns dims [4 lane, 4 lane + 4).
-    float acc[G][4];
-#pragma unroll
-    for (int g = 0; g < G; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
-    for (int vt = warp; vt < nb; vt += kConsumerWarps) {
-        const int t = nb + vt;
-        const int s = t % kStages;
-        const uint32_t ph = (t / kStages) & 1;
-        ok = ok && mbar_wait(full_bar(s), ph, err, kErrAttnLoadWait);
-        const uint8_t* tile = ring_ptr + s * kTileBytes;
-        int valid = ntok - vt * kBS;
-        if (valid > kBS) valid = kBS;
-        for (int tok = 0; tok < valid; ++tok) {      // rows past the sequence end may hold anything: never read them
-            const uint2 vv = *reinterpret_cast<const uint2*>(tile + tok * 256 + lane * 8);
-            const float v0 = bf16_bits_to_f32(vv.x & 0xFFFFu), v1 = __uint_as_float(vv.x & 0xFFFF0000u);
-            const float v2 = bf16_bits_to_f32(vv.y & 0xFFFFu), v3 = __uint_as_float(vv.y & 0xFFFF0000u);
-            const float* pr = scores + (vt * kBS + tok) * G;
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float p = pr[g];
-                acc[g][0] = fmaf(p, v0, acc[g][0]);
-                acc[g][1] = fmaf(p, v1, acc[g][1]);
-                acc[g][2] = fmaf(p, v2, acc[g][2]);
-                acc[g][3] = fmaf(p, v3, acc[g][3]);
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(s));
-    }
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-        *reinterpret_cast<float4*>(red + (warp * G + g) * kD + lane * 4) =
-            make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-    consumer_sync();
-    // partial of this chunk: unnormalised sum relative to the chunk max, plus (max, sum)
-    for (int idx = ctid; idx < G * kD; idx += 128) {
-        const int g = idx / kD, d = idx % kD;
-        const float o = (red[(0 * G + g) * kD + d] + red[(1 * G + g) * kD + d]) +
-                        (red[(2 * G + g) * kD + d] + red[(3 * G + g) * kD + d]);
-        part_o[((int64_t(row) * sh.num_q_heads + h0 + g) * max_chunks + chunk) * kD + d] = ok ? o : __int_as_float(0x7FC00000);
-    }
-    if (ctid < G) {
-        float* ml = part_ml + ((int64_t(row) * sh.num_q_heads + h0 + ctid) * max_chunks + chunk) * 2;
-        ml[0] = mx[ctid];
-        ml[1] = sm[ctid];
-    }
-}
+#include "paged_attn_mma.cuh"
 
 // Merges the chunk partials of one (query row, q head): one warp each, lanes own 4 dims.
 __global__ void __launch_bounds__(128)
@@ -442,28 +230,29 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [pool_rows, E_kv] bf16, box = one block of one kv head: [16 rows, 128 elements]
+// [pool_rows, E_kv] bf16, box = half a block row set of one kv head: [16 rows, 64 elements] = 128-byte rows,
+// written with the 128-byte swizzle
 bool make_pool_map(CUtensorMap* map, const void* pool, int64_t pool_rows, int64_t ekv) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(ekv), static_cast<cuuint64_t>(pool_rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(ekv) * 2};
-    cuuint32_t box[2] = {kD, kBS};
+    cuuint32_t box[2] = {kD / 2, kBS};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int fast_smem_bytes(int g) {
-    return 1024 + kStages * kTileBytes + (kMaxChunkBlocks * kBS * g + kConsumerWarps * g * kD + 8 * g + 8) * 4 +
-           2 * kStages * 8 + 16;
+int fast_smem_bytes(int /*g*/) {
+    // alignment slack + ring + per-warp outputs [4][4][128] + per-warp (max, sum) [2][16] + mbarriers
+    return 1024 + kStages * kTileBytes + (kConsumerWarps * 4 * kD + 32) * 4 + 2 * kStages * 8 + 16;
 }
 
 template <int G>
 cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_t* tables, const uint32_t* seq_lens,
                         float* part_o, float* part_ml, uint32_t* err, cudaStream_t stream) {
-    const int smem = fast_smem_bytes(G);
+    const int smem = fast_smem_bytes(4);   // the kernel lays out four head rows whatever G is
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -472,7 +261,7 @@ cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_
     }
     const PagedAttnShape& sh = plan.shape;
     const int group = sh.num_q_heads / sh.num_kv_heads;
-    dim3 grid(plan.max_chunks, sh.num_kv_heads * (group / G), sh.batch * sh.l_new);
+    dim3 grid(sh.num_kv_heads * (group / G), plan.max_chunks, sh.batch * sh.l_new);
     paged_attention_decode_kernel<G><<<grid, kFastThreads, smem, stream>>>(
         plan.tma_k, plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml, err);
     return cudaGetLastError();
@@ -526,7 +315,7 @@ cudaError_t paged_attention_make_plan(PagedAttnPlan* plan, const PagedAttnShape&
     plan->chunk_blocks = 0;
     plan->max_chunks = 0;
     if (!plan->fast) return cudaSuccess;
-    int cb = want_chunk_blocks > 0 ? want_chunk_blocks : 16;
+    int cb = want_chunk_blocks > 0 ? want_chunk_blocks : kDefaultChunkBlocks;
     if (cb > kMaxChunkBlocks) cb = kMaxChunkBlocks;
     plan->chunk_blocks = cb;
     const int chunk_tokens = cb * kBS;

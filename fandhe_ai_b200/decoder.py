@@ -92,6 +92,18 @@ class DecoderConfig:
                               self.block_size, nb, self.tp_rank, self.tp_size, self.use_graph)
 
 
+def shard_plan(cfg: DecoderConfig, which: int) -> dict:
+    """Rows and columns of full weight matrix `which` that rank cfg.tp_rank keeps (host arithmetic only)."""
+    cc = cfg.to_c()
+    rows, cols, c0, cn = C.c_int64(), C.c_int64(), C.c_int64(), C.c_int64()
+    n = C.c_int32()
+    rr = (C.c_int64 * 6)()
+    check(lib().b200_decoder_shard_plan(C.byref(cc), which, C.byref(rows), C.byref(cols), rr, C.byref(n), C.byref(c0),
+                                        C.byref(cn)))
+    return {"rows": rows.value, "cols": cols.value, "col_start": c0.value, "col_count": cn.value,
+            "row_ranges": [(rr[2 * i], rr[2 * i + 1]) for i in range(n.value)]}
+
+
 def nccl_unique_id() -> bytes:
     buf = (C.c_uint8 * 128)()
     check(lib().b200_nccl_unique_id(buf))

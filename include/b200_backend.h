@@ -322,6 +322,11 @@ int32_t b200_decoder_logits(b200_decoder* dec, float* host, uint64_t capacity_el
 /* generate() with greedy sampling: out is [batch, max_length] and begins with the prompt. */
 int32_t b200_decoder_generate(b200_decoder* dec, const int32_t* prompt, int32_t batch, int32_t prompt_len,
                               int32_t max_length, int32_t* out);
+/* Tensor-parallel shard arithmetic, pure host (no device needed): for rank cfg->tp_rank of cfg->tp_size,
+ * the full shape of matrix `which`, the row ranges it keeps as (start, count) pairs (up to three: q / k / v
+ * heads, or gate / up halves) and the column range it keeps (row-parallel O and down projections). */
+int32_t b200_decoder_shard_plan(const b200_decoder_config* cfg, int32_t which, int64_t* rows, int64_t* cols,
+                                int64_t* row_ranges6, int32_t* n_ranges, int64_t* col_start, int64_t* col_count);
 uint64_t b200_decoder_launches_per_step(const b200_decoder* dec);
 uint64_t b200_decoder_weight_bytes(const b200_decoder* dec);
 int32_t b200_decoder_plan_info(const b200_decoder* dec, int32_t* out10);

@@ -105,6 +105,7 @@ def test_reference_shape_matrix_bf16_pools(be, case):
 @pytest.mark.parametrize("heads,kv_heads,batch,steps", [
     (4, 1, 2, [15, 1, 1]), (4, 1, 2, [16, 1, 1]), (4, 1, 2, [17, 1, 1]),
     (8, 2, 3, [255, 1, 1]), (8, 2, 3, [256, 1]), (8, 2, 3, [257, 1]),     # the split boundary (256 tokens) +- 1
+    (4, 1, 2, [511, 1, 1, 1]), (8, 2, 1, [1030, 1]),                       # the default split boundary (512 tokens)
     (32, 8, 2, [700, 1, 1]), (2, 2, 2, [300, 1]), (4, 2, 2, [300, 1]), (8, 1, 1, [530, 1]),
     (4, 1, 2, [40, 3, 2]),                                                  # l_new > 1 with cached tokens
 ])

@@ -65,7 +65,7 @@ def test_noalloc_entry_matches_the_allocating_entry_on_two_calls_in_a_row(be):
 def test_noalloc_entry_refuses_sizes_beyond_its_static_scratch(be):
     # 64 rows x 32 heads x 32 splits x 520 bytes = 34 MB > 32 MiB: refused before any launch
     batch, heads, kv_heads, dh, bs = 64, 32, 8, 128, 16
-    mbps = 512
+    mbps = 1024
     nblk = 64
     layout = P.PagedKvLayout(nblk, bs, kv_heads * dh, BF16)
     args = P.PagedAttentionArgs(layout, batch, 1, heads, mbps, 0.1, kv_heads)
@@ -75,7 +75,7 @@ def test_noalloc_entry_refuses_sizes_beyond_its_static_scratch(be):
     tables = be.upload(np.zeros((batch, mbps), np.uint32))
     lens = be.upload(np.full(batch, 16, np.uint32))
     with pytest.raises(BackendError) as e:
-        P.paged_attention_forward_noalloc(be, q, pool, pool, tables, lens, 8192, args, out)
+        P.paged_attention_forward_noalloc(be, q, pool, pool, tables, lens, 16384, args, out)
     assert e.value.kind == "Unsupported" and "static scratch" in e.value.message
     assert not be.poisoned
     # the same shape with a smaller bound on the sequence length fits (8 splits) and runs
