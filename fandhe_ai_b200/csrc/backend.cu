@@ -5,11 +5,13 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
 #include "gemm_tc5.cuh"
 #include "kernels.cuh"
+#include "launch.cuh"
 
 namespace b200 {
 
@@ -17,6 +19,14 @@ namespace {
 thread_local std::string g_last_error;
 std::atomic<uint64_t> g_generation{0};
 }  // namespace
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
 
 int32_t fail(int32_t st, const std::string& msg) {
     g_last_error = msg;

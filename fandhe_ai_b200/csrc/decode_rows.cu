@@ -9,6 +9,7 @@
 #include <cooperative_groups.h>
 
 #include "kernels.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace cg = cooperative_groups;
@@ -148,6 +149,8 @@ embed_norm_quant_cl_kernel(const int* __restrict__ ids, const float* __restrict_
                            float* __restrict__ sx, uint32_t* err) {
     __shared__ RowShared sh;
     cg::cluster_group cl = cg::this_cluster();
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y, c0 = blockIdx.x * nc;
     int id = ids[m];
     if (id < 0 || id >= vocab) {
@@ -172,6 +175,8 @@ resid_norm_quant_cl_kernel(const int* __restrict__ raw, int splits, int M, int d
                            float* __restrict__ sx_out) {
     __shared__ RowShared sh;
     cg::cluster_group cl = cg::this_cluster();
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y, c0 = blockIdx.x * nc;
     const size_t plane = static_cast<size_t>(M) * d;
     const size_t base = static_cast<size_t>(m) * d + c0;
@@ -202,6 +207,8 @@ gate_quant_cl_kernel(const int* __restrict__ raw, int splits, int M, int F, int 
                      const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
     __shared__ RowShared sh;
     cg::cluster_group cl = cg::this_cluster();
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y, c0 = blockIdx.x * nc;
     const size_t plane = static_cast<size_t>(M) * 2 * F;
     const size_t base = static_cast<size_t>(m) * 2 * F + c0;
@@ -227,6 +234,8 @@ __global__ void __launch_bounds__(kThreads)
 quant_rows_cl_kernel(const float* __restrict__ x, int n, int nc, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
     __shared__ RowShared sh;
     cg::cluster_group cl = cg::this_cluster();
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y, c0 = blockIdx.x * nc;
     const float* src = x + static_cast<size_t>(m) * n + c0;
     for (int g = threadIdx.x; g < nc / 4; g += kThreads)
@@ -242,6 +251,8 @@ argmax_cl_kernel(const float* __restrict__ logits, int vocab, int chunk, int* __
     __shared__ float part_v;
     __shared__ int part_i;
     cg::cluster_group cl = cg::this_cluster();
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y;
     const int c0 = blockIdx.x * chunk;
     int c1 = c0 + chunk;
@@ -294,6 +305,8 @@ qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int h
                            const uint32_t* __restrict__ positions, const uint32_t* __restrict__ block_tables,
                            int max_blocks_per_seq, int block_size, int num_blocks, float* __restrict__ q_out,
                            uint16_t* __restrict__ k_pool, uint16_t* __restrict__ v_pool, uint32_t* err) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.y;
     const int n = (hq + 2 * hkv) * dh;
     const int half = dh / 2;
@@ -361,19 +374,7 @@ int pick_cluster(int n) {
 
 template <typename... KArgs, typename... Args>
 cudaError_t launch_cluster(void (*kernel)(KArgs...), int cl, int rows, cudaStream_t s, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(cl, rows, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cl;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return launch_ex(kernel, dim3(cl, rows, 1), dim3(kThreads, 1, 1), 0, s, cl, true, args...);
 }
 
 }  // namespace
@@ -425,10 +426,9 @@ cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int 
     int hpc = (2 * kThreads) / (dh / 2);      // two rotary pairs per thread
     if (hpc < 1) hpc = 1;
     dim3 grid((heads + hpc - 1) / hpc, M);
-    qkv_rope_append_par_kernel<<<grid, kThreads, 0, s>>>(raw, splits, M, hq, hkv, dh, hpc, sx_in, sw, cos_t, sin_t, max_pos,
-                                                        positions, block_tables, max_blocks_per_seq, block_size, num_blocks,
-                                                        q_out, k_pool, v_pool, err);
-    return cudaGetLastError();
+    return launch_ex(qkv_rope_append_par_kernel, grid, dim3(kThreads), 0, s, 1, true, raw, splits, M, hq, hkv, dh, hpc, sx_in,
+                     sw, cos_t, sin_t, max_pos, positions, block_tables, max_blocks_per_seq, block_size, num_blocks, q_out,
+                     k_pool, v_pool, err);
 }
 
 }  // namespace b200

@@ -13,6 +13,7 @@
 // gemm_tiled_bias_act_f32 (crates/backend-cuda/src/kernels.rs:368-477) and
 // gemm_mma_f16 (crates/backend-cuda/src/kernels_mma.rs:227-375).
 #include "gemm_tc5.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace b200 {
@@ -107,21 +108,32 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
     if (warp == 0) {
         if (elect_one()) {
-            for (int i = 0; i < num_kb; ++i) {
+            auto load_b = [&](int i, int s) {
+                const uint32_t b_dst = smem_base + s * kStageBytes + kABytes;
+                const int kx = (kb_begin + i) * kBK;
+                tma_load_2d(b_dst, &tma_b, full_bar(s), kx, n0);
+                if (p.gate) tma_load_2d(b_dst + (BN / 2) * kBK, &tma_b, full_bar(s), kx, p.n_half + n0);
+            };
+            auto load_a = [&](int i, int s) {
+                tma_load_2d(smem_base + s * kStageBytes, &tma_a, full_bar(s), (kb_begin + i) * kBK, m0);
+            };
+            // The B operand (weights) does not depend on the kernel that runs before this one: fill the first
+            // pass over the ring with B tiles while that kernel still drains, then wait for it and add the A tiles.
+            const int pre = num_kb < p.stages ? num_kb : p.stages;
+            for (int i = 0; i < pre; ++i) {
+                mbar_arrive_expect_tx(full_bar(i), kStageBytes);
+                load_b(i, i);
+            }
+            pdl_wait();
+            pdl_launch_dependents();
+            for (int i = 0; i < pre; ++i) load_a(i, i);
+            for (int i = pre; i < num_kb; ++i) {
                 const int s = i % p.stages;
                 const uint32_t ph = (i / p.stages) & 1;
                 if (!mbar_wait(empty_bar(s), ph ^ 1u, p.err, kErrProducerWait)) break;
                 mbar_arrive_expect_tx(full_bar(s), kStageBytes);
-                const uint32_t a_dst = smem_base + s * kStageBytes;
-                const uint32_t b_dst = a_dst + kABytes;
-                const int kx = (kb_begin + i) * kBK;
-                tma_load_2d(a_dst, &tma_a, full_bar(s), kx, m0);
-                if (p.gate) {
-                    tma_load_2d(b_dst, &tma_b, full_bar(s), kx, n0);
-                    tma_load_2d(b_dst + (BN / 2) * kBK, &tma_b, full_bar(s), kx, p.n_half + n0);
-                } else {
-                    tma_load_2d(b_dst, &tma_b, full_bar(s), kx, n0);
-                }
+                load_a(i, s);
+                load_b(i, s);
             }
         }
     } else if (warp == 1) {
@@ -150,6 +162,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         const int q = warp & 3;
         const int row = m0 + q * 32 + lane;
         const bool row_ok = row < p.M;
+        pdl_wait();      // scales, bias, residual and the output buffers belong to the surrounding kernels
         bool ready = num_kb > 0 && mbar_wait(tmem_full_bar, 0, p.err, kErrEpilogueWait);
         tc5_fence_after();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -360,8 +373,7 @@ cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t 
     const int out_cols = plan.gate ? BN / 2 : BN;
     const int n_out = plan.gate ? plan.N / 2 : plan.N;
     dim3 grid((n_out + out_cols - 1) / out_cols, (plan.M + kBM - 1) / kBM, plan.splits);
-    gemm_tc5_kernel<BN, kInt8><<<grid, kThreads, smem, stream>>>(plan.tma_a, plan.tma_b, args);
-    return cudaGetLastError();
+    return launch_ex(gemm_tc5_kernel<BN, kInt8>, grid, dim3(kThreads), smem, stream, 1, true, plan.tma_a, plan.tma_b, args);
 }
 
 }  // namespace

@@ -77,6 +77,8 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
 
+    pdl_wait();                 // q, the new K / V rows and seq_lens come from the kernels before this one
+    pdl_launch_dependents();
     const int chunk_tokens = chunk_blocks * kBS;
     // the kv heads of one (row, chunk) are neighbours in the grid: they run at about the same time and read
     // adjacent 256-byte pieces of the same 2 KB token rows

@@ -13,6 +13,7 @@
 #include <mutex>
 
 #include "kernels.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace b200 {
@@ -192,6 +193,8 @@ __global__ void __launch_bounds__(128)
 paged_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_tokens, int max_chunks,
                                float* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t pair = int64_t(blockIdx.x) * 4 + warp;          // row * Hq + h
     const int64_t pairs = int64_t(sh.batch) * sh.l_new * sh.num_q_heads;
@@ -262,9 +265,8 @@ cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_
     const PagedAttnShape& sh = plan.shape;
     const int group = sh.num_q_heads / sh.num_kv_heads;
     dim3 grid(sh.num_kv_heads * (group / G), plan.max_chunks, sh.batch * sh.l_new);
-    paged_attention_decode_kernel<G><<<grid, kFastThreads, smem, stream>>>(
-        plan.tma_k, plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml, err);
-    return cudaGetLastError();
+    return launch_ex(paged_attention_decode_kernel<G>, grid, dim3(kFastThreads), smem, stream, 1, true, plan.tma_k,
+                     plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml, err);
 }
 
 int grid_for(int64_t n, int threads) {
@@ -389,9 +391,8 @@ cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, co
     else e = launch_fast<4>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, err, stream);
     if (e != cudaSuccess) return e;
     const int blocks = static_cast<int>((pairs + 3) / 4);
-    paged_attention_combine_kernel<<<blocks, 128, 0, stream>>>(part_o, part_ml, seq_lens_dev, sh, plan.chunk_blocks * kBS,
-                                                              plan.max_chunks, out);
-    return cudaGetLastError();
+    return launch_ex(paged_attention_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, true, part_o, part_ml,
+                     seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks, out);
 }
 
 }  // namespace b200

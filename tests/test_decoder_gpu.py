@@ -1,5 +1,19 @@
-"""GPU parity of the decode driver against the CPU decoder restatement (oracle/decoder_ref.py):
-greedy token ids must be identical, logits within the composite tolerance."""
+"""GPU parity of the decode driver against the CPU decoder restatement (oracle/decoder_ref.py).
+
+What can be exact and what cannot.  Every block of the decoder ends in a dynamic per-token int8
+quantiser.  A last-bit difference in an activation upstream of a quantiser (the attention kernel sums keys in
+tensor-core order, exp() differs in the last bit between libm and CUDA) can move one value across a rounding
+boundary, and one int8 step is 1/127 of the row maximum: from there on the two implementations differ by
+quantisation noise, not by 1e-3, and a free-running greedy comparison diverges for good after the first
+near-tie.  So:
+  * the first decode step (one cached token: the softmax weight is exactly 1) exercises every GEMM, epilogue
+    and row kernel with no summation-order freedom: logits must match the composite tolerance outright;
+  * later steps are compared teacher-forced (the CPU decoder's tokens are fed to the GPU decoder): logits
+    must stay within a bound relative to the logit range, the greedy choice must agree almost always, and
+    where it differs the two candidates must be closer in the CPU logits than twice the observed deviation;
+  * the int32 accumulators, quantised codes and single kernels are checked bit for bit in
+    tests/test_quant_gemm_gpu.py and tests/test_paged_gpu.py.
+"""
 import numpy as np
 import pytest
 
@@ -10,84 +24,70 @@ from oracle.decoder_ref import DecoderRef, make_weights
 pytestmark = pytest.mark.gpu
 
 
-def run_generate(be, cfg: dict, batch: int, prompt_len: int, max_length: int, seed: int, use_graph: int = 1):
+def make_decoder(be, cfg: dict, batch: int, use_graph: int = 1) -> Decoder:
+    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
+                       cfg["vocab"], cfg.get("rms_eps", 1e-5), cfg.get("rope_theta", 10000.0), max_batch=batch,
+                       max_seq_len=cfg["max_seq_len"], block_size=cfg.get("block_size", 16), use_graph=use_graph)
+    return Decoder(be, dc)
+
+
+def teacher_forced_parity(be, cfg: dict, batch: int, prompt_len: int, max_length: int, seed: int, use_graph: int = 1):
+    """Returns (sampled positions, positions whose greedy choice differed, worst |dlogit| / max |logit|)."""
     weights = make_weights(cfg, seed=seed)
     rng = np.random.default_rng(seed + 1)
     prompt = rng.integers(0, cfg["vocab"], (batch, prompt_len)).astype(np.int32)
     ref = DecoderRef(cfg, weights)
     ids_ref, logits_ref = ref.generate(prompt, max_length)
-    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
-                       cfg["vocab"], cfg.get("rms_eps", 1e-5), cfg.get("rope_theta", 10000.0), max_batch=batch,
-                       max_seq_len=cfg["max_seq_len"], block_size=cfg.get("block_size", 16), use_graph=use_graph)
-    dec = Decoder(be, dc)
-    try:
-        dec.load_weights(weights)
-        ids = dec.generate(prompt, max_length)
-        last_logits = dec.logits()
-    finally:
-        dec.close()
-    return ids, ids_ref, last_logits, logits_ref
-
-
-SMALL = dict(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ff=1024, vocab=2048, max_seq_len=64)
-
-
-@pytest.mark.parametrize("use_graph", [0, 1])
-def test_small_decoder_token_ids_are_identical(be, use_graph):
-    ids, ids_ref, logits, logits_ref = run_generate(be, SMALL, batch=4, prompt_len=20, max_length=40, seed=0,
-                                                    use_graph=use_graph)
-    assert np.array_equal(ids[:, :20], ids_ref[:, :20])
-    assert np.array_equal(ids, ids_ref)
-    fails, max_abs, max_rel = O.compare(logits, logits_ref[-1])
-    assert fails == 0, (max_abs, max_rel)
-
-
-def test_generic_attention_path_head_dim_64(be):
-    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=4, head_dim=64, d_ff=512, vocab=1024, max_seq_len=48)
-    ids, ids_ref, logits, logits_ref = run_generate(be, cfg, batch=3, prompt_len=10, max_length=30, seed=3)
-    assert np.array_equal(ids, ids_ref)
-    assert O.compare(logits, logits_ref[-1])[0] == 0
-
-
-def teacher_forced_parity(be, cfg: dict, batch: int, prompt_len: int, max_length: int, seed: int):
-    """Feeds the CPU decoder's own token sequence to the GPU decoder step by step and compares every
-    sampled step: logits within the composite tolerance, and the greedy choice identical wherever the
-    choice is decided by more than that tolerance.  (The attention and exp() summation orders differ
-    between the sequential CPU loop and the parallel kernels, so two logits that tie within the numeric
-    contract may swap; a free-running comparison would then diverge for good from that token on.)
-    Returns (sampled positions, positions whose choice differed, worst |dlogit| / max |logit|)."""
-    weights = make_weights(cfg, seed=seed)
-    rng = np.random.default_rng(seed + 1)
-    prompt = rng.integers(0, cfg["vocab"], (batch, prompt_len)).astype(np.int32)
-    ids_ref, logits_ref = DecoderRef(cfg, weights).generate(prompt, max_length)
-    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
-                       cfg["vocab"], cfg.get("rms_eps", 1e-5), cfg.get("rope_theta", 10000.0), max_batch=batch,
-                       max_seq_len=cfg["max_seq_len"])
-    dec = Decoder(be, dc)
+    dec = make_decoder(be, cfg, batch, use_graph)
     sampled = flips = 0
     worst = 0.0
     try:
         dec.load_weights(weights)
         dec.begin(batch, [max_length - 1] * batch)
         for t in range(max_length - 1):
-            nxt = dec.step(ids_ref[:, t], want_next=t >= prompt_len - 1)
+            want_out = t == 0 or t >= prompt_len - 1
+            nxt = dec.step(ids_ref[:, t], want_next=want_out)
+            if t == 0:
+                # one cached token: no summation-order freedom anywhere in the stack
+                first = DecoderRef(cfg, weights)
+                first.begin(batch)
+                ref0, _ = first.step(ids_ref[:, 0])
+                fails, max_abs, max_rel = O.compare(dec.logits(), ref0)
+                assert fails == 0, ("first step", max_abs, max_rel)
             if t < prompt_len - 1:
                 continue
-            ref = logits_ref[t - (prompt_len - 1)]
+            want = logits_ref[t - (prompt_len - 1)]
             got = dec.logits()
             assert np.all(np.isfinite(got))
-            # Dynamic per-token int8 quantisation sits after every block: a last-bit difference in an
-            # activation (summation order of the attention, exp) can move a value across a rounding
-            # boundary, and one such step is 1/127 of the row maximum.  Deep stacks therefore agree to
-            # quantisation noise, not to 1e-3; bound the deviation relative to the logit range instead.
-            worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
+            dev = float(np.abs(got - want).max())
+            worst = max(worst, dev / float(np.abs(want).max()))
             for b in range(batch):
                 sampled += 1
                 if nxt[b] != ids_ref[b, t + 1]:
                     flips += 1
+                    assert abs(float(want[b, nxt[b]]) - float(want[b, ids_ref[b, t + 1]])) <= 2.0 * dev + 1e-6, (t, b)
     finally:
         dec.close()
     return sampled, flips, worst
+
+
+SMALL = dict(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, d_ff=1024, vocab=2048, max_seq_len=64)
+
+
+@pytest.mark.parametrize("use_graph", [0, 1])
+def test_small_decoder(be, use_graph):
+    sampled, flips, worst = teacher_forced_parity(be, SMALL, batch=4, prompt_len=20, max_length=40, seed=0,
+                                                  use_graph=use_graph)
+    assert sampled == 4 * 20
+    assert worst < 0.05, worst
+    assert flips <= sampled // 10, (sampled, flips)
+
+
+def test_generic_attention_path_head_dim_64(be):
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=4, head_dim=64, d_ff=512, vocab=1024, max_seq_len=48)
+    sampled, flips, worst = teacher_forced_parity(be, cfg, batch=3, prompt_len=10, max_length=30, seed=3)
+    assert worst < 0.05, worst
+    assert flips <= sampled // 10, (sampled, flips)
 
 
 def test_config4_shape_reduced_steps(be):
@@ -101,12 +101,26 @@ def test_config4_shape_reduced_steps(be):
     assert flips <= sampled // 10, (sampled, flips)
 
 
+def test_graph_replay_equals_eager_steps_bit_for_bit(be):
+    """The same kernels in the same order: a CUDA-graph replay of the step must reproduce the eager step exactly."""
+    weights = make_weights(SMALL, seed=11)
+    prompt = np.random.default_rng(12).integers(0, SMALL["vocab"], (3, 9)).astype(np.int32)
+    outs = []
+    for use_graph in (0, 1):
+        dec = make_decoder(be, SMALL, 3, use_graph)
+        try:
+            dec.load_weights(weights)
+            outs.append((dec.generate(prompt, 30), dec.logits()))
+        finally:
+            dec.close()
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+
+
 def test_step_api_matches_generate_and_feeds_ids_from_the_host(be):
     cfg = SMALL
     weights = make_weights(cfg, seed=7)
-    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
-                       cfg["vocab"], max_batch=2, max_seq_len=cfg["max_seq_len"])
-    dec = Decoder(be, dc)
+    dec = make_decoder(be, cfg, 2)
     try:
         dec.load_weights(weights)
         prompt = np.array([[5, 9, 100, 7], [1, 2, 3, 4]], np.int32)
