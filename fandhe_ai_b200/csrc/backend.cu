@@ -417,7 +417,7 @@ int32_t b200_gemm_i8_s32(b200_ctx* ctx, const b200_buf* a, size_t a_off, const b
                                    int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why);
     if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
     GemmEpilogue ep;
-    if (plan.splits == 1) {
+    if (plan.out_planes == 1) {      // one pass over K, or split-K reduced inside a cluster
         ep.raw = buf_ptr<void>(acc, acc_off);
         e = gemm_launch(plan, ep, ctx->err_dev, ctx->stream);
     } else {
@@ -489,13 +489,17 @@ int32_t b200_gemm_q8_scaled(b200_ctx* ctx, int32_t op_dtype, const b200_buf* a, 
     cudaError_t e = gemm_make_plan(&plan, kind, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m),
                                    int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why);
     if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
-    if (plan.splits > 1) {
+    if (plan.splits > 1 && plan.cluster && !gate) {
+        // split-K reduced inside a cluster: the epilogue runs on the reduced values in the same kernel
+        e = gemm_launch(plan, ep, ctx->err_dev, ctx->stream);
+    } else if (plan.splits > 1) {
         void* ws = ensure_ws(ctx, gemm_raw_elems(plan) * 4);
         if (!ws) return B200_DEVICE_ALLOCATION_FAILED;
         GemmEpilogue raw_ep;
         raw_ep.raw = ws;
         e = gemm_launch(plan, raw_ep, ctx->err_dev, ctx->stream);
-        if (e == cudaSuccess) e = gemm_splitk_epilogue(kind, plan.splits, int(m), int(n), gate ? 1 : 0, ws, ep, ctx->stream);
+        if (e == cudaSuccess)
+            e = gemm_splitk_epilogue(kind, plan.out_planes, int(m), int(n), gate ? 1 : 0, ws, ep, ctx->stream);
     } else {
         if (gate) {
             e = gemm_make_plan(&plan, kind, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m), int(n),

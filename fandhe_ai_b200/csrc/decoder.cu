@@ -450,7 +450,7 @@ int32_t enqueue_step(b200_decoder* d) {
         LayerParams& L = d->layers[l];
         // QKV projection -> RoPE -> append to the paged cache
         CU_TRY(gemm_launch(L.p_qkv, ep, err, s));
-        CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.splits, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv, d->cos_t,
+        CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv, d->cos_t,
                                d->sin_t, c.max_seq_len, d->pos_dev, d->tables_dev, d->max_blocks_per_seq,
                                c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
                                static_cast<uint16_t*>(L.v_pool), err, s));
@@ -462,25 +462,25 @@ int32_t enqueue_step(b200_decoder* d) {
         CU_TRY(gemm_launch(L.p_o, ep, err, s));
         launches += 6;
         if (tp) {
-            CU_TRY(dequant_planes(d->raw, L.p_o.splits, M, dm, d->sx, d->scales + L.s_o, d->part, s));
+            CU_TRY(dequant_planes(d->raw, L.p_o.out_planes, M, dm, d->sx, d->scales + L.s_o, d->part, s));
             if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
             launches += 2;
         }
-        CU_TRY(resid_norm_quant_auto(d->raw, L.p_o.splits, M, dm, d->sx, d->scales + L.s_o, tp ? d->part : nullptr,
+        CU_TRY(resid_norm_quant_auto(d->raw, L.p_o.out_planes, M, dm, d->sx, d->scales + L.s_o, tp ? d->part : nullptr,
                                 d->vectors + L.mlp_norm, c.rms_eps, d->h, d->xq, d->sx, s));
         // gate / up (column-parallel) -> SiLU gate -> quant
         CU_TRY(gemm_launch(L.p_gu, ep, err, s));
-        CU_TRY(gate_quant_auto(d->raw, L.p_gu.splits, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
+        CU_TRY(gate_quant_auto(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
         // down (row-parallel) -> residual -> next norm -> quant
         CU_TRY(gemm_launch(L.p_down, ep, err, s));
         launches += 4;
         if (tp) {
-            CU_TRY(dequant_planes(d->raw, L.p_down.splits, M, dm, d->sx, d->scales + L.s_down, d->part, s));
+            CU_TRY(dequant_planes(d->raw, L.p_down.out_planes, M, dm, d->sx, d->scales + L.s_down, d->part, s));
             if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
             launches += 2;
         }
         const float* next_norm = d->vectors + (l + 1 < c.n_layers ? d->layers[l + 1].attn_norm : d->final_norm);
-        CU_TRY(resid_norm_quant_auto(d->raw, L.p_down.splits, M, dm, d->sx, d->scales + L.s_down, tp ? d->part : nullptr,
+        CU_TRY(resid_norm_quant_auto(d->raw, L.p_down.out_planes, M, dm, d->sx, d->scales + L.s_down, tp ? d->part : nullptr,
                                 next_norm, c.rms_eps, d->h, d->xq, d->sx, s));
         ++launches;
     }

@@ -12,14 +12,18 @@
 // Replaces, for the quantized path, the reference's fused GEMM kernels
 // gemm_tiled_bias_act_f32 (crates/backend-cuda/src/kernels.rs:368-477) and
 // gemm_mma_f16 (crates/backend-cuda/src/kernels_mma.rs:227-375).
+#include <cooperative_groups.h>
+
 #include "gemm_tc5.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 
+namespace cg = cooperative_groups;
+
 namespace b200 {
 namespace {
 
-constexpr int kBM = 128;       // accumulator rows per CTA = TMEM lanes
+constexpr int kBM = 128;      // accumulator rows per CTA = TMEM lanes
 constexpr int kBK = 128;       // operand bytes along K per stage (one swizzle row)
 constexpr int kUmmaK = 32;     // K per tcgen05.mma for 8-bit operands
 constexpr int kThreads = 192;
@@ -32,6 +36,7 @@ struct KernelArgs {
     int kb_per_split;
     int gate;            // B tile = bn/2 gate rows + bn/2 up rows
     int n_half;          // N / 2 in the gate form
+    int cluster_reduce;  // the splits of a tile form a cluster and reduce through distributed shared memory
     GemmEpilogue ep;
     uint32_t* err;
 };
@@ -55,6 +60,30 @@ __device__ __forceinline__ void store_out4(const GemmEpilogue& ep, size_t idx, f
     } else {
         *reinterpret_cast<float4*>(static_cast<float*>(ep.out) + idx) = make_float4(y0, y1, y2, y3);
     }
+}
+
+// Four finished accumulators of (row, columns n .. n + 3): raw store into the single output plane, or the
+// fused epilogue (not the gate form).
+template <bool kInt8>
+__device__ __forceinline__ void emit4(const KernelArgs& p, int row, int n, const uint32_t (&v)[4]) {
+    const GemmEpilogue& ep = p.ep;
+    if (!ep.fused) {
+        *reinterpret_cast<uint4*>(static_cast<uint32_t*>(ep.raw) + static_cast<size_t>(row) * p.N + n) =
+            make_uint4(v[0], v[1], v[2], v[3]);
+        return;
+    }
+    const float sa = ep.a_scale[ep.a_per_row ? row : 0];
+    float y[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const float sb = ep.b_scale[ep.b_per_col ? n + t : 0];
+        const float b = ep.bias ? ep.bias[n + t] : 0.0f;
+        float x = fmaf(acc_to_f32<kInt8>(v[t]), sa * sb, b);
+        if (ep.act == kActSilu) x = silu(x);
+        else if (ep.act == kActRelu) x = fmaxf(x, 0.0f);
+        y[t] = x;
+    }
+    store_out4(ep, static_cast<size_t>(row) * p.N + n, y[0], y[1], y[2], y[3]);
 }
 
 template <int BN, bool kInt8>
@@ -167,7 +196,19 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         tc5_fence_after();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         const GemmEpilogue& ep = p.ep;
-        if (ready) {
+        if (ready && p.cluster_reduce) {
+            // park this CTA's partial tile in its own shared memory, column-major ([col][row]): the operand ring
+            // is idle by now (every MMA has completed), consecutive threads hold consecutive rows
+            uint32_t* part = reinterpret_cast<uint32_t*>(smem_dyn + (smem_base - smem_u32(smem_dyn)));
+            const int rl = q * 32 + lane;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_row + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part[(c0 + j) * kBM + rl] = v[j];
+            }
+        } else if (ready) {
             if (!ep.fused) {
                 uint32_t* raw = static_cast<uint32_t*>(ep.raw) +
                                 (static_cast<size_t>(split) * p.M + (row_ok ? row : 0)) * p.N;
@@ -245,6 +286,39 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 }
             }
         }
+    }
+
+    if (p.cluster_reduce) {
+        // Split-K inside a cluster: the `splits` CTAs of one output tile exchange their partial tiles through
+        // distributed shared memory; CTA `rank` sums a slice of BN / splits columns over all peers in rank
+        // order (exact for int32, fixed order for f32) and writes the finished values, so only one plane
+        // leaves the kernel.  Both barriers are reached by every thread on every path.
+        cg::cluster_group cl = cg::this_cluster();
+        cl.sync();
+        if (warp >= 2) {
+            const int nsplit = static_cast<int>(cl.num_blocks());
+            const int rank = static_cast<int>(cl.block_rank());
+            const int cpr = BN / nsplit;                   // columns per rank, a multiple of 4
+            const int rl = (warp & 3) * 32 + lane;
+            const int row = m0 + rl;
+            uint32_t* part = reinterpret_cast<uint32_t*>(smem_dyn + (smem_base - smem_u32(smem_dyn)));
+            for (int cc = 0; cc < cpr; cc += 4) {
+                const int col = rank * cpr + cc;
+                uint32_t v[4] = {0u, 0u, 0u, 0u};
+                for (int peer = 0; peer < nsplit; ++peer) {
+                    const uint32_t* pp = cl.map_shared_rank(part, peer);
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const uint32_t x = pp[(col + t) * kBM + rl];
+                        if constexpr (kInt8) v[t] += x;    // two's complement wrap = int32 addition
+                        else v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(x));
+                    }
+                }
+                const int n = n0 + col;
+                if (row < p.M && n < p.N) emit4<kInt8>(p, row, n, v);
+            }
+        }
+        cl.sync();
     }
 
     tc5_fence_before();
@@ -373,7 +447,8 @@ cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t 
     const int out_cols = plan.gate ? BN / 2 : BN;
     const int n_out = plan.gate ? plan.N / 2 : plan.N;
     dim3 grid((n_out + out_cols - 1) / out_cols, (plan.M + kBM - 1) / kBM, plan.splits);
-    return launch_ex(gemm_tc5_kernel<BN, kInt8>, grid, dim3(kThreads), smem, stream, 1, true, plan.tma_a, plan.tma_b, args);
+    return launch_ex_z(gemm_tc5_kernel<BN, kInt8>, grid, dim3(kThreads), smem, stream, plan.cluster ? plan.splits : 1, true,
+                       plan.tma_a, plan.tma_b, args);
 }
 
 }  // namespace
@@ -402,14 +477,21 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     const int n_out = gate ? N / 2 : N;
     const int out_cols = gate ? bn / 2 : bn;
     const int tiles = m_tiles * ((n_out + out_cols - 1) / out_cols);
+    // A power-of-two split count up to 8 whose slices tile K exactly can be reduced inside a cluster.
+    auto exact_pow2 = [&](int s) {
+        if (s < 2 || s > 8 || (s & (s - 1)) != 0) return false;
+        const int per = (kb_total + s - 1) / s;
+        return (kb_total + per - 1) / per == s;
+    };
     int splits = want_splits;
     if (splits <= 0) {
         splits = 1;
         if (tiles < 148) {
-            splits = 296 / tiles;
-            if (splits > kb_total / 2) splits = kb_total / 2;
-            if (splits > 16) splits = 16;
-            if (splits < 1) splits = 1;
+            int cap = 296 / tiles;
+            if (cap > kb_total / 2) cap = kb_total / 2;
+            if (cap > 8) cap = 8;
+            for (int s = 2; s <= cap; s *= 2)
+                if (exact_pow2(s)) splits = s;
         }
     }
     if (splits > kb_total) splits = kb_total;
@@ -425,6 +507,9 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     if (stages > 8) stages = 8;
     if (stages < 2) stages = 2;
     plan->stages = stages;
+    // the parked partial tile (bn x 128 accumulators) reuses the operand ring
+    plan->cluster = (!gate && exact_pow2(splits) && stages * stage_bytes >= bn * kBM * 4) ? 1 : 0;
+    plan->out_planes = plan->cluster ? 1 : splits;
     if (!make_operand_map(&plan->tma_a, a, M, K, kBM)) return fail("gemm: cuTensorMapEncodeTiled failed for A");
     if (!make_operand_map(&plan->tma_b, b, N, K, gate ? bn / 2 : bn)) return fail("gemm: cuTensorMapEncodeTiled failed for B");
     return cudaSuccess;
@@ -440,7 +525,8 @@ cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* 
     args.n_half = plan.N / 2;
     args.ep = ep;
     args.err = err;
-    if (ep.fused && plan.splits != 1) return cudaErrorInvalidValue;
+    args.cluster_reduce = plan.cluster;
+    if (ep.fused && plan.splits != 1 && !plan.cluster) return cudaErrorInvalidValue;
     if (!ep.fused && plan.gate) return cudaErrorInvalidValue;   // raw planes always use the plain column layout
     const bool i8 = plan.kind == kGemmI8;
     switch (plan.bn) {

@@ -39,6 +39,8 @@ struct GemmPlan {
     int stages = 3;
     int splits = 1;
     int gate = 0;
+    int cluster = 0;     // the splits of a tile run as one cluster and reduce through distributed shared memory
+    int out_planes = 1;  // raw planes the kernel writes: 1 with the cluster reduction, else `splits`
 };
 
 // Picks tile width / stage count / split count for a shape.  `want_splits` <= 0
@@ -59,6 +61,6 @@ cudaError_t gemm_splitk_epilogue(int kind, int splits, int M, int N, int gate, c
 cudaError_t gemm_sum_planes_i32(const int* raw, int splits, int64_t elems, int* out, cudaStream_t stream);
 
 // Required raw-output elements for a plan: splits * M * N.
-inline size_t gemm_raw_elems(const GemmPlan& p) { return size_t(p.splits) * size_t(p.M) * size_t(p.N); }
+inline size_t gemm_raw_elems(const GemmPlan& p) { return size_t(p.out_planes) * size_t(p.M) * size_t(p.N); }
 
 }  // namespace b200

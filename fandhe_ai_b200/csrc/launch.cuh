@@ -11,8 +11,8 @@ namespace b200 {
 bool pdl_enabled();
 
 template <typename... KArgs, typename... Args>
-cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
-                      bool pdl, Args... args) {
+cudaError_t launch_impl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, dim3 cluster,
+                        bool pdl, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -20,11 +20,11 @@ cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (cluster_x > 1) {
+    if (cluster.x * cluster.y * cluster.z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = cluster_x;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = 1;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     if (pdl && pdl_enabled()) {
@@ -35,6 +35,20 @@ cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     cfg.attrs = attr;
     cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// cluster of `cluster_x` CTAs along grid x (1: no cluster)
+template <typename... KArgs, typename... Args>
+cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
+                      bool pdl, Args... args) {
+    return launch_impl(kernel, grid, block, smem, stream, dim3(cluster_x, 1, 1), pdl, args...);
+}
+
+// cluster of `cluster_z` CTAs along grid z (1: no cluster)
+template <typename... KArgs, typename... Args>
+cudaError_t launch_ex_z(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_z,
+                        bool pdl, Args... args) {
+    return launch_impl(kernel, grid, block, smem, stream, dim3(1, 1, cluster_z), pdl, args...);
 }
 
 }  // namespace b200
