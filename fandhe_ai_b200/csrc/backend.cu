@@ -171,8 +171,8 @@ int32_t b200_ctx_create(int32_t ordinal, b200_ctx** out) {
     ctx->generation = ++g_generation;
     e = cudaSetDevice(ordinal);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->err_dev, 2 * sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMemset(ctx->err_dev, 0, 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->err_dev, 4 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_dev, 0, 4 * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMallocHost(&ctx->err_host, sizeof(uint32_t));
     if (e != cudaSuccess) {
         std::string msg = std::string("ctx_create: ") + cudaGetErrorString(e);
@@ -180,6 +180,7 @@ int32_t b200_ctx_create(int32_t ordinal, b200_ctx** out) {
         return fail(B200_DEVICE_UNAVAILABLE, msg);
     }
     ctx->amax_scratch = ctx->err_dev + 1;
+    ctx->attn_counter = ctx->err_dev + 2;
     *ctx->err_host = 0;
     *out = ctx;
     return B200_OK;

@@ -12,6 +12,7 @@ struct b200_ctx {
     cudaStream_t stream = nullptr;
     uint32_t* err_dev = nullptr;        // device error word written by kernels (0 = none)
     uint32_t* amax_scratch = nullptr;   // one word for tensor-wide amax
+    unsigned int* attn_counter = nullptr;  // work counter of the persistent attention kernel (zero between launches)
     uint32_t* err_host = nullptr;       // pinned mirror used when checking the word
     uint64_t generation = 0;
     bool poisoned = false;

@@ -188,7 +188,7 @@ int32_t run_attention(b200_ctx* ctx, const PagedAttnShape& sh, int kv_bf16, cons
         tables_dev = reinterpret_cast<const uint32_t*>(ws);
         seq_dev = reinterpret_cast<const uint32_t*>(ws + tables_bytes);
     }
-    e = paged_attention_launch(plan, q, k_pool, v_pool, tables_dev, seq_dev, out, ws ? ws + stage : nullptr, ctx->err_dev,
+    e = paged_attention_launch(plan, q, k_pool, v_pool, tables_dev, seq_dev, out, ws ? ws + stage : nullptr, ctx->attn_counter, ctx->sm_count, ctx->err_dev,
                                ctx->stream);
     if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("paged_attention: ") + cudaGetErrorString(e));
     return B200_OK;
@@ -359,7 +359,7 @@ int32_t b200_paged_attention_forward_noalloc(b200_ctx* ctx, const b200_buf* q, s
         return fail(B200_KERNEL_LAUNCH_FAILED, std::string("paged_attention_forward_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
     e = paged_attention_launch(plan, buf_ptr<const float>(q, q_off), k_pool->ptr, v_pool->ptr,
                                buf_ptr<const uint32_t>(block_tables, 0), buf_ptr<const uint32_t>(seq_lens, 0),
-                               buf_ptr<float>(out, out_off), scratch, ctx->err_dev, ctx->stream);
+                               buf_ptr<float>(out, out_off), scratch, ctx->attn_counter, ctx->sm_count, ctx->err_dev, ctx->stream);
     if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("paged_attention_forward_noalloc: ") + cudaGetErrorString(e));
     return B200_OK;
 }

@@ -456,7 +456,7 @@ int32_t enqueue_step(b200_decoder* d) {
                                static_cast<uint16_t*>(L.v_pool), err, s));
         // attention over the cache (this rank's KV heads), then per-token quantisation
         CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
-                                      d->attn_scratch, err, s));
+                                      d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s));
         CU_TRY(quantize_rows_auto(d->attn_out, M, d->hq_l * dh, d->xq, d->sx, s));
         // O projection (row-parallel) -> residual -> norm -> quant
         CU_TRY(gemm_launch(L.p_o, ep, err, s));
@@ -1000,7 +1000,7 @@ int32_t b200_decoder_time_attention(b200_decoder* d, int32_t iters, float* ms_pe
     auto run = [&](int l) {
         LayerParams& L = d->layers[l % c.n_layers];
         return paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
-                                      d->attn_scratch, d->ctx->err_dev, s);
+                                      d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, d->ctx->err_dev, s);
     };
     for (int w = 0; w < 3; ++w) CU_TRY(run(w));
     if (int32_t st = b200_timer_start(d->ctx)) return st;

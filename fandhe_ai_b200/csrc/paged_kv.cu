@@ -180,21 +180,24 @@ constexpr int kD = 128;
 constexpr int kBS = 16;                 // tokens per block = tokens per tile
 constexpr int kTileBytes = kBS * kD * 2;  // 4096
 constexpr int kConsumerWarps = 4;
-constexpr int kStagesPerWarp = 3;       // K, V and the next K of one warp's blocks in flight
+constexpr int kStagesPerWarp = 3;       // K and V of one and a half of a warp's blocks in flight
 constexpr int kStages = kConsumerWarps * kStagesPerWarp;
 constexpr int kFastThreads = 32 * (kConsumerWarps + 1);
 constexpr int kMaxChunkBlocks = 256;    // upper bound of blocks per split (tuning range)
 constexpr int kDefaultChunkBlocks = 32;
+constexpr int kCtasPerSm = 3;           // resident CTAs of the persistent attention kernel per SM
 
-#include "paged_attn_mma.cuh"
+#include "paged_attn_persistent.cuh"
 
 // Merges the chunk partials of one (query row, q head): one warp each, lanes own 4 dims.
 __global__ void __launch_bounds__(128)
 paged_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_tokens, int max_chunks,
-                               float* __restrict__ out) {
+                               float* __restrict__ out, unsigned int* __restrict__ work_counter) {
     pdl_wait();
     pdl_launch_dependents();
+    // every attention CTA has finished: leave the work counter at zero for the next attention launch
+    if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t pair = int64_t(blockIdx.x) * 4 + warp;          // row * Hq + h
     const int64_t pairs = int64_t(sh.batch) * sh.l_new * sh.num_q_heads;
@@ -209,7 +212,7 @@ paged_attention_combine_kernel(const float* __restrict__ part_o, const float* __
     float l = 0.0f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int c = 0; c < nchunks; ++c) {
-        const float w = expf(ml[2 * c] - m);
+        const float w = exp2f(ml[2 * c] - m);       // the partial maxima are in log2 units
         l = fmaf(ml[2 * c + 1], w, l);
         const float4 po = *reinterpret_cast<const float4*>(part_o + (pair * max_chunks + c) * kD + lane * 4);
         o.x = fmaf(po.x, w, o.x); o.y = fmaf(po.y, w, o.y); o.z = fmaf(po.z, w, o.z); o.w = fmaf(po.w, w, o.w);
@@ -233,29 +236,31 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [pool_rows, E_kv] bf16, box = half a block row set of one kv head: [16 rows, 64 elements] = 128-byte rows,
-// written with the 128-byte swizzle
+// The pool is [pool_rows, E_kv] bf16.  One copy brings a whole [16 tokens x 128 dims] tile of one kv head: the
+// map sees the two 64-element halves of a head as a third dimension (stride 128 bytes), so the box
+// [64, 16, 2] lands as two [16 x 128-byte] sub-tiles, each written with the 128-byte swizzle.
 bool make_pool_map(CUtensorMap* map, const void* pool, int64_t pool_rows, int64_t ekv) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(ekv), static_cast<cuuint64_t>(pool_rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ekv) * 2};
-    cuuint32_t box[2] = {kD / 2, kBS};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(ekv - kD / 2), static_cast<cuuint64_t>(pool_rows), 2};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ekv) * 2, kD};
+    cuuint32_t box[3] = {kD / 2, kBS, 2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int fast_smem_bytes(int /*g*/) {
-    // alignment slack + ring + per-warp outputs [4][4][128] + per-warp (max, sum) [2][16] + mbarriers
-    return 1024 + kStages * kTileBytes + (kConsumerWarps * 4 * kD + 32) * 4 + 2 * kStages * 8 + 16;
+int attn_probe() {
+    static int v = [] { const char* e = getenv("B200_ATTN_PROBE"); return e ? atoi(e) : 0; }();
+    return v;
 }
 
 template <int G>
 cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_t* tables, const uint32_t* seq_lens,
-                        float* part_o, float* part_ml, uint32_t* err, cudaStream_t stream) {
-    const int smem = fast_smem_bytes(4);   // the kernel lays out four head rows whatever G is
+                        float* part_o, float* part_ml, unsigned int* work_counter, int sm_count, uint32_t* err,
+                        cudaStream_t stream) {
+    const int smem = attn_smem_bytes();    // the kernel lays out four head rows whatever G is
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -264,9 +269,12 @@ cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_
     }
     const PagedAttnShape& sh = plan.shape;
     const int group = sh.num_q_heads / sh.num_kv_heads;
-    dim3 grid(sh.num_kv_heads * (group / G), plan.max_chunks, sh.batch * sh.l_new);
+    const int64_t items = int64_t(sh.num_kv_heads) * (group / G) * plan.max_chunks * sh.batch * sh.l_new;
+    const int64_t resident = int64_t(sm_count > 0 ? sm_count : 148) * kCtasPerSm;
+    dim3 grid(static_cast<unsigned>(items < resident ? items : resident));
     return launch_ex(paged_attention_decode_kernel<G>, grid, dim3(kFastThreads), smem, stream, 1, true, plan.tma_k,
-                     plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml, err);
+                     plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml,
+                     work_counter, err, attn_probe());
 }
 
 int grid_for(int64_t n, int threads) {
@@ -367,11 +375,11 @@ cudaError_t paged_attention_static_scratch(int device, void** out) {
 
 cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,
                                    const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
-                                   uint32_t* err, cudaStream_t stream) {
+                                   unsigned int* work_counter, int sm_count, uint32_t* err, cudaStream_t stream) {
     const PagedAttnShape& sh = plan.shape;
     const int64_t rows = int64_t(sh.batch) * sh.l_new;
     if (rows == 0) return cudaSuccess;
-    if (!plan.fast) {
+    if (!plan.fast || (reinterpret_cast<uintptr_t>(q) & 15) != 0) {   // the fast kernel bulk-copies 16-byte aligned q rows
         dim3 grid(static_cast<unsigned>(rows), sh.num_q_heads);
         if (plan.kv_bf16)
             paged_attention_generic_kernel<uint16_t><<<grid, kGenThreads, 0, stream>>>(
@@ -386,13 +394,13 @@ cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, co
     float* part_ml = part_o + pairs * plan.max_chunks * kD;
     const int group = sh.num_q_heads / sh.num_kv_heads;
     cudaError_t e;
-    if (group == 1) e = launch_fast<1>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, err, stream);
-    else if (group == 2) e = launch_fast<2>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, err, stream);
-    else e = launch_fast<4>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, err, stream);
+    if (group == 1) e = launch_fast<1>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, work_counter, sm_count, err, stream);
+    else if (group == 2) e = launch_fast<2>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, work_counter, sm_count, err, stream);
+    else e = launch_fast<4>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, work_counter, sm_count, err, stream);
     if (e != cudaSuccess) return e;
     const int blocks = static_cast<int>((pairs + 3) / 4);
     return launch_ex(paged_attention_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, true, part_o, part_ml,
-                     seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks, out);
+                     seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks, out, work_counter);
 }
 
 }  // namespace b200
