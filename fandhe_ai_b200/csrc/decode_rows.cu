@@ -359,6 +359,194 @@ qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int h
     }
 }
 
+// ------------------------------------------------------------------------------------ one wide CTA per row
+// Rows of up to 16384 columns: one CTA of up to 1024 threads owns a token row, every thread keeps VPT groups
+// of four columns in registers, and the two row-wide reductions are plain block reductions (warp shuffles, one
+// shared-memory exchange summed in warp order).  All rows of a decode batch run in one wave with no cluster
+// barriers in the dependency chain; the arithmetic per element is the same as in the cluster kernels.
+constexpr int kWideThreads = 1024;
+constexpr int kWideMaxVpt = 4;
+
+struct WideShared {
+    double wd[32];
+    float wf[32];
+};
+
+__device__ __forceinline__ double wide_sum(double v, WideShared& sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) sh.wd[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double r = 0.0;
+    const int nw = blockDim.x >> 5;
+    for (int w = 0; w < nw; ++w) r += sh.wd[w];
+    return r;
+}
+__device__ __forceinline__ float wide_max(float v, WideShared& sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0) sh.wf[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.0f;
+    const int nw = blockDim.x >> 5;
+    for (int w = 0; w < nw; ++w) r = fmaxf(r, sh.wf[w]);
+    return r;
+}
+__device__ __forceinline__ uint32_t quant4(const float4& v, float s) {
+    const uint32_t b0 = static_cast<uint32_t>(quant_i8(v.x, s)) & 0xFFu;
+    const uint32_t b1 = static_cast<uint32_t>(quant_i8(v.y, s)) & 0xFFu;
+    const uint32_t b2 = static_cast<uint32_t>(quant_i8(v.z, s)) & 0xFFu;
+    const uint32_t b3 = static_cast<uint32_t>(quant_i8(v.w, s)) & 0xFFu;
+    return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+}
+__device__ __forceinline__ float amax4(const float4& v) {
+    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+
+// |max| of the row, scale = amax / 127, int8 store.  v[k] holds group threadIdx.x + k * blockDim.x.
+template <int VPT>
+__device__ __forceinline__ void wide_quant(const float4 (&v)[VPT], int groups, WideShared& sh, int8_t* __restrict__ q_row,
+                                           float* __restrict__ scale_out) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+        if (int(threadIdx.x + k * blockDim.x) < groups) amax = fmaxf(amax, amax4(v[k]));
+    amax = wide_max(amax, sh);
+    const float s = amax / 127.0f;
+    if (threadIdx.x == 0) *scale_out = s;
+    uint32_t* q4 = reinterpret_cast<uint32_t*>(q_row);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) q4[g] = quant4(v[k], s);
+    }
+}
+
+template <int VPT>
+__device__ __forceinline__ void wide_norm_quant(float4 (&v)[VPT], int groups, int n, WideShared& sh,
+                                                const float* __restrict__ norm_w, float eps, int8_t* __restrict__ q_row,
+                                                float* __restrict__ scale_out) {
+    double acc = 0.0;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+        if (int(threadIdx.x + k * blockDim.x) < groups) {
+            const double a = v[k].x, b = v[k].y, c = v[k].z, e = v[k].w;
+            acc = fma(a, a, acc); acc = fma(b, b, acc); acc = fma(c, c, acc); acc = fma(e, e, acc);
+        }
+    acc = wide_sum(acc, sh);
+    const float inv_n = 1.0f / static_cast<float>(n);
+    const float rstd = static_cast<float>(1.0 / sqrt(fma(acc, static_cast<double>(inv_n), static_cast<double>(eps))));
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) {
+            const float4 w4 = *reinterpret_cast<const float4*>(norm_w + 4 * g);
+            v[k].x = __fmul_rn(__fmul_rn(v[k].x, rstd), w4.x);
+            v[k].y = __fmul_rn(__fmul_rn(v[k].y, rstd), w4.y);
+            v[k].z = __fmul_rn(__fmul_rn(v[k].z, rstd), w4.z);
+            v[k].w = __fmul_rn(__fmul_rn(v[k].w, rstd), w4.w);
+        }
+    }
+    wide_quant<VPT>(v, groups, sh, q_row, scale_out);
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kWideThreads)
+resid_norm_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int d, const float* __restrict__ sx_in,
+                             const float* __restrict__ sw, const float* __restrict__ pre, const float* __restrict__ norm_w,
+                             float eps, float* __restrict__ h, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+    __shared__ WideShared sh;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, groups = d / 4;
+    const size_t plane = static_cast<size_t>(M) * d;
+    const size_t base = static_cast<size_t>(m) * d;
+    const float sa = pre ? 0.0f : sx_in[m];
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) {
+            float4 y;
+            if (pre) {
+                y = *reinterpret_cast<const float4*>(pre + base + 4 * g);
+            } else {
+                const int4 a = sum_planes4(raw, splits, plane, base + 4 * g);
+                const float4 w4 = *reinterpret_cast<const float4*>(sw + 4 * g);
+                y.x = fmaf(static_cast<float>(a.x), sa * w4.x, 0.0f);
+                y.y = fmaf(static_cast<float>(a.y), sa * w4.y, 0.0f);
+                y.z = fmaf(static_cast<float>(a.z), sa * w4.z, 0.0f);
+                y.w = fmaf(static_cast<float>(a.w), sa * w4.w, 0.0f);
+            }
+            float4 hv = *reinterpret_cast<const float4*>(h + base + 4 * g);
+            hv.x = y.x + hv.x; hv.y = y.y + hv.y; hv.z = y.z + hv.z; hv.w = y.w + hv.w;
+            *reinterpret_cast<float4*>(h + base + 4 * g) = hv;
+            v[k] = hv;
+        }
+    }
+    wide_norm_quant<VPT>(v, groups, d, sh, norm_w, eps, xq + base, sx_out + m);
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kWideThreads)
+gate_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int F, const float* __restrict__ sx_in,
+                       const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+    __shared__ WideShared sh;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, groups = F / 4;
+    const size_t plane = static_cast<size_t>(M) * 2 * F;
+    const size_t base = static_cast<size_t>(m) * 2 * F;
+    const float sa = sx_in[m];
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) {
+            const int4 ag = sum_planes4(raw, splits, plane, base + 4 * g);
+            const int4 au = sum_planes4(raw, splits, plane, base + F + 4 * g);
+            const float4 wg = *reinterpret_cast<const float4*>(sw + 4 * g);
+            const float4 wu = *reinterpret_cast<const float4*>(sw + F + 4 * g);
+            v[k].x = __fmul_rn(silu(fmaf(static_cast<float>(ag.x), sa * wg.x, 0.0f)), fmaf(static_cast<float>(au.x), sa * wu.x, 0.0f));
+            v[k].y = __fmul_rn(silu(fmaf(static_cast<float>(ag.y), sa * wg.y, 0.0f)), fmaf(static_cast<float>(au.y), sa * wu.y, 0.0f));
+            v[k].z = __fmul_rn(silu(fmaf(static_cast<float>(ag.z), sa * wg.z, 0.0f)), fmaf(static_cast<float>(au.z), sa * wu.z, 0.0f));
+            v[k].w = __fmul_rn(silu(fmaf(static_cast<float>(ag.w), sa * wg.w, 0.0f)), fmaf(static_cast<float>(au.w), sa * wu.w, 0.0f));
+        }
+    }
+    wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * F, sx_out + m);
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kWideThreads)
+quant_rows_wide_kernel(const float* __restrict__ x, int n, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+    __shared__ WideShared sh;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, groups = n / 4;
+    const float* src = x + static_cast<size_t>(m) * n;
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) v[k] = *reinterpret_cast<const float4*>(src + 4 * g);
+    }
+    wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * n, sx_out + m);
+}
+
+// Groups of four columns per thread (1, 2 or 4) and the block size for a row of n columns; vpt = 0 when the
+// row is too wide (or not a multiple of 4) for the one-CTA kernels.
+void wide_shape(int n, int* vpt, int* threads) {
+    *vpt = 0;
+    *threads = 0;
+    if (n <= 0 || n % 4 != 0) return;
+    const int groups = n / 4;
+    int v = (groups + kWideThreads - 1) / kWideThreads;
+    if (v > kWideMaxVpt) return;
+    if (v == 3) v = 4;
+    *vpt = v;
+    *threads = ((groups + v - 1) / v + 31) / 32 * 32;
+}
+
 // Largest power-of-two cluster size <= 8 whose chunks are multiples of 4 columns, fit the shared chunk and
 // keep every thread busy; 0 when the row cannot be chunked that way.
 int pick_cluster(int n) {
@@ -390,6 +578,15 @@ cudaError_t embed_norm_quant_auto(const int* ids, const float* table, int vocab,
 cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, const float* sx_in, const float* sw,
                                   const float* pre, const float* norm_w, float eps, float* h, int8_t* xq, float* sx_out,
                                   cudaStream_t s) {
+    int vpt, threads;
+    wide_shape(d, &vpt, &threads);
+#define B200_WIDE_RESID(V)                                                                                              \
+    return launch_ex(resid_norm_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, d, sx_in, \
+                     sw, pre, norm_w, eps, h, xq, sx_out)
+    if (vpt == 1) B200_WIDE_RESID(1);
+    if (vpt == 2) B200_WIDE_RESID(2);
+    if (vpt == 4) B200_WIDE_RESID(4);
+#undef B200_WIDE_RESID
     const int cl = pick_cluster(d);
     if (cl == 0) return resid_norm_quant(raw, splits, M, d, sx_in, sw, pre, norm_w, eps, h, xq, sx_out, s);
     return launch_cluster(resid_norm_quant_cl_kernel, cl, M, s, raw, splits, M, d, d / cl, sx_in, sw, pre, norm_w, eps, h,
@@ -398,12 +595,26 @@ cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, cons
 
 cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
                             float* sx_out, cudaStream_t s) {
+    int vpt, threads;
+    wide_shape(F, &vpt, &threads);
+#define B200_WIDE_GATE(V)                                                                                        \
+    return launch_ex(gate_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, F, sx_in, \
+                     sw, xq, sx_out)
+    if (vpt == 1) B200_WIDE_GATE(1);
+    if (vpt == 2) B200_WIDE_GATE(2);
+    if (vpt == 4) B200_WIDE_GATE(4);
+#undef B200_WIDE_GATE
     const int cl = pick_cluster(F);
     if (cl == 0) return gate_quant(raw, splits, M, F, sx_in, sw, xq, sx_out, s);
     return launch_cluster(gate_quant_cl_kernel, cl, M, s, raw, splits, M, F, F / cl, sx_in, sw, xq, sx_out);
 }
 
 cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s) {
+    int vpt, threads;
+    wide_shape(n, &vpt, &threads);
+    if (vpt == 1) return launch_ex(quant_rows_wide_kernel<1>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
+    if (vpt == 2) return launch_ex(quant_rows_wide_kernel<2>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
+    if (vpt == 4) return launch_ex(quant_rows_wide_kernel<4>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
     const int cl = pick_cluster(n);
     if (cl == 0) return quantize_i8_per_row(x, M, n, xq, sx_out, s);
     return launch_cluster(quant_rows_cl_kernel, cl, M, s, x, n, n / cl, xq, sx_out);
