@@ -48,12 +48,6 @@ __device__ __forceinline__ double block_sum_d(double v, double* scratch) {
     return warp_sum_d(r);
 }
 
-__device__ __forceinline__ int quant_i8(float x, float scale) {
-    if (scale == 0.0f) return 0;
-    float r = rintf(x / scale);
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    return static_cast<int>(r);
-}
 
 // Sum of the split-K planes of element (m, n): integer addition, exact and order-free.
 __device__ __forceinline__ int sum_planes(const int* raw, int splits, size_t plane, size_t idx) {

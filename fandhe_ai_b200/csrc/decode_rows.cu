@@ -54,12 +54,6 @@ __device__ __forceinline__ float block_max(float v, RowShared& sh) {
     return r;
 }
 
-__device__ __forceinline__ int quant_i8(float x, float scale) {
-    if (scale == 0.0f) return 0;
-    float r = rintf(x / scale);
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    return static_cast<int>(r);
-}
 
 // Row-wide sum over the cluster in rank order.
 __device__ __forceinline__ double cluster_sum(cg::cluster_group& cl, RowShared& sh, double mine) {

@@ -455,9 +455,14 @@ int32_t enqueue_step(b200_decoder* d) {
                                c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
                                static_cast<uint16_t*>(L.v_pool), err, s));
         // attention over the cache (this rank's KV heads), then per-token quantisation
-        CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
-                                      d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s));
-        CU_TRY(quantize_rows_auto(d->attn_out, M, d->hq_l * dh, d->xq, d->sx, s));
+        if (paged_attention_can_quantize(L.attn)) {
+            CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, nullptr,
+                                          d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s, d->xq, d->sx));
+        } else {
+            CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
+                                          d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s));
+            CU_TRY(quantize_rows_auto(d->attn_out, M, d->hq_l * dh, d->xq, d->sx, s));
+        }
         // O projection (row-parallel) -> residual -> norm -> quant
         CU_TRY(gemm_launch(L.p_o, ep, err, s));
         launches += 6;

@@ -39,7 +39,11 @@ size_t paged_attention_scratch_bytes(const PagedAttnPlan& plan);
 // q, out: [batch, l_new, num_q_heads * head_dim] f32.  tables/seq_lens are device arrays.
 cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,
                                    const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
-                                   unsigned int* work_counter, int sm_count, uint32_t* err, cudaStream_t stream);
+                                   unsigned int* work_counter, int sm_count, uint32_t* err, cudaStream_t stream,
+                                   int8_t* xq_out = nullptr, float* sx_out = nullptr);
+// True when the launch can also emit the per-token int8 quantisation of the output rows (xq_out / sx_out):
+// `out` may then be null.  The caller must also pass a 16-byte aligned q.
+bool paged_attention_can_quantize(const PagedAttnPlan& plan);
 
 // Device address (for the given, current device) and size of the file-scope static scratch array that
 // stands in for `scratch` when the caller must not allocate.  The first call on a device looks the address

@@ -221,6 +221,54 @@ paged_attention_combine_kernel(const float* __restrict__ part_o, const float* __
     *reinterpret_cast<float4*>(out + pair * kD + lane * 4) = make_float4(o.x / l, o.y / l, o.z / l, o.w / l);
 }
 
+// The same merge for a whole query row at once (one warp per q head, at most 32 heads), followed by the
+// per-token int8 quantisation of the row [Hq * 128] that the output projection reads: scale = |max| / 127.
+// `out` (f32) is written too when it is not null.
+__global__ void __launch_bounds__(1024)
+paged_attention_combine_quant_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_tokens,
+                                     int max_chunks, float* __restrict__ out, int8_t* __restrict__ xq,
+                                     float* __restrict__ sx, unsigned int* __restrict__ work_counter) {
+    __shared__ float warp_max[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    if (blockIdx.x == 0 && threadIdx.x == 0) *work_counter = 0u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x;
+    const int64_t pair = int64_t(row) * sh.num_q_heads + warp;
+    const int b = row / sh.l_new, i = row % sh.l_new;
+    const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
+    const int nchunks = limit > 0 ? (limit + chunk_tokens - 1) / chunk_tokens : 0;
+    const float* ml = part_ml + pair * max_chunks * 2;
+    float m = -INFINITY;
+    for (int c = 0; c < nchunks; ++c) m = fmaxf(m, ml[2 * c]);
+    float l = 0.0f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < nchunks; ++c) {
+        const float w = exp2f(ml[2 * c] - m);
+        l = fmaf(ml[2 * c + 1], w, l);
+        const float4 po = *reinterpret_cast<const float4*>(part_o + (pair * max_chunks + c) * kD + lane * 4);
+        o.x = fmaf(po.x, w, o.x); o.y = fmaf(po.y, w, o.y); o.z = fmaf(po.z, w, o.z); o.w = fmaf(po.w, w, o.w);
+    }
+    if (nchunks == 0) l = 1.0f;
+    const float4 v = make_float4(o.x / l, o.y / l, o.z / l, o.w / l);
+    if (out) *reinterpret_cast<float4*>(out + pair * kD + lane * 4) = v;
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+    if (lane == 0) warp_max[warp] = amax;
+    __syncthreads();
+    amax = 0.0f;
+    for (int w = 0; w < sh.num_q_heads; ++w) amax = fmaxf(amax, warp_max[w]);
+    const float scale = amax / 127.0f;
+    if (threadIdx.x == 0) sx[row] = scale;
+    const uint32_t b0 = static_cast<uint32_t>(quant_i8(v.x, scale)) & 0xFFu;
+    const uint32_t b1 = static_cast<uint32_t>(quant_i8(v.y, scale)) & 0xFFu;
+    const uint32_t b2 = static_cast<uint32_t>(quant_i8(v.z, scale)) & 0xFFu;
+    const uint32_t b3 = static_cast<uint32_t>(quant_i8(v.w, scale)) & 0xFFu;
+    reinterpret_cast<uint32_t*>(xq + pair * kD)[lane] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -337,6 +385,8 @@ cudaError_t paged_attention_make_plan(PagedAttnPlan* plan, const PagedAttnShape&
     return cudaSuccess;
 }
 
+bool paged_attention_can_quantize(const PagedAttnPlan& plan) { return plan.fast && plan.shape.num_q_heads <= 32; }
+
 size_t paged_attention_scratch_bytes(const PagedAttnPlan& plan) {
     if (!plan.fast) return 0;
     const size_t pairs = size_t(plan.shape.batch) * plan.shape.l_new * plan.shape.num_q_heads;
@@ -375,11 +425,13 @@ cudaError_t paged_attention_static_scratch(int device, void** out) {
 
 cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,
                                    const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
-                                   unsigned int* work_counter, int sm_count, uint32_t* err, cudaStream_t stream) {
+                                   unsigned int* work_counter, int sm_count, uint32_t* err, cudaStream_t stream,
+                                   int8_t* xq_out, float* sx_out) {
     const PagedAttnShape& sh = plan.shape;
     const int64_t rows = int64_t(sh.batch) * sh.l_new;
     if (rows == 0) return cudaSuccess;
     if (!plan.fast || (reinterpret_cast<uintptr_t>(q) & 15) != 0) {   // the fast kernel bulk-copies 16-byte aligned q rows
+        if (xq_out || !out) return cudaErrorInvalidValue;             // only the fast path quantises its output
         dim3 grid(static_cast<unsigned>(rows), sh.num_q_heads);
         if (plan.kv_bf16)
             paged_attention_generic_kernel<uint16_t><<<grid, kGenThreads, 0, stream>>>(
@@ -398,6 +450,10 @@ cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, co
     else if (group == 2) e = launch_fast<2>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, work_counter, sm_count, err, stream);
     else e = launch_fast<4>(plan, q, tables_dev, seq_lens_dev, part_o, part_ml, work_counter, sm_count, err, stream);
     if (e != cudaSuccess) return e;
+    if (xq_out)
+        return launch_ex(paged_attention_combine_quant_kernel, dim3(static_cast<unsigned>(rows)), dim3(32 * sh.num_q_heads),
+                         0, stream, 1, true, part_o, part_ml, seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks,
+                         out, xq_out, sx_out, work_counter);
     const int blocks = static_cast<int>((pairs + 3) / 4);
     return launch_ex(paged_attention_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, true, part_o, part_ml,
                      seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks, out, work_counter);

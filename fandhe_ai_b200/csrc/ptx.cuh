@@ -206,4 +206,13 @@ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
     return u >> 16;
 }
 
+// Symmetric int8 quantisation of one value: round-to-nearest-even of x / scale, clamped to [-127, 127];
+// scale 0 (an all-zero row) gives 0.
+__device__ __forceinline__ int quant_i8(float x, float scale) {
+    if (scale == 0.0f) return 0;
+    float r = rintf(x / scale);
+    r = fminf(fmaxf(r, -127.0f), 127.0f);
+    return static_cast<int>(r);
+}
+
 }  // namespace b200

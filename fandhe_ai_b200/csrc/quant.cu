@@ -33,12 +33,6 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return r;
 }
 
-__device__ __forceinline__ int quant_i8(float x, float scale) {
-    if (scale == 0.0f) return 0;
-    float r = rintf(x / scale);
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    return static_cast<int>(r);
-}
 
 __global__ void __launch_bounds__(kRowThreads)
 quantize_i8_per_row_kernel(const float* __restrict__ x, int64_t cols, int8_t* __restrict__ q, float* __restrict__ scale) {
