@@ -75,9 +75,14 @@ def run_gemm(args):
             shapes.append((m, nk, nk, ACT_NONE))
     shapes.append((1024, 2 * 14336, 4096, ACT_SILU_GATE))
     shapes.append((8192, 2 * 14336, 4096, ACT_SILU_GATE))
-    if args.quick:
+    if args.shape:
+        m, n, k = (int(v) for v in args.shape.split(","))
+        shapes = [(m, n, k, ACT_SILU_GATE if args.gate else ACT_NONE)]
+    elif args.quick:
         shapes = [(128, 4096, 4096, ACT_NONE), (4096, 4096, 4096, ACT_NONE), (8192, 8192, 8192, ACT_NONE)]
     for op, name in ((FP8_E4M3, "fp8_e4m3"), (I8, "int8")):
+        if args.operands and not name.startswith(args.operands):
+            continue
         for m, n, k, act in shapes:
             ms = bench_gemm(be, op, m, n, k, act, args.iters, args.warmup, args.tile, args.splits)
             ops = 2.0 * m * n * k
@@ -155,6 +160,9 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--shape", default="", help="m,n,k: only this GEMM shape")
+    ap.add_argument("--gate", action="store_true", help="with --shape: the SiLU-gated epilogue (n counts gate + up rows)")
+    ap.add_argument("--operands", default="", help="fp8 or int8: only this operand type")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--chunk-blocks", type=int, default=0)

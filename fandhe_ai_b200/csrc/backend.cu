@@ -417,6 +417,7 @@ int32_t b200_gemm_i8_s32(b200_ctx* ctx, const b200_buf* a, size_t a_off, const b
     cudaError_t e = gemm_make_plan(&plan, kGemmI8, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m),
                                    int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why);
     if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
+    if (ctx->tune_splits == 0) gemm_plan_make_persistent(&plan, ctx->sm_count);
     GemmEpilogue ep;
     if (plan.out_planes == 1) {      // one pass over K, or split-K reduced inside a cluster
         ep.raw = buf_ptr<void>(acc, acc_off);
@@ -487,8 +488,22 @@ int32_t b200_gemm_q8_scaled(b200_ctx* ctx, int32_t op_dtype, const b200_buf* a, 
     // and the row-wise finish applies the epilogue; otherwise the epilogue is fused into the GEMM.
     GemmPlan plan;
     const char* why = "";
-    cudaError_t e = gemm_make_plan(&plan, kind, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m),
-                                   int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why);
+    cudaError_t e;
+    if (ctx->tune_splits == 0) {
+        // default: the persistent kernel produces every epilogue (gated too) inside the GEMM launch
+        e = gemm_make_plan(&plan, kind, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m), int(n),
+                           int(k), gate ? 1 : 0, 1, ctx->tune_bn, &why);
+        if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
+        gemm_plan_make_persistent(&plan, ctx->sm_count);
+        if (plan.persist) {
+            e = gemm_launch(plan, ep, ctx->err_dev, ctx->stream);
+            if (e != cudaSuccess)
+                return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("gemm_q8_scaled: ") + cudaGetErrorString(e));
+            return B200_OK;
+        }
+    }
+    e = gemm_make_plan(&plan, kind, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m),
+                       int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why);
     if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
     if (plan.splits > 1 && plan.cluster && !gate) {
         // split-K reduced inside a cluster: the epilogue runs on the reduced values in the same kernel

@@ -14,6 +14,8 @@
 // gemm_mma_f16 (crates/backend-cuda/src/kernels_mma.rs:227-375).
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "gemm_tc5.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -330,6 +332,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
 }
 
+#include "gemm_tc5_persist.cuh"
+
 // Sums the split-K partial planes in plane order and applies the same epilogue as the
 // fused path.  One thread per four output columns.
 template <bool kInt8>
@@ -451,7 +455,42 @@ cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t 
                        plan.tma_a, plan.tma_b, args);
 }
 
+constexpr int kMaxSmem = 232448;   // dynamic shared memory a CTA may ask for on sm_100
+
+template <int BN, bool kInt8>
+cudaError_t launch_persist_t(const GemmPlan& plan, const PersistArgs& args, cudaStream_t stream) {
+    const int stage_bytes = kABytes + BN * kBK;
+    const int smem = plan.stages * stage_bytes + 1024 + 8 * (2 * plan.stages + 5) + 16;
+    static int configured = 0;
+    if (configured < smem) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_persist_kernel<BN, kInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    return launch_ex(gemm_tc5_persist_kernel<BN, kInt8>, dim3(plan.grid), dim3(kPersistThreads), smem, stream, 1, true,
+                     plan.tma_a, plan.tma_b, args);
+}
+
 }  // namespace
+
+void gemm_plan_make_persistent(GemmPlan* plan, int sm_count) {
+    if (sm_count <= 0) return;
+    const int bn = plan->bn;
+    if (bn != 128 && bn != 256) return;
+    const int out_cols = plan->gate ? bn / 2 : bn;
+    const int n_out = plan->gate ? plan->N / 2 : plan->N;
+    const long long tiles = static_cast<long long>((plan->M + kBM - 1) / kBM) * ((n_out + out_cols - 1) / out_cols);
+    if (tiles > 0x3FFFFFFF || tiles < 2LL * sm_count) return;     // below two waves the one-tile kernel does as well
+    const int stage_bytes = kABytes + bn * kBK;
+    int stages = (kMaxSmem - 1024 - 256) / stage_bytes;
+    if (stages > 8) stages = 8;
+    plan->persist = 1;
+    plan->grid = sm_count;
+    plan->stages = stages;
+    plan->splits = 1;
+    plan->cluster = 0;
+    plan->out_planes = 1;
+}
 
 cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* b, int M, int N, int K, int gate,
                            int want_splits, int want_bn, const char** why) {
@@ -486,7 +525,7 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     int splits = want_splits;
     if (splits <= 0) {
         splits = 1;
-        if (tiles < 148) {
+        if (2 * tiles <= 148) {      // splitting pays only when it at least doubles the number of busy SMs
             int cap = 296 / tiles;
             if (cap > kb_total / 2) cap = kb_total / 2;
             if (cap > 8) cap = 8;
@@ -516,6 +555,26 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
 }
 
 cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* err, cudaStream_t stream) {
+    if (plan.persist) {
+        if (!ep.fused && plan.gate) return cudaErrorInvalidValue;   // raw output always uses the plain column layout
+        PersistArgs pa;
+        pa.M = plan.M; pa.N = plan.N; pa.K = plan.K;
+        pa.stages = plan.stages;
+        pa.kb_total = (plan.K + kBK - 1) / kBK;
+        const int out_cols = plan.gate ? plan.bn / 2 : plan.bn;
+        const int n_out = plan.gate ? plan.N / 2 : plan.N;
+        pa.tiles_m = (plan.M + kBM - 1) / kBM;
+        pa.tiles_n = (n_out + out_cols - 1) / out_cols;
+        pa.group_m = 16;
+        pa.gate = plan.gate;
+        pa.n_half = plan.N / 2;
+        pa.vec16 = ((reinterpret_cast<uintptr_t>(ep.b_scale) | reinterpret_cast<uintptr_t>(ep.bias)) & 15) == 0 ? 1 : 0;
+        pa.ep = ep;
+        pa.err = err;
+        const bool i8p = plan.kind == kGemmI8;
+        if (plan.bn == 128) return i8p ? launch_persist_t<128, true>(plan, pa, stream) : launch_persist_t<128, false>(plan, pa, stream);
+        return i8p ? launch_persist_t<256, true>(plan, pa, stream) : launch_persist_t<256, false>(plan, pa, stream);
+    }
     KernelArgs args;
     args.M = plan.M; args.N = plan.N; args.K = plan.K;
     args.stages = plan.stages;

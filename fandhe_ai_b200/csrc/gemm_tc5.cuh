@@ -41,7 +41,14 @@ struct GemmPlan {
     int gate = 0;
     int cluster = 0;     // the splits of a tile run as one cluster and reduce through distributed shared memory
     int out_planes = 1;  // raw planes the kernel writes: 1 with the cluster reduction, else `splits`
+    // persistent form (gemm_plan_make_persistent): one CTA per SM takes whole tiles round-robin
+    int persist = 0;
+    int grid = 0;        // resident CTAs
 };
+
+// Switches a plan to the persistent kernel when the problem has at least two waves of tiles on `sm_count` SMs.
+// Afterwards splits == 1, out_planes == 1 and every epilogue (raw, fused, gated) is produced inside the launch.
+void gemm_plan_make_persistent(GemmPlan* plan, int sm_count);
 
 // Picks tile width / stage count / split count for a shape.  `want_splits` <= 0
 // lets the heuristic choose (it only splits when the tile grid alone would leave
