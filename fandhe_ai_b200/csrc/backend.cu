@@ -417,7 +417,7 @@ int32_t b200_gemm_i8_s32(b200_ctx* ctx, const b200_buf* a, size_t a_off, const b
     cudaError_t e = gemm_make_plan(&plan, kGemmI8, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m),
                                    int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why);
     if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
-    if (ctx->tune_splits == 0) gemm_plan_make_persistent(&plan, ctx->sm_count);
+    if (ctx->tune_splits == 0) gemm_plan_make_persistent(&plan, ctx->sm_count, false);
     GemmEpilogue ep;
     if (plan.out_planes == 1) {      // one pass over K, or split-K reduced inside a cluster
         ep.raw = buf_ptr<void>(acc, acc_off);
@@ -494,7 +494,7 @@ int32_t b200_gemm_q8_scaled(b200_ctx* ctx, int32_t op_dtype, const b200_buf* a, 
         e = gemm_make_plan(&plan, kind, buf_ptr<const void>(a, a_off), buf_ptr<const void>(w, w_off), int(m), int(n),
                            int(k), gate ? 1 : 0, 1, ctx->tune_bn, &why);
         if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
-        gemm_plan_make_persistent(&plan, ctx->sm_count);
+        gemm_plan_make_persistent(&plan, ctx->sm_count, true);
         if (plan.persist) {
             e = gemm_launch(plan, ep, ctx->err_dev, ctx->stream);
             if (e != cudaSuccess)

@@ -778,7 +778,7 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     size_t raw_need = 0;
     auto plan = [&](GemmPlan* p, size_t w_off, int N, int K) -> cudaError_t {
         cudaError_t e = gemm_make_plan(p, kGemmI8, d->xq, d->payload + w_off, M, N, K, 0, d->ctx->tune_splits, d->ctx->tune_bn, &why);
-        if (e == cudaSuccess && d->ctx->tune_splits == 0) gemm_plan_make_persistent(p, d->ctx->sm_count);
+        if (e == cudaSuccess && d->ctx->tune_splits == 0) gemm_plan_make_persistent(p, d->ctx->sm_count, false);
         if (e == cudaSuccess) raw_need = std::max(raw_need, gemm_raw_elems(*p));
         return e;
     };
@@ -798,7 +798,7 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     {
         cudaError_t e = gemm_make_plan(&d->p_lm, kGemmI8, d->xq, d->payload + d->w_lm, M, c.vocab, dm, 0, 1, d->ctx->tune_bn, &why);
         if (e != cudaSuccess) return fail(B200_UNSUPPORTED, std::string("decoder_begin: ") + why);
-        if (d->ctx->tune_splits == 0) gemm_plan_make_persistent(&d->p_lm, d->ctx->sm_count);
+        if (d->ctx->tune_splits == 0) gemm_plan_make_persistent(&d->p_lm, d->ctx->sm_count, true);
     }
     if (raw_need > d->raw_elems) {
         cudaFree(d->raw);

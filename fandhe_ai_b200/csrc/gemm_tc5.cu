@@ -473,19 +473,22 @@ cudaError_t launch_persist_t(const GemmPlan& plan, const PersistArgs& args, cuda
 
 }  // namespace
 
-void gemm_plan_make_persistent(GemmPlan* plan, int sm_count) {
+void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue) {
     if (sm_count <= 0) return;
     const int bn = plan->bn;
     if (bn != 128 && bn != 256) return;
     const int out_cols = plan->gate ? bn / 2 : bn;
     const int n_out = plan->gate ? plan->N / 2 : plan->N;
     const long long tiles = static_cast<long long>((plan->M + kBM - 1) / kBM) * ((n_out + out_cols - 1) / out_cols);
-    if (tiles > 0x3FFFFFFF || tiles < 2LL * sm_count) return;     // below two waves the one-tile kernel does as well
+    // The fused epilogues are what the one-tile kernel is slow at (four epilogue warps, nothing to overlap them
+    // with), so they switch at half a wave of tiles; raw accumulator output switches at two waves.
+    const long long min_tiles = fused_epilogue ? (sm_count + 1) / 2 : 2LL * sm_count;
+    if (tiles > 0x3FFFFFFF || tiles < min_tiles) return;
     const int stage_bytes = kABytes + bn * kBK;
     int stages = (kMaxSmem - 1024 - 256) / stage_bytes;
     if (stages > 8) stages = 8;
     plan->persist = 1;
-    plan->grid = sm_count;
+    plan->grid = tiles < sm_count ? static_cast<int>(tiles) : sm_count;
     plan->stages = stages;
     plan->splits = 1;
     plan->cluster = 0;

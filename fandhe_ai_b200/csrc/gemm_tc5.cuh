@@ -46,9 +46,10 @@ struct GemmPlan {
     int grid = 0;        // resident CTAs
 };
 
-// Switches a plan to the persistent kernel when the problem has at least two waves of tiles on `sm_count` SMs.
-// Afterwards splits == 1, out_planes == 1 and every epilogue (raw, fused, gated) is produced inside the launch.
-void gemm_plan_make_persistent(GemmPlan* plan, int sm_count);
+// Switches a plan to the persistent kernel when the problem has enough tiles for `sm_count` SMs: half a wave when
+// the launch will use a fused epilogue, two waves for raw accumulator output.  Afterwards splits == 1,
+// out_planes == 1 and every epilogue (raw, fused, gated) is produced inside the launch.
+void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue);
 
 // Picks tile width / stage count / split count for a shape.  `want_splits` <= 0
 // lets the heuristic choose (it only splits when the tile grid alone would leave

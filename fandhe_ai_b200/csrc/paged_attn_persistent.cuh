@@ -103,7 +103,7 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
                               const float* __restrict__ q, const uint32_t* __restrict__ block_tables,
                               const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_blocks,
                               int max_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
-                              unsigned int* __restrict__ work_counter, uint32_t* err, int probe) {
+                              unsigned int* __restrict__ work_counter, uint32_t* err) {
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t ring = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     uint8_t* ring_ptr = smem_dyn + (ring - smem_u32(smem_dyn));
@@ -210,7 +210,7 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
                 for (int w = 0; w < kConsumerWarps; ++w) {      // block j0 + w goes to consumer warp w
                     const uint32_t blk = __shfl_sync(0xffffffffu, my_blk, (j0 + w) & 31);
                     if (j0 + w < nb) {
-                        if (lane == 0 && probe != 2) {
+                        if (lane == 0) {
 #pragma unroll
                             for (int kv = 0; kv < 2 && ok; ++kv) {
                                 const int li = cnt[w] + kv;
@@ -303,10 +303,10 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
             // ---- scores of block j
             const int tk = my_tiles;
             const int sk = warp * kStagesPerWarp + tk % kStagesPerWarp;
-            if (ok && probe != 2) ok = wait_warp(full_bar(sk), (tk / kStagesPerWarp) & 1);
+            if (ok) ok = wait_warp(full_bar(sk), (tk / kStagesPerWarp) & 1);
             const uint32_t ktile = ring + sk * kTileBytes;
             float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};   // tokens 0..7 and 8..15
-            if (probe != 1) {
+            {
                 const int tok = (mat >> 1) * 8 + r8;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
@@ -317,7 +317,7 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
                 }
             }
             __syncwarp();
-            if (lane == 0 && probe != 2) mbar_arrive(empty_bar(sk));
+            if (lane == 0) mbar_arrive(empty_bar(sk));
             // rows g and g + 8 of this thread, then the partner lane with the other rows of the same head
             float s00 = c0[0] + c0[2], s01 = c0[1] + c0[3], s10 = c1[0] + c1[2], s11 = c1[1] + c1[3];
             s00 += __shfl_xor_sync(0xffffffffu, s00, 16);
@@ -353,7 +353,7 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
             // ---- weighted sum of block j's V rows
             const int tv = tk + 1;
             const int sv = warp * kStagesPerWarp + tv % kStagesPerWarp;
-            if (ok && probe != 2) ok = wait_warp(full_bar(sv), (tv / kStagesPerWarp) & 1);
+            if (ok) ok = wait_warp(full_bar(sv), (tv / kStagesPerWarp) & 1);
             const uint32_t vtile = ring + sv * kTileBytes;
             const int valid = ntok - j * kBS;
             if (valid < kBS) {
@@ -366,7 +366,7 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
                 fence_proxy_async();      // these stores precede the next TMA write into the same stage
                 __syncwarp();
             }
-            if (probe != 1) {
+            {
                 const int tok = (mat & 1) * 8 + r8;
 #pragma unroll
                 for (int n2 = 0; n2 < 8; ++n2) {          // two 8-dim groups per ldmatrix
@@ -377,7 +377,7 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
                 }
             }
             __syncwarp();
-            if (lane == 0 && probe != 2) mbar_arrive(empty_bar(sv));
+            if (lane == 0) mbar_arrive(empty_bar(sv));
             my_tiles += 2;
         }
 

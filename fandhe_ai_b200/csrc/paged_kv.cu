@@ -299,11 +299,6 @@ bool make_pool_map(CUtensorMap* map, const void* pool, int64_t pool_rows, int64_
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int attn_probe() {
-    static int v = [] { const char* e = getenv("B200_ATTN_PROBE"); return e ? atoi(e) : 0; }();
-    return v;
-}
-
 template <int G>
 cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_t* tables, const uint32_t* seq_lens,
                         float* part_o, float* part_ml, unsigned int* work_counter, int sm_count, uint32_t* err,
@@ -322,7 +317,7 @@ cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_
     dim3 grid(static_cast<unsigned>(items < resident ? items : resident));
     return launch_ex(paged_attention_decode_kernel<G>, grid, dim3(kFastThreads), smem, stream, 1, true, plan.tma_k,
                      plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml,
-                     work_counter, err, attn_probe());
+                     work_counter, err);
 }
 
 int grid_for(int64_t n, int threads) {
