@@ -45,6 +45,10 @@ CONFIGS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the decode-attention kernel divided by its algorithmic bytes, from the
+# ncu capture summarised in profiles/paged_attention_decode_config3_ncu.md: (1171.3 MB + 22.0 MB) / 1162.8 MB.
+ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0263
+
 def read_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -331,9 +335,12 @@ def run_gpu(args, cfg, rank, world, local_rank):
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": batch * 4, "d2h_bytes_per_step": batch * 4},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"kernel": "paged_attention_decode_kernel (+ combine)", "bound": "hbm",
+            "roofline": {"kernel": "paged_attention_decode_kernel (+ combine_quant)", "bound": "hbm",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "ms_per_launch": attn_ms,
+                         "traffic": attn_bytes * ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                         "traffic_note": "DRAM read + write bytes of one ncu capture of the same kernel on a smaller case "
+                                         "(batch 64, 1.16 GB of KV), scaled by the algorithmic bytes of this launch",
+                         "peak_kind": peak_kind, "ms_per_launch": attn_ms,
                          "algorithmic_bytes_per_launch": attn_bytes},
             "cpu_baseline": cpu,
             "plan": plan,
