@@ -331,7 +331,11 @@ def run_gpu(args, cfg, rank, world, local_rank):
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": workload_config(args, cfg, world),
+            "config": dict(workload_config(args, cfg, world),
+                           collective=("none" if world == 1 else
+                                       "row-parallel outputs finished over CUDA-IPC mapped peer blocks (one kernel: peer loads, "
+                                       "residual + RMSNorm + int8, rows delivered to every rank)" if dec.tp_exchange else
+                                       "ncclAllReduce of f32 partials")),
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": batch * 4, "d2h_bytes_per_step": batch * 4},
             "gpu_launches": int(launches),
             "clocks": clocks,

@@ -130,6 +130,7 @@ SIGNATURES = {
     "b200_decoder_init_random": (_I32, [_P, _U64, C.c_float]),
     "b200_nccl_unique_id": (_I32, [_P]),
     "b200_decoder_init_tp": (_I32, [_P, _P]),
+    "b200_decoder_tp_exchange": (_I32, [_P]),
     "b200_decoder_begin": (_I32, [_P, _I32, _P, _P]),
     "b200_decoder_fill_cache_random": (_I32, [_P, _U64, C.c_float]),
     "b200_decoder_step": (_I32, [_P, _P, _P]),

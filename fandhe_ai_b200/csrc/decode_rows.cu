@@ -527,6 +527,150 @@ quant_rows_wide_kernel(const float* __restrict__ x, int n, int8_t* __restrict__ 
     wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * n, sx_out + m);
 }
 
+// ------------------------------------------------------------------------------------ cross-GPU finish
+// Tensor parallel, after a row-parallel GEMM: every rank holds an f32 partial [M, d] of the layer output in its
+// exchange block.  Rank r owns the token rows [r * rows, (r + 1) * rows): it adds the partials of its rows over
+// all ranks (peer loads, rank order), adds the residual stream (which therefore lives only on the owner), applies
+// RMSNorm and the per-token int8 quantisation, and stores the finished int8 row and its scale into the exchange
+// block of every rank - the A operand of the next GEMM.  Two flag exchanges frame it: "my partial is complete"
+// before the loads and "my rows are delivered" after the stores.  Flags are epoch counters written by the peer
+// into the waiting rank's own memory; every wait is bounded and reports kErrPeerWait.
+//
+// Layout of a rank's exchange block: flags (ready[tp] at +0, done[tp] at +256), then sx, xq and part at the
+// given offsets.  One CTA per owned row.
+struct TpFinishArgs {
+    uint8_t* const* peers;     // [tp] base of every rank's exchange block (this rank's own included)
+    size_t o_sx, o_xq, o_part; // byte offsets inside a block
+    int tp, rank;
+    int rows;                  // rows per rank
+    int d;                     // row width
+    const float* norm_w;
+    float eps;
+    float* h;                  // [M, d] residual stream (only the owned rows are kept current)
+    uint32_t* epoch;           // this rank's call counter
+    unsigned int* arrived;     // CTAs of this launch that have delivered their row
+    uint32_t* err;
+};
+
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* err) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        // epochs only grow; the difference is taken modulo 2^32 so that the comparison survives a wrap
+        if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    }
+    atomicCAS(err, 0u, static_cast<uint32_t>(kErrPeerWait));
+    return false;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kWideThreads)
+tp_finish_kernel(TpFinishArgs a) {
+    __shared__ WideShared sh;
+    __shared__ int s_ok, s_last;
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t epoch = *a.epoch + 1;
+    uint8_t* mine = a.peers[a.rank];
+    const uint32_t* ready = reinterpret_cast<const uint32_t*>(mine);
+    const uint32_t* done = reinterpret_cast<const uint32_t*>(mine + 256);
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    // 1. this rank's partial is complete (the GEMM before this kernel has finished): tell every rank
+    if (blockIdx.x == 0 && threadIdx.x < a.tp) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t*>(a.peers[threadIdx.x]) + a.rank, epoch);
+    }
+    // 2. wait for every rank's partial
+    if (threadIdx.x < a.tp) {
+        if (!wait_flag(ready + threadIdx.x, epoch, a.err)) s_ok = 0;
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    const int row = a.rank * a.rows + blockIdx.x;
+    const int groups = a.d / 4;
+    const size_t base = static_cast<size_t>(row) * a.d;
+    float4 v[VPT];
+    if (ok) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int g = threadIdx.x + k * blockDim.x;
+            if (g < groups) {
+                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int p = 0; p < a.tp; ++p) {
+                    const float* part = reinterpret_cast<const float*>(a.peers[p] + a.o_part);
+                    const float4 x = ld_relaxed_sys_f4(part + base + 4 * g);
+                    y.x += x.x; y.y += x.y; y.z += x.z; y.w += x.w;
+                }
+                float4 hv = *reinterpret_cast<const float4*>(a.h + base + 4 * g);
+                hv.x = y.x + hv.x; hv.y = y.y + hv.y; hv.z = y.z + hv.z; hv.w = y.w + hv.w;
+                *reinterpret_cast<float4*>(a.h + base + 4 * g) = hv;
+                v[k] = hv;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // RMSNorm and the per-token scale (same arithmetic as wide_norm_quant)
+    double acc = 0.0;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+        if (int(threadIdx.x + k * blockDim.x) < groups) {
+            const double x0 = v[k].x, x1 = v[k].y, x2 = v[k].z, x3 = v[k].w;
+            acc = fma(x0, x0, acc); acc = fma(x1, x1, acc); acc = fma(x2, x2, acc); acc = fma(x3, x3, acc);
+        }
+    acc = wide_sum(acc, sh);
+    const float inv_n = 1.0f / static_cast<float>(a.d);
+    const float rstd = static_cast<float>(1.0 / sqrt(fma(acc, static_cast<double>(inv_n), static_cast<double>(a.eps))));
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) {
+            const float4 w4 = *reinterpret_cast<const float4*>(a.norm_w + 4 * g);
+            v[k].x = __fmul_rn(__fmul_rn(v[k].x, rstd), w4.x);
+            v[k].y = __fmul_rn(__fmul_rn(v[k].y, rstd), w4.y);
+            v[k].z = __fmul_rn(__fmul_rn(v[k].z, rstd), w4.z);
+            v[k].w = __fmul_rn(__fmul_rn(v[k].w, rstd), w4.w);
+            amax = fmaxf(amax, amax4(v[k]));
+        }
+    }
+    amax = wide_max(amax, sh);
+    const float s = amax / 127.0f;
+    // 3. deliver the row to every rank
+    if (ok) {
+        for (int p = 0; p < a.tp; ++p) {
+            uint32_t* q4 = reinterpret_cast<uint32_t*>(a.peers[p] + a.o_xq + base);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int g = threadIdx.x + k * blockDim.x;
+                if (g < groups) q4[g] = quant4(v[k], s);
+            }
+            if (threadIdx.x == 0) reinterpret_cast<float*>(a.peers[p] + a.o_sx)[row] = s;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 4. the last CTA of this launch tells every rank that this rank's rows are delivered, waits for the others'
+    //    rows and advances the call counter
+    if (threadIdx.x == 0) {
+        const unsigned int seen = atomicAdd(a.arrived, 1u);
+        s_last = seen == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        if (threadIdx.x < a.tp) {
+            __threadfence_system();
+            st_release_sys(reinterpret_cast<uint32_t*>(a.peers[threadIdx.x] + 256) + a.rank, epoch);
+            wait_flag(done + threadIdx.x, epoch, a.err);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            *a.arrived = 0u;
+            *a.epoch = epoch;
+        }
+    }
+}
+
 // Groups of four columns per thread (1, 2 or 4) and the block size for a row of n columns; vpt = 0 when the
 // row is too wide (or not a multiple of 4) for the one-CTA kernels.
 void wide_shape(int n, int* vpt, int* threads) {
@@ -634,6 +778,24 @@ cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int 
     return launch_ex(qkv_rope_append_par_kernel, grid, dim3(kThreads), 0, s, 1, true, raw, splits, M, hq, hkv, dh, hpc, sx_in,
                      sw, cos_t, sin_t, max_pos, positions, block_tables, max_blocks_per_seq, block_size, num_blocks, q_out,
                      k_pool, v_pool, err);
+}
+
+bool tp_finish_supported(int d) {
+    int vpt, threads;
+    wide_shape(d, &vpt, &threads);
+    return vpt != 0;
+}
+
+cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
+                      const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
+                      cudaStream_t s) {
+    int vpt, threads;
+    wide_shape(d, &vpt, &threads);
+    TpFinishArgs a{peers, o_sx, o_xq, o_part, tp, rank, rows, d, norm_w, eps, h, epoch, arrived, err};
+    if (vpt == 1) return launch_ex(tp_finish_kernel<1>, dim3(rows), dim3(threads), 0, s, 1, true, a);
+    if (vpt == 2) return launch_ex(tp_finish_kernel<2>, dim3(rows), dim3(threads), 0, s, 1, true, a);
+    if (vpt == 4) return launch_ex(tp_finish_kernel<4>, dim3(rows), dim3(threads), 0, s, 1, true, a);
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace b200

@@ -18,6 +18,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -197,7 +198,7 @@ namespace {
 
 typedef struct ncclComm* ncclComm_t;
 struct NcclUniqueId { char internal[128]; };
-enum { kNcclInt32 = 2, kNcclFloat32 = 7 };
+enum { kNcclInt8 = 0, kNcclInt32 = 2, kNcclFloat32 = 7 };
 enum { kNcclSum = 0, kNcclMax = 2 };
 
 struct NcclApi {
@@ -206,6 +207,7 @@ struct NcclApi {
     int (*CommInitRank)(ncclComm_t*, int, NcclUniqueId, int) = nullptr;
     int (*CommDestroy)(ncclComm_t) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
     bool ok = false;
 };
@@ -219,6 +221,7 @@ NcclApi& nccl() {
         a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(a.handle, "ncclCommInitRank"));
         a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(a.handle, "ncclCommDestroy"));
         a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(a.handle, "ncclAllReduce"));
+        a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(a.handle, "ncclAllGather"));
         a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(a.handle, "ncclGetErrorString"));
         a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce;
         return a;
@@ -289,6 +292,15 @@ struct b200_decoder {
     bool store_poisoned = false;
     // tensor parallel
     ncclComm_t comm = nullptr;
+    // Exchange block (tp_size > 1): flags, sx, xq and the f32 partial `part` live in one allocation that the other
+    // ranks map through CUDA IPC, so that the finish kernel can read partials from and deliver rows to every rank.
+    uint8_t* tp_block = nullptr;
+    size_t tp_block_bytes = 0;
+    size_t tp_o_sx = 0, tp_o_xq = 0, tp_o_part = 0;
+    void* tp_peer_ptrs[16] = {};                // host copy of the mapped bases (own block at tp_rank)
+    uint8_t** tp_peers_dev = nullptr;           // the same table on the device
+    uint32_t* tp_epoch = nullptr;               // [0] call counter, [1] CTA arrival counter of the finish kernel
+    bool tp_exchange = false;                   // peers are mapped: use the finish kernel instead of ncclAllReduce
     uint64_t launches_per_step = 0;
 };
 
@@ -425,6 +437,62 @@ bool tensor_shape(const b200_decoder* d, int which, int layer, TensorShape* t) {
     return true;
 }
 
+// Maps every other rank's exchange block into this process (CUDA IPC; the 64-byte handles travel through an
+// ncclAllGather) and uploads the table of bases.  On any failure the decoder keeps the ncclAllReduce path.
+// B200_TP_EXCHANGE=0 in the environment keeps that path too.
+void map_peer_blocks(b200_decoder* d) {
+    d->tp_exchange = false;
+    const int tp = d->cfg.tp_size, rank = d->cfg.tp_rank;
+    const char* env = std::getenv("B200_TP_EXCHANGE");
+    if (env && env[0] == '0') return;
+    if (tp < 2 || tp > 16 || !d->tp_block || !nccl().AllGather) return;
+    if (d->cfg.max_batch % tp != 0 || !tp_finish_supported(d->cfg.d_model)) return;
+    cudaStream_t s = d->ctx->stream;
+    cudaIpcMemHandle_t mine;
+    if (cudaIpcGetMemHandle(&mine, d->tp_block) != cudaSuccess) { cudaGetLastError(); return; }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    uint8_t* dev = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&dev), size_t(tp) * 64) != cudaSuccess) { cudaGetLastError(); return; }
+    std::vector<cudaIpcMemHandle_t> all(tp);
+    bool ok = cudaMemcpyAsync(dev + size_t(rank) * 64, &mine, 64, cudaMemcpyHostToDevice, s) == cudaSuccess;
+    ok = ok && nccl().AllGather(dev + size_t(rank) * 64, dev, 64, kNcclInt8, d->comm, s) == 0;
+    ok = ok && cudaMemcpyAsync(all.data(), dev, size_t(tp) * 64, cudaMemcpyDeviceToHost, s) == cudaSuccess;
+    ok = ok && cudaStreamSynchronize(s) == cudaSuccess;
+    cudaFree(dev);
+    if (!ok) { cudaGetLastError(); return; }
+    for (int p = 0; p < tp; ++p) {
+        if (p == rank) { d->tp_peer_ptrs[p] = d->tp_block; continue; }
+        void* ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            for (int q = 0; q < p; ++q)
+                if (q != rank && d->tp_peer_ptrs[q]) { cudaIpcCloseMemHandle(d->tp_peer_ptrs[q]); d->tp_peer_ptrs[q] = nullptr; }
+            ok = false;
+            break;
+        }
+        d->tp_peer_ptrs[p] = ptr;
+    }
+    // every rank must take the same path: agree through a sum over the ranks
+    int* flag = nullptr;
+    int agreed = 0;
+    if (cudaMalloc(reinterpret_cast<void**>(&flag), sizeof(int)) == cudaSuccess) {
+        const int one = ok ? 1 : 0;
+        bool f = cudaMemcpyAsync(flag, &one, sizeof(int), cudaMemcpyHostToDevice, s) == cudaSuccess;
+        f = f && nccl().AllReduce(flag, flag, 1, kNcclInt32, kNcclSum, d->comm, s) == 0;
+        f = f && cudaMemcpyAsync(&agreed, flag, sizeof(int), cudaMemcpyDeviceToHost, s) == cudaSuccess;
+        f = f && cudaStreamSynchronize(s) == cudaSuccess;
+        cudaFree(flag);
+        if (!f) agreed = 0;
+    }
+    cudaGetLastError();
+    if (agreed != tp) return;
+    if (cudaMemcpy(d->tp_peers_dev, d->tp_peer_ptrs, size_t(tp) * sizeof(void*), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    d->tp_exchange = true;
+}
+
 int32_t all_reduce_sum_f32(b200_decoder* d, float* buf, size_t n) {
     int rc = nccl().AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, d->comm, d->ctx->stream);
     if (rc != 0) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, "ncclAllReduce failed");
@@ -446,6 +514,46 @@ int32_t enqueue_step(b200_decoder* d) {
     CU_TRY(embed_norm_quant_auto(d->ids_dev, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, d->h,
                             d->xq, d->sx, err, s));
     ++launches;
+    // A row-parallel projection and what follows it: residual add, RMSNorm with `norm`, per-token int8 rows in xq.
+    // One rank: the row kernel reads the raw accumulators.  Several ranks: the GEMM writes its dequantised f32
+    // partial into the exchange block; then either the finish kernel sums the partials over the ranks' blocks and
+    // delivers the rows (peers mapped), or ncclAllReduce sums them and every rank finishes all rows itself.
+    auto row_parallel = [&](const GemmPlan& p, size_t s_off, const float* norm) -> int32_t {
+        const bool fused_ok = p.persist || p.splits == 1 || p.cluster;
+        if (!tp) {
+            CU_TRY(gemm_launch(p, ep, err, s));
+            CU_TRY(resid_norm_quant_auto(d->raw, p.out_planes, M, dm, d->sx, d->scales + s_off, nullptr, norm, c.rms_eps, d->h,
+                                         d->xq, d->sx, s));
+            launches += 2;
+            return B200_OK;
+        }
+        if (fused_ok) {
+            GemmEpilogue pe;
+            pe.fused = 1;
+            pe.a_scale = d->sx;
+            pe.a_per_row = 1;
+            pe.b_scale = d->scales + s_off;
+            pe.b_per_col = 1;
+            pe.out = d->part;
+            CU_TRY(gemm_launch(p, pe, err, s));
+            ++launches;
+        } else {
+            CU_TRY(gemm_launch(p, ep, err, s));
+            CU_TRY(dequant_planes(d->raw, p.out_planes, M, dm, d->sx, d->scales + s_off, d->part, s));
+            launches += 2;
+        }
+        if (d->tp_exchange && M % c.tp_size == 0) {
+            CU_TRY(tp_finish(d->tp_peers_dev, d->tp_o_sx, d->tp_o_xq, d->tp_o_part, c.tp_size, c.tp_rank, M / c.tp_size, dm, norm,
+                             c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s));
+            ++launches;
+            return B200_OK;
+        }
+        if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
+        CU_TRY(resid_norm_quant_auto(d->raw, p.out_planes, M, dm, d->sx, d->scales + s_off, d->part, norm, c.rms_eps, d->h, d->xq,
+                                     d->sx, s));
+        launches += 2;
+        return B200_OK;
+    };
     for (int l = 0; l < c.n_layers; ++l) {
         LayerParams& L = d->layers[l];
         // QKV projection -> RoPE -> append to the paged cache
@@ -464,30 +572,15 @@ int32_t enqueue_step(b200_decoder* d) {
             CU_TRY(quantize_rows_auto(d->attn_out, M, d->hq_l * dh, d->xq, d->sx, s));
         }
         // O projection (row-parallel) -> residual -> norm -> quant
-        CU_TRY(gemm_launch(L.p_o, ep, err, s));
-        launches += 6;
-        if (tp) {
-            CU_TRY(dequant_planes(d->raw, L.p_o.out_planes, M, dm, d->sx, d->scales + L.s_o, d->part, s));
-            if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
-            launches += 2;
-        }
-        CU_TRY(resid_norm_quant_auto(d->raw, L.p_o.out_planes, M, dm, d->sx, d->scales + L.s_o, tp ? d->part : nullptr,
-                                d->vectors + L.mlp_norm, c.rms_eps, d->h, d->xq, d->sx, s));
+        launches += paged_attention_can_quantize(L.attn) ? 4 : 5;
+        if (int32_t st = row_parallel(L.p_o, L.s_o, d->vectors + L.mlp_norm)) return st;
         // gate / up (column-parallel) -> SiLU gate -> quant
         CU_TRY(gemm_launch(L.p_gu, ep, err, s));
         CU_TRY(gate_quant_auto(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
         // down (row-parallel) -> residual -> next norm -> quant
-        CU_TRY(gemm_launch(L.p_down, ep, err, s));
-        launches += 4;
-        if (tp) {
-            CU_TRY(dequant_planes(d->raw, L.p_down.out_planes, M, dm, d->sx, d->scales + L.s_down, d->part, s));
-            if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
-            launches += 2;
-        }
         const float* next_norm = d->vectors + (l + 1 < c.n_layers ? d->layers[l + 1].attn_norm : d->final_norm);
-        CU_TRY(resid_norm_quant_auto(d->raw, L.p_down.out_planes, M, dm, d->sx, d->scales + L.s_down, tp ? d->part : nullptr,
-                                next_norm, c.rms_eps, d->h, d->xq, d->sx, s));
-        ++launches;
+        launches += 2;
+        if (int32_t st = row_parallel(L.p_down, L.s_down, next_norm)) return st;
     }
     // lm_head with the dequant epilogue fused into the GEMM, then greedy argmax on the device
     GemmEpilogue lm;
@@ -572,11 +665,29 @@ int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_
     A(dmalloc(&d->ids_dev, M));
     A(dmalloc(&d->next_ids_dev, M));
     A(dmalloc(&d->h, M * dm));
-    A(dmalloc(&d->xq, M * widest));
-    A(dmalloc(&d->sx, M));
+    if (tp > 1) {
+        size_t off = 512;                                        // ready[tp] at +0, done[tp] at +256
+        d->tp_o_sx = off; off += align_up(M * sizeof(float), 256);
+        d->tp_o_xq = off; off += align_up(M * widest, 256);
+        d->tp_o_part = off; off += align_up(M * dm * sizeof(float), 256);
+        d->tp_block_bytes = off;
+        A(cudaMalloc(reinterpret_cast<void**>(&d->tp_block), off));
+        if (e == cudaSuccess) e = cudaMemset(d->tp_block, 0, off);
+        if (e == cudaSuccess) {
+            d->sx = reinterpret_cast<float*>(d->tp_block + d->tp_o_sx);
+            d->xq = reinterpret_cast<int8_t*>(d->tp_block + d->tp_o_xq);
+            d->part = reinterpret_cast<float*>(d->tp_block + d->tp_o_part);
+        }
+        A(dmalloc(&d->tp_epoch, 2));
+        if (e == cudaSuccess) e = cudaMemset(d->tp_epoch, 0, 2 * sizeof(uint32_t));
+        A(cudaMalloc(reinterpret_cast<void**>(&d->tp_peers_dev), 16 * sizeof(uint8_t*)));
+    } else {
+        A(dmalloc(&d->xq, M * widest));
+        A(dmalloc(&d->sx, M));
+        A(dmalloc(&d->part, M * dm));
+    }
     A(dmalloc(&d->q, M * d->hq_l * dh));
     A(dmalloc(&d->attn_out, M * d->hq_l * dh));
-    A(dmalloc(&d->part, M * dm));
     A(dmalloc(&d->logits, M * size_t(c.vocab)));
     A(cudaMallocHost(reinterpret_cast<void**>(&d->ids_pinned), M * sizeof(int)));
     A(cudaEventCreateWithFlags(&d->ids_copied, cudaEventDisableTiming));
@@ -625,9 +736,16 @@ int32_t b200_decoder_destroy(b200_decoder* d) {
         cudaFree(L.k_pool);
         cudaFree(L.v_pool);
     }
+    if (d->tp_block) {      // xq, sx and part are carved out of the exchange block
+        for (int p = 0; p < d->cfg.tp_size && p < 16; ++p)
+            if (p != d->cfg.tp_rank && d->tp_peer_ptrs[p]) cudaIpcCloseMemHandle(d->tp_peer_ptrs[p]);
+        d->xq = nullptr;
+        d->sx = nullptr;
+        d->part = nullptr;
+    }
     void* ptrs[] = {d->payload, d->scales, d->vectors, d->embed, d->cos_t, d->sin_t, d->tables_dev, d->seq_lens_dev, d->pos_dev,
                     d->ids_dev, d->next_ids_dev, d->h, d->xq, d->sx, d->raw, d->q, d->attn_out, d->part, d->logits,
-                    d->attn_scratch};
+                    d->attn_scratch, d->tp_block, d->tp_epoch, d->tp_peers_dev};
     for (void* p : ptrs) cudaFree(p);
     if (d->ids_pinned) cudaFreeHost(d->ids_pinned);
     if (d->ids_copied) cudaEventDestroy(d->ids_copied);
@@ -730,8 +848,11 @@ int32_t b200_decoder_init_tp(b200_decoder* d, const uint8_t* unique_id128) {
     std::memcpy(id.internal, unique_id128, 128);
     int rc = nccl().CommInitRank(&d->comm, d->cfg.tp_size, id, d->cfg.tp_rank);
     if (rc != 0) return fail(B200_DEVICE_UNAVAILABLE, "ncclCommInitRank failed");
+    map_peer_blocks(d);
     return B200_OK;
 }
+
+int32_t b200_decoder_tp_exchange(const b200_decoder* d) { return d && d->tp_exchange ? 1 : 0; }
 
 // Starts a generation: clears the page table, reserves blocks for `max_total_len[b]` tokens per row
 // (the reference's generate() always runs to max_length, so the final length is known up front), uploads

@@ -94,4 +94,13 @@ cudaError_t fill_normal_bf16(uint16_t* out, int64_t n, uint64_t seed, uint64_t s
 cudaError_t slice_cols_i8(const int8_t* src, int64_t rows, int64_t ld, int64_t c0, int64_t cols, int8_t* dst,
                           cudaStream_t s);
 
+// Tensor-parallel finish of a row-parallel GEMM over the ranks' exchange blocks (decode_rows.cu): sums the f32
+// partials of the rows this rank owns over all ranks, adds the residual, applies RMSNorm and the per-token int8
+// quantisation and delivers the int8 rows and scales to every rank.  `peers` is a device array of the tp block
+// bases; a block starts with 512 bytes of flags.  Needs one GPU per rank (the ranks wait for each other).
+bool tp_finish_supported(int d);
+cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
+                      const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
+                      cudaStream_t s);
+
 }  // namespace b200

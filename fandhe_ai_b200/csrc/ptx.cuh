@@ -216,6 +216,23 @@ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
     return u >> 16;
 }
 
+// ---------------------------------------------------------------- system-scope accesses (memory of another GPU)
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+// 16-byte load that is not served from this SM's L1 (the line may have been rewritten by its owner GPU)
+__device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* addr) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(addr) : "memory");
+    return v;
+}
+
 // Symmetric int8 quantisation of one value: round-to-nearest-even of x / scale, clamped to [-127, 127];
 // scale 0 (an all-zero row) gives 0.
 __device__ __forceinline__ int quant_i8(float x, float scale) {

@@ -149,6 +149,12 @@ class Decoder:
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
         check(lib().b200_decoder_init_tp(self._h, buf))
 
+    @property
+    def tp_exchange(self) -> bool:
+        """True when the row-parallel outputs are finished over the ranks' mapped exchange blocks (one kernel
+        with peer loads and stores) instead of ncclAllReduce."""
+        return bool(lib().b200_decoder_tp_exchange(self._h))
+
     def begin(self, batch: int, max_total_lens, start_lens=None) -> None:
         mt = np.ascontiguousarray(max_total_lens, dtype=np.int32)
         sl = np.ascontiguousarray(start_lens, dtype=np.int32) if start_lens is not None else None

@@ -240,7 +240,7 @@ int32_t b200_paged_attention_forward_noalloc(b200_ctx* ctx, const b200_buf* q, s
                                              const b200_buf* seq_lens, uint64_t max_seq_len,
                                              const b200_paged_attention_args* args, b200_buf* out, size_t out_off);
 
-/* Blocks per split of the decode-attention kernel (1..32; 0 restores the default), for tuning. */
+/* Blocks per split of the decode-attention kernel (1..256; 0 restores the default of 32), for tuning. */
 int32_t b200_paged_attention_tuning(b200_ctx* ctx, int32_t chunk_blocks);
 
 /* ------------------------------------------------------------------ host page table
@@ -310,6 +310,11 @@ int32_t b200_decoder_init_random(b200_decoder* dec, uint64_t seed, float std);
 /* 128-byte NCCL unique id (rank 0 makes it, the launcher hands it to every rank) and communicator set-up. */
 int32_t b200_nccl_unique_id(uint8_t* out128);
 int32_t b200_decoder_init_tp(b200_decoder* dec, const uint8_t* unique_id128);
+/* 1 when init_tp mapped the other ranks' exchange blocks (CUDA IPC), so that the row-parallel outputs are
+ * finished by one kernel that reads the peers' partial sums and delivers the quantised rows to every rank;
+ * 0 when the step uses ncclAllReduce instead (mapping failed, batch not divisible by the rank count, or
+ * B200_TP_EXCHANGE=0 in the environment).  No reference counterpart (the reference has no tensor parallelism). */
+int32_t b200_decoder_tp_exchange(const b200_decoder* dec);
 /* Starts a generation of `batch` rows: row b starts at start_lens[b] cached tokens (NULL: 0) and may grow
  * to max_total_lens[b]; blocks for the final length are reserved now and the tables uploaded once. */
 int32_t b200_decoder_begin(b200_decoder* dec, int32_t batch, const int32_t* start_lens, const int32_t* max_total_lens);
