@@ -330,7 +330,7 @@ def run_gpu(args, cfg, rank, world, local_rank):
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": dict(workload_config(args, cfg, world),
                            collective=("none" if world == 1 else
                                        "row-parallel outputs finished over CUDA-IPC mapped peer blocks (one kernel: peer loads, "
@@ -367,6 +367,8 @@ def main():
     ap.add_argument("--cpu-layers", type=int, default=2, help="full-size layers in the CPU sample")
     ap.add_argument("--cpu-vocab", type=int, default=8016, help="lm_head rows in the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="strong (default): the named batch at every rank count; weak: batch x ranks")
     ap.add_argument("--attn-chunk-blocks", type=int, default=0, help="KV blocks per attention split (0: default)")
     ap.add_argument("--gemm-splits", type=int, default=0, help="force the split-K count of the layer GEMMs (0: heuristic)")
     ap.add_argument("--gemm-tile", type=int, default=0, help="force the GEMM tile width (0: heuristic)")
@@ -380,6 +382,9 @@ def main():
         return
     if cfg["n_kv_heads"] % world != 0:
         raise SystemExit(f"{world} ranks do not divide {cfg['n_kv_heads']} KV heads")
+    if args.scaling == "weak" and world > 1:
+        # the batch grows with the rank count (each rank keeps the KV bytes of one rank of the 1-GPU run)
+        cfg = dict(cfg, batch=cfg["batch"] * world)
     run_gpu(args, cfg, rank, world, local_rank)
 
 
