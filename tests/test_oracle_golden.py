@@ -299,3 +299,66 @@ def test_int8_quantiser_rule():
     q, s = O.quantize_i8_per_row(w)
     assert np.all(np.abs(q).max(axis=1) == 127)
     assert np.allclose(O.dequantize_i8_per_row(q, s), w, atol=float(s.max()) * 0.5 + 1e-9)
+
+
+# ------------------------------------------------------------------ committed fixtures (tests/golden)
+def _f(v):
+    return float(v)        # "nan" / "inf" strings in the JSON become floats
+
+
+def test_committed_reference_vectors():
+    """tests/golden/reference_vectors.json: the reference's known-answer vectors, transcribed with their
+    source lines.  The oracle (and, for the block table, the product's host logic) must reproduce each one."""
+    import json
+    from pathlib import Path
+
+    vec = json.loads((Path(__file__).parent / "golden" / "reference_vectors.json").read_text())
+    for c in vec["fma_gemm"]:
+        got = O.matmul_reference_fma(np.array(c["a"], np.float32), np.array(c["b"], np.float32))
+        assert got.tolist() == [[float(x) for x in r] for r in c["c"]], c["source"]
+    for c in vec["int8_accumulate"]:
+        a = np.full((c["m"], c["k"]), c["a_fill"], np.int8)
+        b = np.full((c["n"], c["k"]), c["b_fill"], np.int8)
+        assert int(O.gemm_i8_s32(a, b)[0, 0]) == c["acc"], c["source"]
+    for c in vec["bf16_round"]:
+        y = float(np.asarray(O.bf16_to_f32(O.f32_to_bf16(np.float32(_f(c["x"]))))).ravel()[0])
+        want = _f(c["y"])
+        assert (np.isnan(y) and np.isnan(want)) or y == want, c["source"]
+    for c in vec["composite_close"]:
+        assert bool(O.composite_close(_f(c["a"]), _f(c["b"]))) == c["close"], (c["source"], c)
+    for c in vec["rmsnorm"]:
+        x = np.array([c["x"]], np.float32)
+        want = x / np.sqrt(np.float32(c["mean_square"]) + np.float32(c["eps"]))
+        assert np.all(np.abs(O.rmsnorm(x, None, c["eps"]) - want) < 1e-5), c["source"]
+    for c in vec["sigmoid"]:
+        assert O.sigmoid_stable(c["x"]) == c["y"], c["source"]
+    for c in vec["greedy_argmax"]:
+        assert O.greedy_argmax(c["logits"]) == c["index"], c["source"]
+    from fandhe_ai_b200.decoder import BlockTable
+
+    for c in vec["block_table"]:
+        t = BlockTable(c["max_blocks"], c["block_size"])
+        for step in c["appends"]:
+            if "rewind_to" in step:
+                t.rewind_to(step["rewind_to"])
+            else:
+                assert list(t.extend_for_append(c["batch"], step["l_new"])) == step["slots"], c["source"]
+
+
+def test_oracle_reproduces_the_committed_cases():
+    """tests/golden/oracle_cases.npz (made by tests/golden/make_fixtures.py): the oracle of today must give the
+    outputs that were committed, bit for bit."""
+    import importlib.util
+    from pathlib import Path
+
+    gdir = Path(__file__).parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_fixtures", gdir / "make_fixtures.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    fresh = mod.cases()
+    stored = np.load(gdir / "oracle_cases.npz")
+    assert sorted(stored.files) == sorted(fresh)
+    for name in stored.files:
+        a, b = stored[name], np.asarray(fresh[name])
+        assert a.dtype == b.dtype and a.shape == b.shape, name
+        assert a.tobytes() == b.tobytes(), name

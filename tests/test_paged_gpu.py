@@ -295,3 +295,18 @@ def test_stale_and_foreign_buffers_are_errors(be, fresh_be):
     with pytest.raises(BackendError) as e:
         be.download(other)
     assert e.value.kind == "DeviceMismatch"
+
+
+# ---------------------------------------------------------------- committed fixture (no oracle call for the reference)
+def test_committed_attention_case(be):
+    """tests/golden/oracle_cases.npz: GQA 4:2, head_dim 128, bf16 pools, block 16, lengths 37 / 16 / 5 (a block
+    edge and a short row); the split-K kernel against the committed oracle output."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).parent / "golden" / "oracle_cases.npz")
+    batch, hq, hkv, dh, bs, nblk, mbps = (int(v) for v in g["att_shape"])
+    args = P.PagedAttentionArgs(P.PagedKvLayout(nblk, bs, hkv * dh, BF16), batch, 1, hq, mbps, float(g["att_scale"]), hkv)
+    out = P.paged_attention_forward(be, be.upload(g["att_q"]), be.upload(g["att_k_pool"]), be.upload(g["att_v_pool"]),
+                                    g["att_tables"], g["att_lens"], args).numpy()
+    fails, max_abs, max_rel = O.compare(out, g["att_out"])
+    assert fails == 0, (max_abs, max_rel)

@@ -259,3 +259,27 @@ def test_gemm_i8_linearity_and_identity_at_large_size(be):
     # spot-check 64 random rows of the big product against the oracle
     rows = rng.choice(m, 64, replace=False)
     assert np.array_equal(s1[rows], O.gemm_i8_s32(a[rows], w1))
+
+
+# ---------------------------------------------------------------- committed fixtures (no oracle call)
+def test_committed_linear_and_fp8_cases(be):
+    """tests/golden/oracle_cases.npz: quantised codes, scales and int32 accumulators byte-identical, dequantised
+    outputs within the composite tolerance."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).parent / "golden" / "oracle_cases.npz")
+    m, k = g["lin_x"].shape
+    n = g["lin_w"].shape[0]
+    wq, ws = be.quantize_i8_per_row(be.upload(g["lin_w"]), n, k)
+    xq, xs = be.quantize_i8_per_row(be.upload(g["lin_x"]), m, k)
+    assert np.array_equal(wq.numpy(), g["lin_wq"]) and np.array_equal(ws.numpy(), g["lin_ws"])
+    assert np.array_equal(xq.numpy(), g["lin_xq"]) and np.array_equal(xs.numpy(), g["lin_xs"])
+    acc = be.gemm_i8_s32(xq, wq, m, n, k).numpy()
+    assert np.array_equal(acc, g["lin_acc"])
+    bias = be.upload(g["lin_bias"])
+    for act, key in ((ACT_NONE, "lin_y"), (ACT_SILU, "lin_y_silu")):
+        y = be.gemm_q8_scaled(I8, xq, xs, True, wq, ws, True, m, n, k, bias=bias, activation=act).numpy()
+        fails, max_abs, max_rel = O.compare(y, g[key])
+        assert fails == 0, (key, max_abs, max_rel)
+    q, s = be.quantize_fp8_e4m3_per_tensor(be.upload(g["fp8_x"]), g["fp8_x"].size)
+    assert np.array_equal(q.numpy(), g["fp8_q"]) and np.array_equal(s.numpy(), g["fp8_scale"])
