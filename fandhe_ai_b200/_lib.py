@@ -131,6 +131,18 @@ SIGNATURES = {
     "b200_nccl_unique_id": (_I32, [_P]),
     "b200_decoder_init_tp": (_I32, [_P, _P]),
     "b200_decoder_tp_exchange": (_I32, [_P]),
+    "b200_decoder_step_rows": (_I32, [_P, _P, _P, _P]),
+    "b200_decoder_row_restart": (_I32, [_P, _I32, _I32]),
+    "b200_scheduler_create": (_I32, [_P, _I32, _I32, _I32, _P]),
+    "b200_scheduler_destroy": (None, [_P]),
+    "b200_scheduler_submit": (_I32, [_P, _P, _I32, _I32, _P]),
+    "b200_scheduler_queued_len": (_I32, [_P]),
+    "b200_scheduler_active_len": (_I32, [_P]),
+    "b200_scheduler_finished_len": (_I32, [_P]),
+    "b200_scheduler_step": (_I32, [_P, _P]),
+    "b200_scheduler_plan_step": (_I32, [_P, _P, _P, _P, _P, _P, _P]),
+    "b200_scheduler_commit_step": (_I32, [_P, _P, _P]),
+    "b200_scheduler_take_finished": (_I32, [_P, _P, _P, _I32, _P]),
     "b200_decoder_begin": (_I32, [_P, _I32, _P, _P]),
     "b200_decoder_fill_cache_random": (_I32, [_P, _U64, C.c_float]),
     "b200_decoder_step": (_I32, [_P, _P, _P]),

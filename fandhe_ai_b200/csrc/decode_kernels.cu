@@ -224,11 +224,21 @@ __global__ void dequant_planes_kernel(const int* __restrict__ raw, int splits, i
 }
 
 // Start of a decode step: remember each row's position for the new token, then count it in.
-__global__ void begin_step_kernel(uint32_t* seq_lens, uint32_t* positions, int n) {
+// A row that takes part in the step appends at its current length.  A row that sits the step out (no request in
+// its slot) rewrites its last position instead - position 0 of its first block when it is empty - so that every
+// kernel of the step still sees a valid one-token-or-longer sequence and its real contents stay untouched.
+__global__ void begin_step_kernel(uint32_t* seq_lens, uint32_t* positions, const uint32_t* active, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
-        positions[i] = seq_lens[i];
-        seq_lens[i] += 1;
+        const uint32_t len = seq_lens[i];
+        if (active[i]) {
+            positions[i] = len;
+            seq_lens[i] = len + 1;
+        } else {
+            const uint32_t l = len > 0 ? len : 1u;
+            positions[i] = l - 1;
+            seq_lens[i] = l;
+        }
     }
 }
 
@@ -357,8 +367,8 @@ cudaError_t qkv_rope_append(const int* raw, int splits, int M, int hq, int hkv, 
                                                        q_out, k_pool, v_pool, err);
     return cudaGetLastError();
 }
-cudaError_t begin_step(uint32_t* seq_lens, uint32_t* positions, int n, cudaStream_t s) {
-    begin_step_kernel<<<(n + 127) / 128, 128, 0, s>>>(seq_lens, positions, n);
+cudaError_t begin_step(uint32_t* seq_lens, uint32_t* positions, const uint32_t* active, int n, cudaStream_t s) {
+    begin_step_kernel<<<(n + 127) / 128, 128, 0, s>>>(seq_lens, positions, active, n);
     return cudaGetLastError();
 }
 cudaError_t argmax_rows(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s) {

@@ -595,10 +595,17 @@ tp_finish_kernel(TpFinishArgs a) {
             const int g = threadIdx.x + k * blockDim.x;
             if (g < groups) {
                 float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int p = 0; p < a.tp; ++p) {
-                    const float* part = reinterpret_cast<const float*>(a.peers[p] + a.o_part);
-                    const float4 x = ld_relaxed_sys_f4(part + base + 4 * g);
-                    y.x += x.x; y.y += x.y; y.z += x.z; y.w += x.w;
+                // eight ranks at a time: all their loads are in flight before the first addition (one NVLink round
+                // trip instead of one per rank); the additions stay in rank order
+                for (int p0 = 0; p0 < a.tp; p0 += 8) {
+                    float4 x[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (p0 + i < a.tp)
+                            x[i] = ld_relaxed_sys_f4(reinterpret_cast<const float*>(a.peers[p0 + i] + a.o_part) + base + 4 * g);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (p0 + i < a.tp) { y.x += x[i].x; y.y += x[i].y; y.z += x[i].z; y.w += x[i].w; }
                 }
                 float4 hv = *reinterpret_cast<const float4*>(a.h + base + 4 * g);
                 hv.x = y.x + hv.x; hv.y = y.y + hv.y; hv.z = y.z + hv.z; hv.w = y.w + hv.w;

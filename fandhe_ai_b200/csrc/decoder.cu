@@ -268,6 +268,9 @@ struct b200_decoder {
     uint32_t* tables_dev = nullptr;
     uint32_t* seq_lens_dev = nullptr;
     uint32_t* pos_dev = nullptr;                // position of the token being added, per row
+    uint32_t* active_dev = nullptr;             // 1: the row takes part in the step, 0: it sits the step out
+    uint32_t* active_pinned = nullptr;
+    std::vector<uint8_t> active_host;           // what active_dev holds
     int max_blocks_per_seq = 0;
     int* ids_dev = nullptr;
     int* next_ids_dev = nullptr;
@@ -509,7 +512,7 @@ int32_t enqueue_step(b200_decoder* d) {
     uint64_t launches = 0;
     GemmEpilogue ep;
     ep.raw = d->raw;
-    CU_TRY(begin_step(d->seq_lens_dev, d->pos_dev, M, s));
+    CU_TRY(begin_step(d->seq_lens_dev, d->pos_dev, d->active_dev, M, s));
     ++launches;
     CU_TRY(embed_norm_quant_auto(d->ids_dev, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, d->h,
                             d->xq, d->sx, err, s));
@@ -662,6 +665,8 @@ int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_
     A(dmalloc(&d->tables_dev, M * d->max_blocks_per_seq));
     A(dmalloc(&d->seq_lens_dev, M));
     A(dmalloc(&d->pos_dev, M));
+    A(dmalloc(&d->active_dev, M));
+    A(cudaMallocHost(reinterpret_cast<void**>(&d->active_pinned), M * sizeof(uint32_t)));
     A(dmalloc(&d->ids_dev, M));
     A(dmalloc(&d->next_ids_dev, M));
     A(dmalloc(&d->h, M * dm));
@@ -745,9 +750,10 @@ int32_t b200_decoder_destroy(b200_decoder* d) {
     }
     void* ptrs[] = {d->payload, d->scales, d->vectors, d->embed, d->cos_t, d->sin_t, d->tables_dev, d->seq_lens_dev, d->pos_dev,
                     d->ids_dev, d->next_ids_dev, d->h, d->xq, d->sx, d->raw, d->q, d->attn_out, d->part, d->logits,
-                    d->attn_scratch, d->tp_block, d->tp_epoch, d->tp_peers_dev};
+                    d->attn_scratch, d->tp_block, d->tp_epoch, d->tp_peers_dev, d->active_dev};
     for (void* p : ptrs) cudaFree(p);
     if (d->ids_pinned) cudaFreeHost(d->ids_pinned);
+    if (d->active_pinned) cudaFreeHost(d->active_pinned);
     if (d->ids_copied) cudaEventDestroy(d->ids_copied);
     if (d->next_pinned) cudaFreeHost(d->next_pinned);
     b200_block_table_destroy(d->table);
@@ -890,6 +896,9 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     cudaStream_t s = d->ctx->stream;
     CU_TRY(cudaMemcpyAsync(d->tables_dev, flat.data(), flat.size() * 4, cudaMemcpyHostToDevice, s));
     CU_TRY(cudaMemcpyAsync(d->seq_lens_dev, lens.data(), lens.size() * 4, cudaMemcpyHostToDevice, s));
+    for (int b = 0; b < batch; ++b) d->active_pinned[b] = 1u;
+    d->active_host.assign(batch, 1);
+    CU_TRY(cudaMemcpyAsync(d->active_dev, d->active_pinned, size_t(batch) * 4, cudaMemcpyHostToDevice, s));
     CU_TRY(cudaStreamSynchronize(s));
     d->batch = batch;
     d->max_total_len = mx;
@@ -952,13 +961,32 @@ int32_t b200_decoder_fill_cache_random(b200_decoder* d, uint64_t seed, float std
 // the host (pinned staging) first; otherwise the ids produced by the previous step are used in place.
 // next_ids_host != NULL: the sampled ids are copied back and the call returns when they are final.
 int32_t b200_decoder_step(b200_decoder* d, const int32_t* ids_host, int32_t* next_ids_host) {
+    return b200_decoder_step_rows(d, ids_host, nullptr, next_ids_host);
+}
+
+// One step in which only the rows with active[b] != 0 advance (NULL: all rows).  The other rows run through the
+// same kernels on their last position (see begin_step_kernel) and keep their length; their sampled ids mean nothing.
+int32_t b200_decoder_step_rows(b200_decoder* d, const int32_t* ids_host, const uint8_t* active, int32_t* next_ids_host) {
     if (int32_t st = dec_check(d)) return st;
     if (!d->planned) return fail(B200_INVALID_ARGUMENT, "decoder_step: call decoder_begin first");
     cudaStream_t s = d->ctx->stream;
     const int M = d->batch;
+    auto is_active = [&](int b) { return !active || active[b] != 0; };
     for (int b = 0; b < M; ++b)
-        if (d->table->seq_lens[b] + 1 > uint64_t(d->row_limits[b]))
+        if (is_active(b) && d->table->seq_lens[b] + 1 > uint64_t(d->row_limits[b]))
             return fail(B200_INVALID_ARGUMENT, "decoder_step: row " + std::to_string(b) + " is past its reserved length");
+    bool mask_changed = false;
+    for (int b = 0; b < M; ++b)
+        if ((d->active_host[b] != 0) != is_active(b)) mask_changed = true;
+    if (mask_changed) {
+        // the previous copy out of the staging buffer has finished: every step that follows a mask change waits below
+        CU_TRY(cudaStreamSynchronize(s));
+        for (int b = 0; b < M; ++b) {
+            d->active_host[b] = is_active(b) ? 1 : 0;
+            d->active_pinned[b] = d->active_host[b];
+        }
+        CU_TRY(cudaMemcpyAsync(d->active_dev, d->active_pinned, size_t(M) * 4, cudaMemcpyHostToDevice, s));
+    }
     if (ids_host) {
         // the staging buffer is read when the copy executes, not when it is enqueued
         if (d->ids_copy_pending) CU_TRY(cudaEventSynchronize(d->ids_copied));
@@ -990,7 +1018,10 @@ int32_t b200_decoder_step(b200_decoder* d, const int32_t* ids_host, int32_t* nex
         if (e != cudaSuccess) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, std::string("graph instantiate: ") + cudaGetErrorString(e));
         CU_TRY(cudaGraphLaunch(d->graph, s));
     }
-    for (int b = 0; b < M; ++b) d->table->seq_lens[b] += 1;     // commit the logical state after the enqueue succeeded
+    for (int b = 0; b < M; ++b) {      // commit the logical state after the enqueue succeeded
+        if (is_active(b)) d->table->seq_lens[b] += 1;
+        else if (d->table->seq_lens[b] == 0) d->table->seq_lens[b] = 1;
+    }
     d->steps++;
     if (next_ids_host) {
         CU_TRY(cudaMemcpyAsync(d->next_pinned, d->next_ids_dev, size_t(M) * sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -1001,6 +1032,41 @@ int32_t b200_decoder_step(b200_decoder* d, const int32_t* ids_host, int32_t* nex
             return st;
         }
     }
+    return B200_OK;
+}
+
+// Empties row `row` between steps and reserves blocks for a new sequence of up to max_total_len tokens in it: the
+// row's blocks go back to the free stack (last block first), new ones are taken, the row's slice of the device
+// block table and its length (0) are uploaded.  The other rows are untouched.  Continuous batching uses this to
+// put a new request into a finished request's slot.
+int32_t b200_decoder_row_restart(b200_decoder* d, int32_t row, int32_t max_total_len) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!d->planned) return fail(B200_INVALID_ARGUMENT, "decoder_row_restart: call decoder_begin first");
+    if (row < 0 || row >= d->batch) return fail(B200_INVALID_ARGUMENT, "decoder_row_restart: row out of range");
+    if (max_total_len <= 0 || max_total_len > d->max_total_len)
+        return fail(B200_INVALID_ARGUMENT, "decoder_row_restart: length exceeds what decoder_begin planned for");
+    b200_block_table* t = d->table;
+    std::vector<uint32_t> old = t->tables[row];
+    for (auto it = t->tables[row].rbegin(); it != t->tables[row].rend(); ++it) t->returned.push_back(*it);
+    t->tables[row].clear();
+    if (!bt_reserve_row(t, row, uint64_t(max_total_len))) {
+        // cannot happen when the new length fits the blocks just returned plus the free ones; restore otherwise
+        for (size_t i = 0; i < t->tables[row].size(); ++i) t->returned.push_back(t->tables[row][i]);
+        t->tables[row].clear();
+        for (size_t i = 0; i < old.size(); ++i) t->returned.pop_back();
+        t->tables[row] = old;
+        return fail(B200_INVALID_ARGUMENT, "decoder_row_restart: not enough free blocks in the pool");
+    }
+    t->seq_lens[row] = 0;
+    d->row_limits[row] = max_total_len;
+    std::vector<uint32_t> slice(size_t(d->max_blocks_per_seq), 0xFFFFFFFFu);
+    for (size_t i = 0; i < t->tables[row].size(); ++i) slice[i] = t->tables[row][i];
+    const uint32_t zero = 0;
+    cudaStream_t s = d->ctx->stream;
+    CU_TRY(cudaMemcpyAsync(d->tables_dev + size_t(row) * d->max_blocks_per_seq, slice.data(), slice.size() * 4,
+                           cudaMemcpyHostToDevice, s));
+    CU_TRY(cudaMemcpyAsync(d->seq_lens_dev + row, &zero, 4, cudaMemcpyHostToDevice, s));
+    CU_TRY(cudaStreamSynchronize(s));      // the host vectors above go out of scope
     return B200_OK;
 }
 

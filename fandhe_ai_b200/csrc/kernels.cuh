@@ -87,7 +87,7 @@ cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int 
 cudaError_t dequant_planes(const int* raw, int splits, int M, int N, const float* sx, const float* sw, float* y,
                            cudaStream_t s);
 // positions[i] = seq_lens[i]; seq_lens[i] += 1
-cudaError_t begin_step(uint32_t* seq_lens, uint32_t* positions, int n, cudaStream_t s);
+cudaError_t begin_step(uint32_t* seq_lens, uint32_t* positions, const uint32_t* active, int n, cudaStream_t s);
 cudaError_t argmax_rows(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s);
 cudaError_t fill_normal(float* out, int64_t n, uint64_t seed, uint64_t stream_id, float std, cudaStream_t s);
 cudaError_t fill_normal_bf16(uint16_t* out, int64_t n, uint64_t seed, uint64_t stream_id, float std, cudaStream_t s);

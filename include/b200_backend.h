@@ -324,6 +324,14 @@ int32_t b200_decoder_fill_cache_random(b200_decoder* dec, uint64_t seed, float s
  * next_ids_host != NULL: the greedy samples are copied back (this synchronises). */
 int32_t b200_decoder_step(b200_decoder* dec, const int32_t* ids_host, int32_t* next_ids_host);
 int32_t b200_decoder_logits(b200_decoder* dec, float* host, uint64_t capacity_elems);
+/* One step in which only the rows with active[b] != 0 advance (NULL: all rows); the others keep their length and
+ * contents, and their entries of next_ids mean nothing.  With b200_decoder_row_restart this is what continuous
+ * batching over per-row lengths needs (the kernels already take seq_lens[B];
+ * docs/device-resident-kv-paged-attention-design.md:51). */
+int32_t b200_decoder_step_rows(b200_decoder* dec, const int32_t* ids, const uint8_t* active, int32_t* next_ids);
+/* Between steps: empties row `row` (its blocks return to the free stack) and reserves blocks for a new sequence
+ * of up to max_total_len tokens (at most the largest length given to b200_decoder_begin). */
+int32_t b200_decoder_row_restart(b200_decoder* dec, int32_t row, int32_t max_total_len);
 /* generate() with greedy sampling: out is [batch, max_length] and begins with the prompt. */
 int32_t b200_decoder_generate(b200_decoder* dec, const int32_t* prompt, int32_t batch, int32_t prompt_len,
                               int32_t max_length, int32_t* out);
@@ -345,6 +353,34 @@ int32_t b200_timer_stop(b200_ctx* ctx, float* elapsed_ms);
 /* Mean device time of one decode-attention launch on the decoder's current caches (cycling over the
  * layers so that each launch reads a different pool) and the algorithmic bytes of one launch. */
 int32_t b200_decoder_time_attention(b200_decoder* dec, int32_t iters, float* ms_per_launch, uint64_t* bytes_per_launch);
+
+/* ------------------------------------------------------------------ continuous batching
+ * BatchScheduler of the reference (crates/autodiff/src/generate/scheduler.rs:395-): a FIFO queue of requests and
+ * at most max_active requests in progress, one decoder row each; a step admits queued requests into free rows and
+ * advances every request in progress by one token (prompt tokens are fed one per step, then the greedy samples);
+ * a request finishes when it holds max_length tokens.  Rows and requests are processed in ascending order, so a run
+ * is reproducible.  With a decoder, create calls b200_decoder_begin(dec, max_active, ..., max_length per row). */
+typedef struct b200_scheduler b200_scheduler;
+int32_t b200_scheduler_create(b200_decoder* dec_or_null, int32_t max_active, int32_t max_queued, int32_t max_length,
+                              b200_scheduler** out);
+void b200_scheduler_destroy(b200_scheduler* s);
+/* scheduler.rs:445-504: queues a copy of the prompt, no forward; errors (empty prompt, prompt longer than
+ * max_length, max_length above the limit, queue full) leave the state unchanged.  Ids count up from 1. */
+int32_t b200_scheduler_submit(b200_scheduler* s, const int32_t* prompt, int32_t prompt_len, int32_t max_length,
+                              uint64_t* request_id);
+int32_t b200_scheduler_queued_len(const b200_scheduler* s);
+int32_t b200_scheduler_active_len(const b200_scheduler* s);
+int32_t b200_scheduler_finished_len(const b200_scheduler* s);
+/* scheduler.rs:571-589: one iteration; *completed = requests finished by this call. */
+int32_t b200_scheduler_step(b200_scheduler* s, int32_t* completed);
+/* The two host halves of a step (what b200_scheduler_step does around the decoder calls); arrays hold max_active
+ * entries.  Usable without a device. */
+int32_t b200_scheduler_plan_step(b200_scheduler* s, int32_t* ids, uint8_t* active, int32_t* restart_rows,
+                                 int32_t* restart_lens, int32_t* n_restart, int32_t* completed_without_forward);
+int32_t b200_scheduler_commit_step(b200_scheduler* s, const int32_t* sampled, int32_t* completed);
+/* Pops the oldest finished request (prompt + generated tokens); *len = -1 when there is none. */
+int32_t b200_scheduler_take_finished(b200_scheduler* s, uint64_t* request_id, int32_t* tokens, int32_t capacity,
+                                     int32_t* len);
 
 #ifdef __cplusplus
 }
