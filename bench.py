@@ -214,7 +214,7 @@ def run_reference(args, cfg, rank, world):
         "impl": "reference", "metric": "decode_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * cfg["batch"] / val,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": workload_config(args, cfg, 1),
+        "config": workload_config(args, cfg, world),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": sample.threads, "kind": "port",
                          "sample": sample.describe()},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -239,6 +239,7 @@ struct LayerParams {
     void* k_pool = nullptr;
     void* v_pool = nullptr;
     GemmPlan p_qkv, p_o, p_gu, p_down;
+    bool rope_fused = false;                    // the QKV GEMM finishes with RoPE + cache append itself
     PagedAttnPlan attn;
 };
 
@@ -560,11 +561,37 @@ int32_t enqueue_step(b200_decoder* d) {
     for (int l = 0; l < c.n_layers; ++l) {
         LayerParams& L = d->layers[l];
         // QKV projection -> RoPE -> append to the paged cache
-        CU_TRY(gemm_launch(L.p_qkv, ep, err, s));
-        CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv, d->cos_t,
-                               d->sin_t, c.max_seq_len, d->pos_dev, d->tables_dev, d->max_blocks_per_seq,
-                               c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
-                               static_cast<uint16_t*>(L.v_pool), err, s));
+        if (L.rope_fused) {
+            // dequant + RoPE + cache append inside the GEMM's split-K reduction (one tile = one head)
+            GemmEpilogue qe;
+            qe.fused = 1;
+            qe.a_scale = d->sx;
+            qe.a_per_row = 1;
+            qe.b_scale = d->scales + L.s_qkv;
+            qe.b_per_col = 1;
+            qe.rope.enabled = 1;
+            qe.rope.hq = d->hq_l;
+            qe.rope.hkv = d->hkv_l;
+            qe.rope.cos_t = d->cos_t;
+            qe.rope.sin_t = d->sin_t;
+            qe.rope.max_pos = c.max_seq_len;
+            qe.rope.positions = d->pos_dev;
+            qe.rope.block_tables = d->tables_dev;
+            qe.rope.max_blocks_per_seq = d->max_blocks_per_seq;
+            qe.rope.block_size = c.block_size;
+            qe.rope.num_blocks = c.num_blocks;
+            qe.rope.q_out = d->q;
+            qe.rope.k_pool = static_cast<uint16_t*>(L.k_pool);
+            qe.rope.v_pool = static_cast<uint16_t*>(L.v_pool);
+            CU_TRY(gemm_launch(L.p_qkv, qe, err, s));
+            launches -= 1;
+        } else {
+            CU_TRY(gemm_launch(L.p_qkv, ep, err, s));
+            CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv,
+                                        d->cos_t, d->sin_t, c.max_seq_len, d->pos_dev, d->tables_dev, d->max_blocks_per_seq,
+                                        c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
+                                        static_cast<uint16_t*>(L.v_pool), err, s));
+        }
         // attention over the cache (this rank's KV heads), then per-token quantisation
         if (paged_attention_can_quantize(L.attn)) {
             CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, nullptr,
@@ -917,6 +944,7 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     size_t attn_need = 0;
     for (auto& L : d->layers) {
         cudaError_t e = plan(&L.p_qkv, L.wqkv, d->n_qkv, dm);
+        L.rope_fused = e == cudaSuccess && dh == 128 && gemm_plan_can_rope(L.p_qkv, d->hq_l, d->hkv_l);
         if (e == cudaSuccess) e = plan(&L.p_o, L.wo, dm, d->hq_l * dh);
         if (e == cudaSuccess) e = plan(&L.p_gu, L.wgu, 2 * d->f_l, dm);
         if (e == cudaSuccess) e = plan(&L.p_down, L.wdown, dm, d->f_l);

@@ -304,6 +304,75 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const int rl = (warp & 3) * 32 + lane;
             const int row = m0 + rl;
             uint32_t* part = reinterpret_cast<uint32_t*>(smem_dyn + (smem_base - smem_u32(smem_dyn)));
+            if (p.ep.rope.enabled) {
+                // One tile = one head.  This rank finishes the dims [rank * cpr / 2, (rank + 1) * cpr / 2) and their
+                // rotation partners 64 further on: sum over the peers, dequantise, rotate (q and k heads), store.
+                const GemmRope& rp = p.ep.rope;
+                const int half_cpr = cpr / 2;
+                const int head = n0 / BN;
+                bool ok = row < p.M;
+                int pos = 0;
+                uint32_t blk = 0;
+                if (ok) {
+                    pos = static_cast<int>(rp.positions[row]);
+                    bool valid = pos < rp.max_pos;
+                    if (valid) {
+                        blk = rp.block_tables[static_cast<size_t>(row) * rp.max_blocks_per_seq + pos / rp.block_size];
+                        valid = blk < static_cast<uint32_t>(rp.num_blocks);
+                    }
+                    if (!valid) {
+                        atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrAppendSlot));
+                        ok = false;
+                    }
+                }
+                const float sa = ok ? p.ep.a_scale[row] : 0.0f;
+                const float* cr = rp.cos_t + static_cast<size_t>(pos) * 64;
+                const float* sr = rp.sin_t + static_cast<size_t>(pos) * 64;
+                const size_t slot = static_cast<size_t>(blk) * rp.block_size + pos % rp.block_size;
+                for (int cc = 0; cc < half_cpr; cc += 4) {
+                    const int i0 = rank * half_cpr + cc;
+                    int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+                    for (int peer = 0; peer < nsplit; ++peer) {
+                        const uint32_t* pp = cl.map_shared_rank(part, peer);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            lo[t] += static_cast<int>(pp[(i0 + t) * kBM + rl]);
+                            hi[t] += static_cast<int>(pp[(64 + i0 + t) * kBM + rl]);
+                        }
+                    }
+                    if (!ok) continue;
+                    float o1[4], o2[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const float x1 = fmaf(static_cast<float>(lo[t]), sa * p.ep.b_scale[head * BN + i0 + t], 0.0f);
+                        const float x2 = fmaf(static_cast<float>(hi[t]), sa * p.ep.b_scale[head * BN + 64 + i0 + t], 0.0f);
+                        if (head < rp.hq + rp.hkv) {
+                            const float c = cr[i0 + t], sn = sr[i0 + t];
+                            o1[t] = fmaf(x1, c, -__fmul_rn(x2, sn));
+                            o2[t] = fmaf(x2, c, __fmul_rn(x1, sn));
+                        } else {
+                            o1[t] = x1;
+                            o2[t] = x2;
+                        }
+                    }
+                    if (head < rp.hq) {
+                        float* dst = rp.q_out + (static_cast<size_t>(row) * rp.hq + head) * BN + i0;
+                        *reinterpret_cast<float4*>(dst) = make_float4(o1[0], o1[1], o1[2], o1[3]);
+                        *reinterpret_cast<float4*>(dst + 64) = make_float4(o2[0], o2[1], o2[2], o2[3]);
+                    } else {
+                        const bool is_k = head < rp.hq + rp.hkv;
+                        const int kh = is_k ? head - rp.hq : head - rp.hq - rp.hkv;
+                        uint16_t* dst = (is_k ? rp.k_pool : rp.v_pool) + (slot * rp.hkv + kh) * BN + i0;
+                        uint2 a, b;
+                        a.x = f32_to_bf16_bits(o1[0]) | (f32_to_bf16_bits(o1[1]) << 16);
+                        a.y = f32_to_bf16_bits(o1[2]) | (f32_to_bf16_bits(o1[3]) << 16);
+                        b.x = f32_to_bf16_bits(o2[0]) | (f32_to_bf16_bits(o2[1]) << 16);
+                        b.y = f32_to_bf16_bits(o2[2]) | (f32_to_bf16_bits(o2[3]) << 16);
+                        *reinterpret_cast<uint2*>(dst) = a;
+                        *reinterpret_cast<uint2*>(dst + 64) = b;
+                    }
+                }
+            } else
             for (int cc = 0; cc < cpr; cc += 4) {
                 const int col = rank * cpr + cc;
                 uint32_t v[4] = {0u, 0u, 0u, 0u};
@@ -473,6 +542,11 @@ cudaError_t launch_persist_t(const GemmPlan& plan, const PersistArgs& args, cuda
 
 }  // namespace
 
+bool gemm_plan_can_rope(const GemmPlan& plan, int hq, int hkv) {
+    return !plan.persist && plan.cluster && plan.bn == 128 && !plan.gate && plan.kind == kGemmI8 && plan.splits >= 2 &&
+           plan.splits <= 16 && (128 / plan.splits) % 8 == 0 && plan.N == (hq + 2 * hkv) * 128;
+}
+
 void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue) {
     if (sm_count <= 0) return;
     const int bn = plan->bn;
@@ -560,6 +634,7 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
 cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* err, cudaStream_t stream) {
     if (plan.persist) {
         if (!ep.fused && plan.gate) return cudaErrorInvalidValue;   // raw output always uses the plain column layout
+        if (ep.rope.enabled) return cudaErrorInvalidValue;
         PersistArgs pa;
         pa.M = plan.M; pa.N = plan.N; pa.K = plan.K;
         pa.stages = plan.stages;
@@ -589,6 +664,7 @@ cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* 
     args.err = err;
     args.cluster_reduce = plan.cluster;
     if (ep.fused && plan.splits != 1 && !plan.cluster) return cudaErrorInvalidValue;
+    if (ep.rope.enabled && !gemm_plan_can_rope(plan, ep.rope.hq, ep.rope.hkv)) return cudaErrorInvalidValue;
     if (!ep.fused && plan.gate) return cudaErrorInvalidValue;   // raw planes always use the plain column layout
     const bool i8 = plan.kind == kGemmI8;
     switch (plan.bn) {

@@ -16,6 +16,24 @@ namespace b200 {
 enum GemmKind : int { kGemmI8 = 0, kGemmFp8 = 1 };
 enum GemmAct : int { kActNone = 0, kActRelu = 1, kActSilu = 2, kActSiluGate = 3 };
 
+// Optional finish of a QKV projection whose tiles are exactly one head wide (BN = head_dim = 128): dequantise
+// (GemmEpilogue::a_scale per row, b_scale per column), rotate-half RoPE for the q and k heads with the row's
+// position, then q as f32 [M, hq, 128] and k / v as bf16 into the paged pools at the slot the block table gives.
+// Only the one-tile kernel with split-K inside a cluster implements it (gemm_launch refuses other plans).
+struct GemmRope {
+    int enabled = 0;
+    int hq = 0, hkv = 0;                    // heads in this GEMM's N = (hq + 2 hkv) * 128
+    const float* cos_t = nullptr;           // [max_pos, 64]
+    const float* sin_t = nullptr;
+    int max_pos = 0;
+    const uint32_t* positions = nullptr;    // [M] position of the token of each row
+    const uint32_t* block_tables = nullptr; // [M, max_blocks_per_seq]
+    int max_blocks_per_seq = 0, block_size = 0, num_blocks = 0;
+    float* q_out = nullptr;
+    uint16_t* k_pool = nullptr;
+    uint16_t* v_pool = nullptr;
+};
+
 struct GemmEpilogue {
     int fused = 0;                 // 0: write raw accumulators to `raw`; 1: fused epilogue to `out`
     void* raw = nullptr;           // [splits][M][N] int32 (i8) or f32 (fp8)
@@ -28,6 +46,7 @@ struct GemmEpilogue {
     void* out = nullptr;             // [M][N_out] f32 or bf16
     int out_bf16 = 0;
     int act = kActNone;              // kActSiluGate: B rows [0, N/2) are gate, [N/2, N) are up, N_out = N/2
+    GemmRope rope;                   // see GemmRope; needs fused = 1 with per-row / per-column scales, no bias
 };
 
 struct GemmPlan {
@@ -57,6 +76,9 @@ void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue
 // Returns cudaSuccess or an error; `why` receives a static message on failure.
 cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* b, int M, int N, int K,
                            int gate, int want_splits, int want_bn, const char** why);
+
+// True when a launch of this plan may carry a GemmRope epilogue for hq + 2 hkv heads of 128.
+bool gemm_plan_can_rope(const GemmPlan& plan, int hq, int hkv);
 
 // Enqueues the GEMM on `stream`.  `err` is the context's device error word.
 cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* err, cudaStream_t stream);

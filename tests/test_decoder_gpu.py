@@ -137,6 +137,9 @@ def test_step_api_matches_generate_and_feeds_ids_from_the_host(be):
             dec.step(got[:, 11])
         # per layer: QKV GEMM, RoPE/append, attention, merge + quantise, O GEMM, residual/norm/quant, gate-up GEMM,
         # gate/quant, down GEMM, residual/norm/quant (head_dim 128 with 16-token blocks: the fast attention path)
-        assert dec.launches_per_step == 2 + cfg["n_layers"] * 10 + 2
+        # minus the RoPE/append kernel when the QKV GEMM splits K inside a cluster and finishes the heads itself
+        info = dec.plan_info()
+        fused_rope = cfg["head_dim"] == 128 and info["qkv_tile"] == 128 and info["qkv_splits"] > 1
+        assert dec.launches_per_step == 2 + cfg["n_layers"] * (9 if fused_rope else 10) + 2
     finally:
         dec.close()
