@@ -680,7 +680,7 @@ tp_finish_kernel(TpFinishArgs a) {
 
 // Groups of four columns per thread (1, 2 or 4) and the block size for a row of n columns; vpt = 0 when the
 // row is too wide (or not a multiple of 4) for the one-CTA kernels.
-void wide_shape(int n, int* vpt, int* threads) {
+void wide_shape(int n, int* vpt, int* threads, int rows = 1) {
     *vpt = 0;
     *threads = 0;
     if (n <= 0 || n % 4 != 0) return;
@@ -688,6 +688,9 @@ void wide_shape(int n, int* vpt, int* threads) {
     int v = (groups + kWideThreads - 1) / kWideThreads;
     if (v > kWideMaxVpt) return;
     if (v == 3) v = 4;
+    // more rows than SMs: smaller CTAs (more groups per thread) so that several rows share an SM and the batch
+    // still runs as one wave
+    while (rows > 148 && v < kWideMaxVpt && groups / (2 * v) >= 256) v *= 2;
     *vpt = v;
     *threads = ((groups + v - 1) / v + 31) / 32 * 32;
 }
@@ -724,7 +727,7 @@ cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, cons
                                   const float* pre, const float* norm_w, float eps, float* h, int8_t* xq, float* sx_out,
                                   cudaStream_t s) {
     int vpt, threads;
-    wide_shape(d, &vpt, &threads);
+    wide_shape(d, &vpt, &threads, M);
 #define B200_WIDE_RESID(V)                                                                                              \
     return launch_ex(resid_norm_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, d, sx_in, \
                      sw, pre, norm_w, eps, h, xq, sx_out)
@@ -741,7 +744,7 @@ cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, cons
 cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
                             float* sx_out, cudaStream_t s) {
     int vpt, threads;
-    wide_shape(F, &vpt, &threads);
+    wide_shape(F, &vpt, &threads, M);
 #define B200_WIDE_GATE(V)                                                                                        \
     return launch_ex(gate_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, F, sx_in, \
                      sw, xq, sx_out)
@@ -756,7 +759,7 @@ cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const floa
 
 cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s) {
     int vpt, threads;
-    wide_shape(n, &vpt, &threads);
+    wide_shape(n, &vpt, &threads, M);
     if (vpt == 1) return launch_ex(quant_rows_wide_kernel<1>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
     if (vpt == 2) return launch_ex(quant_rows_wide_kernel<2>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
     if (vpt == 4) return launch_ex(quant_rows_wide_kernel<4>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);

@@ -933,9 +933,11 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     const int M = batch, dm = c.d_model, dh = c.head_dim;
     const char* why = "";
     size_t raw_need = 0;
-    auto plan = [&](GemmPlan* p, size_t w_off, int N, int K) -> cudaError_t {
+    // `fused`: the launch will use a fused epilogue (the row-parallel projections under tensor parallelism write
+    // their dequantised partial), which moves the switch to the persistent kernel down to half a wave of tiles
+    auto plan = [&](GemmPlan* p, size_t w_off, int N, int K, bool fused = false) -> cudaError_t {
         cudaError_t e = gemm_make_plan(p, kGemmI8, d->xq, d->payload + w_off, M, N, K, 0, d->ctx->tune_splits, d->ctx->tune_bn, &why);
-        if (e == cudaSuccess && d->ctx->tune_splits == 0) gemm_plan_make_persistent(p, d->ctx->sm_count, false);
+        if (e == cudaSuccess && d->ctx->tune_splits == 0) gemm_plan_make_persistent(p, d->ctx->sm_count, fused);
         if (e == cudaSuccess) raw_need = std::max(raw_need, gemm_raw_elems(*p));
         return e;
     };
@@ -945,9 +947,9 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     for (auto& L : d->layers) {
         cudaError_t e = plan(&L.p_qkv, L.wqkv, d->n_qkv, dm);
         L.rope_fused = e == cudaSuccess && dh == 128 && gemm_plan_can_rope(L.p_qkv, d->hq_l, d->hkv_l);
-        if (e == cudaSuccess) e = plan(&L.p_o, L.wo, dm, d->hq_l * dh);
+        if (e == cudaSuccess) e = plan(&L.p_o, L.wo, dm, d->hq_l * dh, c.tp_size > 1);
         if (e == cudaSuccess) e = plan(&L.p_gu, L.wgu, 2 * d->f_l, dm);
-        if (e == cudaSuccess) e = plan(&L.p_down, L.wdown, dm, d->f_l);
+        if (e == cudaSuccess) e = plan(&L.p_down, L.wdown, dm, d->f_l, c.tp_size > 1);
         if (e != cudaSuccess) return fail(B200_UNSUPPORTED, std::string("decoder_begin: ") + why);
         e = paged_attention_make_plan(&L.attn, sh, 1, L.k_pool, L.v_pool, mx, d->ctx->tune_attn_chunk_blocks);
         if (e != cudaSuccess) return fail(B200_KERNEL_LAUNCH_FAILED, "decoder_begin: attention plan failed");
