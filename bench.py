@@ -45,6 +45,9 @@ CONFIGS = {
     # the per-rank shapes of the 8B model under 8-way tensor parallelism (GEMM widths, heads), as one GPU sees them
     "tp8rank": dict(n_layers=8, d_model=4096, n_heads=4, n_kv_heads=1, head_dim=128, d_ff=1792, vocab=16032, batch=128,
                     prompt_lo=256, prompt_hi=2048),
+    # the same with the batch of the weak-scaling run at 8 GPUs (128 sequences per rank)
+    "tp8rank1024": dict(n_layers=8, d_model=4096, n_heads=4, n_kv_heads=1, head_dim=128, d_ff=1792, vocab=16032,
+                        batch=1024, prompt_lo=256, prompt_hi=2048),
     # a small shape for quick functional runs of this script
     "tiny": dict(n_layers=2, d_model=512, n_heads=8, n_kv_heads=8, head_dim=128, d_ff=1024, vocab=2048, batch=16,
                  prompt_lo=32, prompt_hi=128),
