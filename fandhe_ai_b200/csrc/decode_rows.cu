@@ -550,10 +550,11 @@ struct TpFinishArgs {
     uint32_t* epoch;           // this rank's call counter
     unsigned int* arrived;     // CTAs of this launch that have delivered their row
     uint32_t* err;
+    uint32_t spin_limit;       // polls before a wait gives up
 };
 
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* err) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* err, uint32_t spin_limit) {
+    for (uint32_t it = 0; it < spin_limit; ++it) {
         // epochs only grow; the difference is taken modulo 2^32 so that the comparison survives a wrap
         if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
     }
@@ -581,7 +582,7 @@ tp_finish_kernel(TpFinishArgs a) {
     }
     // 2. wait for every rank's partial
     if (threadIdx.x < a.tp) {
-        if (!wait_flag(ready + threadIdx.x, epoch, a.err)) s_ok = 0;
+        if (!wait_flag(ready + threadIdx.x, epoch, a.err, a.spin_limit)) s_ok = 0;
     }
     __syncthreads();
     const bool ok = s_ok != 0;
@@ -668,7 +669,7 @@ tp_finish_kernel(TpFinishArgs a) {
         if (threadIdx.x < a.tp) {
             __threadfence_system();
             st_release_sys(reinterpret_cast<uint32_t*>(a.peers[threadIdx.x] + 256) + a.rank, epoch);
-            wait_flag(done + threadIdx.x, epoch, a.err);
+            wait_flag(done + threadIdx.x, epoch, a.err, a.spin_limit);
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -798,10 +799,11 @@ bool tp_finish_supported(int d) {
 
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
-                      cudaStream_t s) {
+                      cudaStream_t s, uint32_t spin_limit) {
     int vpt, threads;
     wide_shape(d, &vpt, &threads);
-    TpFinishArgs a{peers, o_sx, o_xq, o_part, tp, rank, rows, d, norm_w, eps, h, epoch, arrived, err};
+    TpFinishArgs a{peers, o_sx, o_xq, o_part, tp, rank, rows, d, norm_w, eps, h, epoch, arrived, err,
+                   spin_limit ? spin_limit : kSpinLimit};
     if (vpt == 1) return launch_ex(tp_finish_kernel<1>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 2) return launch_ex(tp_finish_kernel<2>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 4) return launch_ex(tp_finish_kernel<4>, dim3(rows), dim3(threads), 0, s, 1, true, a);

@@ -887,6 +887,46 @@ int32_t b200_decoder_init_tp(b200_decoder* d, const uint8_t* unique_id128) {
 
 int32_t b200_decoder_tp_exchange(const b200_decoder* d) { return d && d->tp_exchange ? 1 : 0; }
 
+// Failure-detection self-test of the cross-GPU finish kernel on one GPU: launches it as rank 0 of 2 over a scratch
+// exchange block in which nobody ever raises rank 1's flags.  The kernel's bounded waits (2^16 polls here) run
+// out, it records kErrPeerWait in the context's error word, skips its loads and stores, and returns; the next
+// synchronisation reports the failure and poisons the context, and the device stays usable.
+int32_t b200_selftest_peer_wait(b200_ctx* ctx) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (int32_t st = set_device(ctx)) return st;
+    const int d = 512, rows = 2, tp = 2;
+    const size_t o_sx = 512, o_xq = 1024, o_part = 1024 + 4096;
+    const size_t bytes = o_part + size_t(tp) * rows * d * sizeof(float);
+    uint8_t* block = nullptr;
+    uint8_t** peers = nullptr;
+    float* h = nullptr;
+    float* w = nullptr;
+    uint32_t* counters = nullptr;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&block), bytes);
+    if (e == cudaSuccess) e = cudaMemset(block, 0, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&peers), tp * sizeof(uint8_t*));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h), size_t(tp) * rows * d * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(h, 0, size_t(tp) * rows * d * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&w), d * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(w, 0, d * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(counters, 0, 2 * sizeof(uint32_t));
+    uint8_t* host_peers[2] = {block, block};      // "rank 1" is the same block: its flags are never raised
+    if (e == cudaSuccess) e = cudaMemcpy(peers, host_peers, sizeof(host_peers), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess)
+        e = tp_finish(peers, o_sx, o_xq, o_part, tp, 0, rows, d, w, 1e-5f, h, counters, counters + 1, ctx->err_dev, ctx->stream,
+                      1u << 16);
+    int32_t st = B200_OK;
+    if (e != cudaSuccess) st = fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("selftest_peer_wait: ") + cudaGetErrorString(e));
+    else st = b200_synchronize(ctx);              // reports the device error word
+    cudaFree(block);
+    cudaFree(peers);
+    cudaFree(h);
+    cudaFree(w);
+    cudaFree(counters);
+    return st;
+}
+
 // Starts a generation: clears the page table, reserves blocks for `max_total_len[b]` tokens per row
 // (the reference's generate() always runs to max_length, so the final length is known up front), uploads
 // the flattened tables once, and sets seq_lens to `start_lens` (0 for a fresh cache).

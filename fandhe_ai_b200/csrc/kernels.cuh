@@ -101,6 +101,6 @@ cudaError_t slice_cols_i8(const int8_t* src, int64_t rows, int64_t ld, int64_t c
 bool tp_finish_supported(int d);
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
-                      cudaStream_t s);
+                      cudaStream_t s, uint32_t spin_limit = 0);   // 0: the default bound of every device-side wait
 
 }  // namespace b200

@@ -315,6 +315,11 @@ int32_t b200_decoder_init_tp(b200_decoder* dec, const uint8_t* unique_id128);
  * 0 when the step uses ncclAllReduce instead (mapping failed, batch not divisible by the rank count, or
  * B200_TP_EXCHANGE=0 in the environment).  No reference counterpart (the reference has no tensor parallelism). */
 int32_t b200_decoder_tp_exchange(const b200_decoder* dec);
+/* Failure-detection self-test on one GPU: runs the cross-GPU finish kernel as rank 0 of 2 with a peer whose flags
+ * are never raised.  Its bounded waits run out, the kernel records the peer-wait code in the context's error word
+ * and returns; this call then returns KernelLaunchFailed and the context is poisoned (re-create it).  The device
+ * stays usable.  No reference counterpart. */
+int32_t b200_selftest_peer_wait(b200_ctx* ctx);
 /* Starts a generation of `batch` rows: row b starts at start_lens[b] cached tokens (NULL: 0) and may grow
  * to max_total_lens[b]; blocks for the final length are reserved now and the tables uploaded once. */
 int32_t b200_decoder_begin(b200_decoder* dec, int32_t batch, const int32_t* start_lens, const int32_t* max_total_lens);
