@@ -10,16 +10,21 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def test_two_rank_tensor_parallel_decode_matches_the_cpu_decoder():
+@pytest.mark.parametrize("exchange", ["1", "0"])
+def test_two_rank_tensor_parallel_decode_matches_the_cpu_decoder(exchange):
+    """exchange 1: the row-parallel outputs are finished over the CUDA-IPC mapped peer blocks (falls back to
+    ncclAllReduce by itself where IPC is not available); exchange 0: ncclAllReduce is forced."""
     import torch
 
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200_TP_EXCHANGE=exchange)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29731", str(ROOT / "tests" / "multi" / "tp_worker.py")]
     r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert r.returncode == 0 and "TP_OK" in r.stdout, r.stdout[-3000:]
+    if exchange == "0":
+        assert "exchange=0" in r.stdout, r.stdout[-3000:]
 
 
 def test_peer_wait_runs_out_with_an_error_status_and_the_device_stays_usable(fresh_be):
