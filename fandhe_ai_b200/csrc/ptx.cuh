@@ -1,5 +1,5 @@
-// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, no
-// cluster multicast anywhere), tcgen05 (TMEM alloc / MMA / commit / ld) and a few
+// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, every
+// copy lands in the issuing CTA only), tcgen05 (TMEM alloc / MMA / commit / ld) and a few
 // memory-ordering helpers.  Every wait in this file is bounded: a wait that runs
 // out records a code in a device error word and returns false so the kernel can
 // unwind (free TMEM, leave) instead of hanging the GPU.
