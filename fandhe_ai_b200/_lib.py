@@ -88,7 +88,13 @@ SIGNATURES = {
     "b200_ctx_is_poisoned": (_I32, [_P]),
     "b200_ctx_generation": (C.c_uint64, [_P]),
     "b200_ctx_stream": (_P, [_P]),
+    "b200_ctx_recover": (_I32, [_P]),
+    "b200_test_inject_probe_failures": (_I32, [_P, _I32]),
+    "b200_test_poison": (_I32, [_P]),
+    "b200_test_mark_capturing": (_I32, [_P, _I32]),
+    "b200_memory_info": (_I32, [_P, C.POINTER(_SZ), C.POINTER(_SZ)]),
     "b200_gemm_tuning": (_I32, [_P, _I32, _I32]),
+    "b200_gemm_plan_info": (_I32, [_P, _I64, _I64, _I64, _I32, _I32, _P]),
     "b200_alloc_zeroed": (_I32, [_P, _SZ, C.POINTER(_P)]),
     "b200_upload": (_I32, [_P, _P, _SZ, C.POINTER(_P)]),
     "b200_upload_into": (_I32, [_P, _P, _SZ, _P, _SZ]),
@@ -157,6 +163,7 @@ SIGNATURES = {
     "b200_timer_start": (_I32, [_P]),
     "b200_timer_stop": (_I32, [_P, C.POINTER(C.c_float)]),
     "b200_decoder_time_attention": (_I32, [_P, _I32, C.POINTER(C.c_float), C.POINTER(_U64)]),
+    "b200_linear_fp8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _I32, _P, _SZ]),
     "b200_linear_w8a8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _P, _SZ]),
 }
 

@@ -114,6 +114,22 @@ class Backend:
     def gemm_tuning(self, tile_n: int = 0, splits: int = 0) -> None:
         check(lib().b200_gemm_tuning(self._ctx, tile_n, splits))
 
+    def gemm_plan_info(self, m: int, n: int, k: int, gated: bool = False, fused: bool = True) -> dict:
+        """Which kernel form a GEMM of this shape takes (nothing is launched)."""
+        buf = (C.c_int32 * 6)()
+        check(lib().b200_gemm_plan_info(self._ctx, m, n, k, int(gated), int(fused), buf))
+        return dict(zip(["tile", "splits", "cluster", "persistent", "ctas", "stages"], list(buf)))
+
+    def memory_info(self):
+        """(free, total) device memory in bytes."""
+        free, total = C.c_size_t(), C.c_size_t()
+        check(lib().b200_memory_info(self._ctx, C.byref(free), C.byref(total)))
+        return int(free.value), int(total.value)
+
+    def recover(self) -> None:
+        """In-place recovery of a poisoned context (`invalidate` of the reference's ordinal state machine)."""
+        check(lib().b200_ctx_recover(self._ctx))
+
     # ------------------------------------------------------------- QuantOps
     def quantize_i8_per_row(self, x: DeviceBuffer, rows: int, cols: int):
         """Symmetric int8 with one scale per row (per output channel for weights [n, k], per token
@@ -170,6 +186,20 @@ class Backend:
         n_out = n // 2 if activation == ACT_SILU_GATE else n
         out = self.alloc_zeroed((m, n_out), np.float32)
         self.linear_forward_device_into(a, m, k, w_q, 0, w_scale, 0, bias, 0, n, activation, out, residual)
+        return out
+
+
+    def linear_fp8_forward_device(self, a: DeviceBuffer, m: int, k: int, w_fp8: DeviceBuffer, w_scale: DeviceBuffer,
+                                  bias: Optional[DeviceBuffer], n: int, activation: int = ACT_NONE,
+                                  residual: Optional[DeviceBuffer] = None, out_dtype: int = F32, w_off: int = 0,
+                                  w_scale_off: int = 0, bias_off: int = 0) -> DeviceBuffer:
+        """`linear_forward_device` with E4M3 weights (one scale) and the f32 activation quantised per tensor on
+        the device (crates/tensor-core/src/low_precision.rs:193-249 is the f16 / bf16 ancestor)."""
+        n_out = n // 2 if activation == ACT_SILU_GATE else n
+        out = self.alloc_zeroed((m, n_out), np.float32 if out_dtype == F32 else np.uint16)
+        check(lib().b200_linear_fp8(self._ctx, a.handle, 0, m, k, w_fp8.handle, w_off, w_scale.handle, w_scale_off,
+                                    bias.handle if bias else None, bias_off, n, activation,
+                                    residual.handle if residual else None, 0, out_dtype, out.handle, 0))
         return out
 
 

@@ -7,7 +7,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <new>
+#include <thread>
 
 #include "gemm_tc5.cuh"
 #include "kernels.cuh"
@@ -28,6 +30,21 @@ bool pdl_enabled() {
     return on;
 }
 
+int current_sm_count() {
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> cached[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 1;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return 1;
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
+
 int32_t fail(int32_t st, const std::string& msg) {
     g_last_error = msg;
     return st;
@@ -37,10 +54,33 @@ int32_t fail_runtime(b200_ctx* ctx, int32_t st, const std::string& msg) {
     g_last_error = msg;
     return st;
 }
+namespace {
+uint64_t this_thread_token() {
+    const uint64_t h = static_cast<uint64_t>(std::hash<std::thread::id>()(std::this_thread::get_id()));
+    return h | 1ull;      // never 0, which means "nobody"
+}
+}  // namespace
+
+CaptureGuard::CaptureGuard(b200_ctx* c) : ctx(c) { ctx->capture_owner.store(this_thread_token()); }
+CaptureGuard::~CaptureGuard() { ctx->capture_owner.store(0); }
+
+// Entry gate of every call (begin_driver_call of the reference, crates/backend-cuda/src/context_cache.rs:1998):
+// permanent states first, then the two transient ones, which do not poison anything.
 int32_t check_ctx(const b200_ctx* ctx) {
     if (!ctx) return fail(B200_INVALID_ARGUMENT, "context is null");
+    if (ctx->unrecoverable)
+        return fail(B200_DEVICE_CONTEXT_UNRECOVERABLE, "device context of ordinal " + std::to_string(ctx->ordinal) +
+                                                           " could not be recovered (" + ctx->probe_error + "); restart the process");
+    if (ctx->retiring.load())
+        return fail(B200_DEVICE_CONTEXT_RETIRING, "device context of ordinal " + std::to_string(ctx->ordinal) +
+                                                      " is being recovered; retry shortly");
     if (ctx->poisoned)
-        return fail(B200_DEVICE_CONTEXT_POISONED, "device context is poisoned by an earlier runtime failure; re-create it");
+        return fail(B200_DEVICE_CONTEXT_POISONED,
+                    "device context is poisoned by an earlier runtime failure; recover it (b200_ctx_recover) or re-create it");
+    const uint64_t owner = ctx->capture_owner.load();
+    if (owner != 0 && owner != this_thread_token())
+        return fail(B200_DEVICE_CONTEXT_CAPTURE_IN_PROGRESS, "another thread is capturing a CUDA graph on ordinal " +
+                                                                 std::to_string(ctx->ordinal) + "; retry shortly");
     return B200_OK;
 }
 int32_t check_buf(const b200_ctx* ctx, const b200_buf* buf, size_t off, size_t need, const char* name, bool optional) {
@@ -141,6 +181,9 @@ const char* b200_status_name(int32_t st) {
         case B200_INVALID_ARGUMENT: return "InvalidArgument";
         case B200_DEVICE_CONTEXT_POISONED: return "DeviceContextPoisoned";
         case B200_STALE_DEVICE_GENERATION: return "StaleDeviceGeneration";
+        case B200_DEVICE_CONTEXT_RETIRING: return "DeviceContextRetiring";
+        case B200_DEVICE_CONTEXT_UNRECOVERABLE: return "DeviceContextUnrecoverable";
+        case B200_DEVICE_CONTEXT_CAPTURE_IN_PROGRESS: return "DeviceContextCaptureInProgress";
         default: return "Unknown";
     }
 }
@@ -209,7 +252,102 @@ int32_t b200_synchronize(b200_ctx* ctx) {
     return check_error_word(ctx, "synchronize");
 }
 
-int32_t b200_ctx_is_poisoned(const b200_ctx* ctx) { return ctx && ctx->poisoned ? 1 : 0; }
+static __global__ void probe_identity_kernel(const uint32_t* in, uint32_t* out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = in[i];
+}
+
+// The recovery probe of the reference (256-byte allocation -> upload -> identity kernel -> download -> compare,
+// crates/backend-cuda/src/context_cache.rs:2519).  Returns an empty string on success.
+static std::string run_recovery_probe(b200_ctx* ctx) {
+    if (ctx->inject_probe_failures > 0) {
+        --ctx->inject_probe_failures;
+        return "injected probe mismatch";
+    }
+    uint32_t host_in[64], host_out[64];
+    for (int i = 0; i < 64; ++i) { host_in[i] = 0x9E3779B9u * (i + 1); host_out[i] = 0; }
+    uint32_t* dev = nullptr;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&dev), 512);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dev, host_in, 256, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) {
+        probe_identity_kernel<<<1, 64, 0, ctx->stream>>>(dev, dev + 64, 64);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, dev + 64, 256, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (dev) cudaFree(dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return std::string("probe failed: ") + cudaGetErrorString(e);
+    }
+    return std::memcmp(host_in, host_out, 256) == 0 ? std::string() : std::string("probe data mismatch");
+}
+
+// Recovery of a poisoned context in place (invalidate of the reference): drain, clear the device error word,
+// probe, and start a new generation so that every buffer of the old one is refused as stale.
+int32_t b200_ctx_recover(b200_ctx* ctx) {
+    if (!ctx) return fail(B200_INVALID_ARGUMENT, "ctx_recover: context is null");
+    if (ctx->unrecoverable) return check_ctx(ctx);
+    if (!ctx->poisoned) return B200_OK;
+    if (ctx->retiring.exchange(true)) return fail(B200_DEVICE_CONTEXT_RETIRING, "ctx_recover: another thread is recovering this context");
+    constexpr int kLimitProbeRetries = 3;
+    std::string why;
+    cudaError_t e = cudaSetDevice(ctx->ordinal);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->err_dev, 0, 4 * sizeof(uint32_t), ctx->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        why = std::string("drain failed: ") + cudaGetErrorString(e);
+        ctx->probe_failures = kLimitProbeRetries;          // a stream that cannot be drained is final
+    } else {
+        why = run_recovery_probe(ctx);
+        ctx->probe_failures = why.empty() ? 0 : ctx->probe_failures + 1;
+    }
+    int32_t st = B200_OK;
+    if (why.empty()) {
+        ctx->generation = ++g_generation;
+        ctx->poisoned = false;
+        if (ctx->ws) { cudaFree(ctx->ws); ctx->ws = nullptr; ctx->ws_bytes = 0; }
+        ctx->ws_locked = false;
+    } else if (ctx->probe_failures >= kLimitProbeRetries) {
+        ctx->unrecoverable = true;
+        ctx->probe_error = why;
+    } else {
+        st = B200_DEVICE_CONTEXT_POISONED;
+    }
+    ctx->retiring.store(false);
+    if (ctx->unrecoverable) return check_ctx(ctx);
+    if (st != B200_OK) return fail(st, "ctx_recover: " + why + "; the context stays poisoned, recovery may be retried");
+    return B200_OK;
+}
+
+int32_t b200_test_inject_probe_failures(b200_ctx* ctx, int32_t count) {
+    if (!ctx || count < 0) return fail(B200_INVALID_ARGUMENT, "test_inject_probe_failures: bad argument");
+    ctx->inject_probe_failures = count;
+    return B200_OK;
+}
+
+int32_t b200_test_mark_capturing(b200_ctx* ctx, int32_t on) {
+    if (!ctx) return fail(B200_INVALID_ARGUMENT, "test_mark_capturing: context is null");
+    ctx->capture_owner.store(on ? this_thread_token() : 0);
+    return B200_OK;
+}
+
+int32_t b200_memory_info(b200_ctx* ctx, size_t* free_bytes, size_t* total_bytes) {
+    if (!ctx || !free_bytes || !total_bytes) return fail(B200_INVALID_ARGUMENT, "memory_info: null pointer");
+    if (int32_t st = set_device(ctx)) return st;
+    cudaError_t e = cudaMemGetInfo(free_bytes, total_bytes);
+    if (e != cudaSuccess) return fail(B200_DEVICE_UNAVAILABLE, std::string("memory_info: ") + cudaGetErrorString(e));
+    return B200_OK;
+}
+
+int32_t b200_test_poison(b200_ctx* ctx) {
+    if (!ctx) return fail(B200_INVALID_ARGUMENT, "test_poison: context is null");
+    ctx->poisoned = true;
+    return B200_OK;
+}
+
+int32_t b200_ctx_is_poisoned(const b200_ctx* ctx) { return ctx && (ctx->poisoned || ctx->unrecoverable) ? 1 : 0; }
 uint64_t b200_ctx_generation(const b200_ctx* ctx) { return ctx ? ctx->generation : 0; }
 void* b200_ctx_stream(b200_ctx* ctx) { return ctx ? static_cast<void*>(ctx->stream) : nullptr; }
 
@@ -528,6 +666,31 @@ int32_t b200_gemm_q8_scaled(b200_ctx* ctx, int32_t op_dtype, const b200_buf* a, 
     return B200_OK;
 }
 
+// Which kernel form the two GEMM entry points above would use for a shape (nothing is launched).
+int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t gated, int32_t fused, int32_t* out6) {
+    if (!ctx || !out6) return fail(B200_INVALID_ARGUMENT, "gemm_plan_info: null pointer");
+    if (int32_t st = check_gemm_dims("gemm_plan_info", m, n, k)) return st;
+    if (m <= 0 || n <= 0 || k <= 0) return fail(B200_INVALID_ARGUMENT, "gemm_plan_info: m, n, k must be positive");
+    if (int32_t st = set_device(ctx)) return st;
+    GemmPlan plan;
+    const char* why = "";
+    const void* aligned = reinterpret_cast<const void*>(uintptr_t(256));     // never dereferenced, never encoded
+    cudaError_t e;
+    if (fused && ctx->tune_splits == 0) {
+        e = gemm_make_plan(&plan, kGemmI8, aligned, aligned, int(m), int(n), int(k), gated ? 1 : 0, 1, ctx->tune_bn, &why, false);
+        if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
+        gemm_plan_make_persistent(&plan, ctx->sm_count, true);
+    }
+    if (!fused || !plan.persist) {
+        e = gemm_make_plan(&plan, kGemmI8, aligned, aligned, int(m), int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why, false);
+        if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
+        if (!fused && ctx->tune_splits == 0) gemm_plan_make_persistent(&plan, ctx->sm_count, false);
+    }
+    const int v[6] = {plan.bn, plan.splits, plan.cluster, plan.persist, plan.persist ? plan.grid : 0, plan.stages};
+    for (int i = 0; i < 6; ++i) out6[i] = v[i];
+    return B200_OK;
+}
+
 /* ------------------------------------------------------------------ quantized linear */
 
 int32_t b200_linear_w8a8(b200_ctx* ctx, const b200_buf* a, size_t a_off, int64_t m, int64_t k, const b200_buf* w,
@@ -571,6 +734,50 @@ int32_t b200_linear_w8a8(b200_ctx* ctx, const b200_buf* a, size_t a_off, int64_t
     ctx->ws_locked = true;
     int32_t st = b200_gemm_q8_scaled(ctx, B200_I8, &scratch, 0, &scratch, xq_bytes, 1, w, w_off, w_scale, w_scale_off, 1, bias,
                                      bias_off, activation, residual, residual_off, m, n, k, B200_F32, out, out_off);
+    ctx->ws = saved_ws;
+    ctx->ws_bytes = saved_bytes;
+    ctx->ws_locked = false;
+    return st;
+}
+
+
+int32_t b200_linear_fp8(b200_ctx* ctx, const b200_buf* a, size_t a_off, int64_t m, int64_t k, const b200_buf* w,
+                        size_t w_off, const b200_buf* w_scale, size_t w_scale_off, const b200_buf* bias, size_t bias_off,
+                        int64_t n, int32_t activation, const b200_buf* residual, size_t residual_off, int32_t out_dtype,
+                        b200_buf* out, size_t out_off) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (int32_t st = check_gemm_dims("linear_fp8", m, n, k)) return st;
+    if (activation < B200_ACT_NONE || activation > B200_ACT_SILU_GATE)
+        return fail(B200_UNSUPPORTED, "linear_fp8: unknown activation");
+    size_t ab;
+    if (!mul_size(m, k, 4, &ab)) return fail(B200_INVALID_ARGUMENT, "linear_fp8: size overflow");
+    if (int32_t st = check_buf(ctx, a, a_off, ab, "linear_fp8 a")) return st;
+    if (a_off & 15) return fail(B200_INVALID_ARGUMENT, "linear_fp8: a offset must be a multiple of 16 bytes");
+    if (m == 0 || n == 0) return B200_OK;
+    if (k == 0) return fail(B200_UNSUPPORTED, "linear_fp8: k == 0");
+    if (int32_t st = set_device(ctx)) return st;
+    // Scratch: [a as E4M3, m*k bytes][its scale, one f32][split planes of the GEMM entry behind them].
+    const size_t aq_bytes = align_up(size_t(m) * size_t(k), 256);
+    const size_t sa_bytes = 256;
+    const size_t max_planes = ctx->tune_splits > 16 ? size_t(ctx->tune_splits) : 16;
+    const size_t plane_bytes = align_up(size_t(m) * size_t(n) * 4 * max_planes, 256);
+    uint8_t* ws = static_cast<uint8_t*>(ensure_ws(ctx, aq_bytes + sa_bytes + plane_bytes));
+    if (!ws) return B200_DEVICE_ALLOCATION_FAILED;
+    cudaError_t e = quantize_fp8_per_tensor(buf_ptr<const float>(a, a_off), m * k, ws, reinterpret_cast<float*>(ws + aq_bytes),
+                                            ctx->amax_scratch, ctx->stream);
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("linear_fp8 quantize: ") + cudaGetErrorString(e));
+    b200_buf scratch;
+    scratch.owner = ctx;
+    scratch.generation = ctx->generation;
+    scratch.ptr = ws;
+    scratch.bytes = aq_bytes + sa_bytes;
+    void* saved_ws = ctx->ws;
+    size_t saved_bytes = ctx->ws_bytes;
+    ctx->ws = ws + aq_bytes + sa_bytes;
+    ctx->ws_bytes = saved_bytes - (aq_bytes + sa_bytes);
+    ctx->ws_locked = true;
+    int32_t st = b200_gemm_q8_scaled(ctx, B200_FP8_E4M3, &scratch, 0, &scratch, aq_bytes, 0, w, w_off, w_scale, w_scale_off, 0,
+                                     bias, bias_off, activation, residual, residual_off, m, n, k, out_dtype, out, out_off);
     ctx->ws = saved_ws;
     ctx->ws_bytes = saved_bytes;
     ctx->ws_locked = false;

@@ -3,6 +3,8 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <atomic>
 #include <string>
 
 #include "../../include/b200_backend.h"
@@ -16,6 +18,14 @@ struct b200_ctx {
     uint32_t* err_host = nullptr;       // pinned mirror used when checking the word
     uint64_t generation = 0;
     bool poisoned = false;
+    // Recovery state machine of an ordinal (crates/backend-cuda/src/context_cache.rs): Active -> poisoned ->
+    // retiring (b200_ctx_recover drains and probes) -> Active with a new generation, or unrecoverable for good.
+    std::atomic<bool> retiring{false};
+    bool unrecoverable = false;
+    std::string probe_error;            // why recovery failed (diagnostics of the unrecoverable state)
+    int probe_failures = 0;             // consecutive failed recovery probes
+    int inject_probe_failures = 0;      // host-side failure injection for tests: probes that report a mismatch
+    std::atomic<uint64_t> capture_owner{0};   // hashed id of the thread that captures a CUDA graph on this context
     void* ws = nullptr;                 // grow-only scratch for the composite entry points
     size_t ws_bytes = 0;
     bool ws_locked = false;             // set while a composite call lends out part of the scratch
@@ -41,6 +51,13 @@ int32_t fail(int32_t st, const std::string& msg);
 // Same, for a failure after work may have been enqueued: also poisons the context.
 int32_t fail_runtime(b200_ctx* ctx, int32_t st, const std::string& msg);
 int32_t check_ctx(const b200_ctx* ctx);
+// Marks the calling thread as the one capturing a CUDA graph on `ctx` (entry points called from other threads
+// answer B200_DEVICE_CONTEXT_CAPTURE_IN_PROGRESS until the guard is destroyed).
+struct CaptureGuard {
+    b200_ctx* ctx;
+    explicit CaptureGuard(b200_ctx* c);
+    ~CaptureGuard();
+};
 // Validates that `buf` belongs to `ctx`, is of its generation and holds [off, off + need).
 // A null `buf` is accepted only when `optional`.
 int32_t check_buf(const b200_ctx* ctx, const b200_buf* buf, size_t off, size_t need, const char* name,

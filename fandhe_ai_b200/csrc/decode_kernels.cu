@@ -10,6 +10,7 @@
 // maximum (crates/autodiff/src/generate/mod.rs:333-343); embedding lookup is a row gather
 // (crates/backend-cuda/src/kernels_gather_scatter.rs:71-220).
 #include "kernels.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace b200 {
@@ -159,63 +160,6 @@ gate_quant_kernel(const int* __restrict__ raw, int splits, int M, int F, const f
     quant_row_from_smem(row, F, xq + static_cast<size_t>(m) * F, sx_out + m, scratch);
 }
 
-// Finishes the QKV GEMM for one token row: dequantise, rotate q and k heads (rotate-half RoPE with a
-// precomputed cos/sin table row for the token's position), write q (f32) and append k, v to the pools.
-// Row layout of the GEMM output: [q heads | k heads | v heads], each head Dh wide.
-__global__ void __launch_bounds__(kRowThreads)
-qkv_rope_append_kernel(const int* __restrict__ raw, int splits, int M, int hq, int hkv, int dh,
-                       const float* __restrict__ sx_in, const float* __restrict__ sw, const float* __restrict__ cos_t,
-                       const float* __restrict__ sin_t, int max_pos, const uint32_t* __restrict__ positions,
-                       const uint32_t* __restrict__ block_tables, int max_blocks_per_seq, int block_size,
-                       int num_blocks, float* __restrict__ q_out, uint16_t* __restrict__ k_pool,
-                       uint16_t* __restrict__ v_pool, uint32_t* err) {
-    extern __shared__ double smem_d[];
-    float* row = reinterpret_cast<float*>(smem_d + 32);
-    const int m = blockIdx.x;
-    const int n = (hq + 2 * hkv) * dh;
-    const size_t plane = static_cast<size_t>(M) * n;
-    const float sa = sx_in[m];
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const size_t idx = static_cast<size_t>(m) * n + i;
-        row[i] = fmaf(static_cast<float>(sum_planes(raw, splits, plane, idx)), sa * sw[i], 0.0f);
-    }
-    __syncthreads();
-    const int pos = static_cast<int>(positions[m]);      // position of the token being added
-    const int half = dh / 2;
-    bool ok = pos < max_pos;
-    uint32_t blk = 0;
-    if (ok) {
-        blk = block_tables[static_cast<size_t>(m) * max_blocks_per_seq + pos / block_size];
-        ok = blk < static_cast<uint32_t>(num_blocks);
-    }
-    if (!ok) {
-        if (threadIdx.x == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrAppendSlot));
-        return;
-    }
-    const float* cr = cos_t + static_cast<size_t>(pos) * half;
-    const float* sr = sin_t + static_cast<size_t>(pos) * half;
-    const size_t slot = static_cast<size_t>(blk) * block_size + pos % block_size;
-    const int ekv = hkv * dh;
-    // q and k heads: pairs (i, i + half)
-    for (int t = threadIdx.x; t < (hq + hkv) * half; t += blockDim.x) {
-        const int head = t / half, i = t % half;
-        const float x1 = row[head * dh + i], x2 = row[head * dh + i + half];
-        const float c = cr[i], s = sr[i];
-        const float o1 = fmaf(x1, c, -__fmul_rn(x2, s));
-        const float o2 = fmaf(x2, c, __fmul_rn(x1, s));
-        if (head < hq) {
-            q_out[(static_cast<size_t>(m) * hq + head) * dh + i] = o1;
-            q_out[(static_cast<size_t>(m) * hq + head) * dh + i + half] = o2;
-        } else {
-            const int kh = head - hq;
-            k_pool[slot * ekv + kh * dh + i] = static_cast<uint16_t>(f32_to_bf16_bits(o1));
-            k_pool[slot * ekv + kh * dh + i + half] = static_cast<uint16_t>(f32_to_bf16_bits(o2));
-        }
-    }
-    for (int t = threadIdx.x; t < ekv; t += blockDim.x)
-        v_pool[slot * ekv + t] = static_cast<uint16_t>(f32_to_bf16_bits(row[(hq + hkv) * dh + t]));
-}
-
 __global__ void dequant_planes_kernel(const int* __restrict__ raw, int splits, int M, int N,
                                       const float* __restrict__ sx, const float* __restrict__ sw, float* __restrict__ y) {
     const size_t plane = static_cast<size_t>(M) * N;
@@ -312,7 +256,8 @@ __global__ void slice_cols_i8_kernel(const int8_t* __restrict__ src, int64_t row
 
 int grid_for(int64_t n, int threads) {
     int64_t g = (n + threads - 1) / threads;
-    if (g > 148 * 16) g = 148 * 16;
+    const int64_t cap = int64_t(current_sm_count()) * 16;
+    if (g > cap) g = cap;
     if (g < 1) g = 1;
     return static_cast<int>(g);
 }
@@ -352,19 +297,6 @@ cudaError_t gate_quant(const int* raw, int splits, int M, int F, const float* sx
     cudaError_t e = ensure_smem(gate_quant_kernel, row_smem(F));
     if (e != cudaSuccess) return e;
     gate_quant_kernel<<<M, kRowThreads, row_smem(F), s>>>(raw, splits, M, F, sx_in, sw, xq, sx_out);
-    return cudaGetLastError();
-}
-cudaError_t qkv_rope_append(const int* raw, int splits, int M, int hq, int hkv, int dh, const float* sx_in,
-                            const float* sw, const float* cos_t, const float* sin_t, int max_pos,
-                            const uint32_t* positions, const uint32_t* block_tables, int max_blocks_per_seq,
-                            int block_size, int num_blocks, float* q_out, uint16_t* k_pool, uint16_t* v_pool,
-                            uint32_t* err, cudaStream_t s) {
-    const size_t smem = row_smem((hq + 2 * hkv) * dh);
-    cudaError_t e = ensure_smem(qkv_rope_append_kernel, smem);
-    if (e != cudaSuccess) return e;
-    qkv_rope_append_kernel<<<M, kRowThreads, smem, s>>>(raw, splits, M, hq, hkv, dh, sx_in, sw, cos_t, sin_t, max_pos,
-                                                       positions, block_tables, max_blocks_per_seq, block_size, num_blocks,
-                                                       q_out, k_pool, v_pool, err);
     return cudaGetLastError();
 }
 cudaError_t begin_step(uint32_t* seq_lens, uint32_t* positions, const uint32_t* active, int n, cudaStream_t s) {

@@ -1,10 +1,14 @@
-// Cluster versions of the row-wise decode kernels.  A token row is cut into CL column chunks, one CTA
-// each, launched as one thread-block cluster per row; the two row-wide reductions (f64 sum of squares for
-// RMSNorm, |max| for the per-token int8 scale) are exchanged through distributed shared memory and summed
-// in cluster-rank order, so the result does not depend on scheduling.  With 128 rows this puts 512..1024
-// CTAs with 16-byte loads on the machine instead of 128 CTAs with scalar loads.
+// Row-wise kernels of the decode step.
 //
-// The per-element arithmetic is the same as in decode_kernels.cu (and as in the CPU restatement):
+// Between two GEMMs a token row is owned by one CTA of up to 1024 threads that keeps the row in registers
+// (1, 2 or 4 groups of four columns per thread) and does the two row-wide reductions (f64 sum of squares
+// for RMSNorm, |max| for the per-token int8 scale) as block reductions summed in warp order, so the result
+// does not depend on scheduling.  The two kernels that run once per step (embedding gather + first norm,
+// greedy argmax over the vocabulary) cut a row into column chunks, one CTA each, launched as one
+// thread-block cluster per row with the partial results exchanged through distributed shared memory in
+// cluster-rank order.  Rows wider than 16384 columns use the one-CTA kernels of decode_kernels.cu.
+//
+// The per-element arithmetic is the same everywhere (and in the CPU restatement):
 // y = fma(float(sum of planes), sx * sw, 0); h += y; xn = (h * rstd) * w; q = rne(xn / (amax / 127)).
 #include <cooperative_groups.h>
 
@@ -106,25 +110,6 @@ __device__ __forceinline__ void norm_quant_chunk(cg::cluster_group& cl, RowShare
     cl.sync();
 }
 
-// Quantisation only (no norm) of the chunk in sh.chunk.
-__device__ __forceinline__ void quant_chunk(cg::cluster_group& cl, RowShared& sh, int c0, int nc,
-                                            int8_t* __restrict__ q_row, float* __restrict__ scale_out) {
-    float amax = 0.0f;
-    for (int i = threadIdx.x; i < nc; i += kThreads) amax = fmaxf(amax, fabsf(sh.chunk[i]));
-    amax = cluster_max(cl, sh, block_max(amax, sh));
-    const float s = amax / 127.0f;
-    if (cl.block_rank() == 0 && threadIdx.x == 0) *scale_out = s;
-    uint32_t* q4 = reinterpret_cast<uint32_t*>(q_row + c0);
-    for (int i = threadIdx.x; i < nc / 4; i += kThreads) {
-        const uint32_t b0 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 0], s)) & 0xFFu;
-        const uint32_t b1 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 1], s)) & 0xFFu;
-        const uint32_t b2 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 2], s)) & 0xFFu;
-        const uint32_t b3 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 3], s)) & 0xFFu;
-        q4[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-    }
-    cl.sync();
-}
-
 // Sum of the split-K planes of four consecutive elements (16-byte loads).
 __device__ __forceinline__ int4 sum_planes4(const int* __restrict__ raw, int splits, size_t plane, size_t idx) {
     int4 a = make_int4(0, 0, 0, 0);
@@ -160,82 +145,6 @@ embed_norm_quant_cl_kernel(const int* __restrict__ ids, const float* __restrict_
     }
     __syncthreads();
     norm_quant_chunk(cl, sh, d, c0, nc, norm_w, eps, xq + static_cast<size_t>(m) * d, sx + m);
-}
-
-__global__ void __launch_bounds__(kThreads)
-resid_norm_quant_cl_kernel(const int* __restrict__ raw, int splits, int M, int d, int nc,
-                           const float* __restrict__ sx_in, const float* __restrict__ sw, const float* __restrict__ pre,
-                           const float* __restrict__ norm_w, float eps, float* __restrict__ h, int8_t* __restrict__ xq,
-                           float* __restrict__ sx_out) {
-    __shared__ RowShared sh;
-    cg::cluster_group cl = cg::this_cluster();
-    pdl_wait();
-    pdl_launch_dependents();
-    const int m = blockIdx.y, c0 = blockIdx.x * nc;
-    const size_t plane = static_cast<size_t>(M) * d;
-    const size_t base = static_cast<size_t>(m) * d + c0;
-    const float sa = pre ? 0.0f : sx_in[m];
-    for (int g = threadIdx.x; g < nc / 4; g += kThreads) {
-        float4 y;
-        if (pre) {
-            y = *reinterpret_cast<const float4*>(pre + base + 4 * g);
-        } else {
-            const int4 a = sum_planes4(raw, splits, plane, base + 4 * g);
-            const float4 w4 = *reinterpret_cast<const float4*>(sw + c0 + 4 * g);
-            y.x = fmaf(static_cast<float>(a.x), sa * w4.x, 0.0f);
-            y.y = fmaf(static_cast<float>(a.y), sa * w4.y, 0.0f);
-            y.z = fmaf(static_cast<float>(a.z), sa * w4.z, 0.0f);
-            y.w = fmaf(static_cast<float>(a.w), sa * w4.w, 0.0f);
-        }
-        float4 hv = *reinterpret_cast<const float4*>(h + base + 4 * g);
-        hv.x = y.x + hv.x; hv.y = y.y + hv.y; hv.z = y.z + hv.z; hv.w = y.w + hv.w;
-        *reinterpret_cast<float4*>(h + base + 4 * g) = hv;
-        *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = hv;
-    }
-    __syncthreads();
-    norm_quant_chunk(cl, sh, d, c0, nc, norm_w, eps, xq + static_cast<size_t>(m) * d, sx_out + m);
-}
-
-__global__ void __launch_bounds__(kThreads)
-gate_quant_cl_kernel(const int* __restrict__ raw, int splits, int M, int F, int nc, const float* __restrict__ sx_in,
-                     const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
-    __shared__ RowShared sh;
-    cg::cluster_group cl = cg::this_cluster();
-    pdl_wait();
-    pdl_launch_dependents();
-    const int m = blockIdx.y, c0 = blockIdx.x * nc;
-    const size_t plane = static_cast<size_t>(M) * 2 * F;
-    const size_t base = static_cast<size_t>(m) * 2 * F + c0;
-    const float sa = sx_in[m];
-    for (int g = threadIdx.x; g < nc / 4; g += kThreads) {
-        const int4 ag = sum_planes4(raw, splits, plane, base + 4 * g);
-        const int4 au = sum_planes4(raw, splits, plane, base + F + 4 * g);
-        const float4 wg = *reinterpret_cast<const float4*>(sw + c0 + 4 * g);
-        const float4 wu = *reinterpret_cast<const float4*>(sw + F + c0 + 4 * g);
-        float4 o;
-        o.x = __fmul_rn(silu(fmaf(static_cast<float>(ag.x), sa * wg.x, 0.0f)), fmaf(static_cast<float>(au.x), sa * wu.x, 0.0f));
-        o.y = __fmul_rn(silu(fmaf(static_cast<float>(ag.y), sa * wg.y, 0.0f)), fmaf(static_cast<float>(au.y), sa * wu.y, 0.0f));
-        o.z = __fmul_rn(silu(fmaf(static_cast<float>(ag.z), sa * wg.z, 0.0f)), fmaf(static_cast<float>(au.z), sa * wu.z, 0.0f));
-        o.w = __fmul_rn(silu(fmaf(static_cast<float>(ag.w), sa * wg.w, 0.0f)), fmaf(static_cast<float>(au.w), sa * wu.w, 0.0f));
-        *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = o;
-    }
-    __syncthreads();
-    quant_chunk(cl, sh, c0, nc, xq + static_cast<size_t>(m) * F, sx_out + m);
-}
-
-// Per-token int8 quantisation of an f32 matrix row (the attention output before the O projection).
-__global__ void __launch_bounds__(kThreads)
-quant_rows_cl_kernel(const float* __restrict__ x, int n, int nc, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
-    __shared__ RowShared sh;
-    cg::cluster_group cl = cg::this_cluster();
-    pdl_wait();
-    pdl_launch_dependents();
-    const int m = blockIdx.y, c0 = blockIdx.x * nc;
-    const float* src = x + static_cast<size_t>(m) * n + c0;
-    for (int g = threadIdx.x; g < nc / 4; g += kThreads)
-        *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = *reinterpret_cast<const float4*>(src + 4 * g);
-    __syncthreads();
-    quant_chunk(cl, sh, c0, nc, xq + static_cast<size_t>(m) * n, sx_out + m);
 }
 
 // First index of the row maximum; chunk = columns per CTA (a multiple of 4).
@@ -296,12 +205,14 @@ __global__ void __launch_bounds__(kThreads)
 qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int hq, int hkv, int dh, int heads_per_cta,
                            const float* __restrict__ sx_in, const float* __restrict__ sw,
                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
-                           const uint32_t* __restrict__ positions, const uint32_t* __restrict__ block_tables,
+                           const uint32_t* __restrict__ positions, const uint32_t* __restrict__ active,
+                           const uint32_t* __restrict__ block_tables,
                            int max_blocks_per_seq, int block_size, int num_blocks, float* __restrict__ q_out,
                            uint16_t* __restrict__ k_pool, uint16_t* __restrict__ v_pool, uint32_t* err) {
     pdl_wait();
     pdl_launch_dependents();
     const int m = blockIdx.y;
+    const bool keep_kv = active == nullptr || active[m] != 0u;     // a row that sits the step out keeps its cache
     const int n = (hq + 2 * hkv) * dh;
     const int half = dh / 2;
     const size_t plane = static_cast<size_t>(M) * n;
@@ -340,12 +251,12 @@ qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int h
             if (head < hq) {
                 q_out[(static_cast<size_t>(m) * hq + head) * dh + i] = o1;
                 q_out[(static_cast<size_t>(m) * hq + head) * dh + i + half] = o2;
-            } else {
+            } else if (keep_kv) {
                 const int kh = head - hq;
                 k_pool[slot * ekv + kh * dh + i] = static_cast<uint16_t>(f32_to_bf16_bits(o1));
                 k_pool[slot * ekv + kh * dh + i + half] = static_cast<uint16_t>(f32_to_bf16_bits(o2));
             }
-        } else {
+        } else if (keep_kv) {
             const int vh = head - hq - hkv;
             v_pool[slot * ekv + vh * dh + i] = static_cast<uint16_t>(f32_to_bf16_bits(x1));
             v_pool[slot * ekv + vh * dh + i + half] = static_cast<uint16_t>(f32_to_bf16_bits(x2));
@@ -691,7 +602,7 @@ void wide_shape(int n, int* vpt, int* threads, int rows = 1) {
     if (v == 3) v = 4;
     // more rows than SMs: smaller CTAs (more groups per thread) so that several rows share an SM and the batch
     // still runs as one wave
-    while (rows > 148 && v < kWideMaxVpt && groups / (2 * v) >= 256) v *= 2;
+    while (rows > current_sm_count() && v < kWideMaxVpt && groups / (2 * v) >= 256) v *= 2;
     *vpt = v;
     *threads = ((groups + v - 1) / v + 31) / 32 * 32;
 }
@@ -716,7 +627,7 @@ cudaError_t launch_cluster(void (*kernel)(KArgs...), int cl, int rows, cudaStrea
 
 }  // namespace
 
-// Dispatchers: the cluster kernel when the row width allows it, else the one-CTA-per-row kernel.
+// Dispatchers: the wide (or cluster) kernel when the row width allows it, else the one-CTA-per-row kernel.
 cudaError_t embed_norm_quant_auto(const int* ids, const float* table, int vocab, int M, int d, const float* norm_w,
                                   float eps, float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s) {
     const int cl = pick_cluster(d);
@@ -736,10 +647,7 @@ cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, cons
     if (vpt == 2) B200_WIDE_RESID(2);
     if (vpt == 4) B200_WIDE_RESID(4);
 #undef B200_WIDE_RESID
-    const int cl = pick_cluster(d);
-    if (cl == 0) return resid_norm_quant(raw, splits, M, d, sx_in, sw, pre, norm_w, eps, h, xq, sx_out, s);
-    return launch_cluster(resid_norm_quant_cl_kernel, cl, M, s, raw, splits, M, d, d / cl, sx_in, sw, pre, norm_w, eps, h,
-                          xq, sx_out);
+    return resid_norm_quant(raw, splits, M, d, sx_in, sw, pre, norm_w, eps, h, xq, sx_out, s);
 }
 
 cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
@@ -753,9 +661,7 @@ cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const floa
     if (vpt == 2) B200_WIDE_GATE(2);
     if (vpt == 4) B200_WIDE_GATE(4);
 #undef B200_WIDE_GATE
-    const int cl = pick_cluster(F);
-    if (cl == 0) return gate_quant(raw, splits, M, F, sx_in, sw, xq, sx_out, s);
-    return launch_cluster(gate_quant_cl_kernel, cl, M, s, raw, splits, M, F, F / cl, sx_in, sw, xq, sx_out);
+    return gate_quant(raw, splits, M, F, sx_in, sw, xq, sx_out, s);
 }
 
 cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s) {
@@ -764,9 +670,7 @@ cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* 
     if (vpt == 1) return launch_ex(quant_rows_wide_kernel<1>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
     if (vpt == 2) return launch_ex(quant_rows_wide_kernel<2>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
     if (vpt == 4) return launch_ex(quant_rows_wide_kernel<4>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
-    const int cl = pick_cluster(n);
-    if (cl == 0) return quantize_i8_per_row(x, M, n, xq, sx_out, s);
-    return launch_cluster(quant_rows_cl_kernel, cl, M, s, x, n, n / cl, xq, sx_out);
+    return quantize_i8_per_row(x, M, n, xq, sx_out, s);
 }
 
 cudaError_t argmax_rows_auto(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s) {
@@ -779,16 +683,16 @@ cudaError_t argmax_rows_auto(const float* logits, int M, int vocab, int* out_ids
 
 cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int hkv, int dh, const float* sx_in,
                                  const float* sw, const float* cos_t, const float* sin_t, int max_pos,
-                                 const uint32_t* positions, const uint32_t* block_tables, int max_blocks_per_seq,
-                                 int block_size, int num_blocks, float* q_out, uint16_t* k_pool, uint16_t* v_pool,
-                                 uint32_t* err, cudaStream_t s) {
+                                 const uint32_t* positions, const uint32_t* active, const uint32_t* block_tables,
+                                 int max_blocks_per_seq, int block_size, int num_blocks, float* q_out, uint16_t* k_pool,
+                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s) {
     const int heads = hq + 2 * hkv;
     int hpc = (2 * kThreads) / (dh / 2);      // two rotary pairs per thread
     if (hpc < 1) hpc = 1;
     dim3 grid((heads + hpc - 1) / hpc, M);
     return launch_ex(qkv_rope_append_par_kernel, grid, dim3(kThreads), 0, s, 1, true, raw, splits, M, hq, hkv, dh, hpc, sx_in,
-                     sw, cos_t, sin_t, max_pos, positions, block_tables, max_blocks_per_seq, block_size, num_blocks, q_out,
-                     k_pool, v_pool, err);
+                     sw, cos_t, sin_t, max_pos, positions, active, block_tables, max_blocks_per_seq, block_size, num_blocks,
+                     q_out, k_pool, v_pool, err);
 }
 
 bool tp_finish_supported(int d) {

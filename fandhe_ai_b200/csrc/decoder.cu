@@ -245,6 +245,7 @@ struct LayerParams {
 
 struct b200_decoder {
     b200_ctx* ctx = nullptr;
+    uint64_t generation = 0;                    // generation of the context at creation
     b200_decoder_config cfg{};
     int hq_l = 0, hkv_l = 0, f_l = 0;           // per-rank head counts and d_ff
     int n_qkv = 0;                              // (hq_l + 2 hkv_l) * head_dim
@@ -353,6 +354,8 @@ int32_t dec_check(b200_decoder* d) {
     if (!d) return fail(B200_INVALID_ARGUMENT, "decoder is null");
     if (d->store_poisoned) return fail(B200_STORE_POISONED, "the decoder's device state is poisoned by an earlier runtime failure; re-create it");
     if (int32_t st = check_ctx(d->ctx)) return st;
+    if (d->generation != d->ctx->generation)
+        return fail(B200_STALE_DEVICE_GENERATION, "the decoder belongs to an earlier generation of its context (the context was recovered); re-create it");
     return set_device(d->ctx);
 }
 
@@ -576,6 +579,7 @@ int32_t enqueue_step(b200_decoder* d) {
             qe.rope.sin_t = d->sin_t;
             qe.rope.max_pos = c.max_seq_len;
             qe.rope.positions = d->pos_dev;
+            qe.rope.active = d->active_dev;
             qe.rope.block_tables = d->tables_dev;
             qe.rope.max_blocks_per_seq = d->max_blocks_per_seq;
             qe.rope.block_size = c.block_size;
@@ -588,7 +592,7 @@ int32_t enqueue_step(b200_decoder* d) {
         } else {
             CU_TRY(gemm_launch(L.p_qkv, ep, err, s));
             CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv,
-                                        d->cos_t, d->sin_t, c.max_seq_len, d->pos_dev, d->tables_dev, d->max_blocks_per_seq,
+                                        d->cos_t, d->sin_t, c.max_seq_len, d->pos_dev, d->active_dev, d->tables_dev, d->max_blocks_per_seq,
                                         c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
                                         static_cast<uint16_t*>(L.v_pool), err, s));
         }
@@ -646,6 +650,7 @@ int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_
     b200_decoder* d = new (std::nothrow) b200_decoder();
     if (!d) return fail(B200_DEVICE_ALLOCATION_FAILED, "decoder_create: host allocation failed");
     d->ctx = ctx;
+    d->generation = ctx->generation;
     d->cfg = *cfg;
     const auto& c = d->cfg;
     const int tp = c.tp_size;
@@ -1075,6 +1080,7 @@ int32_t b200_decoder_step_rows(b200_decoder* d, const int32_t* ids_host, const u
         d->eager_steps_done++;
     } else {
         cudaGraph_t g = nullptr;
+        CaptureGuard capturing(d->ctx);     // other threads get DeviceContextCaptureInProgress until the capture ends
         CU_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         int32_t st = enqueue_step(d);
         cudaError_t e = cudaStreamEndCapture(s, &g);

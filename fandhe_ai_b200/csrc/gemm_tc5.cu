@@ -326,6 +326,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     }
                 }
                 const float sa = ok ? p.ep.a_scale[row] : 0.0f;
+                const bool keep_kv = ok && (rp.active == nullptr || rp.active[row] != 0u);   // a row that sits the step out
                 const float* cr = rp.cos_t + static_cast<size_t>(pos) * 64;
                 const float* sr = rp.sin_t + static_cast<size_t>(pos) * 64;
                 const size_t slot = static_cast<size_t>(blk) * rp.block_size + pos % rp.block_size;
@@ -359,7 +360,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                         float* dst = rp.q_out + (static_cast<size_t>(row) * rp.hq + head) * BN + i0;
                         *reinterpret_cast<float4*>(dst) = make_float4(o1[0], o1[1], o1[2], o1[3]);
                         *reinterpret_cast<float4*>(dst + 64) = make_float4(o2[0], o2[1], o2[2], o2[3]);
-                    } else {
+                    } else if (keep_kv) {
                         const bool is_k = head < rp.hq + rp.hkv;
                         const int kh = is_k ? head - rp.hq : head - rp.hq - rp.hkv;
                         uint16_t* dst = (is_k ? rp.k_pool : rp.v_pool) + (slot * rp.hkv + kh) * BN + i0;
@@ -511,12 +512,8 @@ template <int BN, bool kInt8>
 cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t stream) {
     const int stage_bytes = kABytes + BN * kBK;
     const int smem = plan.stages * stage_bytes + 1024 + 8 * (2 * plan.stages + 2);
-    static int configured = 0;
-    if (configured < smem) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN, kInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    static int configured[64] = {};
+    if (cudaError_t e = ensure_dynamic_smem(gemm_tc5_kernel<BN, kInt8>, smem, configured)) return e;
     const int out_cols = plan.gate ? BN / 2 : BN;
     const int n_out = plan.gate ? plan.N / 2 : plan.N;
     dim3 grid((n_out + out_cols - 1) / out_cols, (plan.M + kBM - 1) / kBM, plan.splits);
@@ -530,12 +527,8 @@ template <int BN, bool kInt8>
 cudaError_t launch_persist_t(const GemmPlan& plan, const PersistArgs& args, cudaStream_t stream) {
     const int stage_bytes = kABytes + BN * kBK;
     const int smem = plan.stages * stage_bytes + 1024 + 8 * (2 * plan.stages + 5) + 16;
-    static int configured = 0;
-    if (configured < smem) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_persist_kernel<BN, kInt8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    static int configured[64] = {};
+    if (cudaError_t e = ensure_dynamic_smem(gemm_tc5_persist_kernel<BN, kInt8>, smem, configured)) return e;
     return launch_ex(gemm_tc5_persist_kernel<BN, kInt8>, dim3(plan.grid), dim3(kPersistThreads), smem, stream, 1, true,
                      plan.tma_a, plan.tma_b, args);
 }
@@ -570,7 +563,7 @@ void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue
 }
 
 cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* b, int M, int N, int K, int gate,
-                           int want_splits, int want_bn, const char** why) {
+                           int want_splits, int want_bn, const char** why, bool encode_maps) {
     static const char* kNone = "";
     if (why) *why = kNone;
     auto fail = [&](const char* msg) {
@@ -602,8 +595,9 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     int splits = want_splits;
     if (splits <= 0) {
         splits = 1;
-        if (2 * tiles <= 148) {      // splitting pays only when it at least doubles the number of busy SMs
-            int cap = 296 / tiles;
+        const int sms = current_sm_count();
+        if (2 * tiles <= sms) {      // splitting pays only when it at least doubles the number of busy SMs
+            int cap = 2 * sms / tiles;
             if (cap > kb_total / 2) cap = kb_total / 2;
             if (cap > 8) cap = 8;
             for (int s = 2; s <= cap; s *= 2)
@@ -626,6 +620,7 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     // the parked partial tile (bn x 128 accumulators) reuses the operand ring
     plan->cluster = (!gate && exact_pow2(splits) && stages * stage_bytes >= bn * kBM * 4) ? 1 : 0;
     plan->out_planes = plan->cluster ? 1 : splits;
+    if (!encode_maps) return cudaSuccess;      // shape decisions only (plan queries)
     if (!make_operand_map(&plan->tma_a, a, M, K, kBM)) return fail("gemm: cuTensorMapEncodeTiled failed for A");
     if (!make_operand_map(&plan->tma_b, b, N, K, gate ? bn / 2 : bn)) return fail("gemm: cuTensorMapEncodeTiled failed for B");
     return cudaSuccess;
@@ -680,7 +675,7 @@ cudaError_t gemm_splitk_epilogue(int kind, int splits, int M, int N, int gate, c
     const int n_out = gate ? N / 2 : N;
     int64_t groups = static_cast<int64_t>(M) * (n_out / 4);
     int64_t grid = (groups + 255) / 256;
-    if (grid > 148 * 8) grid = 148 * 8;
+    if (grid > int64_t(current_sm_count()) * 8) grid = int64_t(current_sm_count()) * 8;
     if (grid < 1) grid = 1;
     if (kind == kGemmI8)
         splitk_epilogue_kernel<true><<<static_cast<int>(grid), 256, 0, stream>>>(
@@ -693,7 +688,7 @@ cudaError_t gemm_splitk_epilogue(int kind, int splits, int M, int N, int gate, c
 
 cudaError_t gemm_sum_planes_i32(const int* raw, int splits, int64_t elems, int* out, cudaStream_t stream) {
     int64_t grid = (elems + 255) / 256;
-    if (grid > 148 * 8) grid = 148 * 8;
+    if (grid > int64_t(current_sm_count()) * 8) grid = int64_t(current_sm_count()) * 8;
     if (grid < 1) grid = 1;
     sum_planes_i32_kernel<<<static_cast<int>(grid), 256, 0, stream>>>(raw, splits, elems, out);
     return cudaGetLastError();

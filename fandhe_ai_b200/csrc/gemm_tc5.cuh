@@ -27,6 +27,7 @@ struct GemmRope {
     const float* sin_t = nullptr;
     int max_pos = 0;
     const uint32_t* positions = nullptr;    // [M] position of the token of each row
+    const uint32_t* active = nullptr;       // [M] or null: rows with active[m] == 0 leave the pools untouched
     const uint32_t* block_tables = nullptr; // [M, max_blocks_per_seq]
     int max_blocks_per_seq = 0, block_size = 0, num_blocks = 0;
     float* q_out = nullptr;
@@ -74,8 +75,9 @@ void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue
 // lets the heuristic choose (it only splits when the tile grid alone would leave
 // most of the 148 SMs idle); the fused epilogue requires splits == 1.
 // Returns cudaSuccess or an error; `why` receives a static message on failure.
+// encode_maps = false fills in the shape decisions only (no tensor maps; the plan cannot be launched).
 cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* b, int M, int N, int K,
-                           int gate, int want_splits, int want_bn, const char** why);
+                           int gate, int want_splits, int want_bn, const char** why, bool encode_maps = true);
 
 // True when a launch of this plan may carry a GemmRope epilogue for hq + 2 hkv heads of 128.
 bool gemm_plan_can_rope(const GemmPlan& plan, int hq, int hkv);

@@ -61,13 +61,8 @@ cudaError_t resid_norm_quant(const int* raw, int splits, int M, int d, const flo
                              cudaStream_t s);
 cudaError_t gate_quant(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
                        float* sx_out, cudaStream_t s);
-cudaError_t qkv_rope_append(const int* raw, int splits, int M, int hq, int hkv, int dh, const float* sx_in,
-                            const float* sw, const float* cos_t, const float* sin_t, int max_pos,
-                            const uint32_t* positions, const uint32_t* block_tables, int max_blocks_per_seq,
-                            int block_size, int num_blocks, float* q_out, uint16_t* k_pool, uint16_t* v_pool,
-                            uint32_t* err, cudaStream_t s);
-// ---- decode_rows.cu: the same operations as thread-block-cluster kernels (row cut into column chunks,
-// reductions through distributed shared memory); they fall back to the kernels above for odd widths.
+// ---- decode_rows.cu: the same operations with one wide CTA per row (or one cluster per row for the once-per-step
+// kernels); they fall back to the kernels above for rows wider than 16384 columns.
 cudaError_t embed_norm_quant_auto(const int* ids, const float* table, int vocab, int M, int d, const float* norm_w,
                                   float eps, float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s);
 cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, const float* sx_in, const float* sw,
@@ -77,11 +72,12 @@ cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const floa
                             float* sx_out, cudaStream_t s);
 cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s);
 cudaError_t argmax_rows_auto(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s);
+// `active` (null: all rows) marks the rows whose K / V are appended; the others only get their q row.
 cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int hkv, int dh, const float* sx_in,
                                  const float* sw, const float* cos_t, const float* sin_t, int max_pos,
-                                 const uint32_t* positions, const uint32_t* block_tables, int max_blocks_per_seq,
-                                 int block_size, int num_blocks, float* q_out, uint16_t* k_pool, uint16_t* v_pool,
-                                 uint32_t* err, cudaStream_t s);
+                                 const uint32_t* positions, const uint32_t* active, const uint32_t* block_tables,
+                                 int max_blocks_per_seq, int block_size, int num_blocks, float* q_out, uint16_t* k_pool,
+                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s);
 
 // y[m, n] = sum_planes(raw)[m, n] * (sx[m] * sw[n]) as f32 (the addend of a cross-rank sum)
 cudaError_t dequant_planes(const int* raw, int splits, int M, int N, const float* sx, const float* sw, float* y,

@@ -10,6 +10,24 @@ namespace b200 {
 // B200_PDL=0/1 at first use; default on).  Defined in backend.cu.
 bool pdl_enabled();
 
+// Number of SMs of the current device (asked once per device ordinal).  Defined in backend.cu.
+int current_sm_count();
+
+// Raises a kernel's dynamic shared-memory limit to `bytes` on the current device.  Function attributes belong to
+// the device, so the largest value already set is remembered per device ordinal in `cache` (64 entries, zero
+// initialised, one array per kernel instantiation).
+template <typename K>
+cudaError_t ensure_dynamic_smem(K kernel, int bytes, int* cache) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (cache[dev] >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) cache[dev] = bytes;
+    return e;
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_impl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, dim3 cluster,
                         bool pdl, Args... args) {

@@ -167,7 +167,16 @@ paged_attention_decode_kernel(const __grid_constant__ CUtensorMap tma_k, const _
                 row = rem / nslots;
                 kv_slot = rem % nslots;
                 const int b = row / sh.l_new, i = row % sh.l_new;
-                const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
+                // a length above the table width or the planned number of chunks is clamped and flagged: neither
+                // the table row nor the partials of another row are ever touched
+                int64_t len = seq_lens[b];
+                int64_t cap = int64_t(sh.max_blocks_per_seq) * sh.block_size;
+                if (cap > int64_t(max_chunks) * chunk_tokens) cap = int64_t(max_chunks) * chunk_tokens;
+                if (len > cap) {
+                    if (lane == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrAttnSeqLen));
+                    len = cap;
+                }
+                const int limit = int(len) - sh.l_new + i + 1;
                 ntok = limit - chunk * chunk_tokens;
                 if (ntok > 0) { have = true; break; }
             }

@@ -96,6 +96,15 @@ constexpr int kGenMaxDimsPerLane = 8;   // head_dim <= 256
 // (query row, q head); each warp walks tokens warp, warp + 4, ... with an online softmax, lanes
 // stride the head dimension; the four warps are merged at the end.  Writes NaN when it meets an
 // out-of-range block id (the reference kernel's reaction, kernels_paged_kv.rs:86-228).
+//
+// Every floating-point step is written as an explicitly rounded operation in a fixed order (no
+// compiler contraction, butterfly reductions whose result is the same in every lane, exp_det), so a
+// CPU restatement of this order reproduces the output bit for bit:
+//   s_j = butterfly_sum over lanes of fma-chain over t of (q[d] * scale) * k_j[d],  d = lane + 32 t
+//   m' = max(m, s_j); c = exp(m - m'); p = exp(s_j - m'); l = fma(l, c, p); o[d] = fma(p, v_j[d], o[d] * c)
+//   merge of warps w = 0..3 in order: g_w = exp(m_w - max_w m_w); L = fma(l_w, g_w, L); O[d] = fma(o_w[d], g_w, O[d])
+//   out[d] = O[d] / L
+// A sequence length above max_blocks_per_seq * block_size is clamped and flagged (kErrAttnSeqLen).
 template <typename KvT>
 __global__ void __launch_bounds__(kGenThreads)
 paged_attention_generic_kernel(const float* __restrict__ q, const KvT* __restrict__ k_pool, const KvT* __restrict__ v_pool,
@@ -110,13 +119,19 @@ paged_attention_generic_kernel(const float* __restrict__ q, const KvT* __restric
     const int dh = sh.head_dim;
     const int kvh = h / (sh.num_q_heads / sh.num_kv_heads);
     const int64_t ekv = int64_t(sh.num_kv_heads) * dh;
-    const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
+    int64_t len = seq_lens[b];
+    const int64_t cap = int64_t(sh.max_blocks_per_seq) * sh.block_size;
+    if (len > cap) {
+        if (threadIdx.x == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrAttnSeqLen));
+        len = cap;
+    }
+    const int limit = int(len) - sh.l_new + i + 1;
     const float* q_row = q + (int64_t(row) * sh.num_q_heads + h) * dh;
     float qs[kGenMaxDimsPerLane];
 #pragma unroll
     for (int t = 0; t < kGenMaxDimsPerLane; ++t) {
         const int d = lane + 32 * t;
-        qs[t] = d < dh ? q_row[d] * sh.scale : 0.0f;
+        qs[t] = d < dh ? __fmul_rn(q_row[d], sh.scale) : 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
     float acc[kGenMaxDimsPerLane];
@@ -131,18 +146,18 @@ paged_attention_generic_kernel(const float* __restrict__ q, const KvT* __restric
 #pragma unroll
         for (int t = 0; t < kGenMaxDimsPerLane; ++t) {
             const int d = lane + 32 * t;
-            if (d < dh) s = fmaf(qs[t], kv_to_f32<KvT>(k_pool[off + d]), s);
+            if (d < dh) s = __fmaf_rn(qs[t], kv_to_f32<KvT>(k_pool[off + d]), s);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        for (int o = 16; o > 0; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
         const float m_new = fmaxf(m, s);
-        const float corr = expf(m - m_new);      // exp(-inf) = 0 on the first token
-        const float p = expf(s - m_new);
-        l = l * corr + p;
+        const float corr = exp_det(__fsub_rn(m, m_new));      // exp(-inf) = 0 on the first token
+        const float p = exp_det(__fsub_rn(s, m_new));
+        l = __fmaf_rn(l, corr, p);
 #pragma unroll
         for (int t = 0; t < kGenMaxDimsPerLane; ++t) {
             const int d = lane + 32 * t;
-            if (d < dh) acc[t] = fmaf(p, kv_to_f32<KvT>(v_pool[off + d]), acc[t] * corr);
+            if (d < dh) acc[t] = __fmaf_rn(p, kv_to_f32<KvT>(v_pool[off + d]), __fmul_rn(acc[t], corr));
         }
         m = m_new;
     }
@@ -163,14 +178,14 @@ paged_attention_generic_kernel(const float* __restrict__ q, const KvT* __restric
     float w[4], ll = 0.0f;
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-        w[t] = red_m[t] == -INFINITY ? 0.0f : expf(red_m[t] - mm);
-        ll += red_l[t] * w[t];
+        w[t] = red_m[t] == -INFINITY ? 0.0f : exp_det(__fsub_rn(red_m[t], mm));
+        ll = __fmaf_rn(red_l[t], w[t], ll);
     }
     for (int d = threadIdx.x; d < dh; d += kGenThreads) {
         float o = 0.0f;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) o += red_o[t][d] * w[t];
-        o_row[d] = limit > 0 ? o / ll : 0.0f;
+        for (int t = 0; t < 4; ++t) o = __fmaf_rn(red_o[t][d], w[t], o);
+        o_row[d] = limit > 0 ? __fdiv_rn(o, ll) : 0.0f;
     }
 }
 
@@ -193,7 +208,7 @@ constexpr int kCtasPerSm = 3;           // resident CTAs of the persistent atten
 __global__ void __launch_bounds__(128)
 paged_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_tokens, int max_chunks,
-                               float* __restrict__ out, unsigned int* __restrict__ work_counter) {
+                               float* __restrict__ out, unsigned int* __restrict__ work_counter, uint32_t* err) {
     pdl_wait();
     pdl_launch_dependents();
     // every attention CTA has finished: leave the work counter at zero for the next attention launch
@@ -205,7 +220,11 @@ paged_attention_combine_kernel(const float* __restrict__ part_o, const float* __
     const int row = int(pair / sh.num_q_heads);
     const int b = row / sh.l_new, i = row % sh.l_new;
     const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
-    const int nchunks = limit > 0 ? (limit + chunk_tokens - 1) / chunk_tokens : 0;
+    int nchunks = limit > 0 ? (limit + chunk_tokens - 1) / chunk_tokens : 0;
+    if (nchunks > max_chunks) {       // a length above the planned maximum: never read past the row's partials
+        if (lane == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrAttnSeqLen));
+        nchunks = max_chunks;
+    }
     const float* ml = part_ml + pair * max_chunks * 2;
     float m = -INFINITY;
     for (int c = 0; c < nchunks; ++c) m = fmaxf(m, ml[2 * c]);
@@ -228,7 +247,7 @@ __global__ void __launch_bounds__(1024)
 paged_attention_combine_quant_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_tokens,
                                      int max_chunks, float* __restrict__ out, int8_t* __restrict__ xq,
-                                     float* __restrict__ sx, unsigned int* __restrict__ work_counter) {
+                                     float* __restrict__ sx, unsigned int* __restrict__ work_counter, uint32_t* err) {
     __shared__ float warp_max[32];
     pdl_wait();
     pdl_launch_dependents();
@@ -238,7 +257,11 @@ paged_attention_combine_quant_kernel(const float* __restrict__ part_o, const flo
     const int64_t pair = int64_t(row) * sh.num_q_heads + warp;
     const int b = row / sh.l_new, i = row % sh.l_new;
     const int limit = int(seq_lens[b]) - sh.l_new + i + 1;
-    const int nchunks = limit > 0 ? (limit + chunk_tokens - 1) / chunk_tokens : 0;
+    int nchunks = limit > 0 ? (limit + chunk_tokens - 1) / chunk_tokens : 0;
+    if (nchunks > max_chunks) {       // a length above the planned maximum: never read past the row's partials
+        if (lane == 0) atomicCAS(err, 0u, static_cast<uint32_t>(kErrAttnSeqLen));
+        nchunks = max_chunks;
+    }
     const float* ml = part_ml + pair * max_chunks * 2;
     float m = -INFINITY;
     for (int c = 0; c < nchunks; ++c) m = fmaxf(m, ml[2 * c]);
@@ -304,16 +327,12 @@ cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_
                         float* part_o, float* part_ml, unsigned int* work_counter, int sm_count, uint32_t* err,
                         cudaStream_t stream) {
     const int smem = attn_smem_bytes();    // the kernel lays out four head rows whatever G is
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static int configured[64] = {};
+    if (cudaError_t e = ensure_dynamic_smem(paged_attention_decode_kernel<G>, smem, configured)) return e;
     const PagedAttnShape& sh = plan.shape;
     const int group = sh.num_q_heads / sh.num_kv_heads;
     const int64_t items = int64_t(sh.num_kv_heads) * (group / G) * plan.max_chunks * sh.batch * sh.l_new;
-    const int64_t resident = int64_t(sm_count > 0 ? sm_count : 148) * kCtasPerSm;
+    const int64_t resident = int64_t(sm_count > 0 ? sm_count : current_sm_count()) * kCtasPerSm;
     dim3 grid(static_cast<unsigned>(items < resident ? items : resident));
     return launch_ex(paged_attention_decode_kernel<G>, grid, dim3(kFastThreads), smem, stream, 1, true, plan.tma_k,
                      plan.tma_v, q, tables, seq_lens, sh, plan.chunk_blocks, plan.max_chunks, part_o, part_ml,
@@ -322,7 +341,8 @@ cudaError_t launch_fast(const PagedAttnPlan& plan, const float* q, const uint32_
 
 int grid_for(int64_t n, int threads) {
     int64_t g = (n + threads - 1) / threads;
-    if (g > 148 * 16) g = 148 * 16;
+    const int64_t cap = int64_t(current_sm_count()) * 16;
+    if (g > cap) g = cap;
     if (g < 1) g = 1;
     return static_cast<int>(g);
 }
@@ -451,10 +471,10 @@ cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, co
     if (xq_out)
         return launch_ex(paged_attention_combine_quant_kernel, dim3(static_cast<unsigned>(rows)), dim3(32 * sh.num_q_heads),
                          0, stream, 1, true, part_o, part_ml, seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks,
-                         out, xq_out, sx_out, work_counter);
+                         out, xq_out, sx_out, work_counter, err);
     const int blocks = static_cast<int>((pairs + 3) / 4);
     return launch_ex(paged_attention_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, true, part_o, part_ml,
-                     seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks, out, work_counter);
+                     seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks, out, work_counter, err);
 }
 
 }  // namespace b200

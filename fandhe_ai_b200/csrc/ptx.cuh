@@ -24,6 +24,7 @@ enum DeviceErr : uint32_t {
     kErrAttnLoadWait = 0x201,   // attention consumer waited too long for a KV tile
     kErrAttnBlockId = 0x202,    // attention met a block id >= num_blocks in a used slot
     kErrAppendSlot = 0x203,     // append met a slot >= pool rows
+    kErrAttnSeqLen = 0x204,     // attention met a sequence length beyond the table width or the planned maximum
     kErrPeerWait = 0x301,       // cross-GPU flag wait ran out
     kErrTokenId = 0x401,        // embedding gather met an id outside the vocabulary
 };
@@ -198,13 +199,37 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 // ---------------------------------------------------------------- numerics shared by kernels
+// e^x from correctly rounded operations only (multiply, fused multiply-add, add, round-to-integer, exponent
+// bit arithmetic), so that a CPU restatement written with the same operations returns the same bits; the libm
+// and CUDA expf differ from each other in the last place.  Argument reduction x = n ln2 + r with ln2 split in
+// two constants, a degree-5 polynomial in r on top of 1 + r (the classic single-precision minimax set), and
+// the scaling by 2^n as two exact-or-once-rounded multiplications (covers denormal results).  About 1 ulp.
+__device__ __forceinline__ float exp_det(float x) {
+    if (!(x > -104.0f)) return x != x ? x : 0.0f;
+    if (x > 88.8f) return __int_as_float(0x7F800000);
+    const float n = rintf(__fmul_rn(x, 1.44269504088896341f));
+    float r = __fmaf_rn(n, -0.693359375f, x);
+    r = __fmaf_rn(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = __fmaf_rn(p, r, 1.3981999507e-3f);
+    p = __fmaf_rn(p, r, 8.3334519073e-3f);
+    p = __fmaf_rn(p, r, 4.1665795894e-2f);
+    p = __fmaf_rn(p, r, 1.6666665459e-1f);
+    p = __fmaf_rn(p, r, 5.0000001201e-1f);
+    float y = __fadd_rn(__fmaf_rn(p, __fmul_rn(r, r), r), 1.0f);
+    const int ni = static_cast<int>(n);
+    const int a = (ni - (ni & 1)) / 2, b = ni - a;
+    y = __fmul_rn(y, __int_as_float((a + 127) << 23));
+    return __fmul_rn(y, __int_as_float((b + 127) << 23));
+}
+
 // Two-branch sigmoid: never exponentiates a positive argument.
 __device__ __forceinline__ float sigmoid_stable(float x) {
-    if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
-    float e = expf(x);
-    return e / (1.0f + e);
+    if (x >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_det(-x)));
+    const float e = exp_det(x);
+    return __fdiv_rn(e, __fadd_rn(1.0f, e));
 }
-__device__ __forceinline__ float silu(float x) { return x * sigmoid_stable(x); }
+__device__ __forceinline__ float silu(float x) { return __fmul_rn(x, sigmoid_stable(x)); }
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
 

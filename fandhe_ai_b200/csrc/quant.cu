@@ -7,6 +7,7 @@
 // A row (or tensor) whose amax is 0 gets scale 0 and all-zero codes.  The division
 // is the IEEE f32 division, so the CPU restatement produces the same bytes.
 #include "kernels.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 #include <cuda_fp8.h>
 
@@ -104,7 +105,8 @@ __global__ void fp8_encode_kernel(const float* __restrict__ x, int64_t n, const 
 
 int grid_for(int64_t n, int threads) {
     int64_t g = (n + threads - 1) / threads;
-    if (g > 148 * 16) g = 148 * 16;
+    const int64_t cap = int64_t(current_sm_count()) * 16;
+    if (g > cap) g = cap;
     if (g < 1) g = 1;
     return static_cast<int>(g);
 }

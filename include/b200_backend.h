@@ -48,7 +48,10 @@ typedef enum b200_status {
     B200_STORE_POISONED = 8,
     B200_INVALID_ARGUMENT = 9,
     B200_DEVICE_CONTEXT_POISONED = 10,
-    B200_STALE_DEVICE_GENERATION = 11
+    B200_STALE_DEVICE_GENERATION = 11,
+    B200_DEVICE_CONTEXT_RETIRING = 12,             /* transient: the context is being recovered by another call */
+    B200_DEVICE_CONTEXT_UNRECOVERABLE = 13,        /* recovery failed for good: restart the process */
+    B200_DEVICE_CONTEXT_CAPTURE_IN_PROGRESS = 14   /* transient: another thread is capturing a CUDA graph on the context */
 } b200_status;
 
 /* Activation selector of the fused epilogue.  NONE and RELU are the reference's
@@ -85,6 +88,25 @@ int32_t b200_ctx_destroy(b200_ctx* ctx);
  * the stream without a transfer; reports (and poisons on) a device-side error word. */
 int32_t b200_synchronize(b200_ctx* ctx);
 int32_t b200_ctx_is_poisoned(const b200_ctx* ctx);
+/* Recovery of a poisoned context without re-creating it: `invalidate` of the reference's per-ordinal state machine
+ * (crates/backend-cuda/src/context_cache.rs:1998-2560; error variants crates/tensor-core/src/device.rs:334-371).
+ * Drains the stream, clears the device error word and runs the recovery probe (256-byte allocation, upload,
+ * identity kernel, download, compare).  On success the context starts a new generation: every buffer, decoder and
+ * scheduler made before is refused with B200_STALE_DEVICE_GENERATION / B200_STORE_POISONED and must be re-made.
+ * While this runs, calls from other threads answer B200_DEVICE_CONTEXT_RETIRING.  A failed probe leaves the
+ * context poisoned (retry allowed); the third consecutive failure, or a stream that cannot be drained, makes it
+ * B200_DEVICE_CONTEXT_UNRECOVERABLE for the life of the process.  A healthy context is left untouched. */
+int32_t b200_ctx_recover(b200_ctx* ctx);
+/* Failure injection on the host, for tests of the state machine above (no device fault is ever provoked):
+ * the next `count` recovery probes report a mismatch without touching the device; a context is marked poisoned. */
+int32_t b200_test_inject_probe_failures(b200_ctx* ctx, int32_t count);
+int32_t b200_test_poison(b200_ctx* ctx);
+/* on != 0: the calling thread is treated as capturing a CUDA graph on the context (what the decode driver does
+ * around its own capture), so calls from other threads answer B200_DEVICE_CONTEXT_CAPTURE_IN_PROGRESS; 0 ends it. */
+int32_t b200_test_mark_capturing(b200_ctx* ctx, int32_t on);
+/* Free and total device memory of the context's GPU in bytes (cudaMemGetInfo).  No counterpart in the reference;
+ * lets a caller check that a call allocated nothing. */
+int32_t b200_memory_info(b200_ctx* ctx, size_t* free_bytes, size_t* total_bytes);
 uint64_t b200_ctx_generation(const b200_ctx* ctx);
 /* The CUDA stream of the context as an opaque pointer (for event timing by callers). */
 void* b200_ctx_stream(b200_ctx* ctx);
@@ -140,19 +162,34 @@ int32_t b200_gemm_q8_scaled(b200_ctx* ctx, int32_t op_dtype, const b200_buf* a_q
                             const b200_buf* residual, size_t residual_off, int64_t m, int64_t n, int64_t k,
                             int32_t out_dtype, b200_buf* out, size_t out_off);
 
+/* Which kernel form b200_gemm_i8_s32 (fused = 0) or b200_gemm_q8_scaled (fused = 1; gated = 1 for
+ * B200_ACT_SILU_GATE) would use for a shape under the context's current tuning; nothing is launched.
+ * out6 = {tile width, K splits, splits reduced inside a cluster (0/1), persistent kernel (0/1), resident CTAs of the
+ * persistent kernel, operand stages}.  The counterpart of asking the reference's kernel selection what it would run
+ * (crates/backend-cuda/src/gemm_auto.rs:1829-1892); lets a test state which kernel it reached. */
+int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t gated, int32_t fused, int32_t* out6);
+
 /* ------------------------------------------------------------------ quantized linear
  * BackendOps::linear_forward_device_into_tracked (crates/tensor-core/src/backend_ops.rs:4296-4366)
  * for INT8 per-output-channel weights: a [m, k] f32 device-resident, weight given as
  * views (buffer + byte offset) into flat parameter buffers (int8 payload [n, k], f32
- * scales [n], optional f32 bias [n]).  The activation is quantised on the device,
- * per token to int8 (act_dtype B200_I8) or per tensor to E4M3 (B200_FP8_E4M3, with the
- * int8 weights re-encoded as E4M3 is NOT done: that combination is B200_UNSUPPORTED),
- * multiplied on the tensor cores and written, all m*n (or m*n/2) elements, into `out`
- * f32 without reading it. */
+ * scales [n], optional f32 bias [n]).  The activation is quantised on the device per
+ * token to int8, multiplied on the tensor cores (s32 accumulators) and written, all
+ * m*n (or m*n/2 for the gate form) elements, into `out` f32 without reading it. */
 int32_t b200_linear_w8a8(b200_ctx* ctx, const b200_buf* a_f32, size_t a_off, int64_t m, int64_t k,
                          const b200_buf* w_i8, size_t w_off, const b200_buf* w_scale, size_t w_scale_off,
                          const b200_buf* bias, size_t bias_off, int64_t n, int32_t activation,
                          const b200_buf* residual, size_t residual_off, b200_buf* out, size_t out_off);
+
+/* The same operator with FP8-E4M3 operands (the successor of the reference's f16 / bf16 low-precision linear,
+ * crates/tensor-core/src/low_precision.rs:193-249): the weight view holds E4M3 codes [n, k] with ONE f32 scale
+ * (per tensor, amax -> 448); the f32 activation [m, k] is quantised on the device per tensor the same way;
+ * f32 accumulation; epilogue y = act(acc * sa * sw + bias) (+ residual); out_dtype B200_F32 or B200_BF16.
+ * tcgen05 has no MMA that mixes int8 and E4M3 operands, so int8 weights cannot be used here: re-encode them. */
+int32_t b200_linear_fp8(b200_ctx* ctx, const b200_buf* a_f32, size_t a_off, int64_t m, int64_t k,
+                        const b200_buf* w_fp8, size_t w_off, const b200_buf* w_scale, size_t w_scale_off,
+                        const b200_buf* bias, size_t bias_off, int64_t n, int32_t activation,
+                        const b200_buf* residual, size_t residual_off, int32_t out_dtype, b200_buf* out, size_t out_off);
 
 /* ------------------------------------------------------------------ paged KV cache
  * PagedKvLayout / PagedAttentionArgs / PagedAttentionPlan of the reference
@@ -218,7 +255,9 @@ int32_t b200_paged_attention_forward(b200_ctx* ctx, const b200_buf* q, size_t q_
  * sizes the split grid.  The host cannot check the table contents here: a used slot holding an id
  * >= num_blocks makes the kernel set the device error word (reported by the next download /
  * synchronize) instead of touching memory.  No counterpart in the reference, which re-uploads the
- * tables on each call (crates/backend-cuda/src/paged_kv.rs:222-310). */
+ * tables on each call (crates/backend-cuda/src/paged_kv.rs:222-310).  The lengths are guarded on the device in the
+ * same way: a seq_lens entry above max_seq_len (or above max_blocks_per_seq * block_size) is clamped to it
+ * and sets the error word (code 0x204), so neither the table row nor another row's partial results are read. */
 int32_t b200_paged_attention_forward_resident(b200_ctx* ctx, const b200_buf* q, size_t q_off, const b200_buf* k_pool,
                                               const b200_buf* v_pool, const b200_buf* block_tables,
                                               const b200_buf* seq_lens, uint64_t max_seq_len,
@@ -232,7 +271,9 @@ int32_t b200_paged_attention_forward_resident(b200_ctx* ctx, const b200_buf* q, 
  * that loads the library until the process exits).  Requests whose partials need more - query rows x
  * heads x splits x 520 bytes - are refused with B200_UNSUPPORTED before anything is launched.  The first
  * call on a device resolves the array's device address; issue it before starting any stream capture on
- * that device.  All contexts of the process share the array on a given GPU, and it keeps whatever the
+ * that device.  Where the CUDA runtime loads modules lazily and this is the process's first call into the
+ * library on that device, the module load - which is when the driver sets the 32 MiB aside - also happens
+ * inside this first call; call it (or anything else of the library) once during start-up if that matters.  All contexts of the process share the array on a given GPU, and it keeps whatever the
  * last call left; a call rewrites every partial it reads, so nothing has to be cleared, but calls whose
  * kernels overlap on the GPU race on it. */
 int32_t b200_paged_attention_forward_noalloc(b200_ctx* ctx, const b200_buf* q, size_t q_off, const b200_buf* k_pool,

@@ -37,16 +37,74 @@ def make_weights(cfg: dict, seed: int = 0, std: float = 0.02) -> dict:
     return w
 
 
+def wide_shape(n: int, rows: int = 1, sm_count: int = 148):
+    """Launch shape the decode driver picks for a row of n columns owned by one CTA: (groups of four columns per
+    thread, threads), or None when the row is too wide (restates wide_shape() of csrc/decode_rows.cu)."""
+    if n <= 0 or n % 4:
+        return None
+    groups = n // 4
+    v = -(-groups // 1024)
+    if v > 4:
+        return None
+    if v == 3:
+        v = 4
+    while rows > sm_count and v < 4 and groups // (2 * v) >= 256:
+        v *= 2
+    return v, (-(-groups // v) + 31) // 32 * 32
+
+
+def pick_cluster(n: int):
+    """Column chunks (one 256-thread CTA each) of the cluster kernels for a row of n columns, or None
+    (restates pick_cluster() of csrc/decode_rows.cu)."""
+    cl = 8
+    while cl >= 1:
+        if n % (cl * 4) == 0 and n // cl <= 2048 and not (cl > 1 and n // cl < 512):
+            return cl
+        cl //= 2
+    return None
+
+
 class DecoderRef:
-    def __init__(self, cfg: dict, weights: dict, tp: int = 1):
+    """exact=False: the sequential definition (reference order of every reduction, libm exp).
+    exact=True: every floating-point reduction in the order of the CUDA kernels and their exponential, so that
+    logits and greedy ids can be compared bit for bit with the device (shapes that run on the general attention
+    kernel only: head_dim other than 128, or blocks other than 16 tokens); the integer GEMMs go through BLAS."""
+
+    def __init__(self, cfg: dict, weights: dict, tp: int = 1, exact: bool = False, sm_count: int = 148):
         self.cfg = cfg
         self.tp = tp
         self.w = weights
+        self.exact = exact
+        self.sm_count = sm_count
         self.q = {"lm_head": O.quantize_i8_per_row(weights["lm_head"]), "layers": []}
         for lw in weights["layers"]:
             self.q["layers"].append({k: O.quantize_i8_per_row(lw[k]) for k in ("wqkv", "wo", "wgu", "wdown")})
+        self.blas = None
+        if exact:
+            if tp != 1:
+                raise ValueError("exact order is defined for one rank")
+            if cfg["head_dim"] == 128 and cfg.get("block_size", 16) == 16:
+                raise ValueError("this shape runs on the tensor-core attention kernel, whose summation order is not restated")
+            if pick_cluster(cfg["d_model"]) is None or wide_shape(cfg["d_model"]) is None or wide_shape(cfg["d_ff"]) is None:
+                raise ValueError("row width outside the restated kernels")
+            self.blas = {"lm_head": O.int8_weight_for_blas(self.q["lm_head"][0]),
+                         "layers": [{k: O.int8_weight_for_blas(v[0]) for k, v in lq.items()} for lq in self.q["layers"]]}
         self.cos, self.sin = O.rope_table(cfg["max_seq_len"], cfg["head_dim"], cfg.get("rope_theta", 10000.0))
         self.k = None
+
+    def _acc(self, xq, lq_entry, blas_entry):
+        return O.gemm_i8_s32_blas(xq, blas_entry) if blas_entry is not None else O.gemm_i8_s32(xq, lq_entry[0])
+
+    def _norm(self, h, w, eps, first: bool):
+        """RMSNorm of the rows of h: `first` is the embedding kernel (a cluster of 256-thread CTAs per row), the
+        others are the one-wide-CTA-per-row kernels."""
+        if not self.exact:
+            return O.rmsnorm(h, w, eps)
+        d = h.shape[1]
+        if first:
+            return O.rmsnorm_kernel_order(h, w, eps, 1, 256, pick_cluster(d))
+        vpt, threads = wide_shape(d, h.shape[0], self.sm_count)
+        return O.rmsnorm_kernel_order(h, w, eps, 0, threads, vpt)
 
     def begin(self, batch: int):
         c = self.cfg
@@ -82,9 +140,12 @@ class DecoderRef:
         ids = np.asarray(ids)
         h = self.w["embed"][ids].astype(np.float32)
         pos = self.seq.copy()
+        attention = O.paged_attention_kernel_order if self.exact else O.paged_attention
         for l, (lw, lq) in enumerate(zip(self.w["layers"], self.q["layers"])):
-            xn = O.rmsnorm(h, lw["attn_norm"], eps)
-            qkv = O.linear_w8a8(xn, *lq["wqkv"])
+            lb = self.blas["layers"][l] if self.blas else {}
+            xn = self._norm(h, lw["attn_norm"], eps, first=(l == 0))
+            xq, sx = O.quantize_i8_per_row(xn)
+            qkv = O.epilogue_scaled(self._acc(xq, lq["wqkv"], lb.get("wqkv")), sx, True, lq["wqkv"][1], True)
             q = np.empty((b, hq * dh), np.float32)
             k_new = np.empty((b, hkv * dh), np.float32)
             for r in range(b):
@@ -93,20 +154,32 @@ class DecoderRef:
             v_new = np.ascontiguousarray(qkv[:, (hq + hkv) * dh:])
             slots = [int(self.tables[r, pos[r] // self.bs]) * self.bs + int(pos[r] % self.bs) for r in range(b)]
             O.paged_kv_append(k_new, v_new, self.k[l], self.v[l], slots, hkv * dh, True)
-            a = O.paged_attention(q.reshape(b, 1, -1), self.k[l], self.v[l], self.tables, pos + 1, batch=b, l_new=1,
-                                  num_q_heads=hq, num_kv_heads=hkv, head_dim=dh, block_size=self.bs,
-                                  num_blocks=self.nblk, max_blocks_per_seq=self.mbps,
-                                  scale=float(np.float32(1.0) / np.sqrt(np.float32(dh))), kv_bf16=True).reshape(b, -1)
-            h = self._row_parallel(a, *lq["wo"], h)
-            xn = O.rmsnorm(h, lw["mlp_norm"], eps)
+            a = attention(q.reshape(b, 1, -1), self.k[l], self.v[l], self.tables, pos + 1, batch=b, l_new=1,
+                          num_q_heads=hq, num_kv_heads=hkv, head_dim=dh, block_size=self.bs,
+                          num_blocks=self.nblk, max_blocks_per_seq=self.mbps,
+                          scale=float(np.float32(1.0) / np.sqrt(np.float32(dh))), kv_bf16=True).reshape(b, -1)
+            if self.exact:
+                aq, sa = O.quantize_i8_per_row(a)
+                h = (O.epilogue_scaled(self._acc(aq, lq["wo"], lb["wo"]), sa, True, lq["wo"][1], True) + h).astype(np.float32)
+            else:
+                h = self._row_parallel(a, *lq["wo"], h)
+            xn = self._norm(h, lw["mlp_norm"], eps, first=False)
             xq, sx = O.quantize_i8_per_row(xn)
-            acc = O.gemm_i8_s32(xq, lq["wgu"][0])
-            act = O.epilogue_scaled(acc, sx, True, lq["wgu"][1], True, act=O.ACT_SILU_GATE)
-            h = self._row_parallel(act, *lq["wdown"], h)
+            acc = self._acc(xq, lq["wgu"], lb.get("wgu"))
+            if self.exact:
+                act = O.epilogue_det(acc, sx, lq["wgu"][1], act=O.ACT_SILU_GATE)
+                fq, sf = O.quantize_i8_per_row(act)
+                h = (O.epilogue_scaled(self._acc(fq, lq["wdown"], lb["wdown"]), sf, True, lq["wdown"][1], True) + h).astype(np.float32)
+            else:
+                act = O.epilogue_scaled(acc, sx, True, lq["wgu"][1], True, act=O.ACT_SILU_GATE)
+                h = self._row_parallel(act, *lq["wdown"], h)
         self.seq += 1
-        xn = O.rmsnorm(h, self.w["final_norm"], eps)
-        logits = O.linear_w8a8(xn, *self.q["lm_head"])
-        nxt = np.array([O.greedy_argmax(logits[r]) for r in range(b)], np.int32)
+        xn = self._norm(h, self.w["final_norm"], eps, first=False)
+        xq, sx = O.quantize_i8_per_row(xn)
+        logits = O.epilogue_scaled(self._acc(xq, self.q["lm_head"], self.blas["lm_head"] if self.blas else None), sx, True,
+                                   self.q["lm_head"][1], True)
+        nxt = np.argmax(logits, axis=1).astype(np.int32) if self.exact else \
+            np.array([O.greedy_argmax(logits[r]) for r in range(b)], np.int32)
         return logits, nxt
 
     def generate(self, prompt, max_length: int):

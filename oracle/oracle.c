@@ -26,6 +26,9 @@
 #include <omp.h>
 #endif
 
+/* Loops over fewer elements than this run on the calling thread: a parallel region costs more than they do. */
+#define SMALL_WORK ((int64_t)1 << 18)
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -180,7 +183,7 @@ void orc_gemm_fp8_f32(const uint8_t* a, const uint8_t* b, int64_t m, int64_t n, 
 /* ------------------------------------------------------------------ quantisers (PARITY UNPINNED)
  * scale = amax(row) / 127, q = rne(x / scale) clamped to [-127, 127]; amax == 0 -> scale 0, q 0. */
 void orc_quantize_i8_per_row(const float* x, int64_t rows, int64_t cols, int8_t* q, float* scale) {
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) if (rows * cols > SMALL_WORK)
     for (int64_t r = 0; r < rows; ++r) {
         const float* xr = x + r * cols;
         float amax = 0.0f;
@@ -231,7 +234,7 @@ void orc_epilogue(const void* acc, int acc_is_int, int64_t m, int64_t n, const f
                   void* out, int out_bf16) {
     const int gate = act == 3;
     const int64_t n_out = gate ? n / 2 : n;
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) if (m * n > SMALL_WORK)
     for (int64_t i = 0; i < m; ++i) {
         const float sa = a_scale[a_per_row ? i : 0];
         for (int64_t j = 0; j < n_out; ++j) {
@@ -260,7 +263,7 @@ void orc_epilogue(const void* acc, int acc_is_int, int64_t m, int64_t n, const f
  * sum of squares in f64 (fma), one downcast for rstd, out = x * rstd * w
  * (crates/backend-cpu/src/rmsnorm.rs:203-228). */
 void orc_rmsnorm(const float* x, const float* w, float eps, int64_t rows, int64_t hidden, float* out) {
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) if (rows * hidden > SMALL_WORK)
     for (int64_t r = 0; r < rows; ++r) {
         const float* xr = x + r * hidden;
         double acc = 0.0;
@@ -392,6 +395,223 @@ int orc_paged_attention(const float* q, const void* k_pool, const void* v_pool, 
                 }
             }
             free(weights);
+        }
+    }
+    return status;
+}
+
+/* ====================================================================================================
+ * Kernel-order restatements (PARITY UNPINNED, like every piece the reference has no code for).
+ *
+ * The functions above follow the reference's sequential loops.  The CUDA kernels of the decoder sum in
+ * another, fixed, order (lanes, warps, blocks) and use their own exponential; upstream of a per-token int8
+ * quantiser a last-bit difference can flip a code, so a free-running greedy comparison needs the CPU side
+ * to round exactly as the kernels do.  The functions below restate that order with the same correctly
+ * rounded operations (this file is compiled with -ffp-contract=off: only the fmaf()/fma() written here
+ * fuse).  The tests check each of them against its sequential counterpart above within the composite
+ * tolerance on the same inputs.
+ * ==================================================================================================== */
+
+/* e^x from multiply, fused multiply-add, add, round-to-integer and exponent arithmetic only: x = n ln2 + r
+ * (ln2 in two parts), degree-5 polynomial on top of 1 + r, result scaled by 2^n in two multiplications. */
+float orc_exp_det(float x) {
+    if (!(x > -104.0f)) return x != x ? x : 0.0f;
+    if (x > 88.8f) return INFINITY;
+    const float n = rintf(x * 1.44269504088896341f);
+    float r = fmaf(n, -0.693359375f, x);
+    r = fmaf(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    float y = fmaf(p, r * r, r) + 1.0f;
+    const int32_t ni = (int32_t)n;
+    const int32_t a = (ni - (ni & 1)) / 2, b = ni - a;
+    union { uint32_t u; float f; } s1, s2;
+    s1.u = (uint32_t)(a + 127) << 23;
+    s2.u = (uint32_t)(b + 127) << 23;
+    y = y * s1.f;
+    return y * s2.f;
+}
+void orc_exp_det_array(const float* x, int64_t n, float* out) {
+    for (int64_t i = 0; i < n; ++i) out[i] = orc_exp_det(x[i]);
+}
+float orc_sigmoid_det(float x) {
+    if (x >= 0.0f) return 1.0f / (1.0f + orc_exp_det(-x));
+    const float e = orc_exp_det(x);
+    return e / (1.0f + e);
+}
+float orc_silu_det(float x) { return x * orc_sigmoid_det(x); }
+
+/* orc_epilogue with the kernels' exponential inside SiLU (act 2 and 3); no bf16 output. */
+void orc_epilogue_det(const int32_t* acc, int64_t m, int64_t n, const float* a_scale, const float* b_scale,
+                      int act, float* out) {
+    const int gate = act == 3;
+    const int64_t n_out = gate ? n / 2 : n;
+#pragma omp parallel for schedule(static) if (m * n > SMALL_WORK)
+    for (int64_t i = 0; i < m; ++i) {
+        const float sa = a_scale[i];
+        for (int64_t j = 0; j < n_out; ++j) {
+            float y;
+            if (!gate) {
+                y = fmaf((float)acc[i * n + j], sa * b_scale[j], 0.0f);
+                if (act == 1) y = fmaxf(y, 0.0f);
+                else if (act == 2) y = orc_silu_det(y);
+            } else {
+                const float g = fmaf((float)acc[i * n + j], sa * b_scale[j], 0.0f);
+                const float u = fmaf((float)acc[i * n + n_out + j], sa * b_scale[n_out + j], 0.0f);
+                y = orc_silu_det(g) * u;
+            }
+            out[i * n_out + j] = y;
+        }
+    }
+}
+
+/* Sum over a warp the way `v += shfl_xor(v, o)` for o = 16, 8, 4, 2, 1 does: a butterfly whose result is the
+ * same in every lane because addition is commutative. */
+static double butterfly_sum_d(double* v) {
+    for (int o = 16; o > 0; o >>= 1) {
+        double t[32];
+        for (int l = 0; l < 32; ++l) t[l] = v[l] + v[l ^ o];
+        memcpy(v, t, sizeof t);
+    }
+    return v[0];
+}
+static float butterfly_sum_f(float* v) {
+    for (int o = 16; o > 0; o >>= 1) {
+        float t[32];
+        for (int l = 0; l < 32; ++l) t[l] = v[l] + v[l ^ o];
+        memcpy(v, t, sizeof t);
+    }
+    return v[0];
+}
+
+/* f64 sum of squares of x[0, n) in the order of a CTA of `threads` threads (a multiple of 32):
+ *   mode 0 ("wide"): thread t owns the groups of four columns g = t + k * threads, k = 0 .. vpt - 1, and chains
+ *                    fma(v, v, acc) over its columns in ascending order;
+ *   mode 1 ("strided"): thread t owns the columns t, t + threads, ... in ascending order;
+ * then a butterfly over each warp and the warps added in ascending order. */
+static double sumsq_block(const float* x, int64_t n, int threads, int vpt, int mode) {
+    double total = 0.0;
+    for (int w = 0; w < threads / 32; ++w) {
+        double lane[32];
+        for (int l = 0; l < 32; ++l) {
+            const int t = w * 32 + l;
+            double acc = 0.0;
+            if (mode == 0) {
+                for (int k = 0; k < vpt; ++k) {
+                    const int64_t g = t + (int64_t)k * threads;
+                    if (g < n / 4)
+                        for (int e = 0; e < 4; ++e) {
+                            const double v = (double)x[4 * g + e];
+                            acc = fma(v, v, acc);
+                        }
+                }
+            } else {
+                for (int64_t i = t; i < n; i += threads) {
+                    const double v = (double)x[i];
+                    acc = fma(v, v, acc);
+                }
+            }
+            lane[l] = acc;
+        }
+        total += butterfly_sum_d(lane);
+    }
+    return total;
+}
+
+/* RMSNorm with the sum of squares taken in kernel order; the rest is orc_rmsnorm's arithmetic.
+ *   mode 0: one wide CTA per row (`threads` threads, `vpt` groups of four columns per thread);
+ *   mode 1: the row cut into `cl` chunks of hidden / cl columns, one CTA of 256 threads each (strided), the
+ *           chunk sums added in chunk order starting from 0.0. */
+void orc_rmsnorm_kernel_order(const float* x, const float* w, float eps, int64_t rows, int64_t hidden, int mode,
+                              int threads, int vpt_or_cl, float* out) {
+#pragma omp parallel for schedule(static) if (rows * hidden > SMALL_WORK)
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* xr = x + r * hidden;
+        double acc;
+        if (mode == 0) {
+            acc = sumsq_block(xr, hidden, threads, vpt_or_cl, 0);
+        } else {
+            const int64_t nc = hidden / vpt_or_cl;
+            acc = 0.0;
+            for (int c = 0; c < vpt_or_cl; ++c) acc += sumsq_block(xr + c * nc, nc, 256, 0, 1);
+        }
+        const float inv_n = 1.0f / (float)hidden;
+        const float rstd = (float)(1.0 / sqrt(fma(acc, (double)inv_n, (double)eps)));
+        for (int64_t i = 0; i < hidden; ++i) out[r * hidden + i] = xr[i] * rstd * w[i];
+    }
+}
+
+/* orc_paged_attention in the order of the general-shape CUDA kernel (head_dim <= 256): four warps walk the
+ * keys j = warp, warp + 4, ...; lane l holds the dims l, l + 32, ...; per key
+ *   s  = butterfly over lanes of the fma chain over a lane's dims of (q[d] * scale) * k[d]
+ *   m' = max(m, s); c = exp(m - m'); p = exp(s - m'); l = fma(l, c, p); o[d] = fma(p, v[d], o[d] * c)
+ * then the warps are merged in order: g = exp(m_w - max m); L = fma(l_w, g, L); O[d] = fma(o_w[d], g, O[d]);
+ * out[d] = O[d] / L.  exp is orc_exp_det.  Same arguments and return codes as orc_paged_attention. */
+int orc_paged_attention_kernel_order(const float* q, const void* k_pool, const void* v_pool,
+                                     const uint32_t* block_tables, const uint32_t* seq_lens, int64_t batch,
+                                     int64_t l_new, int64_t num_q_heads, int64_t num_kv_heads, int64_t head_dim,
+                                     int64_t block_size, int64_t num_blocks, int64_t max_blocks_per_seq, float scale,
+                                     int kv_bf16, float* out) {
+    if (head_dim > 256) return -3;
+    const int64_t eq = num_q_heads * head_dim;
+    const int64_t ekv = num_kv_heads * head_dim;
+    const int64_t group = num_q_heads / num_kv_heads;
+    int status = 0;
+#pragma omp parallel for schedule(dynamic, 1) collapse(2)
+    for (int64_t row = 0; row < batch * l_new; ++row) {
+        for (int64_t h = 0; h < num_q_heads; ++h) {
+            const int64_t b = row / l_new, i = row % l_new;
+            const int64_t s_total = (int64_t)seq_lens[b];
+            if (s_total < l_new) { status = -2; continue; }
+            const int64_t limit = s_total - l_new + i + 1;
+            const int64_t kvh = h / group;
+            const float* q_row = q + row * eq + h * head_dim;
+            float* o_row = out + row * eq + h * head_dim;
+            float qs[256];
+            for (int64_t d = 0; d < head_dim; ++d) qs[d] = q_row[d] * scale;
+            float wm[4], wl[4], wo[4][256];
+            int bad = 0;
+            for (int w = 0; w < 4 && !bad; ++w) {
+                float m = -INFINITY, l = 0.0f;
+                float* acc = wo[w];
+                for (int64_t d = 0; d < head_dim; ++d) acc[d] = 0.0f;
+                for (int64_t j = w; j < limit; j += 4) {
+                    const uint32_t blk = block_tables[b * max_blocks_per_seq + j / block_size];
+                    if ((int64_t)blk >= num_blocks) { bad = 1; break; }
+                    const int64_t off = ((int64_t)blk * block_size + j % block_size) * ekv + kvh * head_dim;
+                    float lane[32];
+                    for (int ln = 0; ln < 32; ++ln) {
+                        float s = 0.0f;
+                        for (int64_t d = ln; d < head_dim; d += 32) s = fmaf(qs[d], kv_at(k_pool, off + d, kv_bf16), s);
+                        lane[ln] = s;
+                    }
+                    const float s = butterfly_sum_f(lane);
+                    const float m_new = fmaxf(m, s);
+                    const float corr = orc_exp_det(m - m_new);
+                    const float p = orc_exp_det(s - m_new);
+                    l = fmaf(l, corr, p);
+                    for (int64_t d = 0; d < head_dim; ++d) acc[d] = fmaf(p, kv_at(v_pool, off + d, kv_bf16), acc[d] * corr);
+                    m = m_new;
+                }
+                wm[w] = m;
+                wl[w] = l;
+            }
+            if (bad) { status = -1; continue; }
+            const float mm = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+            float g[4], ll = 0.0f;
+            for (int w = 0; w < 4; ++w) {
+                g[w] = wm[w] == -INFINITY ? 0.0f : orc_exp_det(wm[w] - mm);
+                ll = fmaf(wl[w], g[w], ll);
+            }
+            for (int64_t d = 0; d < head_dim; ++d) {
+                float o = 0.0f;
+                for (int w = 0; w < 4; ++w) o = fmaf(wo[w][d], g[w], o);
+                o_row[d] = limit > 0 ? o / ll : 0.0f;
+            }
         }
     }
     return status;

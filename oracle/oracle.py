@@ -265,3 +265,73 @@ def paged_attention(q, k_pool, v_pool, block_tables, seq_lens, *, batch: int, l_
     if rc != 0:
         raise ValueError(f"paged_attention: invalid input ({rc})")
     return out
+
+
+# ---------------------------------------------------------------- kernel-order restatements
+# The CUDA decoder sums in its own fixed order and uses its own exponential; these functions round exactly
+# as those kernels do (see the block comment in oracle.c).  Each is checked against its sequential
+# counterpart above within the composite tolerance in tests/test_oracle_golden.py.
+def exp_det(x) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty_like(x)
+    lib().orc_exp_det_array(_p(x), C.c_int64(x.size), _p(out))
+    return out
+
+
+def silu_det(x: float) -> float:
+    f = lib().orc_silu_det
+    f.restype, f.argtypes = C.c_float, [C.c_float]
+    return float(f(C.c_float(x)))
+
+
+def epilogue_det(acc, a_scale, b_scale, act=ACT_NONE) -> np.ndarray:
+    """int32 accumulators [m, n] -> f32 with per-row / per-column scales, no bias; SiLU uses exp_det."""
+    acc = _c(acc, np.int32)
+    m, n = acc.shape
+    n_out = n // 2 if act == ACT_SILU_GATE else n
+    out = np.empty((m, n_out), np.float32)
+    lib().orc_epilogue_det(_p(acc), C.c_int64(m), C.c_int64(n), _p(_c(a_scale, np.float32)), _p(_c(b_scale, np.float32)),
+                           C.c_int(act), _p(out))
+    return out
+
+
+def rmsnorm_kernel_order(x, w, eps: float, mode: int, threads: int, vpt_or_cl: int) -> np.ndarray:
+    """mode 0: one wide CTA per row (threads, groups of four per thread); mode 1: `vpt_or_cl` chunks of 256 threads."""
+    x = _c(x, np.float32)
+    rows, hidden = x.shape
+    out = np.empty_like(x)
+    lib().orc_rmsnorm_kernel_order(_p(x), _p(_c(w, np.float32)), C.c_float(eps), C.c_int64(rows), C.c_int64(hidden),
+                                   C.c_int(mode), C.c_int(threads), C.c_int(vpt_or_cl), _p(out))
+    return out
+
+
+def paged_attention_kernel_order(q, k_pool, v_pool, block_tables, seq_lens, *, batch: int, l_new: int, num_q_heads: int,
+                                 num_kv_heads: int, head_dim: int, block_size: int, num_blocks: int,
+                                 max_blocks_per_seq: int, scale: float, kv_bf16: bool) -> np.ndarray:
+    q = _c(q, np.float32)
+    block_tables = _c(block_tables, np.uint32)
+    seq_lens = _c(seq_lens, np.uint32)
+    out = np.zeros((batch, l_new, num_q_heads * head_dim), np.float32)
+    f = lib().orc_paged_attention_kernel_order
+    f.restype = C.c_int
+    rc = f(_p(q), _p(k_pool), _p(v_pool), _p(block_tables), _p(seq_lens), C.c_int64(batch), C.c_int64(l_new),
+           C.c_int64(num_q_heads), C.c_int64(num_kv_heads), C.c_int64(head_dim), C.c_int64(block_size),
+           C.c_int64(num_blocks), C.c_int64(max_blocks_per_seq), C.c_float(scale), C.c_int(int(kv_bf16)), _p(out))
+    if rc != 0:
+        raise ValueError(f"paged_attention_kernel_order: invalid input ({rc})")
+    return out
+
+
+def gemm_i8_s32_blas(a, w_float) -> np.ndarray:
+    """The int32 accumulators of gemm_i8_s32 through a floating-point BLAS product, for the long decoder runs.
+    `w_float` is the weight [n, k] converted once with int8_weight_for_blas().  Every product is an integer of
+    at most 127 * 128 and every partial sum an integer below k * 2^14, so the f32 product is exact for
+    k <= 1024 (sums < 2^24) and the f64 product for any k here (sums < 2^53), whatever order BLAS adds in."""
+    a = np.asarray(a)
+    acc = a.astype(w_float.dtype) @ w_float.T
+    return acc.astype(np.int64).astype(np.int32)
+
+
+def int8_weight_for_blas(w_q) -> np.ndarray:
+    w_q = np.asarray(w_q)
+    return np.ascontiguousarray(w_q.astype(np.float32 if w_q.shape[1] <= 1024 else np.float64))

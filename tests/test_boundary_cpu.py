@@ -35,7 +35,8 @@ def test_status_names_follow_backend_error_variants():
     l = lib()
     want = {0: "Ok", 1: "ShapeMismatch", 2: "DeviceMismatch", 3: "DeviceAllocationFailed", 4: "KernelLaunchFailed",
             5: "DeviceUnavailable", 6: "TransferFailed", 7: "Unsupported", 8: "StorePoisoned", 9: "InvalidArgument",
-            10: "DeviceContextPoisoned", 11: "StaleDeviceGeneration"}
+            10: "DeviceContextPoisoned", 11: "StaleDeviceGeneration", 12: "DeviceContextRetiring",
+            13: "DeviceContextUnrecoverable", 14: "DeviceContextCaptureInProgress"}
     for code, name in want.items():
         assert l.b200_status_name(code).decode() == name
 

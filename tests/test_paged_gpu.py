@@ -270,6 +270,71 @@ def test_full_size_properties_config3(be):
         b_.release()
 
 
+def test_config3_full_size_against_the_oracle(be):
+    """Config 3 as stated: batch 64, 32 query / 8 KV heads, head_dim 128, bf16 KV, 16-token blocks, context
+    lengths U[512, 8192], block tables = consecutive slices of a seeded permutation of a 200 000-block pool,
+    q / k / v ~ N(0, 1), scale 1 / sqrt(128).  The device reads the scattered 200k-block pools; the oracle gets
+    the same logical contents through tables renumbered onto a dense copy of the used blocks (the physical
+    position of a block does not enter the arithmetic), so the host never holds the 13 GB of unused pool."""
+    rng = np.random.default_rng(0)
+    batch, heads, kvh, dh, bs, nblk, mbps = 64, 32, 8, 128, 16, 200_000, 512
+    ekv = kvh * dh
+    ctx = rng.integers(512, 8193, batch).astype(np.uint32)
+    perm = rng.permutation(nblk).astype(np.uint32)
+    tables = np.full((batch, mbps), P.SENTINEL, np.uint32)
+    dense = np.full((batch, mbps), P.SENTINEL, np.uint32)
+    at = 0
+    for b in range(batch):
+        used = -(-int(ctx[b]) // bs)
+        tables[b, :used] = perm[at:at + used]
+        dense[b, :used] = np.arange(at, at + used, dtype=np.uint32)
+        at += used
+    used_total = at
+    k_rows = O.f32_to_bf16(rng.standard_normal((used_total * bs, ekv), dtype=np.float32))
+    v_rows = O.f32_to_bf16(rng.standard_normal((used_total * bs, ekv), dtype=np.float32))
+    q = rng.standard_normal((batch, 1, heads * dh), dtype=np.float32)
+    k_pool = be.alloc_zeroed((nblk * bs, ekv), np.uint16)
+    v_pool = be.alloc_zeroed((nblk * bs, ekv), np.uint16)
+    for idx in np.argsort(perm[:used_total]):
+        blk = int(perm[idx])
+        be.upload_into(k_rows[idx * bs:(idx + 1) * bs], k_pool, blk * bs * ekv * 2)
+        be.upload_into(v_rows[idx * bs:(idx + 1) * bs], v_pool, blk * bs * ekv * 2)
+    args = P.PagedAttentionArgs(P.PagedKvLayout(nblk, bs, ekv, BF16), batch, 1, heads, mbps, float(1.0 / np.sqrt(dh)), kvh)
+    out = P.paged_attention_forward(be, be.upload(q), k_pool, v_pool, tables, ctx, args).numpy()
+    k_pool.release()
+    v_pool.release()
+    ref = O.paged_attention(q, k_rows, v_rows, dense, ctx, batch=batch, l_new=1, num_q_heads=heads, num_kv_heads=kvh,
+                            head_dim=dh, block_size=bs, num_blocks=used_total, max_blocks_per_seq=mbps, scale=args.scale,
+                            kv_bf16=True)
+    fails, max_abs, max_rel = O.compare(out, ref)
+    assert fails == 0, (fails, max_abs, max_rel)
+
+
+def test_sequence_lengths_beyond_the_plan_are_clamped_and_flagged(fresh_be):
+    """Device-resident seq_lens cannot be validated on the host.  An entry above max_seq_len (here also above
+    the table width) must not make any kernel read past a table row or another row's partial results: the
+    kernels clamp it and set the device error word, which the next synchronisation reports."""
+    be = fresh_be
+    for heads, kvh, dh in ((8, 2, 128), (4, 4, 64)):            # tensor-core split path, general kernel
+        rng = np.random.default_rng(dh)
+        bs, nblk, mbps, batch = 16, 64, 8, 3
+        ekv = kvh * dh
+        tables = rng.permutation(nblk).astype(np.uint32)[: batch * mbps].reshape(batch, mbps)
+        lens = np.array([40, 100_000, 128], np.uint32)          # row 1 claims far more than 8 blocks x 16 tokens
+        k = be.upload(O.f32_to_bf16(rng.standard_normal((nblk * bs, ekv), dtype=np.float32)))
+        v = be.upload(O.f32_to_bf16(rng.standard_normal((nblk * bs, ekv), dtype=np.float32)))
+        q = be.upload(rng.standard_normal((batch, 1, heads * dh), dtype=np.float32))
+        out = be.alloc_zeroed((batch, 1, heads * dh), np.float32)
+        args = P.PagedAttentionArgs(P.PagedKvLayout(nblk, bs, ekv, BF16), batch, 1, heads, mbps, 0.1, kvh)
+        P.paged_attention_forward_resident(be, q, k, v, be.upload(tables), be.upload(lens), 128, args, out)
+        with pytest.raises(BackendError) as e:
+            be.synchronize_device()
+        assert e.value.kind == "KernelLaunchFailed" and "0x204" in e.value.message
+        assert be.poisoned
+        be.recover()                                            # a flagged index is not a fault: recover in place
+        assert not be.poisoned
+
+
 def test_invalid_arguments_are_rejected_before_any_launch(be):
     layout = P.PagedKvLayout(4, 2, 4, F32)
     pool = be.alloc_zeroed((8, 4), np.float32)

@@ -241,6 +241,165 @@ def test_fp8_operands_quantised_on_device_are_identical_and_gated_epilogue(be):
     judge_vs_truth(y, ref, truth, "gated")
 
 
+# ---------------------------------------------------------------- the persistent kernel (large tile grids)
+def tile_rows(m, per_tile, seed):
+    """Row sample that touches every 128-row tile: first and last row of each tile plus random ones."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    for t0 in range(0, m, 128):
+        t1 = min(t0 + 128, m)
+        rows += [t0, t1 - 1] + rng.integers(t0, t1, max(per_tile - 2, 0)).tolist()
+    return np.unique(np.array(rows))
+
+
+# m, n, k, tile width the heuristic picks; every shape has at least half a wave of tiles (fused epilogues switch
+# to the persistent kernel there) and the last two have M / N / K tails
+PERSISTENT_FUSED = [(2048, 4096, 4096, 256), (4096, 4096, 1024, 256), (256, 8192, 512, 128), (300, 4112, 528, 128),
+                    (1000, 2320, 272, 256)]
+
+
+@pytest.mark.parametrize("m,n,k,tile", PERSISTENT_FUSED)
+def test_persistent_kernel_int8_epilogues(be, m, n, k, tile):
+    info = be.gemm_plan_info(m, n, k, fused=True)
+    assert info["persistent"] == 1 and info["tile"] == tile, info
+    rng = np.random.default_rng(m + n + k)
+    a, w = rand_i8(m, (m, k)), rand_i8(n, (n, k))
+    sa = rng.uniform(0.5e-2, 2e-2, m).astype(np.float32)
+    sw = rng.uniform(0.5e-3, 2e-3, n).astype(np.float32)
+    bias = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+    rows = tile_rows(m, 4, 1)
+    acc = O.gemm_i8_s32(a[rows], w)
+    a_d, w_d, sa_d, sw_d, b_d = be.upload(a), be.upload(w), be.upload(sa), be.upload(sw), be.upload(bias)
+    # dequant + bias: the same fma on the same integers -> identical bits; bf16 = that value rounded once
+    y = be.gemm_q8_scaled(I8, a_d, sa_d, True, w_d, sw_d, True, m, n, k, bias=b_d).numpy()
+    ref = O.epilogue_scaled(acc, sa[rows], True, sw, True, bias)
+    assert np.array_equal(y[rows], ref)
+    y16 = be.gemm_q8_scaled(I8, a_d, sa_d, True, w_d, sw_d, True, m, n, k, bias=b_d, out_dtype=BF16).numpy()
+    assert np.array_equal(y16, O.f32_to_bf16(y))
+    # ReLU (exact), SiLU and SiLU-gate (fast exponential: composite tolerance), residual
+    y = be.gemm_q8_scaled(I8, a_d, sa_d, True, w_d, sw_d, True, m, n, k, bias=b_d, activation=ACT_RELU).numpy()
+    assert np.array_equal(y[rows], O.epilogue_scaled(acc, sa[rows], True, sw, True, bias, act=O.ACT_RELU))
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    y = be.gemm_q8_scaled(I8, a_d, sa_d, True, w_d, sw_d, True, m, n, k, bias=b_d, activation=ACT_SILU,
+                          residual=be.upload(res)).numpy()
+    fails, max_abs, max_rel = O.compare(y[rows], O.epilogue_scaled(acc, sa[rows], True, sw, True, bias, act=O.ACT_SILU,
+                                                                   residual=res[rows]))
+    assert fails == 0, ("silu + residual", max_abs, max_rel)
+    if n % 32 == 0:
+        assert be.gemm_plan_info(m, n, k, gated=True, fused=True)["persistent"] == 1
+        y = be.gemm_q8_scaled(I8, a_d, sa_d, True, w_d, sw_d, True, m, n, k, bias=b_d, activation=ACT_SILU_GATE).numpy()
+        assert y.shape == (m, n // 2)
+        fails, max_abs, max_rel = O.compare(y[rows], O.epilogue_scaled(acc, sa[rows], True, sw, True, bias,
+                                                                       act=O.ACT_SILU_GATE))
+        assert fails == 0, ("gate", max_abs, max_rel)
+        y16 = be.gemm_q8_scaled(I8, a_d, sa_d, True, w_d, sw_d, True, m, n, k, bias=b_d, activation=ACT_SILU_GATE,
+                                out_dtype=BF16).numpy()
+        assert np.array_equal(y16, O.f32_to_bf16(y))
+
+
+@pytest.mark.parametrize("m,n,k,tile", [(4096, 4096, 512, 256), (384, 16384, 256, 128), (2700, 4112, 144, 256)])
+def test_persistent_kernel_raw_int32_accumulators(be, m, n, k, tile):
+    info = be.gemm_plan_info(m, n, k, fused=False)
+    assert info["persistent"] == 1 and info["tile"] == tile, info       # raw output switches at two waves of tiles
+    a, w = rand_i8(m + 1, (m, k)), rand_i8(n + 1, (n, k))
+    acc = be.gemm_i8_s32(be.upload(a), be.upload(w), m, n, k).numpy()
+    rows = tile_rows(m, 6, 2)
+    assert np.array_equal(acc[rows], O.gemm_i8_s32(a[rows], w))
+    # every element, through an exact identity: column sums of the accumulators = (sum of A rows) . W
+    colsum = acc.astype(np.int64).sum(axis=0)
+    want = a.astype(np.int64).sum(axis=0) @ w.astype(np.int64).T
+    assert np.array_equal(colsum, want)
+
+
+@pytest.mark.parametrize("m,n,k,tile", [(2048, 4096, 1024, 256), (256, 8192, 512, 128), (1000, 2320, 272, 256)])
+def test_persistent_kernel_fp8(be, m, n, k, tile):
+    assert be.gemm_plan_info(m, n, k, fused=True)["persistent"] == 1
+    aq, sa, bq, sb = fp8_operands(m + n, m, n, k)
+    rows = tile_rows(m, 3, 3)
+    truth = fp8_truth(aq[rows], bq, sa, sb)
+    seq = O.epilogue_scaled(O.gemm_fp8_f32(aq[rows], bq), sa, False, sb, False)
+    a_d, sa_d, b_d, sb_d = be.upload(aq), be.upload(sa), be.upload(bq), be.upload(sb)
+    y32 = be.gemm_q8_scaled(FP8_E4M3, a_d, sa_d, False, b_d, sb_d, False, m, n, k, out_dtype=F32).numpy()
+    judge_vs_truth(y32[rows], seq, truth, "persistent f32 out")
+    y16 = be.gemm_q8_scaled(FP8_E4M3, a_d, sa_d, False, b_d, sb_d, False, m, n, k, out_dtype=BF16).numpy()
+    assert np.array_equal(y16, O.f32_to_bf16(y32))
+    if n % 32 == 0:
+        y = be.gemm_q8_scaled(FP8_E4M3, a_d, sa_d, False, b_d, sb_d, False, m, n, k, activation=ACT_SILU_GATE).numpy()
+        f = n // 2
+        g, u = truth[:, :f], truth[:, f:]
+        ref = O.epilogue_scaled(O.gemm_fp8_f32(aq[rows], bq), sa, False, sb, False, act=O.ACT_SILU_GATE)
+        judge_vs_truth(y[rows], ref, g / (1.0 + np.exp(-g)) * u, "persistent gated")
+
+
+def test_gated_projection_of_the_8b_shape_on_sampled_rows(be):
+    """The gate/up projection of the 8B shape with the SiLU-gate epilogue (N = 2 x 14336, K = 4096) at M = 4096:
+    int8 and FP8 through the persistent 256-wide kernel, a few hundred sampled rows against the oracle."""
+    m, f, k = 4096, 14336, 4096
+    assert be.gemm_plan_info(m, 2 * f, k, gated=True, fused=True) ["persistent"] == 1
+    rng = np.random.default_rng(77)
+    rows = tile_rows(m, 8, 4)[:256]
+    a, w = rand_i8(5, (m, k)), rand_i8(6, (2 * f, k))
+    sa = rng.uniform(0.5e-2, 2e-2, m).astype(np.float32)
+    sw = rng.uniform(0.5e-3, 2e-3, 2 * f).astype(np.float32)
+    w_d = be.upload(w)
+    y = be.gemm_q8_scaled(I8, be.upload(a), be.upload(sa), True, w_d, be.upload(sw), True, m, 2 * f, k,
+                          activation=ACT_SILU_GATE, out_dtype=BF16).numpy()
+    ref = O.epilogue_scaled(O.gemm_i8_s32(a[rows], w), sa[rows], True, sw, True, act=O.ACT_SILU_GATE)
+    # bf16 output: compare after widening; one bf16 rounding (2^-9 relative) sits on top of the f32 tolerance
+    got = O.bf16_to_f32(y[rows])
+    assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.abs(ref) + 1e-5)
+    w_d.release()
+    rows = rows[:48]
+    aq, sa8, bq, sb8 = fp8_operands(91, m, 2 * f, k)
+    y = be.gemm_q8_scaled(FP8_E4M3, be.upload(aq), be.upload(sa8), False, be.upload(bq), be.upload(sb8), False, m, 2 * f, k,
+                          activation=ACT_SILU_GATE).numpy()
+    truth = fp8_truth(aq[rows], bq, sa8, sb8)
+    ref = O.epilogue_scaled(O.gemm_fp8_f32(aq[rows], bq), sa8, False, sb8, False, act=O.ACT_SILU_GATE)
+    g, u = truth[:, :f], truth[:, f:]
+    judge_vs_truth(y[rows], ref, g / (1.0 + np.exp(-g)) * u, "8B gated fp8")
+
+
+# ---------------------------------------------------------------- FP8 linear through the operator call
+@pytest.mark.parametrize("m,n,k,act", [(128, 4096, 4096, ACT_NONE), (16, 512, 1024, ACT_SILU), (64, 512, 1024, ACT_SILU_GATE),
+                                       (1024, 4096, 1024, ACT_NONE)])
+def test_linear_fp8_operator(be, m, n, k, act):
+    """b200_linear_fp8: f32 activation quantised per tensor on the device, E4M3 weight view with one scale."""
+    x = normal(m + k, (m, k))
+    w = normal(n, (n, k), 0.02)
+    bias = normal(3, (n,), 0.05)
+    wq, ws = O.quantize_fp8_per_tensor(w)
+    xq, xs = O.quantize_fp8_per_tensor(x)
+    y = be.linear_fp8_forward_device(be.upload(x), m, k, be.upload(wq), be.upload(ws), be.upload(bias), n, act).numpy()
+    acc = O.gemm_fp8_f32(xq, wq)
+    seq = O.epilogue_scaled(acc, xs, False, ws, False, bias, act=act)
+    lin = (O.e4m3_to_f32(xq).astype(np.float64) @ O.e4m3_to_f32(wq).astype(np.float64).T) * (float(xs[0]) * float(ws[0]))
+    lin = lin + bias.astype(np.float64)
+    if act == ACT_SILU:
+        truth = lin / (1.0 + np.exp(-lin))
+    elif act == ACT_SILU_GATE:
+        g, u = lin[:, : n // 2], lin[:, n // 2:]
+        truth = g / (1.0 + np.exp(-g)) * u
+    else:
+        truth = lin
+    assert y.shape == seq.shape
+    judge_vs_truth(y, seq, truth, "linear_fp8")
+    y16 = be.linear_fp8_forward_device(be.upload(x), m, k, be.upload(wq), be.upload(ws), be.upload(bias), n, act,
+                                       out_dtype=BF16).numpy()
+    assert np.array_equal(y16, O.f32_to_bf16(y))
+
+
+def test_linear_fp8_rejects_bad_requests_before_any_launch(be):
+    x = be.upload(normal(1, (8, 24)))
+    w = be.upload(np.zeros((16, 24), np.uint8))
+    s = be.upload(np.ones(1, np.float32))
+    with pytest.raises(BackendError) as e:
+        be.linear_fp8_forward_device(x, 8, 24, w, s, None, 16)          # k not a multiple of 16
+    assert e.value.kind == "Unsupported" and not be.poisoned
+    with pytest.raises(BackendError) as e:
+        be.linear_fp8_forward_device(x, 8, 32, w, s, None, 16)          # a is smaller than m x k
+    assert e.value.kind == "ShapeMismatch" and not be.poisoned
+
+
 # ---------------------------------------------------------------- size-independent properties at full size
 def test_gemm_i8_linearity_and_identity_at_large_size(be):
     # acc(A, W1 + W2) == acc(A, W1) + acc(A, W2) in exact integers; W = identity copies A

@@ -47,7 +47,14 @@ def test_noalloc_entry_matches_the_allocating_entry_on_two_calls_in_a_row(be):
         want = be.alloc_zeroed(q.shape, np.float32)
         P.paged_attention_forward_resident(be, qd, kd, vd, td, sd, int(ctx.max()), args, want)
         got = be.upload(np.full(q.shape, np.nan, np.float32))
+        be.synchronize_device()
+        free_before = be.memory_info()[0]
         P.paged_attention_forward_noalloc(be, qd, kd, vd, td, sd, int(ctx.max()), args, got)
+        be.synchronize_device()
+        if seed == 22:
+            # the property the entry exists for: by the second call nothing is left to set up, and the amount of
+            # free device memory is the same after the call as before it
+            assert be.memory_info()[0] == free_before
         a, b = got.numpy(), want.numpy()
         assert np.all(np.isfinite(a))
         assert O.compare(a, b)[0] == 0
