@@ -68,7 +68,6 @@ def bench_gemm(be: Backend, op: int, m: int, n: int, k: int, act: int, iters: in
 
 def run_gemm(args):
     be = Backend(0)
-    hbm, bf16, kind = peaks()
     shapes = []
     for nk in (4096, 8192, 14336):
         for m in (1, 16, 128, 1024, 4096, 8192):
@@ -84,23 +83,13 @@ def run_gemm(args):
         if args.operands and not name.startswith(args.operands):
             continue
         for m, n, k, act in shapes:
-            ms = bench_gemm(be, op, m, n, k, act, args.iters, args.warmup, args.tile, args.splits)
-            ops = 2.0 * m * n * k
-            tops = ops / (ms * 1e-3) / 1e12
-            n_out = n // 2 if act == ACT_SILU_GATE else n
-            gbs = (m * k + n * k + 2 * m * n_out) / (ms * 1e-3) / 1e9
-            print(json.dumps({"kernel": "gemm_tc5", "operands": name, "m": m, "n": n, "k": k,
-                              "epilogue": "silu_gate" if act == ACT_SILU_GATE else "dequant", "out": "bf16",
-                              "ms": round(ms, 5), "tops": round(tops, 1),
-                              "frac_of_2x_bf16_peak": round(tops / (2 * bf16), 4), "frac_of_4500_nominal": round(tops / 4500, 4),
-                              "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4), "peak_kind": kind}), flush=True)
+            print(json.dumps(measure_gemm(be, op, m, n, k, act, args.iters, args.warmup, args.tile, args.splits)), flush=True)
     be.close()
 
 
-def run_attention(args):
+def measure_attention_config3(be: Backend, iters: int, warmup: int, chunk_blocks: int = 0, host_call: bool = True) -> dict:
     """Config 3: batch 64, 32 query / 8 KV heads, head_dim 128, bf16 KV, block 16, contexts U[512, 8192], block
     tables = consecutive slices of a seeded permutation of a 200k-block pool."""
-    be = Backend(0)
     hbm, _, kind = peaks()
     rng = np.random.default_rng(0)
     batch, hq, hkv, dh, bs, nblk = 64, 32, 8, 128, 16, 200_000
@@ -127,30 +116,55 @@ def run_attention(args):
     q = be.upload(rng.standard_normal((batch, 1, hq * dh)).astype(np.float32))
     out = be.alloc_zeroed((batch, 1, hq * dh), np.float32)
     tdev, sdev = be.upload(tables), be.upload(ctx)
-    if args.chunk_blocks:
-        P.paged_attention_tuning(be, args.chunk_blocks)
+    if chunk_blocks:
+        P.paged_attention_tuning(be, chunk_blocks)
     algo = int(ctx.astype(np.int64).sum()) * hkv * dh * 2 * 2 + 2 * batch * hq * dh * 4 + int(sum(-(-int(c) // bs) for c in ctx)) * 4
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         P.paged_attention_forward_resident(be, q, k_pool, v_pool, tdev, sdev, int(ctx.max()), a, out)
     be.synchronize_device()
     be.timer_start()
-    for _ in range(args.iters):
+    for _ in range(iters):
         P.paged_attention_forward_resident(be, q, k_pool, v_pool, tdev, sdev, int(ctx.max()), a, out)
-    ms = be.timer_stop() / args.iters
-    # through the reference-shaped call: host block tables and seq_lens validated and uploaded per call
-    import time
-    be.synchronize_device()
-    t0 = time.perf_counter()
-    for _ in range(args.iters):
-        P.paged_attention_forward(be, q, k_pool, v_pool, tables, ctx, a, out)
-    be.synchronize_device()
-    ms_host = (time.perf_counter() - t0) * 1e3 / args.iters
+    ms = be.timer_stop() / iters
     gbs = algo / (ms * 1e-3) / 1e9
-    print(json.dumps({"kernel": "paged_attention_decode (+combine)", "batch": batch, "sum_ctx": int(ctx.sum()),
-                      "algorithmic_bytes": algo, "ms": round(ms, 5), "gbs": round(gbs, 1),
-                      "frac_of_hbm_peak": round(gbs / hbm, 4), "peak_kind": kind,
-                      "ms_host_tables_call": round(ms_host, 5),
-                      "note": "the KV read per launch (1.1 GB) is far above the L2 size"}), flush=True)
+    res = {"kernel": "paged_attention_decode (+combine)", "batch": batch, "sum_ctx": int(ctx.sum()),
+           "algorithmic_bytes": algo, "ms": round(ms, 5), "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4),
+           "frac_of_8000_nominal": round(gbs / 8000.0, 4), "peak_kind": kind,
+           "note": "the KV read per launch (1.1 GB) is far above the L2 size"}
+    if host_call:
+        # through the reference-shaped call: host block tables and seq_lens validated and uploaded per call
+        import time
+        be.synchronize_device()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            P.paged_attention_forward(be, q, k_pool, v_pool, tables, ctx, a, out)
+        be.synchronize_device()
+        res["ms_host_tables_call"] = round((time.perf_counter() - t0) * 1e3 / iters, 5)
+    for b_ in (k_pool, v_pool, q, out, tdev, sdev):
+        b_.release()
+    if chunk_blocks:
+        P.paged_attention_tuning(be, 0)
+    return res
+
+
+def measure_gemm(be: Backend, op: int, m: int, n: int, k: int, act: int, iters: int, warmup: int, tile: int = 0,
+                 splits: int = 0) -> dict:
+    """One GEMM shape: T(FL)OPS and the two fractions (of 2 x the measured bf16 burst peak, of the 4500 nominal)."""
+    hbm, bf16, kind = peaks()
+    ms = bench_gemm(be, op, m, n, k, act, iters, warmup, tile, splits)
+    tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    n_out = n // 2 if act == ACT_SILU_GATE else n
+    gbs = (m * k + n * k + 2 * m * n_out) / (ms * 1e-3) / 1e9
+    return {"kernel": "gemm_tc5", "operands": "int8" if op == I8 else "fp8_e4m3", "m": m, "n": n, "k": k,
+            "epilogue": "silu_gate" if act == ACT_SILU_GATE else "dequant", "out": "bf16", "ms": round(ms, 5),
+            "tops": round(tops, 1), "frac_of_2x_bf16_peak": round(tops / (2 * bf16), 4),
+            "frac_of_4500_nominal": round(tops / 4500, 4), "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4),
+            "peak_kind": kind}
+
+
+def run_attention(args):
+    be = Backend(0)
+    print(json.dumps(measure_attention_config3(be, args.iters, args.warmup, args.chunk_blocks)), flush=True)
     be.close()
 
 

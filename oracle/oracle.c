@@ -37,6 +37,15 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Sets the number of threads of the parallel loops (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------ bf16
  * IEEE round-to-nearest-even f32 -> bf16 and exact widening, the behaviour of the `half`
  * crate (=2.7.1) that the reference relies on (crates/backend-cpu/src/typed_bf16.rs:72,86;

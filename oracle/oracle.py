@@ -66,6 +66,10 @@ def num_threads() -> int:
 
 
 # ---------------------------------------------------------------- scalars / conversions
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(C.c_int(int(n)))
+
+
 def f32_to_bf16(x) -> np.ndarray:
     x = _c(x, np.float32)
     out = np.empty(x.shape, np.uint16)

@@ -182,17 +182,19 @@ def fp8_truth(aq, bq, sa, sb):
     return (a @ b.T) * (float(sa[0]) * float(sb[0]))
 
 
-def judge_vs_truth(got, seq, truth, label):
+def judge_vs_truth(got, seq, truth, label, rel_extra=0.0):
     """The tensor core sums K in its own order, so outputs that nearly cancel (|y| << sqrt(K)) cannot meet
     rel < 1e-3 against a sequential f32 chain - the sequential chain itself misses it against the exact
     value.  Following the reference's treatment of tensor-core kernels (baseline non-regression instead of
     loosened tolerances, crates/backend-cuda/tests/common/parity_baseline.rs), the kernel's error against
-    the f64 ground truth must not exceed the sequential f32 FMA chain's."""
+    the f64 ground truth must not exceed the sequential f32 FMA chain's.  `rel_extra` is an allowance relative to
+    the magnitude of the outputs for an epilogue that is itself approximate: the persistent kernel evaluates SiLU
+    with the hardware exponential and reciprocal (relative error about 1e-6, against the 1e-3 of the contract)."""
     err_gpu = np.abs(got.astype(np.float64) - truth)
     err_seq = np.abs(seq.astype(np.float64) - truth)
     assert np.all(np.isfinite(got)), label
-    assert err_gpu.max() <= 2.0 * err_seq.max() + 1e-7, (label, err_gpu.max(), err_seq.max())
-    assert err_gpu.mean() <= 1.5 * err_seq.mean() + 1e-9, (label, err_gpu.mean(), err_seq.mean())
+    assert err_gpu.max() <= 2.0 * err_seq.max() + rel_extra * np.abs(truth).max() + 1e-7, (label, err_gpu.max(), err_seq.max())
+    assert err_gpu.mean() <= 1.5 * err_seq.mean() + rel_extra * np.abs(truth).mean() + 1e-9, (label, err_gpu.mean(), err_seq.mean())
     # and wherever the result is not a near-cancellation, the composite tolerance holds outright
     big = np.abs(truth) > 1e3 * err_seq.max()
     fails, max_abs, max_rel = O.compare(got[big], seq[big])
@@ -328,7 +330,7 @@ def test_persistent_kernel_fp8(be, m, n, k, tile):
         f = n // 2
         g, u = truth[:, :f], truth[:, f:]
         ref = O.epilogue_scaled(O.gemm_fp8_f32(aq[rows], bq), sa, False, sb, False, act=O.ACT_SILU_GATE)
-        judge_vs_truth(y[rows], ref, g / (1.0 + np.exp(-g)) * u, "persistent gated")
+        judge_vs_truth(y[rows], ref, g / (1.0 + np.exp(-g)) * u, "persistent gated", rel_extra=2e-6)
 
 
 def test_gated_projection_of_the_8b_shape_on_sampled_rows(be):
@@ -356,7 +358,7 @@ def test_gated_projection_of_the_8b_shape_on_sampled_rows(be):
     truth = fp8_truth(aq[rows], bq, sa8, sb8)
     ref = O.epilogue_scaled(O.gemm_fp8_f32(aq[rows], bq), sa8, False, sb8, False, act=O.ACT_SILU_GATE)
     g, u = truth[:, :f], truth[:, f:]
-    judge_vs_truth(y[rows], ref, g / (1.0 + np.exp(-g)) * u, "8B gated fp8")
+    judge_vs_truth(y[rows], ref, g / (1.0 + np.exp(-g)) * u, "8B gated fp8", rel_extra=2e-6)
 
 
 # ---------------------------------------------------------------- FP8 linear through the operator call
