@@ -443,12 +443,18 @@ quant_rows_wide_kernel(const float* __restrict__ x, int n, int8_t* __restrict__ 
 // exchange block.  Rank r owns the token rows [r * rows, (r + 1) * rows): it adds the partials of its rows over
 // all ranks (peer loads, rank order), adds the residual stream (which therefore lives only on the owner), applies
 // RMSNorm and the per-token int8 quantisation, and stores the finished int8 row and its scale into the exchange
-// block of every rank - the A operand of the next GEMM.  Two flag exchanges frame it: "my partial is complete"
-// before the loads and "my rows are delivered" after the stores.  Flags are epoch counters written by the peer
-// into the waiting rank's own memory; every wait is bounded and reports kErrPeerWait.
+// block of every rank - the A operand of the next GEMM.
 //
-// Layout of a rank's exchange block: flags (ready[tp] at +0, done[tp] at +256), then sx, xq and part at the
-// given offsets.  One CTA per owned row.
+// Flags are epoch counters that a rank writes into the other ranks' blocks (layout of a block: ready[tp] at +0,
+// delivered[tp] at +256, then sx, xq and part at the given offsets):
+//   ready[s]      rank s has finished the partial of this epoch           (waited for here, before the loads)
+//   delivered[s]  rank s has stored its finished rows of this epoch here  (waited for by the consumer of xq: the
+//                 next GEMM polls them right before it loads its A operand, so the wait overlaps its weight prefetch)
+// This kernel does not wait for the other ranks' rows.  What keeps a fast rank from overwriting data a slow one
+// still reads: a rank rewrites `part` only after a GEMM that waited for every delivered flag of the previous epoch
+// (a rank delivers after its peer loads), and peers store into xq / sx only after this rank raised its next ready
+// flag, which it does after its own readers of xq / sx have finished.  Every wait is bounded by time and a rank
+// that gives up poisons the flags it owns (see wait_peer_flag).  One CTA per owned row.
 struct TpFinishArgs {
     uint8_t* const* peers;     // [tp] base of every rank's exchange block (this rank's own included)
     size_t o_sx, o_xq, o_part; // byte offsets inside a block
@@ -461,17 +467,8 @@ struct TpFinishArgs {
     uint32_t* epoch;           // this rank's call counter
     unsigned int* arrived;     // CTAs of this launch that have delivered their row
     uint32_t* err;
-    uint32_t spin_limit;       // polls before a wait gives up
+    uint64_t timeout_ns;       // bound of every flag wait
 };
-
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* err, uint32_t spin_limit) {
-    for (uint32_t it = 0; it < spin_limit; ++it) {
-        // epochs only grow; the difference is taken modulo 2^32 so that the comparison survives a wrap
-        if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    }
-    atomicCAS(err, 0u, static_cast<uint32_t>(kErrPeerWait));
-    return false;
-}
 
 template <int VPT>
 __global__ void __launch_bounds__(kWideThreads)
@@ -483,7 +480,6 @@ tp_finish_kernel(TpFinishArgs a) {
     const uint32_t epoch = *a.epoch + 1;
     uint8_t* mine = a.peers[a.rank];
     const uint32_t* ready = reinterpret_cast<const uint32_t*>(mine);
-    const uint32_t* done = reinterpret_cast<const uint32_t*>(mine + 256);
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     // 1. this rank's partial is complete (the GEMM before this kernel has finished): tell every rank
@@ -493,7 +489,7 @@ tp_finish_kernel(TpFinishArgs a) {
     }
     // 2. wait for every rank's partial
     if (threadIdx.x < a.tp) {
-        if (!wait_flag(ready + threadIdx.x, epoch, a.err, a.spin_limit)) s_ok = 0;
+        if (!wait_peer_flag(ready + threadIdx.x, epoch, a.err, a.timeout_ns)) s_ok = 0;
     }
     __syncthreads();
     const bool ok = s_ok != 0;
@@ -517,7 +513,10 @@ tp_finish_kernel(TpFinishArgs a) {
                             x[i] = ld_relaxed_sys_f4(reinterpret_cast<const float*>(a.peers[p0 + i] + a.o_part) + base + 4 * g);
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        if (p0 + i < a.tp) { y.x += x[i].x; y.y += x[i].y; y.z += x[i].z; y.w += x[i].w; }
+                        if (p0 + i < a.tp) {
+                            y.x = __fadd_rn(y.x, x[i].x); y.y = __fadd_rn(y.y, x[i].y);
+                            y.z = __fadd_rn(y.z, x[i].z); y.w = __fadd_rn(y.w, x[i].w);
+                        }
                 }
                 float4 hv = *reinterpret_cast<const float4*>(a.h + base + 4 * g);
                 hv.x = y.x + hv.x; hv.y = y.y + hv.y; hv.z = y.z + hv.z; hv.w = y.w + hv.w;
@@ -569,18 +568,21 @@ tp_finish_kernel(TpFinishArgs a) {
     }
     __threadfence_system();
     __syncthreads();
-    // 4. the last CTA of this launch tells every rank that this rank's rows are delivered, waits for the others'
-    //    rows and advances the call counter
+    // 4. the last CTA of this launch tells every rank that this rank's rows are delivered (or, after a failed wait,
+    //    that they never will be) and advances the call counter
     if (threadIdx.x == 0) {
         const unsigned int seen = atomicAdd(a.arrived, 1u);
         s_last = seen == gridDim.x - 1 ? 1 : 0;
     }
     __syncthreads();
     if (s_last) {
+        // a failure in any CTA of this launch has set the error word by now
+        const bool failed = !ok || *reinterpret_cast<volatile uint32_t*>(a.err) != 0u;
         if (threadIdx.x < a.tp) {
             __threadfence_system();
-            st_release_sys(reinterpret_cast<uint32_t*>(a.peers[threadIdx.x] + 256) + a.rank, epoch);
-            wait_flag(done + threadIdx.x, epoch, a.err, a.spin_limit);
+            uint32_t* peer = reinterpret_cast<uint32_t*>(a.peers[threadIdx.x]);
+            if (failed) st_release_sys(peer + a.rank, kPeerPoison);
+            st_release_sys(peer + 64 + a.rank, failed ? kPeerPoison : epoch);
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -703,11 +705,11 @@ bool tp_finish_supported(int d) {
 
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
-                      cudaStream_t s, uint32_t spin_limit) {
+                      cudaStream_t s, uint64_t timeout_ns) {
     int vpt, threads;
     wide_shape(d, &vpt, &threads);
     TpFinishArgs a{peers, o_sx, o_xq, o_part, tp, rank, rows, d, norm_w, eps, h, epoch, arrived, err,
-                   spin_limit ? spin_limit : kSpinLimit};
+                   timeout_ns ? timeout_ns : kPeerWaitNs};
     if (vpt == 1) return launch_ex(tp_finish_kernel<1>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 2) return launch_ex(tp_finish_kernel<2>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 4) return launch_ex(tp_finish_kernel<4>, dim3(rows), dim3(threads), 0, s, 1, true, a);

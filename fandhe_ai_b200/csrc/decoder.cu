@@ -306,6 +306,7 @@ struct b200_decoder {
     uint8_t** tp_peers_dev = nullptr;           // the same table on the device
     uint32_t* tp_epoch = nullptr;               // [0] call counter, [1] CTA arrival counter of the finish kernel
     bool tp_exchange = false;                   // peers are mapped: use the finish kernel instead of ncclAllReduce
+    uint64_t tp_timeout_ns = 0;                 // bound of every cross-GPU wait (0: the kernels' default of two seconds)
     uint64_t launches_per_step = 0;
 };
 
@@ -516,6 +517,23 @@ int32_t enqueue_step(b200_decoder* d) {
     uint64_t launches = 0;
     GemmEpilogue ep;
     ep.raw = d->raw;
+    // With the exchange blocks mapped, the int8 rows a GEMM reads after a row-parallel output were stored by the other
+    // ranks' finish kernels: such a GEMM waits for their delivered flags (after it has put its weight tiles in flight).
+    const bool exchange = tp && d->tp_exchange && M % c.tp_size == 0;
+    GemmPeerWait delivered;
+    if (exchange) {
+        delivered.flags = reinterpret_cast<const uint32_t*>(d->tp_block) + 64;
+        delivered.n = c.tp_size;
+        delivered.epoch = d->tp_epoch;
+        delivered.timeout_ns = 0;
+    }
+    auto after_exchange = [&](GemmEpilogue e) {
+        if (exchange) {
+            e.wait = delivered;
+            if (e.wait.timeout_ns == 0) e.wait.timeout_ns = d->tp_timeout_ns;
+        }
+        return e;
+    };
     CU_TRY(begin_step(d->seq_lens_dev, d->pos_dev, d->active_dev, M, s));
     ++launches;
     CU_TRY(embed_norm_quant_auto(d->ids_dev, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, d->h,
@@ -549,9 +567,9 @@ int32_t enqueue_step(b200_decoder* d) {
             CU_TRY(dequant_planes(d->raw, p.out_planes, M, dm, d->sx, d->scales + s_off, d->part, s));
             launches += 2;
         }
-        if (d->tp_exchange && M % c.tp_size == 0) {
+        if (exchange) {
             CU_TRY(tp_finish(d->tp_peers_dev, d->tp_o_sx, d->tp_o_xq, d->tp_o_part, c.tp_size, c.tp_rank, M / c.tp_size, dm, norm,
-                             c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s));
+                             c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s, d->tp_timeout_ns));
             ++launches;
             return B200_OK;
         }
@@ -587,10 +605,10 @@ int32_t enqueue_step(b200_decoder* d) {
             qe.rope.q_out = d->q;
             qe.rope.k_pool = static_cast<uint16_t*>(L.k_pool);
             qe.rope.v_pool = static_cast<uint16_t*>(L.v_pool);
-            CU_TRY(gemm_launch(L.p_qkv, qe, err, s));
+            CU_TRY(gemm_launch(L.p_qkv, l > 0 ? after_exchange(qe) : qe, err, s));
             launches -= 1;
         } else {
-            CU_TRY(gemm_launch(L.p_qkv, ep, err, s));
+            CU_TRY(gemm_launch(L.p_qkv, l > 0 ? after_exchange(ep) : ep, err, s));
             CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv,
                                         d->cos_t, d->sin_t, c.max_seq_len, d->pos_dev, d->active_dev, d->tables_dev, d->max_blocks_per_seq,
                                         c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
@@ -609,7 +627,7 @@ int32_t enqueue_step(b200_decoder* d) {
         launches += paged_attention_can_quantize(L.attn) ? 4 : 5;
         if (int32_t st = row_parallel(L.p_o, L.s_o, d->vectors + L.mlp_norm)) return st;
         // gate / up (column-parallel) -> SiLU gate -> quant
-        CU_TRY(gemm_launch(L.p_gu, ep, err, s));
+        CU_TRY(gemm_launch(L.p_gu, after_exchange(ep), err, s));
         CU_TRY(gate_quant_auto(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
         // down (row-parallel) -> residual -> next norm -> quant
         const float* next_norm = d->vectors + (l + 1 < c.n_layers ? d->layers[l + 1].attn_norm : d->final_norm);
@@ -624,7 +642,7 @@ int32_t enqueue_step(b200_decoder* d) {
     lm.b_scale = d->scales + d->s_lm;
     lm.b_per_col = 1;
     lm.out = d->logits;
-    CU_TRY(gemm_launch(d->p_lm, lm, err, s));
+    CU_TRY(gemm_launch(d->p_lm, after_exchange(lm), err, s));
     CU_TRY(argmax_rows_auto(d->logits, M, c.vocab, d->next_ids_dev, s));
     launches += 2;
     d->launches_per_step = launches;
@@ -893,8 +911,9 @@ int32_t b200_decoder_init_tp(b200_decoder* d, const uint8_t* unique_id128) {
 int32_t b200_decoder_tp_exchange(const b200_decoder* d) { return d && d->tp_exchange ? 1 : 0; }
 
 // Failure-detection self-test of the cross-GPU finish kernel on one GPU: launches it as rank 0 of 2 over a scratch
-// exchange block in which nobody ever raises rank 1's flags.  The kernel's bounded waits (2^16 polls here) run
-// out, it records kErrPeerWait in the context's error word, skips its loads and stores, and returns; the next
+// exchange block in which nobody ever raises rank 1's flags.  The kernel's bounded wait (20 ms here) runs out, it
+// records kErrPeerWait in the context's error word, skips its loads and stores, writes the poison value into the
+// flags it owns at its peer (so that the peer would stop with an error of its own) and returns; the next
 // synchronisation reports the failure and poisons the context, and the device stays usable.
 int32_t b200_selftest_peer_wait(b200_ctx* ctx) {
     if (int32_t st = check_ctx(ctx)) return st;
@@ -902,13 +921,16 @@ int32_t b200_selftest_peer_wait(b200_ctx* ctx) {
     const int d = 512, rows = 2, tp = 2;
     const size_t o_sx = 512, o_xq = 1024, o_part = 1024 + 4096;
     const size_t bytes = o_part + size_t(tp) * rows * d * sizeof(float);
-    uint8_t* block = nullptr;
+    uint8_t* block = nullptr;        // rank 0's block
+    uint8_t* peer_block = nullptr;   // "rank 1": a block whose owner never runs
     uint8_t** peers = nullptr;
     float* h = nullptr;
     float* w = nullptr;
     uint32_t* counters = nullptr;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&block), bytes);
     if (e == cudaSuccess) e = cudaMemset(block, 0, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&peer_block), bytes);
+    if (e == cudaSuccess) e = cudaMemset(peer_block, 0, bytes);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&peers), tp * sizeof(uint8_t*));
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h), size_t(tp) * rows * d * sizeof(float));
     if (e == cudaSuccess) e = cudaMemset(h, 0, size_t(tp) * rows * d * sizeof(float));
@@ -916,15 +938,85 @@ int32_t b200_selftest_peer_wait(b200_ctx* ctx) {
     if (e == cudaSuccess) e = cudaMemset(w, 0, d * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(counters, 0, 2 * sizeof(uint32_t));
-    uint8_t* host_peers[2] = {block, block};      // "rank 1" is the same block: its flags are never raised
+    uint8_t* host_peers[2] = {block, peer_block};
     if (e == cudaSuccess) e = cudaMemcpy(peers, host_peers, sizeof(host_peers), cudaMemcpyHostToDevice);
     if (e == cudaSuccess)
         e = tp_finish(peers, o_sx, o_xq, o_part, tp, 0, rows, d, w, 1e-5f, h, counters, counters + 1, ctx->err_dev, ctx->stream,
-                      1u << 16);
+                      20ull * 1000 * 1000);
+    uint32_t peer_flags[128] = {};
+    if (e == cudaSuccess) e = cudaMemcpyAsync(peer_flags, peer_block, sizeof(peer_flags), cudaMemcpyDeviceToHost, ctx->stream);
     int32_t st = B200_OK;
     if (e != cudaSuccess) st = fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("selftest_peer_wait: ") + cudaGetErrorString(e));
     else st = b200_synchronize(ctx);              // reports the device error word
     cudaFree(block);
+    cudaFree(peer_block);
+    cudaFree(peers);
+    cudaFree(h);
+    cudaFree(w);
+    cudaFree(counters);
+    if (st == B200_KERNEL_LAUNCH_FAILED && (peer_flags[0] != 0xFFFFFFFFu || peer_flags[64] != 0xFFFFFFFFu))
+        return fail(B200_INVALID_ARGUMENT, "selftest_peer_wait: the wait ran out but the peer's flags were not poisoned");
+    return st;
+}
+
+// Numerical self-test of the finish kernel on one GPU, with nothing to wait for: `tp` exchange blocks live on this
+// device, every rank's partial [tp * rows, d] is uploaded into its block and all ready flags are raised by the host
+// beforehand; the kernel then runs as rank `rank`.  Returns, for the rows that rank owns, the updated residual rows,
+// the int8 rows and scales as delivered into EVERY block ([tp][rows][d] and [tp][rows]), and the flags words of every
+// block ([tp][128]) so that the caller can check the delivered epoch.
+int32_t b200_selftest_tp_finish(b200_ctx* ctx, int32_t tp, int32_t rank, int32_t rows, int32_t d, const float* partials,
+                                const float* residual, const float* norm_w, float eps, float* h_out, int8_t* xq_out,
+                                float* sx_out, uint32_t* flags_out) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (tp < 1 || tp > 16 || rank < 0 || rank >= tp || rows <= 0 || d <= 0 || !partials || !residual || !norm_w || !h_out ||
+        !xq_out || !sx_out || !flags_out)
+        return fail(B200_INVALID_ARGUMENT, "selftest_tp_finish: bad argument");
+    if (!tp_finish_supported(d)) return fail(B200_UNSUPPORTED, "selftest_tp_finish: row width not supported by the finish kernel");
+    if (int32_t st = set_device(ctx)) return st;
+    const size_t M = size_t(tp) * rows;
+    const size_t o_sx = 512;
+    const size_t o_xq = o_sx + (M * 4 + 255) / 256 * 256;
+    const size_t o_part = o_xq + (M * d + 255) / 256 * 256;
+    const size_t bytes = o_part + M * d * sizeof(float);
+    std::vector<uint8_t*> blocks(tp, nullptr);
+    uint8_t** peers = nullptr;
+    float* h = nullptr;
+    float* w = nullptr;
+    uint32_t* counters = nullptr;
+    cudaStream_t s = ctx->stream;
+    cudaError_t e = cudaSuccess;
+    std::vector<uint32_t> ready(128, 0u);
+    for (int p = 0; p < tp; ++p) ready[p] = 1u;          // epoch 1: every partial is complete
+    for (int p = 0; p < tp && e == cudaSuccess; ++p) {
+        e = cudaMalloc(reinterpret_cast<void**>(&blocks[p]), bytes);
+        if (e == cudaSuccess) e = cudaMemsetAsync(blocks[p], 0, bytes, s);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(blocks[p], ready.data(), 512, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(blocks[p] + o_part, partials + size_t(p) * M * d, M * d * sizeof(float), cudaMemcpyHostToDevice, s);
+    }
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&peers), tp * sizeof(uint8_t*));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(peers, blocks.data(), tp * sizeof(uint8_t*), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&h), M * d * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h, residual, M * d * sizeof(float), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&w), d * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w, norm_w, d * sizeof(float), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&counters), 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemsetAsync(counters, 0, 2 * sizeof(uint32_t), s);
+    if (e == cudaSuccess)
+        e = tp_finish(peers, o_sx, o_xq, o_part, tp, rank, rows, d, w, eps, h, counters, counters + 1, ctx->err_dev, s,
+                      50ull * 1000 * 1000);
+    const size_t row0 = size_t(rank) * rows;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, h + row0 * d, size_t(rows) * d * sizeof(float), cudaMemcpyDeviceToHost, s);
+    for (int p = 0; p < tp && e == cudaSuccess; ++p) {
+        e = cudaMemcpyAsync(xq_out + size_t(p) * rows * d, blocks[p] + o_xq + row0 * d, size_t(rows) * d, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(sx_out + size_t(p) * rows, blocks[p] + o_sx + row0 * 4, size_t(rows) * 4, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(flags_out + size_t(p) * 128, blocks[p], 512, cudaMemcpyDeviceToHost, s);
+    }
+    int32_t st = B200_OK;
+    if (e != cudaSuccess) st = fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("selftest_tp_finish: ") + cudaGetErrorString(e));
+    else st = b200_synchronize(ctx);
+    for (uint8_t* b : blocks) cudaFree(b);
     cudaFree(peers);
     cudaFree(h);
     cudaFree(w);
@@ -1016,6 +1108,17 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     CU_TRY(cudaMalloc(&d->attn_scratch, attn_need > 0 ? attn_need : 16));
     d->planned = true;
     d->steps = 0;
+    if (c.tp_size > 1 && d->comm) {
+        // every rank has loaded its weights and uploaded its tables before any rank's first step starts to wait for
+        // the others inside a kernel (host skew of seconds between the ranks must not look like a dead peer)
+        int* flag = nullptr;
+        CU_TRY(dmalloc(&flag, 1));
+        cudaError_t e = cudaMemsetAsync(flag, 0, sizeof(int), s);
+        int rc = e == cudaSuccess ? nccl().AllReduce(flag, flag, 1, kNcclInt32, kNcclSum, d->comm, s) : 1;
+        if (rc == 0) e = cudaStreamSynchronize(s);
+        cudaFree(flag);
+        if (rc != 0 || e != cudaSuccess) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, "decoder_begin: barrier across the ranks failed");
+    }
     return B200_OK;
 }
 

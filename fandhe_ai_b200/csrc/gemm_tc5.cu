@@ -138,7 +138,28 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const int num_kb = kb_end > kb_begin ? kb_end - kb_begin : 0;
 
     if (warp == 0) {
-        if (elect_one()) {
+        const bool leader = elect_one();
+        if (p.ep.wait.flags != nullptr) {
+            // The A operand comes from other GPUs: the leader puts the weight tiles of the first ring pass in flight,
+            // then the lanes wait for the peers' flags (one flag per lane) and only then the A tiles are loaded.
+            if (leader) {
+                const int pre = num_kb < p.stages ? num_kb : p.stages;
+                for (int i = 0; i < pre; ++i) {
+                    mbar_arrive_expect_tx(full_bar(i), kStageBytes);
+                    const uint32_t b_dst = smem_base + i * kStageBytes + kABytes;
+                    const int kx = (kb_begin + i) * kBK;
+                    tma_load_2d(b_dst, &tma_b, full_bar(i), kx, n0);
+                    if (p.gate) tma_load_2d(b_dst + (BN / 2) * kBK, &tma_b, full_bar(i), kx, p.n_half + n0);
+                }
+            }
+            __syncwarp();
+            pdl_wait();
+            if (lane < p.ep.wait.n) wait_peer_flag(p.ep.wait.flags + lane, *p.ep.wait.epoch, p.err, p.ep.wait.timeout_ns);
+            __syncwarp();
+        }
+        if (leader) {
+            const bool b_in_flight = p.ep.wait.flags != nullptr;
+            if (b_in_flight) fence_proxy_async_all();
             auto load_b = [&](int i, int s) {
                 const uint32_t b_dst = smem_base + s * kStageBytes + kABytes;
                 const int kx = (kb_begin + i) * kBK;
@@ -151,11 +172,13 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             // The B operand (weights) does not depend on the kernel that runs before this one: fill the first
             // pass over the ring with B tiles while that kernel still drains, then wait for it and add the A tiles.
             const int pre = num_kb < p.stages ? num_kb : p.stages;
-            for (int i = 0; i < pre; ++i) {
-                mbar_arrive_expect_tx(full_bar(i), kStageBytes);
-                load_b(i, i);
+            if (!b_in_flight) {
+                for (int i = 0; i < pre; ++i) {
+                    mbar_arrive_expect_tx(full_bar(i), kStageBytes);
+                    load_b(i, i);
+                }
+                pdl_wait();
             }
-            pdl_wait();
             pdl_launch_dependents();
             for (int i = 0; i < pre; ++i) load_a(i, i);
             for (int i = pre; i < num_kb; ++i) {

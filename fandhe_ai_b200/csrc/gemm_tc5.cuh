@@ -35,6 +35,16 @@ struct GemmRope {
     uint16_t* v_pool = nullptr;
 };
 
+// Optional wait of a GEMM whose A operand (and per-row scales) are delivered by other GPUs: right before the first
+// A tile is loaded, the producer warp waits until each of the `n` flags (epoch counters in this GPU's memory, raised
+// by the peers) has reached *epoch.  The weight tiles of the first ring pass are already in flight by then.
+struct GemmPeerWait {
+    const uint32_t* flags = nullptr;   // [n]; null: no wait
+    int n = 0;
+    const uint32_t* epoch = nullptr;   // device word holding the epoch to wait for
+    uint64_t timeout_ns = 0;
+};
+
 struct GemmEpilogue {
     int fused = 0;                 // 0: write raw accumulators to `raw`; 1: fused epilogue to `out`
     void* raw = nullptr;           // [splits][M][N] int32 (i8) or f32 (fp8)
@@ -48,6 +58,7 @@ struct GemmEpilogue {
     int out_bf16 = 0;
     int act = kActNone;              // kActSiluGate: B rows [0, N/2) are gate, [N/2, N) are up, N_out = N/2
     GemmRope rope;                   // see GemmRope; needs fused = 1 with per-row / per-column scales, no bias
+    GemmPeerWait wait;               // see GemmPeerWait
 };
 
 struct GemmPlan {

@@ -126,7 +126,31 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     const int out_cols = p.gate ? BN / 2 : BN;
 
     if (warp == 0) {
-        if (elect_one()) {
+        const bool leader = elect_one();
+        bool b_in_flight = false;
+        if (p.ep.wait.flags != nullptr && cta < tiles) {
+            // The A operand comes from other GPUs: weight tiles of the first ring pass first, then the lanes wait for
+            // the peers' flags (one flag per lane), then the A tiles (see GemmPeerWait).
+            if (leader) {
+                int m_idx, n_idx;
+                tile_origin(p, cta, m_idx, n_idx);
+                const int n0 = n_idx * out_cols;
+                const int pre = p.kb_total < p.stages ? p.kb_total : p.stages;
+                for (int k = 0; k < pre; ++k) {
+                    mbar_arrive_expect_tx(full_bar(k), kStageBytes);
+                    const uint32_t b_dst = smem_base + k * kStageBytes + kABytes;
+                    tma_load_2d(b_dst, &tma_b, full_bar(k), k * kBK, n0);
+                    if (p.gate) tma_load_2d(b_dst + (BN / 2) * kBK, &tma_b, full_bar(k), k * kBK, p.n_half + n0);
+                }
+            }
+            __syncwarp();
+            pdl_wait();
+            if (lane < p.ep.wait.n) wait_peer_flag(p.ep.wait.flags + lane, *p.ep.wait.epoch, p.err, p.ep.wait.timeout_ns);
+            __syncwarp();
+            b_in_flight = true;
+        }
+        if (leader) {
+            if (b_in_flight) fence_proxy_async_all();
             int i = 0;                 // K blocks issued so far: ring position and phase
             bool waited = false;       // griddepcontrol.wait done
             bool ok = true;
@@ -145,11 +169,13 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                     // The B operand (weights) does not depend on the kernel before this one: fill the ring with B
                     // tiles while that kernel drains, then wait for it and add the A tiles.
                     const int pre = p.kb_total < p.stages ? p.kb_total : p.stages;
-                    for (int k = 0; k < pre; ++k) {
-                        mbar_arrive_expect_tx(full_bar(k), kStageBytes);
-                        load_b(k, k);
+                    if (!b_in_flight) {
+                        for (int k = 0; k < pre; ++k) {
+                            mbar_arrive_expect_tx(full_bar(k), kStageBytes);
+                            load_b(k, k);
+                        }
+                        pdl_wait();
                     }
-                    pdl_wait();
                     pdl_launch_dependents();
                     waited = true;
                     for (int k = 0; k < pre; ++k) load_a(k, k);

@@ -93,10 +93,12 @@ cudaError_t slice_cols_i8(const int8_t* src, int64_t rows, int64_t ld, int64_t c
 // Tensor-parallel finish of a row-parallel GEMM over the ranks' exchange blocks (decode_rows.cu): sums the f32
 // partials of the rows this rank owns over all ranks, adds the residual, applies RMSNorm and the per-token int8
 // quantisation and delivers the int8 rows and scales to every rank.  `peers` is a device array of the tp block
-// bases; a block starts with 512 bytes of flags.  Needs one GPU per rank (the ranks wait for each other).
+// bases; a block starts with 512 bytes of flags (ready[tp] at +0, delivered[tp] at +256).  The kernel waits for the
+// peers' partials but not for their rows: the consumer of the delivered rows waits for the delivered flags.
+// Needs one GPU per rank unless the flags are raised beforehand.
 bool tp_finish_supported(int d);
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
-                      cudaStream_t s, uint32_t spin_limit = 0);   // 0: the default bound of every device-side wait
+                      cudaStream_t s, uint64_t timeout_ns = 0);   // 0: the default bound of a cross-GPU wait
 
 }  // namespace b200

@@ -26,6 +26,7 @@ enum DeviceErr : uint32_t {
     kErrAppendSlot = 0x203,     // append met a slot >= pool rows
     kErrAttnSeqLen = 0x204,     // attention met a sequence length beyond the table width or the planned maximum
     kErrPeerWait = 0x301,       // cross-GPU flag wait ran out
+    kErrPeerFailed = 0x302,     // a peer GPU reported that its own wait ran out (poisoned flag)
     kErrTokenId = 0x401,        // embedding gather met an id outside the vocabulary
 };
 
@@ -61,6 +62,11 @@ __device__ __forceinline__ void fence_barrier_init() {
 }
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Orders earlier generic-proxy accesses (here: the acquire of a flag another GPU raised) before later
+// asynchronous-proxy accesses (TMA loads of the rows that flag announces), for global memory too.
+__device__ __forceinline__ void fence_proxy_async_all() {
+    asm volatile("fence.proxy.async;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
@@ -256,6 +262,34 @@ __device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* addr) {
     asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(addr) : "memory");
     return v;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Flags that one GPU raises in another GPU's memory are epoch counters: the waiting side polls its own memory
+// until the flag has reached `epoch` (difference taken modulo 2^32).  Every such wait is bounded by time; a
+// rank that gives up writes kPeerPoison into the flags it owns at its peers, so that they stop at once with
+// an error of their own instead of consuming rows that were never delivered.
+constexpr uint32_t kPeerPoison = 0xFFFFFFFFu;
+constexpr uint64_t kPeerWaitNs = 2000000000ull;      // default bound of a cross-GPU wait: two seconds
+
+__device__ __forceinline__ bool wait_peer_flag(const uint32_t* flag, uint32_t epoch, uint32_t* err, uint64_t timeout_ns) {
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 0;; ++it) {
+        const uint32_t v = ld_acquire_sys(flag);
+        if (v == kPeerPoison) {
+            atomicCAS(err, 0u, static_cast<uint32_t>(kErrPeerFailed));
+            return false;
+        }
+        if (static_cast<int32_t>(v - epoch) >= 0) return true;
+        if ((it & 63u) == 63u && global_timer_ns() - t0 > timeout_ns) break;
+    }
+    atomicCAS(err, 0u, static_cast<uint32_t>(kErrPeerWait));
+    return false;
 }
 
 // Symmetric int8 quantisation of one value: round-to-nearest-even of x / scale, clamped to [-127, 127];

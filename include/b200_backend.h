@@ -352,15 +352,25 @@ int32_t b200_decoder_init_random(b200_decoder* dec, uint64_t seed, float std);
 int32_t b200_nccl_unique_id(uint8_t* out128);
 int32_t b200_decoder_init_tp(b200_decoder* dec, const uint8_t* unique_id128);
 /* 1 when init_tp mapped the other ranks' exchange blocks (CUDA IPC), so that the row-parallel outputs are
- * finished by one kernel that reads the peers' partial sums and delivers the quantised rows to every rank;
+ * finished by one kernel that reads the peers' partial sums and delivers the quantised rows to every rank (the
+ * GEMM that consumes those rows waits for the peers' delivered flags right before it loads its A operand);
  * 0 when the step uses ncclAllReduce instead (mapping failed, batch not divisible by the rank count, or
  * B200_TP_EXCHANGE=0 in the environment).  No reference counterpart (the reference has no tensor parallelism). */
 int32_t b200_decoder_tp_exchange(const b200_decoder* dec);
 /* Failure-detection self-test on one GPU: runs the cross-GPU finish kernel as rank 0 of 2 with a peer whose flags
- * are never raised.  Its bounded waits run out, the kernel records the peer-wait code in the context's error word
- * and returns; this call then returns KernelLaunchFailed and the context is poisoned (re-create it).  The device
- * stays usable.  No reference counterpart. */
+ * are never raised.  Its time-bounded wait (20 ms here, two seconds in a real run) runs out, the kernel records the
+ * peer-wait code in the context's error word, poisons the flags it owns at the peer and returns; this call then
+ * returns KernelLaunchFailed and the context is poisoned (recover or re-create it).  The device stays usable.
+ * No reference counterpart. */
 int32_t b200_selftest_peer_wait(b200_ctx* ctx);
+/* Numerical self-test of the finish kernel on one GPU with nothing to wait for: `tp` exchange blocks on this device,
+ * partials[tp][tp * rows][d] uploaded and every ready flag raised beforehand, the kernel run as rank `rank` with the
+ * residual rows residual[tp * rows][d].  Outputs for the rows that rank owns: h_out[rows][d] (updated residual),
+ * xq_out[tp][rows][d] and sx_out[tp][rows] (the int8 rows and scales found in EVERY block afterwards),
+ * flags_out[tp][128] (each block's flag words: ready at 0.., delivered at 64..).  No reference counterpart. */
+int32_t b200_selftest_tp_finish(b200_ctx* ctx, int32_t tp, int32_t rank, int32_t rows, int32_t d, const float* partials,
+                                const float* residual, const float* norm_w, float eps, float* h_out, int8_t* xq_out,
+                                float* sx_out, uint32_t* flags_out);
 /* Starts a generation of `batch` rows: row b starts at start_lens[b] cached tokens (NULL: 0) and may grow
  * to max_total_lens[b]; blocks for the final length are reserved now and the tables uploaded once. */
 int32_t b200_decoder_begin(b200_decoder* dec, int32_t batch, const int32_t* start_lens, const int32_t* max_total_lens);

@@ -4,6 +4,7 @@ import subprocess
 import sys
 from pathlib import Path
 
+import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
@@ -49,3 +50,48 @@ def test_peer_wait_runs_out_with_an_error_status_and_the_device_stays_usable(fre
         assert q.numpy()[1, 31] == 127 and not other.poisoned
     finally:
         other.close()
+
+
+@pytest.mark.parametrize("tp,d", [(2, 512), (4, 4096), (8, 4096), (8, 768)])
+def test_finish_kernel_numerics_on_one_gpu(be, tp, d):
+    """The cross-GPU finish kernel with nothing to wait for: `tp` exchange blocks on one device, every ready flag
+    raised beforehand.  Run as each rank in turn, its rows must equal the CPU restatement bit for bit (partials
+    added in rank order, residual, RMSNorm in kernel order, per-token int8) in EVERY rank's block, and its
+    delivered flag must carry the epoch everywhere."""
+    import ctypes as C
+
+    from fandhe_ai_b200._lib import check, lib
+    from oracle import oracle as O
+    from oracle.decoder_ref import wide_shape
+
+    rows = 3
+    m = tp * rows
+    rng = np.random.default_rng(tp * 1000 + d)
+    partials = (rng.standard_normal((tp, m, d)) * 0.3).astype(np.float32)
+    residual = rng.standard_normal((m, d)).astype(np.float32)
+    norm_w = rng.uniform(0.5, 1.5, d).astype(np.float32)
+    total = np.zeros((m, d), np.float32)
+    for p in range(tp):
+        total = (total + partials[p]).astype(np.float32)           # rank order
+    h_want = (total + residual).astype(np.float32)
+    vpt, threads = wide_shape(d)
+    xn = O.rmsnorm_kernel_order(h_want, norm_w, 1e-5, 0, threads, vpt)
+    q_want, s_want = O.quantize_i8_per_row(xn)
+    for rank in range(tp):
+        h_out = np.empty((rows, d), np.float32)
+        xq_out = np.empty((tp, rows, d), np.int8)
+        sx_out = np.empty((tp, rows), np.float32)
+        flags = np.empty((tp, 128), np.uint32)
+        check(lib().b200_selftest_tp_finish(be._ctx, tp, rank, rows, d, partials.ctypes.data_as(C.c_void_p),
+                                            residual.ctypes.data_as(C.c_void_p), norm_w.ctypes.data_as(C.c_void_p),
+                                            C.c_float(1e-5), h_out.ctypes.data_as(C.c_void_p),
+                                            xq_out.ctypes.data_as(C.c_void_p), sx_out.ctypes.data_as(C.c_void_p),
+                                            flags.ctypes.data_as(C.c_void_p)))
+        own = slice(rank * rows, (rank + 1) * rows)
+        assert np.array_equal(h_out, h_want[own]), rank
+        for p in range(tp):
+            assert np.array_equal(xq_out[p], q_want[own]), (rank, p)
+            assert np.array_equal(sx_out[p], s_want[own]), (rank, p)
+            assert flags[p, 64 + rank] == 1, (rank, p, flags[p, 64:64 + tp])     # delivered, epoch 1
+            assert flags[p, rank] == 1                                           # ready, raised again by the kernel
+    assert not be.poisoned
