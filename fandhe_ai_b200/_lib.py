@@ -164,6 +164,10 @@ SIGNATURES = {
     "b200_timer_start": (_I32, [_P]),
     "b200_timer_stop": (_I32, [_P, C.POINTER(C.c_float)]),
     "b200_decoder_time_attention": (_I32, [_P, _I32, C.POINTER(C.c_float), C.POINTER(_U64)]),
+    "b200_quantize_i8_block": (_I32, [_P, _P, _SZ, _I64, _I64, _I64, _I32, _P, _SZ, _P, _SZ]),
+    "b200_dequantize_i8_block": (_I32, [_P, _P, _SZ, _P, _SZ, _I64, _I64, _I64, _I32, _P, _SZ]),
+    "b200_gemm_i8_block_scaled": (_I32, [_P, _P, _SZ, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I64, _I64, _I64, _P, _SZ]),
+    "b200_quant_check": (_I32, [_P]),
     "b200_linear_fp8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _I32, _P, _SZ]),
     "b200_linear_w8a8": (_I32, [_P, _P, _SZ, _I64, _I64, _P, _SZ, _P, _SZ, _P, _SZ, _I64, _I32, _P, _SZ, _P, _SZ]),
 }

@@ -168,6 +168,36 @@ class Backend:
             residual.handle if residual else None, 0, m, n, k, out_dtype, out.handle, 0))
         return out
 
+    # ------------------------------------------------------------- QuantOps, block-scale contract
+    def quantize_i8_block(self, x: DeviceBuffer, rows: int, cols: int, scales_block_major: bool = False, block_len: int = 128):
+        """One power-of-two scale per 128 values of a row (the reference's proposed contract).  Returns
+        (q int8 [rows, cols], delta f32 [rows, nb] or [nb, rows])."""
+        nb = -(-cols // 128)
+        q = self.alloc_zeroed((rows, cols), np.int8)
+        d = self.alloc_zeroed((nb, rows) if scales_block_major else (rows, nb), np.float32)
+        check(lib().b200_quantize_i8_block(self._ctx, x.handle, 0, rows, cols, block_len, int(scales_block_major), q.handle, 0,
+                                           d.handle, 0))
+        return q, d
+
+    def dequantize_i8_block(self, q: DeviceBuffer, delta: DeviceBuffer, rows: int, cols: int,
+                            scales_block_major: bool = False, block_len: int = 128) -> DeviceBuffer:
+        x = self.alloc_zeroed((rows, cols), np.float32)
+        check(lib().b200_dequantize_i8_block(self._ctx, q.handle, 0, delta.handle, 0, rows, cols, block_len,
+                                             int(scales_block_major), x.handle, 0))
+        return x
+
+    def gemm_i8_block_scaled(self, a: DeviceBuffer, a_delta: DeviceBuffer, w: DeviceBuffer, w_delta: DeviceBuffer, m: int,
+                             n: int, k: int, block_len: int = 128) -> DeviceBuffer:
+        """`gemm_i8_s32_scaled` of the proposed QuantOps: a_delta [m, nb], w_delta [nb, n]; f32 [m, n]."""
+        out = self.alloc_zeroed((m, n), np.float32)
+        check(lib().b200_gemm_i8_block_scaled(self._ctx, a.handle, 0, a_delta.handle, 0, w.handle, 0, w_delta.handle, 0, m, n, k,
+                                              block_len, out.handle, 0))
+        return out
+
+    def quant_check(self) -> None:
+        """Synchronises; raises InvalidArgument when a block-scale call met a non-finite input or result."""
+        check(lib().b200_quant_check(self._ctx))
+
     # ------------------------------------------------------------- BackendOps (quantized linear)
     def linear_forward_device_into(self, a: DeviceBuffer, m: int, k: int, w_q: DeviceBuffer, w_off: int,
                                    w_scale: DeviceBuffer, w_scale_off: int, bias: Optional[DeviceBuffer],

@@ -224,6 +224,7 @@ int32_t b200_ctx_create(int32_t ordinal, b200_ctx** out) {
     }
     ctx->amax_scratch = ctx->err_dev + 1;
     ctx->attn_counter = ctx->err_dev + 2;
+    ctx->quant_status = ctx->err_dev + 3;
     *ctx->err_host = 0;
     *out = ctx;
     return B200_OK;
@@ -688,6 +689,114 @@ int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int3
     }
     const int v[6] = {plan.bn, plan.splits, plan.cluster, plan.persist, plan.persist ? plan.grid : 0, plan.stages};
     for (int i = 0; i < 6; ++i) out6[i] = v[i];
+    return B200_OK;
+}
+
+/* ------------------------------------------------------------------ block-scale contract (QuantOps of the reference) */
+
+static constexpr int64_t kBlockLen = 128;
+static constexpr int64_t kKSafe = 133144;      // floor(i32::MAX / 127^2): longest chain of same-sign products that cannot wrap
+
+int32_t b200_quantize_i8_block(b200_ctx* ctx, const b200_buf* x, size_t x_off, int64_t rows, int64_t cols, int64_t block_len,
+                               int32_t scales_block_major, b200_buf* q, size_t q_off, b200_buf* delta, size_t delta_off) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (block_len <= 0) return fail(B200_INVALID_ARGUMENT, "quantize_i8_block: block length must be positive");
+    if (block_len > kKSafe)
+        return fail(B200_INVALID_ARGUMENT, "quantize_i8_block: block length " + std::to_string(block_len) +
+                                               " exceeds K_safe = 133144 (an s32 accumulator over one block could wrap)");
+    if (block_len != kBlockLen) return fail(B200_UNSUPPORTED, "quantize_i8_block: only blocks of 128 values are implemented");
+    size_t xb, qb, db;
+    const int64_t nb = cols > 0 ? (cols + kBlockLen - 1) / kBlockLen : 0;
+    if (!mul_size(rows, cols, 4, &xb) || !mul_size(rows, cols, 1, &qb) || !mul_size(rows, nb, 4, &db))
+        return fail(B200_INVALID_ARGUMENT, "quantize_i8_block: rows/cols negative or overflowing");
+    if (int32_t st = check_buf(ctx, x, x_off, xb, "quantize_i8_block x")) return st;
+    if (int32_t st = check_buf(ctx, q, q_off, qb, "quantize_i8_block q")) return st;
+    if (int32_t st = check_buf(ctx, delta, delta_off, db, "quantize_i8_block delta")) return st;
+    if ((x_off & 3) || (delta_off & 3)) return fail(B200_INVALID_ARGUMENT, "quantize_i8_block: misaligned offset");
+    if (rows == 0 || cols == 0) return B200_OK;
+    if (int32_t st = set_device(ctx)) return st;
+    cudaError_t e = quantize_i8_block_pow2(buf_ptr<const float>(x, x_off), rows, cols, buf_ptr<int8_t>(q, q_off),
+                                           buf_ptr<float>(delta, delta_off), scales_block_major ? 1 : 0, ctx->quant_status, ctx->stream);
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("quantize_i8_block: ") + cudaGetErrorString(e));
+    return B200_OK;
+}
+
+int32_t b200_dequantize_i8_block(b200_ctx* ctx, const b200_buf* q, size_t q_off, const b200_buf* delta, size_t delta_off,
+                                 int64_t rows, int64_t cols, int64_t block_len, int32_t scales_block_major, b200_buf* x,
+                                 size_t x_off) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (block_len != kBlockLen) return fail(B200_UNSUPPORTED, "dequantize_i8_block: only blocks of 128 values are implemented");
+    size_t xb, qb, db;
+    const int64_t nb = cols > 0 ? (cols + kBlockLen - 1) / kBlockLen : 0;
+    if (!mul_size(rows, cols, 4, &xb) || !mul_size(rows, cols, 1, &qb) || !mul_size(rows, nb, 4, &db))
+        return fail(B200_INVALID_ARGUMENT, "dequantize_i8_block: rows/cols negative or overflowing");
+    if (int32_t st = check_buf(ctx, q, q_off, qb, "dequantize_i8_block q")) return st;
+    if (int32_t st = check_buf(ctx, delta, delta_off, db, "dequantize_i8_block delta")) return st;
+    if (int32_t st = check_buf(ctx, x, x_off, xb, "dequantize_i8_block x")) return st;
+    if ((x_off & 3) || (delta_off & 3)) return fail(B200_INVALID_ARGUMENT, "dequantize_i8_block: misaligned offset");
+    if (rows == 0 || cols == 0) return B200_OK;
+    if (int32_t st = set_device(ctx)) return st;
+    cudaError_t e = dequantize_i8_block(buf_ptr<const int8_t>(q, q_off), buf_ptr<const float>(delta, delta_off), rows, cols,
+                                        scales_block_major ? 1 : 0, buf_ptr<float>(x, x_off), ctx->stream);
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("dequantize_i8_block: ") + cudaGetErrorString(e));
+    return B200_OK;
+}
+
+int32_t b200_gemm_i8_block_scaled(b200_ctx* ctx, const b200_buf* a, size_t a_off, const b200_buf* a_delta, size_t a_delta_off,
+                                  const b200_buf* w, size_t w_off, const b200_buf* w_delta, size_t w_delta_off, int64_t m,
+                                  int64_t n, int64_t k, int64_t block_len, b200_buf* out, size_t out_off) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (block_len <= 0) return fail(B200_INVALID_ARGUMENT, "gemm_i8_block_scaled: block length must be positive");
+    if (block_len > kKSafe)
+        return fail(B200_INVALID_ARGUMENT, "gemm_i8_block_scaled: block length " + std::to_string(block_len) +
+                                               " exceeds K_safe = 133144 (the s32 accumulator of one block could wrap)");
+    if (block_len != kBlockLen) return fail(B200_UNSUPPORTED, "gemm_i8_block_scaled: only blocks of 128 values are implemented");
+    if (int32_t st = check_gemm_dims("gemm_i8_block_scaled", m, n, k)) return st;
+    const int64_t nb = k > 0 ? (k + kBlockLen - 1) / kBlockLen : 0;
+    size_t ab, wb, cb, adb, wdb;
+    if (!mul_size(m, k, 1, &ab) || !mul_size(n, k, 1, &wb) || !mul_size(m, n, 4, &cb) || !mul_size(m, nb, 4, &adb) ||
+        !mul_size(n, nb, 4, &wdb))
+        return fail(B200_INVALID_ARGUMENT, "gemm_i8_block_scaled: size overflow");
+    if (int32_t st = check_buf(ctx, a, a_off, ab, "gemm_i8_block_scaled a")) return st;
+    if (int32_t st = check_buf(ctx, a_delta, a_delta_off, adb, "gemm_i8_block_scaled a_delta")) return st;
+    if (int32_t st = check_buf(ctx, w, w_off, wb, "gemm_i8_block_scaled w")) return st;
+    if (int32_t st = check_buf(ctx, w_delta, w_delta_off, wdb, "gemm_i8_block_scaled w_delta")) return st;
+    if (int32_t st = check_buf(ctx, out, out_off, cb, "gemm_i8_block_scaled out")) return st;
+    if ((a_off & 15) || (w_off & 15) || (out_off & 15) || (a_delta_off & 3) || (w_delta_off & 3))
+        return fail(B200_INVALID_ARGUMENT, "gemm_i8_block_scaled: misaligned offset (operands/out 16 bytes, scales 4 bytes)");
+    if (m == 0 || n == 0) return B200_OK;
+    if (int32_t st = set_device(ctx)) return st;
+    if (k == 0) {
+        cudaError_t e = cudaMemsetAsync(buf_ptr<uint8_t>(out, out_off), 0, cb, ctx->stream);
+        if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, cudaGetErrorString(e));
+        return B200_OK;
+    }
+    const char* why = "";
+    cudaError_t e = gemm_i8_block_scaled(buf_ptr<const void>(a, a_off), buf_ptr<const float>(a_delta, a_delta_off),
+                                         buf_ptr<const void>(w, w_off), buf_ptr<const float>(w_delta, w_delta_off), int(m), int(n),
+                                         int(k), buf_ptr<float>(out, out_off), ctx->quant_status, ctx->err_dev, ctx->stream, &why);
+    if (e == cudaErrorInvalidValue && why[0]) return fail(B200_INVALID_ARGUMENT, why);
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("gemm_i8_block_scaled: ") + cudaGetErrorString(e));
+    return B200_OK;
+}
+
+// Waits for the stream and reports (and clears) what the block-scale kernels flagged since the last check.  A flagged
+// request was outside the contract, not a device failure: nothing is poisoned.
+int32_t b200_quant_check(b200_ctx* ctx) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (int32_t st = set_device(ctx)) return st;
+    uint32_t word = 0;
+    cudaError_t e = cudaMemcpyAsync(ctx->err_host, ctx->quant_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) {
+        word = *ctx->err_host;
+        *ctx->err_host = 0;
+        e = cudaMemsetAsync(ctx->quant_status, 0, sizeof(uint32_t), ctx->stream);
+    }
+    if (e != cudaSuccess) return fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("quant_check: ") + cudaGetErrorString(e));
+    if (int32_t st = check_error_word(ctx, "quant_check")) return st;
+    if (word & 1u) return fail(B200_INVALID_ARGUMENT, "quant_check: an input of the block quantiser was not finite (NaN or infinity); its block was zeroed");
+    if (word & 2u) return fail(B200_INVALID_ARGUMENT, "quant_check: a result of the block-scaled GEMM overflowed f32 when the f64 sum over the blocks was narrowed");
     return B200_OK;
 }
 

@@ -15,6 +15,7 @@ struct b200_ctx {
     uint32_t* err_dev = nullptr;        // device error word written by kernels (0 = none)
     uint32_t* amax_scratch = nullptr;   // one word for tensor-wide amax
     unsigned int* attn_counter = nullptr;  // work counter of the persistent attention kernel (zero between launches)
+    uint32_t* quant_status = nullptr;   // block-scale contract: bit 0 non-finite input met, bit 1 non-finite result
     uint32_t* err_host = nullptr;       // pinned mirror used when checking the word
     uint64_t generation = 0;
     bool poisoned = false;

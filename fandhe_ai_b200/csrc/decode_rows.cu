@@ -475,17 +475,21 @@ __global__ void __launch_bounds__(kWideThreads)
 tp_finish_kernel(TpFinishArgs a) {
     __shared__ WideShared sh;
     __shared__ int s_ok, s_last;
+    __shared__ uint8_t* s_peer[16];
+    // the table of block bases is read once, before anything waits: a pointer fetched from memory between two
+    // remote loads would put one memory round trip in front of each of them
+    if (threadIdx.x < a.tp) s_peer[threadIdx.x] = a.peers[threadIdx.x];
+    if (threadIdx.x == 0) s_ok = 1;
     pdl_wait();
     pdl_launch_dependents();
     const uint32_t epoch = *a.epoch + 1;
-    uint8_t* mine = a.peers[a.rank];
-    const uint32_t* ready = reinterpret_cast<const uint32_t*>(mine);
-    if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
+    uint8_t* mine = s_peer[a.rank];
+    const uint32_t* ready = reinterpret_cast<const uint32_t*>(mine);
     // 1. this rank's partial is complete (the GEMM before this kernel has finished): tell every rank
     if (blockIdx.x == 0 && threadIdx.x < a.tp) {
         __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t*>(a.peers[threadIdx.x]) + a.rank, epoch);
+        st_release_sys(reinterpret_cast<uint32_t*>(s_peer[threadIdx.x]) + a.rank, epoch);
     }
     // 2. wait for every rank's partial
     if (threadIdx.x < a.tp) {
@@ -507,10 +511,13 @@ tp_finish_kernel(TpFinishArgs a) {
                 // trip instead of one per rank); the additions stay in rank order
                 for (int p0 = 0; p0 < a.tp; p0 += 8) {
                     float4 x[8];
+                    const float* src[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        if (p0 + i < a.tp)
-                            x[i] = ld_relaxed_sys_f4(reinterpret_cast<const float*>(a.peers[p0 + i] + a.o_part) + base + 4 * g);
+                        src[i] = reinterpret_cast<const float*>(s_peer[p0 + i < a.tp ? p0 + i : 0] + a.o_part) + base + 4 * g;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (p0 + i < a.tp) x[i] = ld_relaxed_sys_f4(src[i]);
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         if (p0 + i < a.tp) {
@@ -557,13 +564,13 @@ tp_finish_kernel(TpFinishArgs a) {
     // 3. deliver the row to every rank
     if (ok) {
         for (int p = 0; p < a.tp; ++p) {
-            uint32_t* q4 = reinterpret_cast<uint32_t*>(a.peers[p] + a.o_xq + base);
+            uint32_t* q4 = reinterpret_cast<uint32_t*>(s_peer[p] + a.o_xq + base);
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 const int g = threadIdx.x + k * blockDim.x;
                 if (g < groups) q4[g] = quant4(v[k], s);
             }
-            if (threadIdx.x == 0) reinterpret_cast<float*>(a.peers[p] + a.o_sx)[row] = s;
+            if (threadIdx.x == 0) reinterpret_cast<float*>(s_peer[p] + a.o_sx)[row] = s;
         }
     }
     __threadfence_system();
@@ -580,7 +587,7 @@ tp_finish_kernel(TpFinishArgs a) {
         const bool failed = !ok || *reinterpret_cast<volatile uint32_t*>(a.err) != 0u;
         if (threadIdx.x < a.tp) {
             __threadfence_system();
-            uint32_t* peer = reinterpret_cast<uint32_t*>(a.peers[threadIdx.x]);
+            uint32_t* peer = reinterpret_cast<uint32_t*>(s_peer[threadIdx.x]);
             if (failed) st_release_sys(peer + a.rank, kPeerPoison);
             st_release_sys(peer + 64 + a.rank, failed ? kPeerPoison : epoch);
         }

@@ -558,6 +558,10 @@ cudaError_t launch_persist_t(const GemmPlan& plan, const PersistArgs& args, cuda
 
 }  // namespace
 
+bool gemm_make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    return make_operand_map(map, base, rows, cols, box_rows);
+}
+
 bool gemm_plan_can_rope(const GemmPlan& plan, int hq, int hkv) {
     return !plan.persist && plan.cluster && plan.bn == 128 && !plan.gate && plan.kind == kGemmI8 && plan.splits >= 2 &&
            plan.splits <= 16 && (128 / plan.splits) % 8 == 0 && plan.N == (hq + 2 * hkv) * 128;

@@ -103,6 +103,18 @@ cudaError_t gemm_splitk_epilogue(int kind, int splits, int M, int N, int gate, c
                                  const GemmEpilogue& ep, cudaStream_t stream);
 cudaError_t gemm_sum_planes_i32(const int* raw, int splits, int64_t elems, int* out, cudaStream_t stream);
 
+// 2-D tensor map over a row-major [rows, cols] matrix of bytes with boxes of [box_rows, 128 bytes] and the 128-byte
+// swizzle: the operand layout every tcgen05 kernel of this library consumes.
+bool gemm_make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+// ---- gemm_block_scaled.cu: INT8 GEMM under the block-scale contract (one power-of-two scale per 128 values of K on
+// both operands; per block: s32 partial -> f32 -> one multiplication by the composed scale -> widened to f64; the
+// blocks added in ascending order in f64; one narrowing to f32).
+//   a [M, K] int8, a_delta [M, nb] f32;  b [N, K] int8, b_delta [nb, N] f32;  out [M, N] f32;  nb = ceil(K / 128).
+// `status` is a device word: bit 1 is set when a result is not finite after the narrowing.
+cudaError_t gemm_i8_block_scaled(const void* a, const float* a_delta, const void* b, const float* b_delta, int M, int N, int K,
+                                 float* out, uint32_t* status, uint32_t* err, cudaStream_t stream, const char** why);
+
 // Required raw-output elements for a plan: splits * M * N.
 inline size_t gemm_raw_elems(const GemmPlan& p) { return size_t(p.out_planes) * size_t(p.M) * size_t(p.N); }
 

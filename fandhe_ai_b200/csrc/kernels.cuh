@@ -15,6 +15,13 @@ cudaError_t dequantize_i8_per_row(const int8_t* q, const float* scale, int64_t r
 cudaError_t quantize_fp8_per_tensor(const float* x, int64_t n, uint8_t* q, float* scale, uint32_t* amax_scratch,
                                     cudaStream_t s);
 
+// Block-scale contract: one power-of-two scale per 128 values of a row.  `transposed` selects the layout of the scale
+// array: [rows, nb] (0) or [nb, rows] (1).  `status` is a device word: bit 0 is set when an input value is not finite.
+cudaError_t quantize_i8_block_pow2(const float* x, int64_t rows, int64_t cols, int8_t* q, float* delta, int transposed,
+                                   uint32_t* status, cudaStream_t s);
+cudaError_t dequantize_i8_block(const int8_t* q, const float* delta, int64_t rows, int64_t cols, int transposed, float* x,
+                                cudaStream_t s);
+
 // ---- paged_kv.cu
 struct PagedAttnShape {
     int batch, l_new, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks, max_blocks_per_seq;

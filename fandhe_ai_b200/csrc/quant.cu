@@ -103,6 +103,53 @@ __global__ void fp8_encode_kernel(const float* __restrict__ x, int64_t n, const 
     }
 }
 
+// ---- block-scale contract (docs/int8-quant-grade-up-verification-plan.md:177-241 of the reference): blocks of 128
+// values along a row, delta = pow2ceil(max(amax_block, 1e-4) / 127), q = rne(x / delta) (never clamps: |x / delta| <= 127).
+constexpr int kQuantBlock = 128;
+
+// smallest power of two >= x for a positive, finite, normal x
+__device__ __forceinline__ float pow2ceil(float x) {
+    const uint32_t b = __float_as_uint(x);
+    return (b & 0x7FFFFFu) == 0u ? x : __uint_as_float(((b >> 23) + 1u) << 23);
+}
+
+// One warp per (row, block): lane l holds values 4 l .. 4 l + 3 of the block.  `delta_rs` / `delta_bs` are the strides
+// of the scale array per row and per block, so that it can be written as [rows, nb] or as [nb, rows].
+__global__ void __launch_bounds__(256)
+quantize_i8_block_pow2_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, int64_t nb, int8_t* __restrict__ q,
+                              float* __restrict__ delta, int64_t delta_rs, int64_t delta_bs, uint32_t* status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t item = warp; item < rows * nb; item += warps) {
+        const int64_t r = item / nb, b = item % nb;
+        const int64_t c0 = b * kQuantBlock + 4 * lane;
+        float v[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) v[t] = c0 + t < cols ? x[r * cols + c0 + t] : 0.0f;
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        bool finite = isfinite(v[0]) && isfinite(v[1]) && isfinite(v[2]) && isfinite(v[3]);
+        amax = warp_max(amax);
+        finite = __all_sync(0xffffffffu, finite) != 0;
+        float d = 1.0f;
+        if (finite) d = pow2ceil(fmaxf(amax, 1e-4f) / 127.0f);
+        else if (lane == 0) atomicOr(status, 1u);        // rejected input: codes of this block are zero
+        if (lane == 0) delta[r * delta_rs + b * delta_bs] = d;
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            if (c0 + t < cols) q[r * cols + c0 + t] = finite ? static_cast<int8_t>(static_cast<int>(rintf(v[t] / d))) : int8_t(0);
+    }
+}
+
+__global__ void dequantize_i8_block_kernel(const int8_t* __restrict__ q, const float* __restrict__ delta, int64_t rows,
+                                           int64_t cols, int64_t delta_rs, int64_t delta_bs, float* __restrict__ x) {
+    const int64_t n = rows * cols;
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t r = i / cols, b = (i % cols) / kQuantBlock;
+        x[i] = static_cast<float>(q[i]) * delta[r * delta_rs + b * delta_bs];
+    }
+}
+
 int grid_for(int64_t n, int threads) {
     int64_t g = (n + threads - 1) / threads;
     const int64_t cap = int64_t(current_sm_count()) * 16;
@@ -133,6 +180,24 @@ cudaError_t quantize_fp8_per_tensor(const float* x, int64_t n, uint8_t* q, float
     if (n > 0) amax_kernel<<<grid_for(n, 256), 256, 0, s>>>(x, n, amax_scratch);
     fp8_scale_kernel<<<1, 1, 0, s>>>(amax_scratch, scale);
     if (n > 0) fp8_encode_kernel<<<grid_for(n, 256), 256, 0, s>>>(x, n, scale, q);
+    return cudaGetLastError();
+}
+
+cudaError_t quantize_i8_block_pow2(const float* x, int64_t rows, int64_t cols, int8_t* q, float* delta, int transposed,
+                                   uint32_t* status, cudaStream_t s) {
+    if (rows == 0 || cols == 0) return cudaSuccess;
+    const int64_t nb = (cols + kQuantBlock - 1) / kQuantBlock;
+    const int64_t rs = transposed ? 1 : nb, bs = transposed ? rows : 1;
+    quantize_i8_block_pow2_kernel<<<grid_for(rows * nb * 32, 256), 256, 0, s>>>(x, rows, cols, nb, q, delta, rs, bs, status);
+    return cudaGetLastError();
+}
+
+cudaError_t dequantize_i8_block(const int8_t* q, const float* delta, int64_t rows, int64_t cols, int transposed, float* x,
+                                cudaStream_t s) {
+    if (rows == 0 || cols == 0) return cudaSuccess;
+    const int64_t nb = (cols + kQuantBlock - 1) / kQuantBlock;
+    dequantize_i8_block_kernel<<<grid_for(rows * cols, 256), 256, 0, s>>>(q, delta, rows, cols, transposed ? 1 : nb,
+                                                                         transposed ? rows : 1, x);
     return cudaGetLastError();
 }
 

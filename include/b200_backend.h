@@ -162,6 +162,37 @@ int32_t b200_gemm_q8_scaled(b200_ctx* ctx, int32_t op_dtype, const b200_buf* a_q
                             const b200_buf* residual, size_t residual_off, int64_t m, int64_t n, int64_t k,
                             int32_t out_dtype, b200_buf* out, size_t out_off);
 
+/* ------------------------------------------------------------------ block-scale INT8 contract
+ * The variant the reference proposes for its own quantisation backend (QuantOps {quantize, dequantize,
+ * gemm_i8_s32_scaled}, docs/backend-int8-quantization-decision.md:88-94; numeric contract
+ * docs/int8-quant-grade-up-verification-plan.md:177-241):
+ *   - one scale per `block_len` = 128 consecutive values of K, on both operands (per token x block for activations,
+ *     per output channel x block for weights); delta = pow2ceil(max(amax_block, 1e-4) / 127), q = rne(x / delta),
+ *     so |q| <= 127 without clamping and every scale is a power of two;
+ *   - per block: s32 partial (exact) -> f32 (exact: |partial| <= 128 * 127^2 = 2 064 512 < 2^24) -> ONE multiplication
+ *     by the composed scale delta_a * delta_b (exact) -> widened to f64; the blocks are added in ascending order in
+ *     f64 and the sum is narrowed to f32 once.  The result is a pure function of the inputs: bit-identical to the
+ *     CPU restatement (acceptance rule fail_count == 0).
+ * The scale array of x [rows, cols] is [rows, nb] (scales_block_major = 0) or [nb, rows] (1), nb = ceil(cols / 128);
+ * the GEMM takes the activation scales as [m, nb] and the weight scales as [nb, n].
+ * Requests outside the contract are typed errors, never wrap-arounds or infinities: a block length above
+ * K_safe = floor(i32::MAX / 127^2) = 133 144 is B200_INVALID_ARGUMENT (lengths other than 128 are B200_UNSUPPORTED);
+ * a NaN / infinite input value and a result that overflows f32 at the final narrowing are recorded on the device and
+ * reported by b200_quant_check as B200_INVALID_ARGUMENT (the context is not poisoned; the affected block is zeroed /
+ * the affected output holds the infinity). */
+int32_t b200_quantize_i8_block(b200_ctx* ctx, const b200_buf* x_f32, size_t x_off, int64_t rows, int64_t cols,
+                               int64_t block_len, int32_t scales_block_major, b200_buf* q_i8, size_t q_off,
+                               b200_buf* delta_f32, size_t delta_off);
+int32_t b200_dequantize_i8_block(b200_ctx* ctx, const b200_buf* q_i8, size_t q_off, const b200_buf* delta_f32,
+                                 size_t delta_off, int64_t rows, int64_t cols, int64_t block_len,
+                                 int32_t scales_block_major, b200_buf* x_f32, size_t x_off);
+int32_t b200_gemm_i8_block_scaled(b200_ctx* ctx, const b200_buf* a_i8, size_t a_off, const b200_buf* a_delta,
+                                  size_t a_delta_off, const b200_buf* w_i8, size_t w_off, const b200_buf* w_delta,
+                                  size_t w_delta_off, int64_t m, int64_t n, int64_t k, int64_t block_len, b200_buf* out_f32,
+                                  size_t out_off);
+/* Synchronises and reports what the three calls above flagged since the last check (then clears it). */
+int32_t b200_quant_check(b200_ctx* ctx);
+
 /* Which kernel form b200_gemm_i8_s32 (fused = 0) or b200_gemm_q8_scaled (fused = 1; gated = 1 for
  * B200_ACT_SILU_GATE) would use for a shape under the context's current tuning; nothing is launched.
  * out6 = {tile width, K splits, splits reduced inside a cluster (0/1), persistent kernel (0/1), resident CTAs of the

@@ -625,3 +625,82 @@ int orc_paged_attention_kernel_order(const float* q, const void* k_pool, const v
     }
     return status;
 }
+
+/* ====================================================================================================
+ * Block-scale INT8 contract proposed by the reference for its quantisation backend
+ * (docs/int8-quant-grade-up-verification-plan.md:177-241).  PARITY UNPINNED beyond the accumulator vectors the
+ * reference holds (K = 128 chain of 127 * 127 = 2 064 512, K_safe = 133 144): the document is a pre-registered
+ * contract without code; this is its literal restatement.
+ *   delta = pow2ceil(max(amax_block, 1e-4) / 127),  q = rne(x / delta)            blocks of 128 along K
+ *   per block: s32 partial -> f32 (exact) -> * (delta_a * delta_b) once -> widen to f64
+ *   blocks added in ascending order in f64, one narrowing to f32
+ * ==================================================================================================== */
+#define ORC_QBLOCK 128
+
+float orc_pow2ceil(float x) {
+    uint32_t b;
+    memcpy(&b, &x, 4);
+    if ((b & 0x7FFFFFu) == 0u) return x;
+    b = ((b >> 23) + 1u) << 23;
+    float r;
+    memcpy(&r, &b, 4);
+    return r;
+}
+
+/* x [rows, cols] -> q int8 [rows, cols], delta [rows, nb] (transposed == 0) or [nb, rows] (transposed != 0).
+ * Returns 1 when a value was not finite (its block gets delta 1 and zero codes), else 0. */
+int orc_quantize_i8_block(const float* x, int64_t rows, int64_t cols, int transposed, int8_t* q, float* delta) {
+    const int64_t nb = (cols + ORC_QBLOCK - 1) / ORC_QBLOCK;
+    int bad = 0;
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t b = 0; b < nb; ++b) {
+            const int64_t c0 = b * ORC_QBLOCK, c1 = c0 + ORC_QBLOCK < cols ? c0 + ORC_QBLOCK : cols;
+            float amax = 0.0f;
+            int finite = 1;
+            for (int64_t c = c0; c < c1; ++c) {
+                const float v = x[r * cols + c];
+                if (!isfinite(v)) finite = 0;
+                amax = fmaxf(amax, fabsf(v));
+            }
+            float d = 1.0f;
+            if (finite) d = orc_pow2ceil(fmaxf(amax, 1e-4f) / 127.0f);
+            else bad = 1;
+            delta[transposed ? b * rows + r : r * nb + b] = d;
+            for (int64_t c = c0; c < c1; ++c) q[r * cols + c] = finite ? (int8_t)(int)rintf(x[r * cols + c] / d) : (int8_t)0;
+        }
+    return bad;
+}
+
+void orc_dequantize_i8_block(const int8_t* q, const float* delta, int64_t rows, int64_t cols, int transposed, float* x) {
+    const int64_t nb = (cols + ORC_QBLOCK - 1) / ORC_QBLOCK;
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t c = 0; c < cols; ++c) {
+            const int64_t b = c / ORC_QBLOCK;
+            x[r * cols + c] = (float)q[r * cols + c] * delta[transposed ? b * rows + r : r * nb + b];
+        }
+}
+
+/* a [m, k] int8 with da [m, nb]; w [n, k] int8 with dw [nb, n]; out [m, n] f32.
+ * Returns 1 when a result is not finite after the narrowing, else 0. */
+int orc_gemm_i8_block_scaled(const int8_t* a, const float* da, const int8_t* w, const float* dw, int64_t m, int64_t n,
+                             int64_t k, float* out) {
+    const int64_t nb = (k + ORC_QBLOCK - 1) / ORC_QBLOCK;
+    int bad = 0;
+#pragma omp parallel for schedule(static) collapse(2) reduction(|| : bad)
+    for (int64_t i = 0; i < m; ++i)
+        for (int64_t j = 0; j < n; ++j) {
+            double acc = 0.0;
+            for (int64_t b = 0; b < nb; ++b) {
+                const int64_t p0 = b * ORC_QBLOCK, p1 = p0 + ORC_QBLOCK < k ? p0 + ORC_QBLOCK : k;
+                int32_t part = 0;
+                for (int64_t p = p0; p < p1; ++p) part += (int32_t)a[i * k + p] * (int32_t)w[j * k + p];
+                const float dout = da[i * nb + b] * dw[b * n + j];      /* composed scale first */
+                const float val = (float)part * dout;                    /* one multiplication */
+                acc += (double)val;                                      /* widen, ascending blocks */
+            }
+            const float y = (float)acc;                                  /* one narrowing */
+            if (!isfinite(y)) bad = 1;
+            out[i * n + j] = y;
+        }
+    return bad;
+}

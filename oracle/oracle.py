@@ -339,3 +339,44 @@ def gemm_i8_s32_blas(a, w_float) -> np.ndarray:
 def int8_weight_for_blas(w_q) -> np.ndarray:
     w_q = np.asarray(w_q)
     return np.ascontiguousarray(w_q.astype(np.float32 if w_q.shape[1] <= 1024 else np.float64))
+
+
+# ---------------------------------------------------------------- block-scale INT8 contract
+def pow2ceil(x: float) -> float:
+    f = lib().orc_pow2ceil
+    f.restype, f.argtypes = C.c_float, [C.c_float]
+    return float(f(C.c_float(x)))
+
+
+def quantize_i8_block(x, transposed: bool = False):
+    """(q int8 [rows, cols], delta f32 [rows, nb] or [nb, rows], saw_non_finite)."""
+    x = _c(x, np.float32)
+    rows, cols = x.shape
+    nb = -(-cols // 128)
+    q = np.empty((rows, cols), np.int8)
+    d = np.empty((nb, rows) if transposed else (rows, nb), np.float32)
+    f = lib().orc_quantize_i8_block
+    f.restype = C.c_int
+    bad = f(_p(x), C.c_int64(rows), C.c_int64(cols), C.c_int(int(transposed)), _p(q), _p(d))
+    return q, d, bool(bad)
+
+
+def dequantize_i8_block(q, delta, transposed: bool = False) -> np.ndarray:
+    q = _c(q, np.int8)
+    rows, cols = q.shape
+    out = np.empty((rows, cols), np.float32)
+    lib().orc_dequantize_i8_block(_p(q), _p(_c(delta, np.float32)), C.c_int64(rows), C.c_int64(cols), C.c_int(int(transposed)),
+                                  _p(out))
+    return out
+
+
+def gemm_i8_block_scaled(a, da, w, dw):
+    """a [m, k] int8, da [m, nb]; w [n, k] int8, dw [nb, n] -> (out f32 [m, n], overflowed_at_narrowing)."""
+    a, w = _c(a, np.int8), _c(w, np.int8)
+    m, k = a.shape
+    n = w.shape[0]
+    out = np.empty((m, n), np.float32)
+    f = lib().orc_gemm_i8_block_scaled
+    f.restype = C.c_int
+    bad = f(_p(a), _p(_c(da, np.float32)), _p(w), _p(_c(dw, np.float32)), C.c_int64(m), C.c_int64(n), C.c_int64(k), _p(out))
+    return out, bool(bad)
