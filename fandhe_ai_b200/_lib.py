@@ -133,6 +133,10 @@ SIGNATURES = {
     "b200_decoder_create": (_I32, [_P, C.POINTER(DecoderConfigC), C.POINTER(_P)]),
     "b200_decoder_destroy": (_I32, [_P]),
     "b200_decoder_load_tensor": (_I32, [_P, _I32, _I32, _P, _I64, _I64]),
+    "b200_decoder_load_tensor_i8": (_I32, [_P, _I32, _I32, _P, _P, _I64, _I64]),
+    "b200_decoder_load_safetensors": (_I32, [_P, C.c_char_p]),
+    "b200_decoder_load_safetensors_bytes": (_I32, [_P, _P, _SZ]),
+    "b200_safetensors_validate": (_I32, [_P, _SZ, C.POINTER(_U64)]),
     "b200_decoder_init_random": (_I32, [_P, _U64, C.c_float]),
     "b200_nccl_unique_id": (_I32, [_P]),
     "b200_decoder_init_tp": (_I32, [_P, _P]),
@@ -150,6 +154,11 @@ SIGNATURES = {
     "b200_scheduler_step": (_I32, [_P, _P]),
     "b200_scheduler_plan_step": (_I32, [_P, _P, _P, _P, _P, _P, _P]),
     "b200_scheduler_commit_step": (_I32, [_P, _P, _P]),
+    "b200_scheduler_failed_len": (_I32, [_P]),
+    "b200_scheduler_take_failed": (_I32, [_P, _P, _P, _P, _I32, _P]),
+    "b200_scheduler_configure": (_I32, [_P, _I32, _I32]),
+    "b200_decoder_prefill": (_I32, [_P, _I32, _I32, _P, _I32]),
+    "b200_decoder_vocab": (_I32, [_P]),
     "b200_scheduler_take_finished": (_I32, [_P, _P, _P, _I32, _P]),
     "b200_decoder_begin": (_I32, [_P, _I32, _P, _P]),
     "b200_decoder_fill_cache_random": (_I32, [_P, _U64, C.c_float]),

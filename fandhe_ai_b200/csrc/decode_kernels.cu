@@ -186,6 +186,16 @@ __global__ void begin_step_kernel(uint32_t* seq_lens, uint32_t* positions, const
     }
 }
 
+// Prefill of l_new tokens per sequence: token row m = b * l_new + i sits at position seq_lens[b] + i.
+__global__ void prefill_positions_kernel(const uint32_t* seq_lens, uint32_t* positions, int count, int l_new) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m < count * l_new) positions[m] = seq_lens[m / l_new] + static_cast<uint32_t>(m % l_new);
+}
+__global__ void prefill_advance_kernel(uint32_t* seq_lens, int count, int l_new) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < count) seq_lens[b] += static_cast<uint32_t>(l_new);
+}
+
 // First index of the maximum of each row (strict '>' keeps the earliest index on ties).
 __global__ void __launch_bounds__(kRowThreads)
 argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_ids) {
@@ -301,6 +311,15 @@ cudaError_t gate_quant(const int* raw, int splits, int M, int F, const float* sx
 }
 cudaError_t begin_step(uint32_t* seq_lens, uint32_t* positions, const uint32_t* active, int n, cudaStream_t s) {
     begin_step_kernel<<<(n + 127) / 128, 128, 0, s>>>(seq_lens, positions, active, n);
+    return cudaGetLastError();
+}
+cudaError_t prefill_positions(const uint32_t* seq_lens, uint32_t* positions, int count, int l_new, cudaStream_t s) {
+    const int n = count * l_new;
+    prefill_positions_kernel<<<(n + 255) / 256, 256, 0, s>>>(seq_lens, positions, count, l_new);
+    return cudaGetLastError();
+}
+cudaError_t prefill_advance(uint32_t* seq_lens, int count, int l_new, cudaStream_t s) {
+    prefill_advance_kernel<<<(count + 127) / 128, 128, 0, s>>>(seq_lens, count, l_new);
     return cudaGetLastError();
 }
 cudaError_t argmax_rows(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s) {

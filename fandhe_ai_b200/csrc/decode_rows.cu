@@ -202,7 +202,7 @@ argmax_cl_kernel(const float* __restrict__ logits, int vocab, int chunk, int* __
 // Finishes the QKV GEMM: one CTA per (row, group of heads); no row-wide reduction is needed.
 // q and k heads are rotated (rotate-half pairs (i, i + dh/2)), v heads are only dequantised.
 __global__ void __launch_bounds__(kThreads)
-qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int hq, int hkv, int dh, int heads_per_cta,
+qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int rows_per_seq, int hq, int hkv, int dh, int heads_per_cta,
                            const float* __restrict__ sx_in, const float* __restrict__ sw,
                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
                            const uint32_t* __restrict__ positions, const uint32_t* __restrict__ active,
@@ -221,7 +221,7 @@ qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int h
     bool ok = pos < max_pos;
     uint32_t blk = 0;
     if (ok) {
-        blk = block_tables[static_cast<size_t>(m) * max_blocks_per_seq + pos / block_size];
+        blk = block_tables[static_cast<size_t>(m / rows_per_seq) * max_blocks_per_seq + pos / block_size];
         ok = blk < static_cast<uint32_t>(num_blocks);
     }
     if (!ok) {
@@ -694,12 +694,12 @@ cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int 
                                  const float* sw, const float* cos_t, const float* sin_t, int max_pos,
                                  const uint32_t* positions, const uint32_t* active, const uint32_t* block_tables,
                                  int max_blocks_per_seq, int block_size, int num_blocks, float* q_out, uint16_t* k_pool,
-                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s) {
+                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s, int rows_per_seq) {
     const int heads = hq + 2 * hkv;
     int hpc = (2 * kThreads) / (dh / 2);      // two rotary pairs per thread
     if (hpc < 1) hpc = 1;
     dim3 grid((heads + hpc - 1) / hpc, M);
-    return launch_ex(qkv_rope_append_par_kernel, grid, dim3(kThreads), 0, s, 1, true, raw, splits, M, hq, hkv, dh, hpc, sx_in,
+    return launch_ex(qkv_rope_append_par_kernel, grid, dim3(kThreads), 0, s, 1, true, raw, splits, M, rows_per_seq, hq, hkv, dh, hpc, sx_in,
                      sw, cos_t, sin_t, max_pos, positions, active, block_tables, max_blocks_per_seq, block_size, num_blocks,
                      q_out, k_pool, v_pool, err);
 }

@@ -20,6 +20,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <new>
 #include <string>
 #include <vector>
@@ -27,6 +28,7 @@
 #include "backend.h"
 #include "gemm_tc5.cuh"
 #include "kernels.cuh"
+#include "safetensors.h"
 
 using namespace b200;
 
@@ -308,6 +310,22 @@ struct b200_decoder {
     bool tp_exchange = false;                   // peers are mapped: use the finish kernel instead of ncclAllReduce
     uint64_t tp_timeout_ns = 0;                 // bound of every cross-GPU wait (0: the kernels' default of two seconds)
     uint64_t launches_per_step = 0;
+    // multi-token prefill: buffers for up to prefill_rows token rows (grown on demand)
+    struct Prefill {
+        size_t rows = 0;
+        int* ids = nullptr;
+        uint32_t* pos = nullptr;
+        float* h = nullptr;
+        int8_t* xq = nullptr;
+        float* sx = nullptr;
+        int* raw = nullptr;
+        size_t raw_elems = 0;
+        float* q = nullptr;
+        float* attn = nullptr;
+        float* part = nullptr;
+        void* attn_scratch = nullptr;
+        size_t attn_scratch_bytes = 0;
+    } pf;
 };
 
 namespace {
@@ -368,16 +386,12 @@ void drop_graph(b200_decoder* d) {
     d->eager_steps_done = 0;
 }
 
-// Quantises a full f32 matrix [rows, cols] (device, temporary) per row and stores either a row subset
-// or a column slice into the payload; scales follow.
-int32_t store_weight(b200_decoder* d, const float* w_full, int64_t rows, int64_t cols, const std::vector<std::pair<int64_t, int64_t>>& row_ranges,
-                     int64_t c0, int64_t ccount, size_t payload_off, size_t scale_off) {
+// Keeps this rank's shard of a full quantised matrix (int8 [rows, cols] and one scale per row, both on the device):
+// either a row subset or a column slice goes into the payload; the scales follow.
+int32_t store_weight_q(b200_decoder* d, const int8_t* q_full, const float* s_full, int64_t cols,
+                       const std::vector<std::pair<int64_t, int64_t>>& row_ranges, int64_t c0, int64_t ccount, size_t payload_off,
+                       size_t scale_off) {
     cudaStream_t s = d->ctx->stream;
-    int8_t* q_full = nullptr;
-    float* s_full = nullptr;
-    CU_TRY(dmalloc(&q_full, size_t(rows) * cols));
-    CU_TRY(dmalloc(&s_full, size_t(rows)));
-    CU_TRY(quantize_i8_per_row(w_full, rows, cols, q_full, s_full, s));
     size_t out_row = 0;
     for (auto rr : row_ranges) {
         const int64_t r0 = rr.first, rn = rr.second;
@@ -386,9 +400,22 @@ int32_t store_weight(b200_decoder* d, const float* w_full, int64_t rows, int64_t
         out_row += rn;
     }
     CU_TRY(cudaStreamSynchronize(s));
+    return B200_OK;
+}
+
+// Quantises a full f32 matrix [rows, cols] (device, temporary) per row and keeps this rank's shard.
+int32_t store_weight(b200_decoder* d, const float* w_full, int64_t rows, int64_t cols, const std::vector<std::pair<int64_t, int64_t>>& row_ranges,
+                     int64_t c0, int64_t ccount, size_t payload_off, size_t scale_off) {
+    cudaStream_t s = d->ctx->stream;
+    int8_t* q_full = nullptr;
+    float* s_full = nullptr;
+    CU_TRY(dmalloc(&q_full, size_t(rows) * cols));
+    CU_TRY(dmalloc(&s_full, size_t(rows)));
+    CU_TRY(quantize_i8_per_row(w_full, rows, cols, q_full, s_full, s));
+    const int32_t st = store_weight_q(d, q_full, s_full, cols, row_ranges, c0, ccount, payload_off, scale_off);
     cudaFree(q_full);
     cudaFree(s_full);
-    return B200_OK;
+    return st;
 }
 
 struct TensorShape {
@@ -798,6 +825,8 @@ int32_t b200_decoder_destroy(b200_decoder* d) {
         d->sx = nullptr;
         d->part = nullptr;
     }
+    void* pf_ptrs[] = {d->pf.ids, d->pf.pos, d->pf.h, d->pf.xq, d->pf.sx, d->pf.raw, d->pf.q, d->pf.attn, d->pf.part, d->pf.attn_scratch};
+    for (void* p : pf_ptrs) cudaFree(p);
     void* ptrs[] = {d->payload, d->scales, d->vectors, d->embed, d->cos_t, d->sin_t, d->tables_dev, d->seq_lens_dev, d->pos_dev,
                     d->ids_dev, d->next_ids_dev, d->h, d->xq, d->sx, d->raw, d->q, d->attn_out, d->part, d->logits,
                     d->attn_scratch, d->tp_block, d->tp_epoch, d->tp_peers_dev, d->active_dev};
@@ -846,6 +875,133 @@ int32_t b200_decoder_load_tensor(b200_decoder* d, int32_t which, int32_t layer, 
     int32_t st = store_weight(d, tmp, rows, cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off);
     cudaFree(tmp);
     return st;
+}
+
+// The same for a matrix that is already quantised: int8 payload [rows, cols] with one f32 scale per row, as a weight
+// file stores it (see b200_decoder_load_safetensors).  Nothing is re-quantised; the rank keeps its shard.
+int32_t b200_decoder_load_tensor_i8(b200_decoder* d, int32_t which, int32_t layer, const int8_t* q_host, const float* scale_host,
+                                    int64_t rows, int64_t cols) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!q_host || !scale_host) return fail(B200_INVALID_ARGUMENT, "decoder_load_tensor_i8: host pointer is null");
+    TensorShape t;
+    if (!tensor_shape(d, which, layer, &t)) return fail(B200_INVALID_ARGUMENT, "decoder_load_tensor_i8: not a quantised matrix, or layer out of range");
+    if (rows != t.rows || cols != t.cols) {
+        char msg[160];
+        std::snprintf(msg, sizeof msg, "decoder_load_tensor_i8: shape [%lld, %lld] differs from the expected [%lld, %lld]",
+                      (long long)rows, (long long)cols, (long long)t.rows, (long long)t.cols);
+        return fail(B200_SHAPE_MISMATCH, msg);
+    }
+    cudaStream_t s = d->ctx->stream;
+    int8_t* q_full = nullptr;
+    float* s_full = nullptr;
+    CU_TRY(dmalloc(&q_full, size_t(rows) * cols));
+    CU_TRY(dmalloc(&s_full, size_t(rows)));
+    CU_TRY(cudaMemcpyAsync(q_full, q_host, size_t(rows) * cols, cudaMemcpyHostToDevice, s));
+    CU_TRY(cudaMemcpyAsync(s_full, scale_host, size_t(rows) * 4, cudaMemcpyHostToDevice, s));
+    const int32_t st = store_weight_q(d, q_full, s_full, cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off);
+    cudaFree(q_full);
+    cudaFree(s_full);
+    return st;
+}
+
+// Loads every tensor of the decoder from a safetensors buffer.  Names (no renaming, no transposition, as in the
+// reference's loader): "embed.weight" F32 [vocab, d], "final_norm.weight" F32 [d], "layers.<l>.attn_norm.weight" and
+// "layers.<l>.mlp_norm.weight" F32 [d], and for each matrix M in {"lm_head", "layers.<l>.wqkv", ".wo", ".wgu",
+// ".wdown"} either "M.qweight" I8 [rows, cols] with "M.scale" F32 [rows], or "M.weight" F32 [rows, cols] (quantised on
+// the device).  Every missing name is reported in one error; a tensor with another dtype or shape is an error, never
+// skipped; tensors the decoder does not know are an error too.
+int32_t b200_decoder_load_safetensors_bytes(b200_decoder* d, const uint8_t* bytes, size_t len) {
+    if (int32_t st = dec_check(d)) return st;
+    std::vector<StTensor> ts;
+    std::string err;
+    if (!safetensors_parse(bytes, len, &ts, &err)) return fail(B200_INVALID_ARGUMENT, err);
+    std::map<std::string, const StTensor*> by_name;
+    for (const StTensor& t : ts) by_name[t.name] = &t;
+    const auto& c = d->cfg;
+    struct Want { std::string name; int which; int layer; bool matrix; };
+    std::vector<Want> wants;
+    wants.push_back({"embed", B200_W_EMBED, 0, false});
+    wants.push_back({"final_norm", B200_W_FINAL_NORM, 0, false});
+    wants.push_back({"lm_head", B200_W_LM_HEAD, 0, true});
+    for (int l = 0; l < c.n_layers; ++l) {
+        const std::string pre = "layers." + std::to_string(l) + ".";
+        wants.push_back({pre + "attn_norm", B200_W_ATTN_NORM, l, false});
+        wants.push_back({pre + "wqkv", B200_W_QKV, l, true});
+        wants.push_back({pre + "wo", B200_W_O, l, true});
+        wants.push_back({pre + "mlp_norm", B200_W_MLP_NORM, l, false});
+        wants.push_back({pre + "wgu", B200_W_GATE_UP, l, true});
+        wants.push_back({pre + "wdown", B200_W_DOWN, l, true});
+    }
+    std::string missing;
+    size_t used = 0;
+    for (const Want& w : wants) {
+        const bool has_f32 = by_name.count(w.name + ".weight") != 0;
+        const bool has_q = w.matrix && by_name.count(w.name + ".qweight") != 0 && by_name.count(w.name + ".scale") != 0;
+        if (!has_f32 && !has_q) missing += (missing.empty() ? "" : ", ") + w.name + (w.matrix ? ".qweight + .scale (or .weight)" : ".weight");
+        used += has_q ? 2 : (has_f32 ? 1 : 0);
+    }
+    if (!missing.empty()) return fail(B200_INVALID_ARGUMENT, "load_safetensors: missing tensors: " + missing);
+    if (used != ts.size()) {
+        for (const StTensor& t : ts) {
+            bool known = false;
+            for (const Want& w : wants) {
+                const bool q_form = w.matrix && by_name.count(w.name + ".qweight") != 0 && by_name.count(w.name + ".scale") != 0;
+                if ((q_form && (t.name == w.name + ".qweight" || t.name == w.name + ".scale")) || (!q_form && t.name == w.name + ".weight"))
+                    known = true;
+            }
+            if (!known) return fail(B200_INVALID_ARGUMENT, "load_safetensors: tensor " + t.name + " is not part of this decoder (or is given twice, as .weight and .qweight)");
+        }
+    }
+    auto shape2 = [](const StTensor& t, int64_t* rows, int64_t* cols) {
+        if (t.shape.size() == 1) { *rows = 1; *cols = int64_t(t.shape[0]); return true; }
+        if (t.shape.size() == 2) { *rows = int64_t(t.shape[0]); *cols = int64_t(t.shape[1]); return true; }
+        return false;
+    };
+    for (const Want& w : wants) {
+        int64_t rows = 0, cols = 0;
+        const bool q_form = w.matrix && by_name.count(w.name + ".qweight") != 0;
+        if (q_form) {
+            const StTensor& q = *by_name[w.name + ".qweight"];
+            const StTensor& sc = *by_name[w.name + ".scale"];
+            if (q.dtype != "I8") return fail(B200_UNSUPPORTED, "load_safetensors: " + q.name + " has dtype " + q.dtype + ", expected I8");
+            if (sc.dtype != "F32") return fail(B200_UNSUPPORTED, "load_safetensors: " + sc.name + " has dtype " + sc.dtype + ", expected F32");
+            if (!shape2(q, &rows, &cols) || q.shape.size() != 2) return fail(B200_SHAPE_MISMATCH, "load_safetensors: " + q.name + " must be a matrix");
+            if (sc.shape.size() != 1 || int64_t(sc.shape[0]) != rows)
+                return fail(B200_SHAPE_MISMATCH, "load_safetensors: " + sc.name + " must hold one scale per row of " + q.name);
+            // the scales start on a 4-byte boundary inside the file only by luck: copy them to an aligned vector
+            std::vector<float> scales(size_t(rows), 0.0f);
+            std::memcpy(scales.data(), sc.data, size_t(rows) * 4);
+            if (int32_t st = b200_decoder_load_tensor_i8(d, w.which, w.layer, reinterpret_cast<const int8_t*>(q.data), scales.data(), rows, cols))
+                return st;
+        } else {
+            const StTensor& t = *by_name[w.name + ".weight"];
+            if (t.dtype != "F32") return fail(B200_UNSUPPORTED, "load_safetensors: " + t.name + " has dtype " + t.dtype + ", expected F32");
+            if (!shape2(t, &rows, &cols)) return fail(B200_SHAPE_MISMATCH, "load_safetensors: " + t.name + " must have one or two dimensions");
+            std::vector<float> vals(size_t(rows) * cols);
+            std::memcpy(vals.data(), t.data, vals.size() * 4);
+            if (int32_t st = b200_decoder_load_tensor(d, w.which, w.layer, vals.data(), rows, cols)) return st;
+        }
+    }
+    return B200_OK;
+}
+
+int32_t b200_decoder_load_safetensors(b200_decoder* d, const char* path) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!path) return fail(B200_INVALID_ARGUMENT, "load_safetensors: path is null");
+    FILE* f = std::fopen(path, "rb");
+    if (!f) return fail(B200_INVALID_ARGUMENT, std::string("load_safetensors: cannot open ") + path);
+    std::vector<uint8_t> bytes;
+    std::fseek(f, 0, SEEK_END);
+    const long n = std::ftell(f);
+    std::fseek(f, 0, SEEK_SET);
+    bool ok = n >= 0;
+    if (ok) {
+        bytes.resize(size_t(n));
+        ok = n == 0 || std::fread(bytes.data(), 1, size_t(n), f) == size_t(n);
+    }
+    std::fclose(f);
+    if (!ok) return fail(B200_TRANSFER_FAILED, std::string("load_safetensors: cannot read ") + path);
+    return b200_decoder_load_safetensors_bytes(d, bytes.data(), bytes.size());
 }
 
 int32_t b200_decoder_init_random(b200_decoder* d, uint64_t seed, float std) {
@@ -1214,6 +1370,152 @@ int32_t b200_decoder_step_rows(b200_decoder* d, const int32_t* ids_host, const u
     return B200_OK;
 }
 
+// Multi-token prefill: the rows [row0, row0 + count) each consume l_new tokens (ids [count, l_new], host) in one pass
+// over M = count * l_new token rows - the GEMMs run at M rows, every token's K / V is appended, attention uses the
+// reference's mask j <= seq_len - l_new + i (crates/backend-cpu/src/paged_kv.rs:137-140) - and the rows' lengths grow
+// by l_new.  Nothing is sampled: a caller that wants the next token feeds the last prompt token through
+// b200_decoder_step.  Prompts longer than the workspace are consumed in chunks, which the mask rule allows (a chunk
+// is "l_new tokens on top of a non-empty cache").
+namespace {
+
+constexpr int kPrefillRowsCap = 2048;      // token rows per pass
+
+int32_t prefill_pass(b200_decoder* d, int row0, int count, int l_new, const int32_t* ids_host) {
+    const auto& c = d->cfg;
+    cudaStream_t s = d->ctx->stream;
+    uint32_t* err = d->ctx->err_dev;
+    const int M = count * l_new, dm = c.d_model, dh = c.head_dim;
+    const bool tp = c.tp_size > 1;
+    auto& pf = d->pf;
+    const size_t widest = std::max<size_t>(std::max<size_t>(dm, d->f_l), size_t(d->hq_l) * dh);
+    if (pf.rows < size_t(M)) {
+        void* old[] = {pf.ids, pf.pos, pf.h, pf.xq, pf.sx, pf.q, pf.attn, pf.part};
+        CU_TRY(cudaStreamSynchronize(s));
+        for (void* p : old) cudaFree(p);
+        pf = b200_decoder::Prefill{};
+        const size_t R = size_t(M);
+        CU_TRY(dmalloc(&pf.ids, R));
+        CU_TRY(dmalloc(&pf.pos, R));
+        CU_TRY(dmalloc(&pf.h, R * dm));
+        CU_TRY(dmalloc(&pf.xq, R * widest));
+        CU_TRY(dmalloc(&pf.sx, R));
+        CU_TRY(dmalloc(&pf.q, R * d->hq_l * dh));
+        CU_TRY(dmalloc(&pf.attn, R * d->hq_l * dh));
+        if (tp) CU_TRY(dmalloc(&pf.part, R * dm));
+        pf.rows = R;
+    }
+    // plans for M rows (raw accumulators everywhere: the row kernels sum the planes and apply the scales)
+    const char* why = "";
+    GemmPlan p_qkv, p_o, p_gu, p_down;
+    size_t raw_need = 0;
+    auto plan = [&](GemmPlan* p, const int8_t* w, int N, int K, bool fused) -> cudaError_t {
+        cudaError_t e = gemm_make_plan(p, kGemmI8, pf.xq, w, M, N, K, 0, 0, 0, &why);
+        if (e == cudaSuccess) gemm_plan_make_persistent(p, d->ctx->sm_count, fused);
+        if (e == cudaSuccess && !(fused && (p->persist || p->splits == 1 || p->cluster))) raw_need = std::max(raw_need, gemm_raw_elems(*p));
+        return e;
+    };
+    PagedAttnShape sh{count, l_new, d->hq_l, d->hkv_l, dh, c.block_size, c.num_blocks, d->max_blocks_per_seq, 1.0f / std::sqrt(float(dh))};
+    CU_TRY(cudaMemcpyAsync(pf.ids, ids_host, size_t(M) * sizeof(int), cudaMemcpyHostToDevice, s));
+    const uint32_t* tables = d->tables_dev + size_t(row0) * d->max_blocks_per_seq;
+    uint32_t* lens = d->seq_lens_dev + row0;
+    CU_TRY(prefill_positions(lens, pf.pos, count, l_new, s));
+    CU_TRY(prefill_advance(lens, count, l_new, s));
+    CU_TRY(embed_norm_quant_auto(pf.ids, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, pf.h, pf.xq, pf.sx, err, s));
+    for (int l = 0; l < c.n_layers; ++l) {
+        LayerParams& L = d->layers[l];
+        raw_need = 0;
+        cudaError_t e = plan(&p_qkv, d->payload + L.wqkv, d->n_qkv, dm, false);
+        if (e == cudaSuccess) e = plan(&p_o, d->payload + L.wo, dm, d->hq_l * dh, tp);
+        if (e == cudaSuccess) e = plan(&p_gu, d->payload + L.wgu, 2 * d->f_l, dm, false);
+        if (e == cudaSuccess) e = plan(&p_down, d->payload + L.wdown, dm, d->f_l, tp);
+        if (e != cudaSuccess) return fail(B200_UNSUPPORTED, std::string("decoder_prefill: ") + why);
+        if (raw_need > pf.raw_elems) {
+            CU_TRY(cudaStreamSynchronize(s));
+            cudaFree(pf.raw);
+            pf.raw = nullptr;
+            CU_TRY(dmalloc(&pf.raw, raw_need));
+            pf.raw_elems = raw_need;
+        }
+        PagedAttnPlan ap;
+        if (paged_attention_make_plan(&ap, sh, 1, L.k_pool, L.v_pool, d->max_total_len, d->ctx->tune_attn_chunk_blocks) != cudaSuccess)
+            return fail(B200_KERNEL_LAUNCH_FAILED, "decoder_prefill: attention plan failed");
+        const size_t need = paged_attention_scratch_bytes(ap);
+        if (need > pf.attn_scratch_bytes) {
+            CU_TRY(cudaStreamSynchronize(s));
+            cudaFree(pf.attn_scratch);
+            pf.attn_scratch = nullptr;
+            CU_TRY(cudaMalloc(&pf.attn_scratch, need));
+            pf.attn_scratch_bytes = need;
+        }
+        GemmEpilogue ep;
+        ep.raw = pf.raw;
+        CU_TRY(gemm_launch(p_qkv, ep, err, s));
+        CU_TRY(qkv_rope_append_auto(pf.raw, p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, pf.sx, d->scales + L.s_qkv, d->cos_t, d->sin_t,
+                                    c.max_seq_len, pf.pos, nullptr, tables, d->max_blocks_per_seq, c.block_size, c.num_blocks, pf.q,
+                                    static_cast<uint16_t*>(L.k_pool), static_cast<uint16_t*>(L.v_pool), err, s, l_new));
+        // nothing is sampled from a prefill pass: once the last layer's K / V rows are in the cache the pass is complete
+        if (l + 1 == c.n_layers) break;
+        CU_TRY(paged_attention_launch(ap, pf.q, L.k_pool, L.v_pool, tables, lens, pf.attn, pf.attn_scratch, d->ctx->attn_counter,
+                                      d->ctx->sm_count, err, s));
+        CU_TRY(quantize_rows_auto(pf.attn, M, d->hq_l * dh, pf.xq, pf.sx, s));
+        auto row_parallel = [&](const GemmPlan& p, size_t s_off, const float* norm) -> int32_t {
+            if (!tp) {
+                CU_TRY(gemm_launch(p, ep, err, s));
+                CU_TRY(resid_norm_quant_auto(pf.raw, p.out_planes, M, dm, pf.sx, d->scales + s_off, nullptr, norm, c.rms_eps, pf.h, pf.xq, pf.sx, s));
+                return B200_OK;
+            }
+            if (p.persist || p.splits == 1 || p.cluster) {
+                GemmEpilogue pe;
+                pe.fused = 1;
+                pe.a_scale = pf.sx;
+                pe.a_per_row = 1;
+                pe.b_scale = d->scales + s_off;
+                pe.b_per_col = 1;
+                pe.out = pf.part;
+                CU_TRY(gemm_launch(p, pe, err, s));
+            } else {
+                CU_TRY(gemm_launch(p, ep, err, s));
+                CU_TRY(dequant_planes(pf.raw, p.out_planes, M, dm, pf.sx, d->scales + s_off, pf.part, s));
+            }
+            if (int32_t st = all_reduce_sum_f32(d, pf.part, size_t(M) * dm)) return st;
+            CU_TRY(resid_norm_quant_auto(pf.raw, 1, M, dm, pf.sx, d->scales + s_off, pf.part, norm, c.rms_eps, pf.h, pf.xq, pf.sx, s));
+            return B200_OK;
+        };
+        if (int32_t st = row_parallel(p_o, L.s_o, d->vectors + L.mlp_norm)) return st;
+        CU_TRY(gemm_launch(p_gu, ep, err, s));
+        CU_TRY(gate_quant_auto(pf.raw, p_gu.out_planes, M, d->f_l, pf.sx, d->scales + L.s_gu, pf.xq, pf.sx, s));
+        if (int32_t st = row_parallel(p_down, L.s_down, d->vectors + d->layers[l + 1].attn_norm)) return st;
+    }
+    return B200_OK;
+}
+
+}  // namespace
+
+int32_t b200_decoder_prefill(b200_decoder* d, int32_t row0, int32_t count, const int32_t* ids, int32_t l_new) {
+    if (int32_t st = dec_check(d)) return st;
+    if (!d->planned) return fail(B200_INVALID_ARGUMENT, "decoder_prefill: call decoder_begin first");
+    if (row0 < 0 || count <= 0 || row0 + count > d->batch) return fail(B200_INVALID_ARGUMENT, "decoder_prefill: rows out of range");
+    if (l_new <= 0 || !ids) return fail(B200_INVALID_ARGUMENT, "decoder_prefill: need l_new > 0 and ids");
+    for (int b = row0; b < row0 + count; ++b)
+        if (d->table->seq_lens[b] + uint64_t(l_new) > uint64_t(d->row_limits[b]))
+            return fail(B200_INVALID_ARGUMENT, "decoder_prefill: row " + std::to_string(b) + " would pass its reserved length");
+    for (int64_t i = 0; i < int64_t(count) * l_new; ++i)
+        if (ids[i] < 0 || ids[i] >= d->cfg.vocab) return fail(B200_INVALID_ARGUMENT, "decoder_prefill: token id outside the vocabulary");
+    int chunk = kPrefillRowsCap / count;
+    if (chunk < 1) chunk = 1;
+    std::vector<int32_t> part;
+    for (int t0 = 0; t0 < l_new; t0 += chunk) {
+        const int n = std::min(chunk, l_new - t0);
+        part.resize(size_t(count) * n);
+        for (int b = 0; b < count; ++b)
+            for (int i = 0; i < n; ++i) part[size_t(b) * n + i] = ids[size_t(b) * l_new + t0 + i];
+        if (int32_t st = prefill_pass(d, row0, count, n, part.data())) return st;
+        CU_TRY(cudaStreamSynchronize(d->ctx->stream));      // `part` is reused by the next chunk
+        for (int b = row0; b < row0 + count; ++b) d->table->seq_lens[b] += uint64_t(n);
+    }
+    return B200_OK;
+}
+
 // Empties row `row` between steps and reserves blocks for a new sequence of up to max_total_len tokens in it: the
 // row's blocks go back to the free stack (last block first), new ones are taken, the row's slice of the device
 // block table and its length (0) are uploaded.  The other rows are untouched.  Continuous batching uses this to
@@ -1258,9 +1560,9 @@ int32_t b200_decoder_logits(b200_decoder* d, float* host, uint64_t capacity_elem
     return b200_synchronize(d->ctx);
 }
 
-// generate() of the reference (crates/autodiff/src/generate/mod.rs:500-613) with greedy sampling: the
-// prompt [batch, prompt_len] is consumed token by token through the same decode step (teacher forcing),
-// then the model's own tokens are fed back until max_length; out is [batch, max_length] (prompt included).
+// generate() of the reference (crates/autodiff/src/generate/mod.rs:500-613) with greedy sampling: prefill once -
+// all but the last prompt token in multi-token passes, the last one through the decode step that samples the first
+// new token - then the model's own tokens are fed back until max_length; out is [batch, max_length] (prompt included).
 // There is no end-of-sequence stop, as in the reference.
 int32_t b200_decoder_generate(b200_decoder* d, const int32_t* prompt, int32_t batch, int32_t prompt_len, int32_t max_length,
                               int32_t* out) {
@@ -1274,7 +1576,16 @@ int32_t b200_decoder_generate(b200_decoder* d, const int32_t* prompt, int32_t ba
     std::vector<int32_t> ids(batch), next(batch);
     for (int b = 0; b < batch; ++b)
         for (int t = 0; t < prompt_len; ++t) out[size_t(b) * max_length + t] = prompt[size_t(b) * prompt_len + t];
-    for (int t = 0; t < max_length - 1; ++t) {
+    // prefill once (all but the last prompt token in multi-token passes), then one forward per token
+    int first = 0;
+    if (prompt_len > 1) {
+        std::vector<int32_t> head(size_t(batch) * (prompt_len - 1));
+        for (int b = 0; b < batch; ++b)
+            for (int t = 0; t < prompt_len - 1; ++t) head[size_t(b) * (prompt_len - 1) + t] = prompt[size_t(b) * prompt_len + t];
+        if (int32_t st = b200_decoder_prefill(d, 0, batch, head.data(), prompt_len - 1)) return st;
+        first = prompt_len - 1;
+    }
+    for (int t = first; t < max_length - 1; ++t) {
         const bool in_prompt = t < prompt_len;
         if (in_prompt)
             for (int b = 0; b < batch; ++b) ids[b] = prompt[size_t(b) * prompt_len + t];
@@ -1307,6 +1618,7 @@ int32_t b200_decoder_shard_plan(const b200_decoder_config* cfg, int32_t which, i
     return B200_OK;
 }
 
+int32_t b200_decoder_vocab(const b200_decoder* d) { return d ? d->cfg.vocab : 0; }
 uint64_t b200_decoder_launches_per_step(const b200_decoder* d) { return d ? d->launches_per_step : 0; }
 uint64_t b200_decoder_weight_bytes(const b200_decoder* d) { return d ? d->payload_bytes : 0; }
 

@@ -84,7 +84,12 @@ cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int 
                                  const float* sw, const float* cos_t, const float* sin_t, int max_pos,
                                  const uint32_t* positions, const uint32_t* active, const uint32_t* block_tables,
                                  int max_blocks_per_seq, int block_size, int num_blocks, float* q_out, uint16_t* k_pool,
-                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s);
+                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s, int rows_per_seq = 1);
+// Prefill: `rows_per_seq` consecutive token rows belong to one sequence (row m uses table row m / rows_per_seq).
+// positions[m] = seq_lens[m / l_new] + m % l_new for m < count * l_new ...
+cudaError_t prefill_positions(const uint32_t* seq_lens, uint32_t* positions, int count, int l_new, cudaStream_t s);
+// ... and afterwards seq_lens[b] += l_new for b < count.
+cudaError_t prefill_advance(uint32_t* seq_lens, int count, int l_new, cudaStream_t s);
 
 // y[m, n] = sum_planes(raw)[m, n] * (sx[m] * sw[n]) as f32 (the addend of a cross-rank sum)
 cudaError_t dequant_planes(const int* raw, int splits, int M, int N, const float* sx, const float* sw, float* y,

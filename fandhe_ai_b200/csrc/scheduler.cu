@@ -4,10 +4,13 @@
 // and a bounded set of requests in progress, admits from the queue into free places at the start of every step,
 // advances every request in progress by one token, finishes a request when it reaches its max_length, and
 // processes requests in the order of their ids so that runs are reproducible.  Here a place is a row of the
-// decoder's batch: a request is admitted by restarting a free row (b200_decoder_row_restart), its prompt is fed
-// one token per step (the decoder has no multi-token prefill), then the sampled tokens are fed back; rows without
-// a request sit the step out (b200_decoder_step_rows).  One step is therefore one launch of the decoder's graph
-// whatever mix of prompt and generated tokens the rows are at.
+// decoder's batch: a request is admitted by restarting a free row (b200_decoder_row_restart); all but the last token
+// of its prompt go through one multi-token prefill pass of that row (b200_decoder_prefill), the last prompt token and
+// then the sampled tokens are fed through the batched decode step; rows without a request sit the step out
+// (b200_decoder_step_rows).  With prefill switched off the prompt is fed one token per step instead.
+//
+// A request that cannot be served - a token id outside the vocabulary, no cache blocks for its row - is set apart
+// with its error and never reaches the device (take_failed, scheduler.rs:568-589, 718); the other requests go on.
 //
 // The host logic is split from the device calls so that it can be tested without a GPU: plan_step decides
 // admissions and the token every row feeds, commit_step takes the sampled tokens.  Sampling is greedy (first
@@ -45,6 +48,10 @@ struct b200_scheduler {
     bool step_planned = false;
     std::vector<int32_t> ids, sampled, restart_rows, restart_lens;
     std::vector<uint8_t> active;
+    struct Failure { uint64_t id; int32_t status; std::string message; };
+    std::deque<Failure> failed;
+    bool prefill = false;          // admitted prompts go through a multi-token prefill pass (all but the last token)
+    int32_t vocab = 0;             // 0: token ids are not checked on admission
 };
 
 namespace {
@@ -75,6 +82,8 @@ int32_t b200_scheduler_create(b200_decoder* dec, int32_t max_active, int32_t max
     s->restart_rows.assign(max_active, 0);
     s->restart_lens.assign(max_active, 0);
     if (dec) {
+        s->prefill = true;
+        s->vocab = b200_decoder_vocab(dec);
         std::vector<int32_t> lens(max_active, max_length);
         if (int32_t st = b200_decoder_begin(dec, max_active, nullptr, lens.data())) {
             delete s;
@@ -129,11 +138,20 @@ int32_t b200_scheduler_plan_step(b200_scheduler* s, int32_t* ids, uint8_t* activ
         while (!s->busy[row] && !s->queue.empty()) {
             Request r = std::move(s->queue.front());
             s->queue.pop_front();
+            if (s->vocab > 0) {                     // a request the model cannot embed is set apart, the others go on
+                bool bad = false;
+                for (int32_t t : r.tokens) bad = bad || t < 0 || t >= s->vocab;
+                if (bad) {
+                    s->failed.push_back({r.id, B200_INVALID_ARGUMENT, "the prompt holds a token id outside the vocabulary"});
+                    continue;
+                }
+            }
             if (r.prompt_len == r.max_length) {     // nothing to generate (scheduler.rs:506-515)
                 s->finished.push_back(std::move(r));
                 ++done;
                 continue;
             }
+            if (s->prefill) r.fed = r.prompt_len - 1;   // the step function prefills tokens [0, prompt_len - 1)
             s->restart_rows[nr] = row;
             s->restart_lens[nr] = r.max_length;
             ++nr;
@@ -196,11 +214,30 @@ int32_t b200_scheduler_step(b200_scheduler* s, int32_t* completed) {
         if (completed) *completed = done0;
         return B200_OK;
     }
-    for (int32_t i = 0; i < nr; ++i)
-        if (int32_t st = b200_decoder_row_restart(s->dec, rr[i], rl[i])) {
+    for (int32_t i = 0; i < nr; ++i) {
+        const int32_t row = rr[i];
+        Request& r = s->rows[row];
+        int32_t st = b200_decoder_row_restart(s->dec, row, rl[i]);
+        if (st == B200_OK && s->prefill && r.prompt_len > 1) st = b200_decoder_prefill(s->dec, row, 1, r.tokens.data(), r.prompt_len - 1);
+        if (st == B200_INVALID_ARGUMENT || st == B200_UNSUPPORTED) {
+            // this request cannot be served (no blocks for its row, ...): set it apart and free the row
+            s->failed.push_back({r.id, st, b200_last_error()});
+            s->rows[row] = Request();
+            s->busy[row] = 0;
+            s->active[row] = 0;
+            s->ids[row] = 0;
+        } else if (st != B200_OK) {
             s->step_planned = false;
             return st;
         }
+    }
+    any = false;
+    for (uint8_t b : s->active) any = any || b != 0;
+    if (!any) {
+        s->step_planned = false;
+        if (completed) *completed = done0;
+        return B200_OK;
+    }
     if (int32_t st = b200_decoder_step_rows(s->dec, s->ids.data(), s->active.data(), s->sampled.data())) {
         s->step_planned = false;
         return st;
@@ -208,6 +245,36 @@ int32_t b200_scheduler_step(b200_scheduler* s, int32_t* completed) {
     int32_t done1 = 0;
     if (int32_t st = b200_scheduler_commit_step(s, s->sampled.data(), &done1)) return st;
     if (completed) *completed = done0 + done1;
+    return B200_OK;
+}
+
+int32_t b200_scheduler_failed_len(const b200_scheduler* s) { return s ? static_cast<int32_t>(s->failed.size()) : 0; }
+
+// take_failed (scheduler.rs:718): pops the oldest request that was set apart: its id, the status code and the message.
+// *have = 0 when there is none.
+int32_t b200_scheduler_take_failed(b200_scheduler* s, uint64_t* request_id, int32_t* status, char* message, int32_t capacity,
+                                   int32_t* have) {
+    if (!s || !have) return sched_invalid("null argument");
+    *have = 0;
+    if (s->failed.empty()) return B200_OK;
+    const b200_scheduler::Failure& f = s->failed.front();
+    if (request_id) *request_id = f.id;
+    if (status) *status = f.status;
+    if (message && capacity > 0) {
+        std::strncpy(message, f.message.c_str(), size_t(capacity) - 1);
+        message[capacity - 1] = 0;
+    }
+    *have = 1;
+    s->failed.pop_front();
+    return B200_OK;
+}
+
+// Host-logic switches for a scheduler without a decoder: whether admitted prompts are prefilled (all but the last
+// token count as fed on admission) and the vocabulary size token ids are checked against (0: no check).
+int32_t b200_scheduler_configure(b200_scheduler* s, int32_t prefill, int32_t vocab) {
+    if (!s || vocab < 0) return sched_invalid("bad argument");
+    s->prefill = prefill != 0;
+    s->vocab = vocab;
     return B200_OK;
 }
 

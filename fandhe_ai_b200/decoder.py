@@ -142,6 +142,10 @@ class Decoder:
             self.load_tensor(W_GATE_UP, l, lw["wgu"])
             self.load_tensor(W_DOWN, l, lw["wdown"])
 
+    def load_safetensors(self, path) -> None:
+        """Loads every tensor from a safetensors file (int8 payloads with per-row scales, or f32 tensors)."""
+        check(lib().b200_decoder_load_safetensors(self._h, str(path).encode()))
+
     def init_random(self, seed: int = 0, std: float = 0.02) -> None:
         check(lib().b200_decoder_init_random(self._h, seed, std))
 
@@ -164,6 +168,12 @@ class Decoder:
 
     def fill_cache_random(self, seed: int = 1, std: float = 1.0) -> None:
         check(lib().b200_decoder_fill_cache_random(self._h, seed, std))
+
+    def prefill(self, ids, row0: int = 0) -> None:
+        """Multi-token prefill: ids [count, l_new] for the rows [row0, row0 + count); nothing is sampled."""
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        count, l_new = a.shape
+        check(lib().b200_decoder_prefill(self._h, row0, count, a.ctypes.data_as(C.c_void_p), l_new))
 
     def step(self, ids=None, want_next: bool = True):
         ids_c = np.ascontiguousarray(ids, dtype=np.int32) if ids is not None else None
@@ -211,3 +221,27 @@ class Decoder:
         k = ["qkv_tile", "qkv_splits", "o_tile", "o_splits", "gu_tile", "gu_splits", "down_tile", "down_splits",
              "attn_chunk_blocks", "attn_max_chunks"]
         return dict(zip(k, list(buf)))
+
+
+def write_safetensors(path, tensors: dict) -> None:
+    """Writes {name: numpy array} (float32 / int8 / any dtype of the format) as a safetensors file: 8-byte little-endian
+    header length, JSON header, contiguous data.  For tests and for exporting quantised weights."""
+    import json
+
+    names = {"float32": "F32", "int8": "I8", "uint8": "U8", "float16": "F16", "int32": "I32", "int64": "I64",
+             "float64": "F64", "bool": "BOOL", "uint16": "U16"}
+    header, blobs, at = {}, [], 0
+    for name, arr in tensors.items():
+        a = np.ascontiguousarray(arr)
+        raw = a.tobytes()
+        header[name] = {"dtype": names[str(a.dtype)], "shape": list(a.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    text = json.dumps(header, separators=(",", ":")).encode()
+    text += b" " * (-len(text) % 8)
+    with open(path, "wb") as f:
+        f.write(len(text).to_bytes(8, "little"))
+        f.write(text)
+        for raw in blobs:
+            f.write(raw)
+

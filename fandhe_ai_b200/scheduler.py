@@ -84,6 +84,23 @@ class BatchScheduler:
             return None
         return int(rid.value), buf[: n.value].copy()
 
+    @property
+    def failed_len(self) -> int:
+        return int(lib().b200_scheduler_failed_len(self._h))
+
+    def take_failed(self) -> Optional[tuple[int, str, str]]:
+        """Pops the oldest request that was set apart: (request id, error kind, message), or None."""
+        rid, status, have = C.c_uint64(), C.c_int32(), C.c_int32()
+        msg = C.create_string_buffer(512)
+        check(lib().b200_scheduler_take_failed(self._h, C.byref(rid), C.byref(status), msg, 512, C.byref(have)))
+        if not have.value:
+            return None
+        return int(rid.value), lib().b200_status_name(status.value).decode(), msg.value.decode()
+
+    def configure(self, prefill: bool, vocab: int = 0) -> None:
+        """Host-logic switches of a scheduler without a decoder (see b200_scheduler_configure)."""
+        check(lib().b200_scheduler_configure(self._h, int(prefill), vocab))
+
     def run_until_idle(self, max_steps: int = 1 << 20) -> dict[int, np.ndarray]:
         """Steps until queue and rows are empty; returns {request id: tokens}."""
         out: dict[int, np.ndarray] = {}

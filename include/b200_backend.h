@@ -377,6 +377,24 @@ int32_t b200_decoder_destroy(b200_decoder* dec);
  * device (one scale per full row) and this rank's shard is kept. */
 int32_t b200_decoder_load_tensor(b200_decoder* dec, int32_t which, int32_t layer, const float* host, int64_t rows,
                                  int64_t cols);
+/* The same for a matrix that is already quantised (int8 [rows, cols] and one f32 scale per row, both on the host):
+ * nothing is re-quantised, this rank's shard is kept. */
+int32_t b200_decoder_load_tensor_i8(b200_decoder* dec, int32_t which, int32_t layer, const int8_t* q_host,
+                                    const float* scale_host, int64_t rows, int64_t cols);
+/* Weight wire format: a safetensors file (or byte buffer) holding every tensor of the decoder.  Extends the
+ * reference's loader (crates/onnx-interop/src/st_load.rs:128-222, 433-562; crates/facade/src/interop/safetensors.rs:182),
+ * which rejects the I8 dtype today (st_load.rs:624), with per-output-channel int8 weights: for each matrix M of
+ * {"lm_head", "layers.<l>.wqkv", "layers.<l>.wo", "layers.<l>.wgu", "layers.<l>.wdown"} either "M.qweight" I8
+ * [rows, cols] with "M.scale" F32 [rows], or "M.weight" F32 [rows, cols] (quantised on the device); plus
+ * "embed.weight", "final_norm.weight", "layers.<l>.attn_norm.weight", "layers.<l>.mlp_norm.weight" in F32.
+ * The reference's rules hold: layout validated first, no renaming or transposition, nothing skipped silently
+ * (a wrong dtype or shape and an unknown tensor are errors), all missing names reported in one error. */
+int32_t b200_decoder_load_safetensors(b200_decoder* dec, const char* path);
+int32_t b200_decoder_load_safetensors_bytes(b200_decoder* dec, const uint8_t* bytes, size_t len);
+/* validate_safetensors_layout_from_bytes (crates/onnx-interop/src/st_load.rs:128-132): header and layout only (header
+ * length, JSON, offsets contiguous from 0 to the end of the buffer, byte length = shape x dtype width); any dtype of the
+ * format; needs no device. */
+int32_t b200_safetensors_validate(const uint8_t* bytes, size_t len, uint64_t* n_tensors);
 /* Synthetic weights N(0, std^2) from a counter-based generator (norm weights 1), identical on every rank. */
 int32_t b200_decoder_init_random(b200_decoder* dec, uint64_t seed, float std);
 /* 128-byte NCCL unique id (rank 0 makes it, the launcher hands it to every rank) and communicator set-up. */
@@ -416,6 +434,14 @@ int32_t b200_decoder_logits(b200_decoder* dec, float* host, uint64_t capacity_el
  * batching over per-row lengths needs (the kernels already take seq_lens[B];
  * docs/device-resident-kv-paged-attention-design.md:51). */
 int32_t b200_decoder_step_rows(b200_decoder* dec, const int32_t* ids, const uint8_t* active, int32_t* next_ids);
+/* Multi-token prefill: the rows [row0, row0 + count) each consume l_new tokens (ids [count, l_new], host) in one
+ * pass over count * l_new token rows: GEMMs at that many rows, every token's K / V appended, attention under the
+ * reference's mask j <= seq_len - l_new + i (crates/backend-cpu/src/paged_kv.rs:137-140;
+ * docs/device-resident-kv-paged-attention-design.md:149).  The rows' lengths grow by l_new; nothing is sampled (feed the
+ * last prompt token through b200_decoder_step for that).  Long prompts are consumed in chunks internally.  The
+ * counterpart of the prefill forward of generate() (crates/autodiff/src/generate/mod.rs:500-560). */
+int32_t b200_decoder_prefill(b200_decoder* dec, int32_t row0, int32_t count, const int32_t* ids, int32_t l_new);
+int32_t b200_decoder_vocab(const b200_decoder* dec);
 /* Between steps: empties row `row` (its blocks return to the free stack) and reserves blocks for a new sequence
  * of up to max_total_len tokens (at most the largest length given to b200_decoder_begin). */
 int32_t b200_decoder_row_restart(b200_decoder* dec, int32_t row, int32_t max_total_len);
@@ -444,7 +470,8 @@ int32_t b200_decoder_time_attention(b200_decoder* dec, int32_t iters, float* ms_
 /* ------------------------------------------------------------------ continuous batching
  * BatchScheduler of the reference (crates/autodiff/src/generate/scheduler.rs:395-): a FIFO queue of requests and
  * at most max_active requests in progress, one decoder row each; a step admits queued requests into free rows and
- * advances every request in progress by one token (prompt tokens are fed one per step, then the greedy samples);
+ * advances every request in progress by one token (an admitted prompt is prefilled up to its last token in one
+ * multi-token pass; the last prompt token and then the greedy samples go through the batched decode step);
  * a request finishes when it holds max_length tokens.  Rows and requests are processed in ascending order, so a run
  * is reproducible.  With a decoder, create calls b200_decoder_begin(dec, max_active, ..., max_length per row). */
 typedef struct b200_scheduler b200_scheduler;
@@ -465,6 +492,17 @@ int32_t b200_scheduler_step(b200_scheduler* s, int32_t* completed);
 int32_t b200_scheduler_plan_step(b200_scheduler* s, int32_t* ids, uint8_t* active, int32_t* restart_rows,
                                  int32_t* restart_lens, int32_t* n_restart, int32_t* completed_without_forward);
 int32_t b200_scheduler_commit_step(b200_scheduler* s, const int32_t* sampled, int32_t* completed);
+/* Requests set apart because they could not be served (a prompt token outside the vocabulary, no cache blocks for
+ * the row): the reference keeps per-request failures out of step()'s error path in the same way
+ * (crates/autodiff/src/generate/scheduler.rs:568-589, take_failed :718).  take_failed pops the oldest one: its id,
+ * the status code and the message; *have = 0 when there is none. */
+int32_t b200_scheduler_failed_len(const b200_scheduler* s);
+int32_t b200_scheduler_take_failed(b200_scheduler* s, uint64_t* request_id, int32_t* status, char* message,
+                                   int32_t capacity, int32_t* have);
+/* For a scheduler without a decoder (host logic only): whether admitted prompts count as prefilled up to their last
+ * token, and the vocabulary size that token ids are checked against on admission (0: no check).  With a decoder
+ * both are set by create (prefill on, the decoder's vocabulary). */
+int32_t b200_scheduler_configure(b200_scheduler* s, int32_t prefill, int32_t vocab);
 /* Pops the oldest finished request (prompt + generated tokens); *len = -1 when there is none. */
 int32_t b200_scheduler_take_finished(b200_scheduler* s, uint64_t* request_id, int32_t* tokens, int32_t capacity,
                                      int32_t* len);

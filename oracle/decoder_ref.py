@@ -182,6 +182,54 @@ class DecoderRef:
             np.array([O.greedy_argmax(logits[r]) for r in range(b)], np.int32)
         return logits, nxt
 
+    def prefill(self, ids):
+        """ids [B, L]: every row consumes L tokens in one pass over B * L token rows (row m = b * L + i): the K / V of
+        all of them are appended and row (b, i) attends to the keys j <= seq_len - L + i, the reference's mask rule
+        (crates/backend-cpu/src/paged_kv.rs:137-140).  Nothing is sampled.  The arithmetic per token row is that of
+        step(); in kernel order the launch shape of the row kernels follows the number of token rows."""
+        c = self.cfg
+        d, dh, hq, hkv, f = c["d_model"], c["head_dim"], c["n_heads"], c["n_kv_heads"], c["d_ff"]
+        eps = c.get("rms_eps", 1e-5)
+        ids = np.asarray(ids)
+        b, L = ids.shape
+        assert b == self.batch
+        m = b * L
+        h = self.w["embed"][ids.reshape(-1)].astype(np.float32)
+        pos = (self.seq[:, None] + np.arange(L)[None, :]).reshape(-1)
+        row_of = np.repeat(np.arange(b), L)
+        attention = O.paged_attention_kernel_order if self.exact else O.paged_attention
+        for l, (lw, lq) in enumerate(zip(self.w["layers"], self.q["layers"])):
+            lb = self.blas["layers"][l] if self.blas else {}
+            xn = self._norm(h, lw["attn_norm"], eps, first=(l == 0))
+            xq, sx = O.quantize_i8_per_row(xn)
+            qkv = O.epilogue_scaled(self._acc(xq, lq["wqkv"], lb.get("wqkv")), sx, True, lq["wqkv"][1], True)
+            q = np.empty((m, hq * dh), np.float32)
+            k_new = np.empty((m, hkv * dh), np.float32)
+            for r in range(m):
+                q[r] = O.rope_apply(qkv[r, : hq * dh], hq, dh, self.cos[pos[r]], self.sin[pos[r]])
+                k_new[r] = O.rope_apply(qkv[r, hq * dh:(hq + hkv) * dh], hkv, dh, self.cos[pos[r]], self.sin[pos[r]])
+            v_new = np.ascontiguousarray(qkv[:, (hq + hkv) * dh:])
+            slots = [int(self.tables[row_of[r], pos[r] // self.bs]) * self.bs + int(pos[r] % self.bs) for r in range(m)]
+            O.paged_kv_append(k_new, v_new, self.k[l], self.v[l], slots, hkv * dh, True)
+            if l + 1 == len(self.w["layers"]):
+                break               # the last layer's K / V rows are in the cache: nothing else of the pass is used
+            a = attention(q.reshape(b, L, -1), self.k[l], self.v[l], self.tables, self.seq + L, batch=b, l_new=L,
+                          num_q_heads=hq, num_kv_heads=hkv, head_dim=dh, block_size=self.bs,
+                          num_blocks=self.nblk, max_blocks_per_seq=self.mbps,
+                          scale=float(np.float32(1.0) / np.sqrt(np.float32(dh))), kv_bf16=True).reshape(m, -1)
+            aq, sa = O.quantize_i8_per_row(a)
+            h = (O.epilogue_scaled(self._acc(aq, lq["wo"], lb.get("wo")), sa, True, lq["wo"][1], True) + h).astype(np.float32)
+            xn = self._norm(h, lw["mlp_norm"], eps, first=False)
+            xq, sx = O.quantize_i8_per_row(xn)
+            acc = self._acc(xq, lq["wgu"], lb.get("wgu"))
+            if self.exact:
+                act = O.epilogue_det(acc, sx, lq["wgu"][1], act=O.ACT_SILU_GATE)
+            else:
+                act = O.epilogue_scaled(acc, sx, True, lq["wgu"][1], True, act=O.ACT_SILU_GATE)
+            fq, sf = O.quantize_i8_per_row(act)
+            h = (O.epilogue_scaled(self._acc(fq, lq["wdown"], lb.get("wdown")), sf, True, lq["wdown"][1], True) + h).astype(np.float32)
+        self.seq += L
+
     def generate(self, prompt, max_length: int):
         """Greedy generate: returns (ids [B, max_length], logits of every step that sampled a token)."""
         prompt = np.asarray(prompt, np.int32)

@@ -260,3 +260,126 @@ def test_step_api_matches_generate_and_feeds_ids_from_the_host(be):
         assert dec.launches_per_step == 2 + cfg["n_layers"] * (9 if fused_rope else 10) + 2
     finally:
         dec.close()
+
+
+def test_int8_weights_from_a_safetensors_file(be, tmp_path):
+    """The weight wire format: int8 payloads with per-row scales (and, alternatively, f32 tensors) in a safetensors
+    file give the decoder the same state as loading the f32 tensors one by one: identical logits, and identical to
+    the kernel-order CPU decoder."""
+    from fandhe_ai_b200 import BackendError
+    from fandhe_ai_b200.decoder import write_safetensors
+
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=512, max_seq_len=32)
+    weights = make_weights(cfg, seed=51)
+    as_f32 = {"embed.weight": weights["embed"], "final_norm.weight": weights["final_norm"], "lm_head.weight": weights["lm_head"]}
+    as_i8 = {"embed.weight": weights["embed"], "final_norm.weight": weights["final_norm"]}
+    as_i8["lm_head.qweight"], as_i8["lm_head.scale"] = O.quantize_i8_per_row(weights["lm_head"])
+    for l, lw in enumerate(weights["layers"]):
+        for norm in ("attn_norm", "mlp_norm"):
+            as_f32[f"layers.{l}.{norm}.weight"] = lw[norm]
+            as_i8[f"layers.{l}.{norm}.weight"] = lw[norm]
+        for m in ("wqkv", "wo", "wgu", "wdown"):
+            as_f32[f"layers.{l}.{m}.weight"] = lw[m]
+            as_i8[f"layers.{l}.{m}.qweight"], as_i8[f"layers.{l}.{m}.scale"] = O.quantize_i8_per_row(lw[m])
+    write_safetensors(tmp_path / "f32.safetensors", as_f32)
+    write_safetensors(tmp_path / "i8.safetensors", as_i8)
+    ids = np.random.default_rng(52).integers(0, cfg["vocab"], (6, 3)).astype(np.int32)
+    ref = DecoderRef(cfg, weights, exact=True)
+    ref.begin(3)
+    want = [ref.step(ids[t])[0] for t in range(6)]
+    for source in ("i8.safetensors", "f32.safetensors"):
+        dec = make_decoder(be, cfg, 3)
+        try:
+            dec.load_safetensors(tmp_path / source)
+            dec.begin(3, [6] * 3)
+            for t in range(6):
+                dec.step(ids[t])
+                assert np.array_equal(dec.logits(), want[t]), (source, t)
+        finally:
+            dec.close()
+    # nothing is skipped silently: every missing name is reported at once, wrong dtypes and strangers are errors
+    dec = make_decoder(be, cfg, 3)
+    try:
+        broken = {k: v for k, v in as_i8.items() if k not in ("layers.1.wo.scale", "final_norm.weight")}
+        write_safetensors(tmp_path / "missing.safetensors", broken)
+        with pytest.raises(BackendError) as e:
+            dec.load_safetensors(tmp_path / "missing.safetensors")
+        assert e.value.kind == "InvalidArgument" and "final_norm.weight" in e.value.message and "layers.1.wo" in e.value.message
+        wrong = dict(as_i8)
+        wrong["layers.0.wgu.qweight"] = wrong["layers.0.wgu.qweight"].astype(np.uint8)
+        write_safetensors(tmp_path / "dtype.safetensors", wrong)
+        with pytest.raises(BackendError) as e:
+            dec.load_safetensors(tmp_path / "dtype.safetensors")
+        assert e.value.kind == "Unsupported" and "U8" in e.value.message
+        write_safetensors(tmp_path / "extra.safetensors", dict(as_i8, **{"rotary.inv_freq": np.ones(4, np.float32)}))
+        with pytest.raises(BackendError) as e:
+            dec.load_safetensors(tmp_path / "extra.safetensors")
+        assert "rotary.inv_freq" in e.value.message
+        shape = dict(as_i8)
+        shape["layers.0.wo.qweight"] = shape["layers.0.wo.qweight"][:, :-16]
+        write_safetensors(tmp_path / "shape.safetensors", shape)
+        with pytest.raises(BackendError) as e:
+            dec.load_safetensors(tmp_path / "shape.safetensors")
+        assert e.value.kind == "ShapeMismatch"
+        assert not be.poisoned
+    finally:
+        dec.close()
+
+
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_multi_token_prefill(be, head_dim):
+    """Prefill in multi-token passes (GEMMs at count x l_new rows, the reference's mask j <= seq_len - l_new + i) leaves
+    the cache in the state that feeding the same tokens one per step leaves it in.  head_dim 64: the logits of the
+    following step equal the kernel-order CPU decoder's, bit for bit (which itself prefilled or not gives the same
+    bits, tests/test_kernel_order_cpu.py).  head_dim 128 (tensor-core attention per query row): equal, bit for bit,
+    to the device fed token by token, and within the usual bound of the sequential CPU decoder."""
+    cfg = dict(n_layers=3, d_model=256, n_heads=256 // head_dim, n_kv_heads=128 // head_dim, head_dim=head_dim, d_ff=512,
+               vocab=512, max_seq_len=48)
+    weights = make_weights(cfg, seed=71)
+    ids = np.random.default_rng(72).integers(0, cfg["vocab"], (3, 24)).astype(np.int32)
+    ref = DecoderRef(cfg, weights, exact=(head_dim == 64))
+    ref.begin(3)
+    ref.prefill(ids[:, :5])
+    ref.prefill(ids[:, 5:19])
+    want = [ref.step(ids[:, t])[0] for t in range(19, 24)]
+    dec = make_decoder(be, cfg, 3)
+    try:
+        dec.load_weights(weights)
+        dec.begin(3, [24] * 3)
+        for t in range(19):
+            dec.step(ids[:, t], want_next=False)
+        by_steps = []
+        for t in range(19, 24):
+            dec.step(ids[:, t])
+            by_steps.append(dec.logits())
+        dec.begin(3, [24] * 3)
+        dec.prefill(ids[:, :5])
+        dec.prefill(ids[:, 5:19])
+        for i, t in enumerate(range(19, 24)):
+            dec.step(ids[:, t])
+            got = dec.logits()
+            assert np.array_equal(got, by_steps[i]), (i, float(np.abs(got - by_steps[i]).max()))
+            if head_dim == 64:
+                assert np.array_equal(got, want[i]), i
+            else:
+                assert float(np.abs(got - want[i]).max()) < 0.05 * float(np.abs(want[i]).max()), i
+        with pytest.raises(Exception):
+            dec.prefill(ids[:, :2])                              # the reserved length is used up
+    finally:
+        dec.close()
+
+
+def test_prefill_of_a_long_prompt_runs_in_chunks(be):
+    """4 rows x 700 tokens exceed one pass (2048 token rows): the prompt goes through in chunks of 512 tokens, each
+    chunk attending to the cache the earlier ones left; generate() must give the CPU decoder's ids."""
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=512, max_seq_len=720)
+    weights = make_weights(cfg, seed=81)
+    prompt = np.random.default_rng(82).integers(0, cfg["vocab"], (4, 701)).astype(np.int32)
+    want, _ = DecoderRef(cfg, weights, exact=True).generate(prompt, 712)
+    dec = make_decoder(be, cfg, 4)
+    try:
+        dec.load_weights(weights)
+        got = dec.generate(prompt, 712)
+    finally:
+        dec.close()
+    assert np.array_equal(got, want), np.argwhere(got != want)[:4].tolist()

@@ -82,3 +82,31 @@ def test_limits_and_invalid_requests_leave_the_state_unchanged():
         s.plan_step()
     with pytest.raises(BackendError):        # the device half needs a decoder
         s.step()
+
+
+def test_with_prefill_an_admitted_prompt_counts_as_fed_up_to_its_last_token():
+    s = BatchScheduler(None, 2, 4, 16)
+    s.configure(prefill=True)
+    s.submit([7, 8, 9], 6)
+    s.submit([5], 3)
+    out, trace = drive(s, lambda row, tok: tok + 100)
+    # the first batched step already feeds the LAST prompt token of request 1 (7 and 8 go through the prefill pass)
+    assert [int(t[0][0]) for t in trace] == [9, 109, 209]
+    assert [int(t[0][1]) for t in trace[:2]] == [5, 105]
+    assert out == {1: [7, 8, 9, 109, 209, 309], 2: [5, 105, 205]}
+
+
+def test_a_request_with_a_token_outside_the_vocabulary_is_set_apart_and_the_others_go_on():
+    s = BatchScheduler(None, 2, 8, 8)
+    s.configure(prefill=False, vocab=50)
+    good1 = s.submit([1, 2], 4)
+    bad = s.submit([3, 50], 4)              # 50 is outside [0, 50)
+    worse = s.submit([-1], 4)
+    good2 = s.submit([4], 3)
+    out, trace = drive(s, lambda row, tok: (tok + 1) % 50)
+    assert sorted(out) == [good1, good2] and s.failed_len == 2
+    # the failed requests never took a row: the second row went to the next good request at once
+    assert trace[0][2] == [(0, 4), (1, 3)]
+    first, second = s.take_failed(), s.take_failed()
+    assert first[0] == bad and second[0] == worse and first[1] == "InvalidArgument" and "vocabulary" in first[2]
+    assert s.take_failed() is None and s.failed_len == 0

@@ -1,4 +1,5 @@
-"""Continuous batching on the GPU: a request's tokens do not depend on what the other rows are doing."""
+"""Continuous batching on the GPU: every request's tokens equal those of the CPU decoder run on that request alone,
+whatever the other rows are doing; requests that cannot be served are set apart."""
 import numpy as np
 import pytest
 
@@ -73,5 +74,44 @@ def test_full_rows_match_generate(be):
         s.close()
         for i, rid in enumerate(ids):
             assert np.array_equal(got[rid], want[i]), i
+    finally:
+        dec.close()
+
+
+CFG64 = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=512, max_seq_len=40)
+
+
+def test_requests_through_shared_rows_match_the_cpu_decoder_request_by_request(be):
+    """Each request against the kernel-order CPU decoder (oracle/decoder_ref.py, exact=True) run on that request
+    alone with batch 1: identical token ids.  Prompts of different lengths are prefilled on admission while other rows
+    are in the middle of their generation; more requests than rows."""
+    from oracle.decoder_ref import DecoderRef, make_weights
+
+    slots, max_len = 3, 40
+    weights = make_weights(CFG64, seed=61)
+    rng = np.random.default_rng(62)
+    reqs = [(rng.integers(0, CFG64["vocab"], int(rng.integers(1, 14))).astype(np.int32), int(rng.integers(15, max_len + 1)))
+            for _ in range(7)]
+    want = []
+    for prompt, length in reqs:
+        ids, _ = DecoderRef(CFG64, weights, exact=True).generate(prompt[None, :], length)
+        want.append(ids[0])
+    dc = DecoderConfig(CFG64["n_layers"], CFG64["d_model"], CFG64["n_heads"], CFG64["n_kv_heads"], CFG64["head_dim"],
+                       CFG64["d_ff"], CFG64["vocab"], max_batch=slots, max_seq_len=max_len, block_size=16,
+                       num_blocks=slots * 3, use_graph=1)
+    dec = Decoder(be, dc)
+    try:
+        dec.load_weights(weights)
+        s = BatchScheduler(dec, slots, 16, max_len)
+        ids = [s.submit(p, n) for p, n in reqs[:4]]
+        bad = s.submit([3, CFG64["vocab"]], 10)                  # a token the model cannot embed
+        ids += [s.submit(p, n) for p, n in reqs[4:]]
+        got = s.run_until_idle()
+        assert sorted(got) == sorted(ids)
+        for rid, w in zip(ids, want):
+            assert np.array_equal(got[rid], w), (rid, got[rid].tolist(), w.tolist())
+        failed = s.take_failed()
+        assert failed is not None and failed[0] == bad and failed[1] == "InvalidArgument" and s.take_failed() is None
+        s.close()
     finally:
         dec.close()
