@@ -354,8 +354,8 @@ void* b200_ctx_stream(b200_ctx* ctx) { return ctx ? static_cast<void*>(ctx->stre
 
 int32_t b200_gemm_tuning(b200_ctx* ctx, int32_t tile_n, int32_t splits) {
     if (!ctx) return fail(B200_INVALID_ARGUMENT, "gemm_tuning: context is null");
-    if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256)
-        return fail(B200_INVALID_ARGUMENT, "gemm_tuning: tile_n must be 0 (heuristic), 64, 128 or 256");
+    if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 224 && tile_n != 256)
+        return fail(B200_INVALID_ARGUMENT, "gemm_tuning: tile_n must be 0 (heuristic), 64, 128, 224 or 256");
     if (splits < 0 || splits > 64) return fail(B200_INVALID_ARGUMENT, "gemm_tuning: splits must be in 0..64");
     ctx->tune_bn = tile_n;
     ctx->tune_splits = splits;

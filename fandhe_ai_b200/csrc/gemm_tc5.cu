@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, KernelArgs p) {
     constexpr int kBBytes = BN * kBK;
     constexpr int kStageBytes = kABytes + kBBytes;
-    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kTmemCols = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;     // a power of two
     constexpr uint32_t kIdesc = kInt8 ? umma_idesc(1, 2, kBM, BN) : umma_idesc(0, 1, kBM, BN);
 
     extern __shared__ uint8_t smem_dyn[];
@@ -608,8 +608,20 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     const int m_tiles = (M + kBM - 1) / kBM;
     const int kb_total = (K + kBK - 1) / kBK;
     int bn = want_bn;
-    if (bn <= 0) bn = (M >= 512) ? 256 : 128;
-    if (bn != 64 && bn != 128 && bn != 256) return fail("gemm: tile width must be 64, 128 or 256");
+    if (bn <= 0) {
+        bn = (M >= 512) ? 256 : 128;
+        const int sms = current_sm_count();
+        const int tiles128 = (N + 127) / 128;
+        if (m_tiles == 1 && !gate) {
+            // One row of tiles (decode shapes): what counts is how evenly the weight stream spreads over the SMs.
+            // 224-wide tiles when they turn a grid of more than one CTA per SM into a single even wave ...
+            if (tiles128 > sms && N % 224 == 0 && N / 224 <= sms) bn = 224;
+            // ... and 64-wide tiles for narrow outputs, so that K is cut into fewer, longer slices per tile
+            else if (tiles128 >= 16 && 4 * tiles128 <= sms && N % 64 == 0) bn = 64;
+        }
+    }
+    if (bn != 64 && bn != 128 && bn != 224 && bn != 256) return fail("gemm: tile width must be 64, 128, 224 or 256");
+    if (gate && bn == 224) return fail("gemm: the gated layout takes tile widths 64, 128 or 256");
     const int n_out = gate ? N / 2 : N;
     const int out_cols = gate ? bn / 2 : bn;
     const int tiles = m_tiles * ((n_out + out_cols - 1) / out_cols);
@@ -640,7 +652,7 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     plan->splits = splits;
     const int stage_bytes = kABytes + bn * kBK;
     // Small grids keep two CTAs per SM resident (about 100 KB each); big ones take the whole SM.
-    int stages = (m_tiles * 1 >= 4 || bn == 256) ? (200 * 1024) / stage_bytes : (100 * 1024) / stage_bytes;
+    int stages = (m_tiles * 1 >= 4 || bn >= 224) ? (200 * 1024) / stage_bytes : (100 * 1024) / stage_bytes;
     if (stages > 8) stages = 8;
     if (stages < 2) stages = 2;
     plan->stages = stages;
@@ -692,6 +704,7 @@ cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* 
     switch (plan.bn) {
         case 64: return i8 ? launch_t<64, true>(plan, args, stream) : launch_t<64, false>(plan, args, stream);
         case 128: return i8 ? launch_t<128, true>(plan, args, stream) : launch_t<128, false>(plan, args, stream);
+        case 224: return i8 ? launch_t<224, true>(plan, args, stream) : launch_t<224, false>(plan, args, stream);
         case 256: return i8 ? launch_t<256, true>(plan, args, stream) : launch_t<256, false>(plan, args, stream);
         default: return cudaErrorInvalidValue;
     }

@@ -111,7 +111,7 @@ uint64_t b200_ctx_generation(const b200_ctx* ctx);
 /* The CUDA stream of the context as an opaque pointer (for event timing by callers). */
 void* b200_ctx_stream(b200_ctx* ctx);
 
-/* Overrides the GEMM tile width (64/128/256) and split-K count for later calls on this
+/* Overrides the GEMM tile width (64/128/224/256) and split-K count for later calls on this
  * context; 0 restores the heuristic.  The counterpart of the reference's per-shape kernel
  * selection (crates/backend-cuda/src/gemm_auto.rs:1829-1892), exposed for tests and tuning. */
 int32_t b200_gemm_tuning(b200_ctx* ctx, int32_t tile_n, int32_t splits);

@@ -65,6 +65,7 @@ def rand_i8(seed, shape):
     (128, 128, 128, 0, 0), (128, 4096, 4096, 0, 0), (1, 4096, 4096, 0, 0), (16, 1024, 4096, 64, 0),
     (100, 272, 2064, 0, 0), (300, 1040, 528, 128, 1), (128, 512, 4096, 128, 8), (128, 512, 1024, 256, 3),
     (257, 256, 384, 256, 1), (1024, 512, 512, 256, 1), (128, 256, 16, 0, 0),
+    (128, 28672, 256, 0, 0), (100, 448, 2064, 224, 2), (128, 672, 1024, 224, 4), (300, 1008, 528, 224, 1),
 ])
 def test_gemm_i8_s32_is_bit_exact(be, m, n, k, tile, splits):
     a, w = rand_i8(m + n, (m, k)), rand_i8(k + 1, (n, k))
@@ -74,6 +75,16 @@ def test_gemm_i8_s32_is_bit_exact(be, m, n, k, tile, splits):
     finally:
         be.gemm_tuning(0, 0)
     assert np.array_equal(acc, O.gemm_i8_s32(a, w))
+
+
+def test_decode_shapes_pick_even_waves(be):
+    """One row of tiles: 224-wide tiles when 128-wide ones would need more CTAs than SMs (the gate / up projection of
+    the 8B shape: 28672 / 224 = 128 CTAs), 64-wide tiles with fewer K slices for narrow outputs."""
+    assert be.gemm_plan_info(128, 28672, 4096, fused=False)["tile"] == 224
+    info = be.gemm_plan_info(128, 4096, 4096, fused=False)
+    assert info["tile"] == 64 and info["splits"] == 4 and info["cluster"] == 1
+    assert be.gemm_plan_info(128, 6144, 4096, fused=False)["tile"] == 128
+    assert be.gemm_plan_info(128, 768, 4096, fused=False)["tile"] == 128        # one head per tile stays possible
 
 
 def test_gemm_i8_extreme_values_and_k128_chain(be):
