@@ -687,7 +687,7 @@ int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int3
         if (e != cudaSuccess) return fail(B200_INVALID_ARGUMENT, why);
         if (!fused && ctx->tune_splits == 0) gemm_plan_make_persistent(&plan, ctx->sm_count, false);
     }
-    const int v[6] = {plan.bn, plan.splits, plan.cluster, plan.persist, plan.persist ? plan.grid : 0, plan.stages};
+    const int v[6] = {plan.bn, plan.splits, plan.cluster, plan.persist ? (plan.pair ? 2 : 1) : 0, plan.persist ? plan.grid : 0, plan.stages};
     for (int i = 0; i < 6; ++i) out6[i] = v[i];
     return B200_OK;
 }

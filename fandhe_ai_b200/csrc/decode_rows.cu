@@ -438,6 +438,80 @@ quant_rows_wide_kernel(const float* __restrict__ x, int n, int8_t* __restrict__ 
     wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * n, sx_out + m);
 }
 
+// ------------------------------------------------------------------------------------ rows under a global scale
+// Tensor parallelism with exact integer sums: the per-token scale of a row that is split over the ranks comes from
+// the maximum over ALL ranks' columns, so the row maximum is taken first (and merged across the ranks by the
+// caller), and the quantiser then uses the merged maximum instead of the local one.
+template <int VPT>
+__global__ void __launch_bounds__(kWideThreads)
+rows_amax_wide_kernel(const float* __restrict__ x, int n, float* __restrict__ amax_out) {
+    __shared__ WideShared sh;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, groups = n / 4;
+    const float* src = x + static_cast<size_t>(m) * n;
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) amax = fmaxf(amax, amax4(*reinterpret_cast<const float4*>(src + 4 * g)));
+    }
+    amax = wide_max(amax, sh);
+    if (threadIdx.x == 0) amax_out[m] = amax;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kWideThreads)
+quant_rows_scaled_wide_kernel(const float* __restrict__ x, int n, const float* __restrict__ amax_in, int8_t* __restrict__ xq,
+                              float* __restrict__ sx_out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, groups = n / 4;
+    const float* src = x + static_cast<size_t>(m) * n;
+    const float s = amax_in[m] / 127.0f;
+    if (threadIdx.x == 0) sx_out[m] = s;
+    uint32_t* q4 = reinterpret_cast<uint32_t*>(xq + static_cast<size_t>(m) * n);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) q4[g] = quant4(*reinterpret_cast<const float4*>(src + 4 * g), s);
+    }
+}
+
+// a = silu(gate) * up of this rank's columns as f32 (the arithmetic of gate_quant_wide) and the row maximum of |a|
+template <int VPT>
+__global__ void __launch_bounds__(kWideThreads)
+gate_f32_wide_kernel(const int* __restrict__ raw, int splits, int M, int F, const float* __restrict__ sx_in,
+                     const float* __restrict__ sw, float* __restrict__ out, float* __restrict__ amax_out) {
+    __shared__ WideShared sh;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, groups = F / 4;
+    const size_t plane = static_cast<size_t>(M) * 2 * F;
+    const size_t base = static_cast<size_t>(m) * 2 * F;
+    const float sa = sx_in[m];
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int g = threadIdx.x + k * blockDim.x;
+        if (g < groups) {
+            const int4 ag = sum_planes4(raw, splits, plane, base + 4 * g);
+            const int4 au = sum_planes4(raw, splits, plane, base + F + 4 * g);
+            const float4 wg = *reinterpret_cast<const float4*>(sw + 4 * g);
+            const float4 wu = *reinterpret_cast<const float4*>(sw + F + 4 * g);
+            float4 v;
+            v.x = __fmul_rn(silu(fmaf(static_cast<float>(ag.x), sa * wg.x, 0.0f)), fmaf(static_cast<float>(au.x), sa * wu.x, 0.0f));
+            v.y = __fmul_rn(silu(fmaf(static_cast<float>(ag.y), sa * wg.y, 0.0f)), fmaf(static_cast<float>(au.y), sa * wu.y, 0.0f));
+            v.z = __fmul_rn(silu(fmaf(static_cast<float>(ag.z), sa * wg.z, 0.0f)), fmaf(static_cast<float>(au.z), sa * wu.z, 0.0f));
+            v.w = __fmul_rn(silu(fmaf(static_cast<float>(ag.w), sa * wg.w, 0.0f)), fmaf(static_cast<float>(au.w), sa * wu.w, 0.0f));
+            *reinterpret_cast<float4*>(out + static_cast<size_t>(m) * F + 4 * g) = v;
+            amax = fmaxf(amax, amax4(v));
+        }
+    }
+    amax = wide_max(amax, sh);
+    if (threadIdx.x == 0) amax_out[m] = amax;
+}
+
 // ------------------------------------------------------------------------------------ cross-GPU finish
 // Tensor parallel, after a row-parallel GEMM: every rank holds an f32 partial [M, d] of the layer output in its
 // exchange block.  Rank r owns the token rows [r * rows, (r + 1) * rows): it adds the partials of its rows over
@@ -702,6 +776,44 @@ cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int 
     return launch_ex(qkv_rope_append_par_kernel, grid, dim3(kThreads), 0, s, 1, true, raw, splits, M, rows_per_seq, hq, hkv, dh, hpc, sx_in,
                      sw, cos_t, sin_t, max_pos, positions, active, block_tables, max_blocks_per_seq, block_size, num_blocks,
                      q_out, k_pool, v_pool, err);
+}
+
+cudaError_t rows_amax(const float* x, int M, int n, float* amax_out, cudaStream_t s) {
+    int vpt, threads;
+    wide_shape(n, &vpt, &threads, M);
+    if (vpt == 1) return launch_ex(rows_amax_wide_kernel<1>, dim3(M), dim3(threads), 0, s, 1, true, x, n, amax_out);
+    if (vpt == 2) return launch_ex(rows_amax_wide_kernel<2>, dim3(M), dim3(threads), 0, s, 1, true, x, n, amax_out);
+    if (vpt == 4) return launch_ex(rows_amax_wide_kernel<4>, dim3(M), dim3(threads), 0, s, 1, true, x, n, amax_out);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t quantize_rows_with_amax(const float* x, int M, int n, const float* amax, int8_t* xq, float* sx_out, cudaStream_t s) {
+    int vpt, threads;
+    wide_shape(n, &vpt, &threads, M);
+    if (vpt == 1) return launch_ex(quant_rows_scaled_wide_kernel<1>, dim3(M), dim3(threads), 0, s, 1, true, x, n, amax, xq, sx_out);
+    if (vpt == 2) return launch_ex(quant_rows_scaled_wide_kernel<2>, dim3(M), dim3(threads), 0, s, 1, true, x, n, amax, xq, sx_out);
+    if (vpt == 4) return launch_ex(quant_rows_scaled_wide_kernel<4>, dim3(M), dim3(threads), 0, s, 1, true, x, n, amax, xq, sx_out);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t gate_rows_f32(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, float* out,
+                          float* amax_out, cudaStream_t s) {
+    int vpt, threads;
+    wide_shape(F, &vpt, &threads, M);
+#define B200_GATE_F32(V)                                                                                           \
+    return launch_ex(gate_f32_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, F, sx_in, sw, \
+                     out, amax_out)
+    if (vpt == 1) B200_GATE_F32(1);
+    if (vpt == 2) B200_GATE_F32(2);
+    if (vpt == 4) B200_GATE_F32(4);
+#undef B200_GATE_F32
+    return cudaErrorInvalidValue;
+}
+
+bool rows_scaled_supported(int n) {
+    int vpt, threads;
+    wide_shape(n, &vpt, &threads);
+    return vpt != 0;
 }
 
 bool tp_finish_supported(int d) {

@@ -309,6 +309,11 @@ struct b200_decoder {
     uint32_t* tp_epoch = nullptr;               // [0] call counter, [1] CTA arrival counter of the finish kernel
     bool tp_exchange = false;                   // peers are mapped: use the finish kernel instead of ncclAllReduce
     uint64_t tp_timeout_ns = 0;                 // bound of every cross-GPU wait (0: the kernels' default of two seconds)
+    // exact integer sums under tensor parallelism (cfg.tp_exact_int8): merged row maxima, f32 rows before the
+    // quantiser, the int32 sum of the planes that goes through the all-reduce
+    float* tp_amax = nullptr;                   // [M]
+    float* tp_rows_f32 = nullptr;               // [M, max(f_l, hq_l * head_dim)]
+    int* tp_acc = nullptr;                      // [M, d_model]
     uint64_t launches_per_step = 0;
     // multi-token prefill: buffers for up to prefill_rows token rows (grown on demand)
     struct Prefill {
@@ -362,6 +367,9 @@ int32_t check_config(const b200_decoder_config& c) {
         c.vocab % 16 != 0 || (c.head_dim * (c.n_heads + 2 * c.n_kv_heads) / c.tp_size) % 16 != 0)
         return fail(B200_UNSUPPORTED, "decoder config: GEMM dimensions must be multiples of 16");
     if (c.max_batch <= 0 || c.max_seq_len <= 0) return bad("max_batch / max_seq_len must be positive");
+    if (c.tp_exact_int8 && c.tp_size > 1 &&
+        (!rows_scaled_supported(c.d_ff / c.tp_size) || !rows_scaled_supported(c.n_heads / c.tp_size * c.head_dim)))
+        return fail(B200_UNSUPPORTED, "decoder config: tp_exact_int8 needs rows of at most 16384 columns per rank");
     if (c.block_size <= 0 || c.block_size > 256 || (c.block_size & (c.block_size - 1))) return bad("block_size must be a power of two <= 256");
     if (c.num_blocks <= 0) return bad("num_blocks must be positive");
     if (!(c.rms_eps >= 0.0f) || !std::isfinite(c.rms_eps)) return bad("rms_eps must be finite and non-negative");
@@ -481,6 +489,7 @@ void map_peer_blocks(b200_decoder* d) {
     const char* env = std::getenv("B200_TP_EXCHANGE");
     if (env && env[0] == '0') return;
     if (tp < 2 || tp > 16 || !d->tp_block || !nccl().AllGather) return;
+    if (d->cfg.tp_exact_int8) return;          // the exact mode sums integers through ncclAllReduce
     if (d->cfg.max_batch % tp != 0 || !tp_finish_supported(d->cfg.d_model)) return;
     cudaStream_t s = d->ctx->stream;
     cudaIpcMemHandle_t mine;
@@ -528,6 +537,18 @@ void map_peer_blocks(b200_decoder* d) {
     d->tp_exchange = true;
 }
 
+int32_t all_reduce_max_f32(b200_decoder* d, float* buf, size_t n) {
+    int rc = nccl().AllReduce(buf, buf, n, kNcclFloat32, kNcclMax, d->comm, d->ctx->stream);
+    if (rc != 0) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, "ncclAllReduce (max) failed");
+    return B200_OK;
+}
+
+int32_t all_reduce_sum_i32(b200_decoder* d, int* buf, size_t n) {
+    int rc = nccl().AllReduce(buf, buf, n, kNcclInt32, kNcclSum, d->comm, d->ctx->stream);
+    if (rc != 0) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, "ncclAllReduce (int32 sum) failed");
+    return B200_OK;
+}
+
 int32_t all_reduce_sum_f32(b200_decoder* d, float* buf, size_t n) {
     int rc = nccl().AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, d->comm, d->ctx->stream);
     if (rc != 0) return dec_fail(d, B200_KERNEL_LAUNCH_FAILED, "ncclAllReduce failed");
@@ -570,7 +591,31 @@ int32_t enqueue_step(b200_decoder* d) {
     // One rank: the row kernel reads the raw accumulators.  Several ranks: the GEMM writes its dequantised f32
     // partial into the exchange block; then either the finish kernel sums the partials over the ranks' blocks and
     // delivers the rows (peers mapped), or ncclAllReduce sums them and every rank finishes all rows itself.
+    const bool exact_tp = tp && c.tp_exact_int8 != 0;
+    // Exact integer sums: the A rows were quantised under the row maximum merged over all ranks (quant_global below),
+    // so the ranks' int32 partials add up to the accumulators of one GPU; the dequantisation is the one-GPU kernel.
+    auto row_parallel_exact = [&](const GemmPlan& p, size_t s_off, const float* norm) -> int32_t {
+        CU_TRY(gemm_launch(p, ep, err, s));
+        int* acc = d->raw;
+        if (p.out_planes > 1) {
+            CU_TRY(gemm_sum_planes_i32(d->raw, p.out_planes, int64_t(M) * dm, d->tp_acc, s));
+            acc = d->tp_acc;
+            ++launches;
+        }
+        if (int32_t st = all_reduce_sum_i32(d, acc, size_t(M) * dm)) return st;
+        CU_TRY(resid_norm_quant_auto(acc, 1, M, dm, d->sx, d->scales + s_off, nullptr, norm, c.rms_eps, d->h, d->xq, d->sx, s));
+        launches += 3;
+        return B200_OK;
+    };
+    // rows [M, n] of this rank -> int8 under the maximum over the whole row (all ranks)
+    auto quant_global = [&](const float* rows, int n) -> int32_t {
+        if (int32_t st = all_reduce_max_f32(d, d->tp_amax, size_t(M))) return st;
+        CU_TRY(quantize_rows_with_amax(rows, M, n, d->tp_amax, d->xq, d->sx, s));
+        launches += 2;
+        return B200_OK;
+    };
     auto row_parallel = [&](const GemmPlan& p, size_t s_off, const float* norm) -> int32_t {
+        if (exact_tp) return row_parallel_exact(p, s_off, norm);
         const bool fused_ok = p.persist || p.splits == 1 || p.cluster;
         if (!tp) {
             CU_TRY(gemm_launch(p, ep, err, s));
@@ -642,7 +687,13 @@ int32_t enqueue_step(b200_decoder* d) {
                                         static_cast<uint16_t*>(L.v_pool), err, s));
         }
         // attention over the cache (this rank's KV heads), then per-token quantisation
-        if (paged_attention_can_quantize(L.attn)) {
+        if (exact_tp) {
+            CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
+                                          d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s));
+            CU_TRY(rows_amax(d->attn_out, M, d->hq_l * dh, d->tp_amax, s));
+            if (int32_t st = quant_global(d->attn_out, d->hq_l * dh)) return st;
+            launches += 1 - (paged_attention_can_quantize(L.attn) ? 0 : 1);
+        } else if (paged_attention_can_quantize(L.attn)) {
             CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, nullptr,
                                           d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s, d->xq, d->sx));
         } else {
@@ -655,6 +706,10 @@ int32_t enqueue_step(b200_decoder* d) {
         if (int32_t st = row_parallel(L.p_o, L.s_o, d->vectors + L.mlp_norm)) return st;
         // gate / up (column-parallel) -> SiLU gate -> quant
         CU_TRY(gemm_launch(L.p_gu, after_exchange(ep), err, s));
+        if (exact_tp) {
+            CU_TRY(gate_rows_f32(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->tp_rows_f32, d->tp_amax, s));
+            if (int32_t st = quant_global(d->tp_rows_f32, d->f_l)) return st;
+        } else
         CU_TRY(gate_quant_auto(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
         // down (row-parallel) -> residual -> next norm -> quant
         const float* next_norm = d->vectors + (l + 1 < c.n_layers ? d->layers[l + 1].attn_norm : d->final_norm);
@@ -768,6 +823,11 @@ int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_
         A(dmalloc(&d->sx, M));
         A(dmalloc(&d->part, M * dm));
     }
+    if (tp > 1 && c.tp_exact_int8) {
+        A(dmalloc(&d->tp_amax, M));
+        A(dmalloc(&d->tp_rows_f32, M * std::max<size_t>(d->f_l, size_t(d->hq_l) * dh)));
+        A(dmalloc(&d->tp_acc, M * dm));
+    }
     A(dmalloc(&d->q, M * d->hq_l * dh));
     A(dmalloc(&d->attn_out, M * d->hq_l * dh));
     A(dmalloc(&d->logits, M * size_t(c.vocab)));
@@ -829,7 +889,7 @@ int32_t b200_decoder_destroy(b200_decoder* d) {
     for (void* p : pf_ptrs) cudaFree(p);
     void* ptrs[] = {d->payload, d->scales, d->vectors, d->embed, d->cos_t, d->sin_t, d->tables_dev, d->seq_lens_dev, d->pos_dev,
                     d->ids_dev, d->next_ids_dev, d->h, d->xq, d->sx, d->raw, d->q, d->attn_out, d->part, d->logits,
-                    d->attn_scratch, d->tp_block, d->tp_epoch, d->tp_peers_dev, d->active_dev};
+                    d->attn_scratch, d->tp_block, d->tp_epoch, d->tp_peers_dev, d->active_dev, d->tp_amax, d->tp_rows_f32, d->tp_acc};
     for (void* p : ptrs) cudaFree(p);
     if (d->ids_pinned) cudaFreeHost(d->ids_pinned);
     if (d->active_pinned) cudaFreeHost(d->active_pinned);
@@ -1240,9 +1300,10 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     for (auto& L : d->layers) {
         cudaError_t e = plan(&L.p_qkv, L.wqkv, d->n_qkv, dm);
         L.rope_fused = e == cudaSuccess && dh == 128 && gemm_plan_can_rope(L.p_qkv, d->hq_l, d->hkv_l);
-        if (e == cudaSuccess) e = plan(&L.p_o, L.wo, dm, d->hq_l * dh, c.tp_size > 1);
+        const bool partial_f32 = c.tp_size > 1 && !c.tp_exact_int8;     // the row-parallel GEMMs write dequantised partials
+        if (e == cudaSuccess) e = plan(&L.p_o, L.wo, dm, d->hq_l * dh, partial_f32);
         if (e == cudaSuccess) e = plan(&L.p_gu, L.wgu, 2 * d->f_l, dm);
-        if (e == cudaSuccess) e = plan(&L.p_down, L.wdown, dm, d->f_l, c.tp_size > 1);
+        if (e == cudaSuccess) e = plan(&L.p_down, L.wdown, dm, d->f_l, partial_f32);
         if (e != cudaSuccess) return fail(B200_UNSUPPORTED, std::string("decoder_begin: ") + why);
         e = paged_attention_make_plan(&L.attn, sh, 1, L.k_pool, L.v_pool, mx, d->ctx->tune_attn_chunk_blocks);
         if (e != cudaSuccess) return fail(B200_KERNEL_LAUNCH_FAILED, "decoder_begin: attention plan failed");
@@ -1496,6 +1557,8 @@ int32_t b200_decoder_prefill(b200_decoder* d, int32_t row0, int32_t count, const
     if (!d->planned) return fail(B200_INVALID_ARGUMENT, "decoder_prefill: call decoder_begin first");
     if (row0 < 0 || count <= 0 || row0 + count > d->batch) return fail(B200_INVALID_ARGUMENT, "decoder_prefill: rows out of range");
     if (l_new <= 0 || !ids) return fail(B200_INVALID_ARGUMENT, "decoder_prefill: need l_new > 0 and ids");
+    if (d->cfg.tp_size > 1 && d->cfg.tp_exact_int8)
+        return fail(B200_UNSUPPORTED, "decoder_prefill: multi-token passes are not implemented for tp_exact_int8; feed the prompt through decoder_step");
     for (int b = row0; b < row0 + count; ++b)
         if (d->table->seq_lens[b] + uint64_t(l_new) > uint64_t(d->row_limits[b]))
             return fail(B200_INVALID_ARGUMENT, "decoder_prefill: row " + std::to_string(b) + " would pass its reserved length");
@@ -1578,7 +1641,7 @@ int32_t b200_decoder_generate(b200_decoder* d, const int32_t* prompt, int32_t ba
         for (int t = 0; t < prompt_len; ++t) out[size_t(b) * max_length + t] = prompt[size_t(b) * prompt_len + t];
     // prefill once (all but the last prompt token in multi-token passes), then one forward per token
     int first = 0;
-    if (prompt_len > 1) {
+    if (prompt_len > 1 && !(d->cfg.tp_size > 1 && d->cfg.tp_exact_int8)) {
         std::vector<int32_t> head(size_t(batch) * (prompt_len - 1));
         for (int b = 0; b < batch; ++b)
             for (int t = 0; t < prompt_len - 1; ++t) head[size_t(b) * (prompt_len - 1) + t] = prompt[size_t(b) * prompt_len + t];

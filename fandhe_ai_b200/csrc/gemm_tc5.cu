@@ -546,14 +546,14 @@ cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t 
 
 constexpr int kMaxSmem = 232448;   // dynamic shared memory a CTA may ask for on sm_100
 
-template <int BN, bool kInt8>
+template <int BN, bool kInt8, bool kPair>
 cudaError_t launch_persist_t(const GemmPlan& plan, const PersistArgs& args, cudaStream_t stream) {
-    const int stage_bytes = kABytes + BN * kBK;
+    const int stage_bytes = kABytes + (kPair ? BN / 2 : BN) * kBK;
     const int smem = plan.stages * stage_bytes + 1024 + 8 * (2 * plan.stages + 5) + 16;
     static int configured[64] = {};
-    if (cudaError_t e = ensure_dynamic_smem(gemm_tc5_persist_kernel<BN, kInt8>, smem, configured)) return e;
-    return launch_ex(gemm_tc5_persist_kernel<BN, kInt8>, dim3(plan.grid), dim3(kPersistThreads), smem, stream, 1, true,
-                     plan.tma_a, plan.tma_b, args);
+    if (cudaError_t e = ensure_dynamic_smem(gemm_tc5_persist_kernel<BN, kInt8, kPair>, smem, configured)) return e;
+    return launch_ex(gemm_tc5_persist_kernel<BN, kInt8, kPair>, dim3(plan.grid), dim3(kPersistThreads), smem, stream, kPair ? 2 : 1,
+                     true, plan.tma_a, plan.tma_b, args);
 }
 
 }  // namespace
@@ -578,11 +578,28 @@ void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue
     // with), so they switch at half a wave of tiles; raw accumulator output switches at two waves.
     const long long min_tiles = fused_epilogue ? (sm_count + 1) / 2 : 2LL * sm_count;
     if (tiles > 0x3FFFFFFF || tiles < min_tiles) return;
-    const int stage_bytes = kABytes + bn * kBK;
+    // CTA pairs for 256-wide tiles of problems with at least two tile rows: each CTA moves a third less through its
+    // shared memory per MMA (B200_GEMM_PAIR=0 in the environment keeps the one-CTA form, for measurements)
+    static const bool pair_allowed = [] {
+        const char* e = std::getenv("B200_GEMM_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    // (with at most one 128 x 256 tile per SM the one-CTA form has as many rounds and more streams in flight: measured)
+    const bool pair = pair_allowed && bn == 256 && plan->M > kBM && sm_count >= 2 && tiles > sm_count;
+    const int stage_bytes = kABytes + (pair ? bn / 2 : bn) * kBK;
     int stages = (kMaxSmem - 1024 - 256) / stage_bytes;
     if (stages > 8) stages = 8;
+    if (pair) {
+        // B is fetched in boxes of bn / 2 rows (the gated layout already is)
+        if (!plan->gate && plan->b_ptr != nullptr && !make_operand_map(&plan->tma_b, plan->b_ptr, plan->N, plan->K, bn / 2)) return;
+        const long long pair_tiles = static_cast<long long>((plan->M + 2 * kBM - 1) / (2 * kBM)) * ((n_out + out_cols - 1) / out_cols);
+        const long long pairs = pair_tiles < sm_count / 2 ? pair_tiles : sm_count / 2;
+        plan->grid = static_cast<int>(2 * pairs);
+    } else {
+        plan->grid = tiles < sm_count ? static_cast<int>(tiles) : sm_count;
+    }
+    plan->pair = pair ? 1 : 0;
     plan->persist = 1;
-    plan->grid = tiles < sm_count ? static_cast<int>(tiles) : sm_count;
     plan->stages = stages;
     plan->splits = 1;
     plan->cluster = 0;
@@ -605,6 +622,7 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
         return fail("gemm: operand base addresses must be 16-byte aligned");
     plan->kind = kind;
     plan->M = M; plan->N = N; plan->K = K; plan->gate = gate;
+    plan->b_ptr = encode_maps ? b : nullptr;
     const int m_tiles = (M + kBM - 1) / kBM;
     const int kb_total = (K + kBK - 1) / kBK;
     int bn = want_bn;
@@ -675,17 +693,21 @@ cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* 
         pa.kb_total = (plan.K + kBK - 1) / kBK;
         const int out_cols = plan.gate ? plan.bn / 2 : plan.bn;
         const int n_out = plan.gate ? plan.N / 2 : plan.N;
-        pa.tiles_m = (plan.M + kBM - 1) / kBM;
+        pa.tiles_m = plan.pair ? (plan.M + 2 * kBM - 1) / (2 * kBM) : (plan.M + kBM - 1) / kBM;
         pa.tiles_n = (n_out + out_cols - 1) / out_cols;
-        pa.group_m = 16;
+        pa.group_m = plan.pair ? 8 : 16;
         pa.gate = plan.gate;
         pa.n_half = plan.N / 2;
         pa.vec16 = ((reinterpret_cast<uintptr_t>(ep.b_scale) | reinterpret_cast<uintptr_t>(ep.bias)) & 15) == 0 ? 1 : 0;
         pa.ep = ep;
         pa.err = err;
         const bool i8p = plan.kind == kGemmI8;
-        if (plan.bn == 128) return i8p ? launch_persist_t<128, true>(plan, pa, stream) : launch_persist_t<128, false>(plan, pa, stream);
-        return i8p ? launch_persist_t<256, true>(plan, pa, stream) : launch_persist_t<256, false>(plan, pa, stream);
+        if (plan.pair) {
+            if (plan.bn != 256 || ep.wait.flags != nullptr) return cudaErrorInvalidValue;
+            return i8p ? launch_persist_t<256, true, true>(plan, pa, stream) : launch_persist_t<256, false, true>(plan, pa, stream);
+        }
+        if (plan.bn == 128) return i8p ? launch_persist_t<128, true, false>(plan, pa, stream) : launch_persist_t<128, false, false>(plan, pa, stream);
+        return i8p ? launch_persist_t<256, true, false>(plan, pa, stream) : launch_persist_t<256, false, false>(plan, pa, stream);
     }
     KernelArgs args;
     args.M = plan.M; args.N = plan.N; args.K = plan.K;

@@ -75,6 +75,8 @@ struct GemmPlan {
     // persistent form (gemm_plan_make_persistent): one CTA per SM takes whole tiles round-robin
     int persist = 0;
     int grid = 0;        // resident CTAs
+    int pair = 0;        // persistent form on CTA pairs (cta_group::2): 256-row tiles, each CTA loads half of the B rows
+    const void* b_ptr = nullptr;   // operand B as given to gemm_make_plan (the pair form re-encodes its tensor map)
 };
 
 // Switches a plan to the persistent kernel when the problem has enough tiles for `sm_count` SMs: half a wave when

@@ -9,6 +9,15 @@
 // to beat: it runs on eight warps (two per TMEM lane quarter, half of the columns each), loads the per-column
 // scales and bias with 16-byte loads once per 32 columns, and converts / stores 16 bytes at a time.
 //
+// Pair form (kPair): two CTAs of a cluster share one 256 x BN accumulator tile through tcgen05.mma.cta_group::2.  CTA
+// rank r holds the A rows [256 t + 128 r, + 128) and HALF of the B rows (BN / 2), and finds the accumulator rows of its
+// A rows in its own tensor memory; the even CTA issues the MMAs for both, reading both CTAs' shared memory.  Per MMA
+// volume a CTA then moves 16 KB + 16 KB per K block through its shared memory instead of 16 KB + 32 KB: the operand
+// feed from L2, which limits the 128 x 256 form, drops by a third.  Every CTA fetches its own operand halves (no
+// multicast loads); what crosses the pair are barrier arrivals: both CTAs' loads count on the leader's full barriers,
+// the leader's commits arrive on both CTAs' empty / accumulator-full barriers, and both CTAs' epilogue threads arrive on
+// the leader's accumulator-empty barriers.
+//
 // The arithmetic per element is that of the one-tile kernel: y = act(fma(float(acc), sa * sb, bias)) (+ residual),
 // except that SiLU uses the fast exponential and reciprocal.
 
@@ -78,13 +87,15 @@ __device__ __forceinline__ void store32(const GemmEpilogue& ep, size_t idx, floa
     }
 }
 
-template <int BN, bool kInt8>
+template <int BN, bool kInt8, bool kPair>
 __global__ void __launch_bounds__(kPersistThreads, 1)
 gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, PersistArgs p) {
-    constexpr int kBBytes = BN * kBK;
+    constexpr int kBRows = kPair ? BN / 2 : BN;      // B rows this CTA brings in per stage
+    constexpr int kBBytes = kBRows * kBK;
     constexpr int kStageBytes = kABytes + kBBytes;
+    constexpr int kTileRows = kPair ? 2 * kBM : kBM; // accumulator rows per tile (pair: over both CTAs)
     constexpr uint32_t kTmemCols = 2 * BN;      // two accumulator buffers
-    constexpr uint32_t kIdesc = kInt8 ? umma_idesc(1, 2, kBM, BN) : umma_idesc(0, 1, kBM, BN);
+    constexpr uint32_t kIdesc = kInt8 ? umma_idesc(1, 2, kTileRows, BN) : umma_idesc(0, 1, kTileRows, BN);
 
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -98,8 +109,9 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int grid = static_cast<int>(gridDim.x);
-    const int cta = static_cast<int>(blockIdx.x);
+    const uint32_t rank = kPair ? cluster_ctarank() : 0u;          // 0: the CTA that issues the MMAs
+    const int grid = static_cast<int>(gridDim.x) / (kPair ? 2 : 1);    // tiles in flight: CTAs, or CTA pairs
+    const int cta = static_cast<int>(blockIdx.x) / (kPair ? 2 : 1);
     const int tiles = p.tiles_m * p.tiles_n;
 
     if (warp == 0 && lane == 0) {
@@ -111,16 +123,22 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full(b), 1);
-            mbar_init(tmem_empty(b), kEpilogueThreads);
+            mbar_init(tmem_empty(b), kEpilogueThreads * (kPair ? 2 : 1));
         }
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, kTmemCols);
-        tmem_relinquish();
+        if constexpr (kPair) {
+            tmem_alloc_pair(tmem_slot, kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc5_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();      // the peer's barriers exist before anything arrives on them
     tc5_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
     const int out_cols = p.gate ? BN / 2 : BN;
@@ -128,7 +146,7 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     if (warp == 0) {
         const bool leader = elect_one();
         bool b_in_flight = false;
-        if (p.ep.wait.flags != nullptr && cta < tiles) {
+        if (!kPair && p.ep.wait.flags != nullptr && cta < tiles) {
             // The A operand comes from other GPUs: weight tiles of the first ring pass first, then the lanes wait for
             // the peers' flags (one flag per lane), then the A tiles (see GemmPeerWait).
             if (leader) {
@@ -157,7 +175,26 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             for (int tile = cta; ok && tile < tiles; tile += grid) {
                 int m_idx, n_idx;
                 tile_origin(p, tile, m_idx, n_idx);
-                const int m0 = m_idx * kBM, n0 = n_idx * out_cols;
+                const int m0 = m_idx * kTileRows + static_cast<int>(rank) * kBM, n0 = n_idx * out_cols;
+                if constexpr (kPair) {
+                    // this CTA's operand halves; their bytes count on the leader's full barrier, which expects both CTAs'
+                    if (!waited) {
+                        pdl_wait();
+                        pdl_launch_dependents();
+                        waited = true;
+                    }
+                    const int nb0 = p.gate ? (rank == 0 ? n0 : p.n_half + n0) : n0 + static_cast<int>(rank) * (BN / 2);
+                    for (int kb = 0; kb < p.kb_total; ++kb, ++i) {
+                        const int s = i % p.stages;
+                        const uint32_t ph = (i / p.stages) & 1;
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, p.err, kErrProducerWait)) { ok = false; break; }
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kStageBytes);
+                        const uint32_t bar = mapa_shared(full_bar(s), 0);
+                        tma_load_2d_pair(smem_base + s * kStageBytes, &tma_a, bar, kb * kBK, m0);
+                        tma_load_2d_pair(smem_base + s * kStageBytes + kABytes, &tma_b, bar, kb * kBK, nb0);
+                    }
+                    continue;
+                }
                 auto load_b = [&](int kb, int s) {
                     const uint32_t b_dst = smem_base + s * kStageBytes + kABytes;
                     tma_load_2d(b_dst, &tma_b, full_bar(s), kb * kBK, n0);
@@ -197,7 +234,7 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             }
         }
     } else if (warp == 1) {
-        if (elect_one()) {
+        if (elect_one() && rank == 0) {
             int i = 0, j = 0;
             bool ok = true;
             for (int tile = cta; ok && tile < tiles; tile += grid, ++j) {
@@ -216,12 +253,16 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                     const uint64_t adesc = umma_desc_k128(a_src);
                     const uint64_t bdesc = umma_desc_k128(a_src + kABytes);
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k)
-                        umma_ss<kInt8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
-                    tc5_commit(empty_bar(s));
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        if constexpr (kPair) umma_ss_pair<kInt8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        else umma_ss<kInt8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    if constexpr (kPair) tc5_commit_pair(empty_bar(s), 3);      // the stage is free in both CTAs
+                    else tc5_commit(empty_bar(s));
                 }
                 if (!ok) break;
-                tc5_commit(tmem_full(buf));
+                if constexpr (kPair) tc5_commit_pair(tmem_full(buf), 3);       // each CTA drains its own accumulator rows
+                else tc5_commit(tmem_full(buf));
             }
         }
     } else {
@@ -240,7 +281,7 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(buf * BN) + (static_cast<uint32_t>(q * 32) << 16);
             int m_idx, n_idx;
             tile_origin(p, tile, m_idx, n_idx);
-            const int m0 = m_idx * kBM, n0 = n_idx * out_cols;
+            const int m0 = m_idx * kTileRows + static_cast<int>(rank) * kBM, n0 = n_idx * out_cols;
             const int row = m0 + rl;
             const bool row_ok = row < p.M;
             const size_t row_c = static_cast<size_t>(row_ok ? row : 0);
@@ -345,17 +386,20 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                     }
                 }
             }
-            // hand the accumulator buffer back to the MMA warp
+            // hand the accumulator buffer back to the MMA warp (of the leader CTA)
             tc5_fence_before();
-            mbar_arrive(tmem_empty(buf));
+            if (kPair && rank != 0) mbar_arrive_cluster(mapa_shared(tmem_empty(buf), 0));
+            else mbar_arrive(tmem_empty(buf));
         }
     }
 
     tc5_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();      // neither CTA frees tensor or shared memory the other may still use
     if (warp == 1) {
         __syncwarp();
         tc5_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+        else tmem_dealloc(tmem_base, kTmemCols);
     }
 }

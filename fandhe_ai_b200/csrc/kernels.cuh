@@ -102,6 +102,15 @@ cudaError_t fill_normal_bf16(uint16_t* out, int64_t n, uint64_t seed, uint64_t s
 cudaError_t slice_cols_i8(const int8_t* src, int64_t rows, int64_t ld, int64_t c0, int64_t cols, int8_t* dst,
                           cudaStream_t s);
 
+// Rows quantised under a scale that comes from outside (tensor parallelism with exact integer sums: the row maximum
+// is merged across the ranks between the two calls).  Rows of up to 16384 columns, a multiple of 4.
+bool rows_scaled_supported(int n);
+cudaError_t rows_amax(const float* x, int M, int n, float* amax_out, cudaStream_t s);
+cudaError_t quantize_rows_with_amax(const float* x, int M, int n, const float* amax, int8_t* xq, float* sx_out, cudaStream_t s);
+// a = silu(gate) * up of the columns [0, F) / [F, 2F) of the raw planes as f32 [M, F], and the row maxima of |a|
+cudaError_t gate_rows_f32(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, float* out,
+                          float* amax_out, cudaStream_t s);
+
 // Tensor-parallel finish of a row-parallel GEMM over the ranks' exchange blocks (decode_rows.cu): sums the f32
 // partials of the rows this rank owns over all ranks, adds the residual, applies RMSNorm and the per-token int8
 // quantisation and delivers the int8 rows and scales to every rank.  `peers` is a device array of the tp block

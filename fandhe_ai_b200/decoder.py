@@ -84,12 +84,13 @@ class DecoderConfig:
     tp_rank: int = 0
     tp_size: int = 1
     use_graph: int = 1
+    tp_exact_int8: int = 0       # tensor parallel: one global per-token scale + int32 all-reduce (results independent of tp_size)
 
     def to_c(self) -> DecoderConfigC:
         nb = self.num_blocks or self.max_batch * -(-self.max_seq_len // self.block_size)
         return DecoderConfigC(self.n_layers, self.d_model, self.n_heads, self.n_kv_heads, self.head_dim, self.d_ff,
                               self.vocab, self.rms_eps, self.rope_theta, self.max_batch, self.max_seq_len,
-                              self.block_size, nb, self.tp_rank, self.tp_size, self.use_graph)
+                              self.block_size, nb, self.tp_rank, self.tp_size, self.use_graph, self.tp_exact_int8)
 
 
 def shard_plan(cfg: DecoderConfig, which: int) -> dict:

@@ -195,8 +195,8 @@ int32_t b200_quant_check(b200_ctx* ctx);
 
 /* Which kernel form b200_gemm_i8_s32 (fused = 0) or b200_gemm_q8_scaled (fused = 1; gated = 1 for
  * B200_ACT_SILU_GATE) would use for a shape under the context's current tuning; nothing is launched.
- * out6 = {tile width, K splits, splits reduced inside a cluster (0/1), persistent kernel (0/1), resident CTAs of the
- * persistent kernel, operand stages}.  The counterpart of asking the reference's kernel selection what it would run
+ * out6 = {tile width, K splits, splits reduced inside a cluster (0/1), persistent kernel (0: no, 1: one CTA per tile,
+ * 2: CTA pairs on 256-row tiles), resident CTAs of the persistent kernel, operand stages}.  The counterpart of asking the reference's kernel selection what it would run
  * (crates/backend-cuda/src/gemm_auto.rs:1829-1892); lets a test state which kernel it reached. */
 int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t gated, int32_t fused, int32_t* out6);
 
@@ -357,6 +357,11 @@ typedef struct b200_decoder_config {
     int32_t num_blocks;     /* blocks per K / V pool per layer */
     int32_t tp_rank, tp_size;   /* tensor parallel: this process's rank and the number of ranks */
     int32_t use_graph;      /* replay each step as a CUDA graph after the first (eager) one */
+    int32_t tp_exact_int8;  /* tp_size > 1: quantise the rows that are split over the ranks under ONE per-token scale (the row
+                             * maximum merged over the ranks with a max all-reduce) and all-reduce the int32 partial sums, so
+                             * that logits and ids do not depend on tp_size (bit-identical to one GPU); costs two more
+                             * collectives per layer and runs on ncclAllReduce.  0: every rank scales its slice of a row by
+                             * itself and the ranks add dequantised f32 partials (the fast path). */
 } b200_decoder_config;
 
 typedef enum b200_weight {

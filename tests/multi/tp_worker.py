@@ -24,6 +24,8 @@ def main():
 
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     dist.init_process_group("gloo", rank=rank, world_size=world)
+    if os.environ.get("B200_TP_EXACT") == "1":
+        return exact_mode(dist, rank, world, local)
     cfg = dict(n_layers=2, d_model=512, n_heads=8, n_kv_heads=4, head_dim=128, d_ff=1024, vocab=2048, max_seq_len=48)
     weights = make_weights(cfg, seed=5)
     batch, steps = 4, 10
@@ -60,6 +62,44 @@ def main():
             ok = False
         msg = f"exchange={int(exchange)} worst |dlogit| / max|logit| vs the CPU decoder at tp={world}: {worst:.3e}"
     be.close()
+    flag = [ok]
+    dist.broadcast_object_list(flag, src=0)
+    if rank == 0:
+        print(("TP_OK " if ok else "TP_FAIL ") + msg, flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if flag[0] else 1)
+
+
+def exact_mode(dist, rank, world, local):
+    """tp_exact_int8: rows split over the ranks are quantised under one scale (row maximum merged over the ranks) and the
+    int32 partial sums are all-reduced, so the logits must be those of ONE GPU, bit for bit: compared with the
+    kernel-order CPU decoder without any tensor parallelism (head_dim 64: the general attention kernel)."""
+    from fandhe_ai_b200 import Backend
+    from fandhe_ai_b200.decoder import Decoder, DecoderConfig, nccl_unique_id
+    from oracle.decoder_ref import DecoderRef, make_weights
+
+    cfg = dict(n_layers=2, d_model=512, n_heads=8, n_kv_heads=4, head_dim=64, d_ff=1024, vocab=2048, max_seq_len=48)
+    weights = make_weights(cfg, seed=15)
+    batch, steps = 4, 10
+    be = Backend(local)
+    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
+                       cfg["vocab"], max_batch=batch, max_seq_len=cfg["max_seq_len"], tp_rank=rank, tp_size=world,
+                       tp_exact_int8=1)
+    dec = Decoder(be, dc)
+    obj = [nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(obj, src=0)
+    dec.init_tp(obj[0])
+    dec.load_weights(weights)
+    prompt = np.random.default_rng(19).integers(0, cfg["vocab"], (batch, 5)).astype(np.int32)
+    got_ids = dec.generate(prompt, 5 + steps)
+    got_logits = dec.logits()
+    dec.close()
+    be.close()
+    ok, msg = True, ""
+    if rank == 0:
+        want_ids, logits = DecoderRef(cfg, weights, exact=True).generate(prompt, 5 + steps)
+        ok = bool(np.array_equal(got_ids, want_ids) and np.array_equal(got_logits, logits[-1]))
+        msg = f"exact tp={world}: ids equal {np.array_equal(got_ids, want_ids)}, last logits max |d| {float(np.abs(got_logits - logits[-1]).max()):.3e}"
     flag = [ok]
     dist.broadcast_object_list(flag, src=0)
     if rank == 0:

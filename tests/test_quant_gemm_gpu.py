@@ -266,15 +266,18 @@ def tile_rows(m, per_tile, seed):
 
 
 # m, n, k, tile width the heuristic picks; every shape has at least half a wave of tiles (fused epilogues switch
-# to the persistent kernel there) and the last two have M / N / K tails
+# to the persistent kernel there); 256-wide tiles beyond one wave run on CTA pairs; the last four have M / N / K tails
+# (640 rows: five 128-row tiles, so the second CTA of the last pair has no row at all)
 PERSISTENT_FUSED = [(2048, 4096, 4096, 256), (4096, 4096, 1024, 256), (256, 8192, 512, 128), (300, 4112, 528, 128),
-                    (1000, 2320, 272, 256)]
+                    (1000, 2320, 272, 256), (1000, 5136, 272, 256), (640, 8208, 144, 256)]
 
 
 @pytest.mark.parametrize("m,n,k,tile", PERSISTENT_FUSED)
 def test_persistent_kernel_int8_epilogues(be, m, n, k, tile):
     info = be.gemm_plan_info(m, n, k, fused=True)
-    assert info["persistent"] == 1 and info["tile"] == tile, info
+    # 256-wide tiles of problems with more than one tile row run on CTA pairs (cta_group::2), the others on one CTA per tile
+    many_tiles = -(-m // 128) * -(-n // 256) > 148
+    assert info["persistent"] == (2 if tile == 256 and many_tiles else 1) and info["tile"] == tile, info
     rng = np.random.default_rng(m + n + k)
     a, w = rand_i8(m, (m, k)), rand_i8(n, (n, k))
     sa = rng.uniform(0.5e-2, 2e-2, m).astype(np.float32)
@@ -299,7 +302,7 @@ def test_persistent_kernel_int8_epilogues(be, m, n, k, tile):
                                                                    residual=res[rows]))
     assert fails == 0, ("silu + residual", max_abs, max_rel)
     if n % 32 == 0:
-        assert be.gemm_plan_info(m, n, k, gated=True, fused=True)["persistent"] == 1
+        assert be.gemm_plan_info(m, n, k, gated=True, fused=True)["persistent"] >= 1
         y = be.gemm_q8_scaled(I8, a_d, sa_d, True, w_d, sw_d, True, m, n, k, bias=b_d, activation=ACT_SILU_GATE).numpy()
         assert y.shape == (m, n // 2)
         fails, max_abs, max_rel = O.compare(y[rows], O.epilogue_scaled(acc, sa[rows], True, sw, True, bias,
@@ -310,10 +313,10 @@ def test_persistent_kernel_int8_epilogues(be, m, n, k, tile):
         assert np.array_equal(y16, O.f32_to_bf16(y))
 
 
-@pytest.mark.parametrize("m,n,k,tile", [(4096, 4096, 512, 256), (384, 16384, 256, 128), (2700, 4112, 144, 256)])
+@pytest.mark.parametrize("m,n,k,tile", [(4096, 4096, 512, 256), (384, 16384, 256, 128), (2700, 4112, 144, 256), (640, 16400, 144, 256)])
 def test_persistent_kernel_raw_int32_accumulators(be, m, n, k, tile):
     info = be.gemm_plan_info(m, n, k, fused=False)
-    assert info["persistent"] == 1 and info["tile"] == tile, info       # raw output switches at two waves of tiles
+    assert info["persistent"] == (2 if tile == 256 else 1) and info["tile"] == tile, info   # raw output switches at two waves of tiles
     a, w = rand_i8(m + 1, (m, k)), rand_i8(n + 1, (n, k))
     acc = be.gemm_i8_s32(be.upload(a), be.upload(w), m, n, k).numpy()
     rows = tile_rows(m, 6, 2)
@@ -324,9 +327,9 @@ def test_persistent_kernel_raw_int32_accumulators(be, m, n, k, tile):
     assert np.array_equal(colsum, want)
 
 
-@pytest.mark.parametrize("m,n,k,tile", [(2048, 4096, 1024, 256), (256, 8192, 512, 128), (1000, 2320, 272, 256)])
+@pytest.mark.parametrize("m,n,k,tile", [(2048, 4096, 1024, 256), (256, 8192, 512, 128), (1000, 2320, 272, 256), (640, 8208, 144, 256)])
 def test_persistent_kernel_fp8(be, m, n, k, tile):
-    assert be.gemm_plan_info(m, n, k, fused=True)["persistent"] == 1
+    assert be.gemm_plan_info(m, n, k, fused=True)["persistent"] in (1, 2)
     aq, sa, bq, sb = fp8_operands(m + n, m, n, k)
     rows = tile_rows(m, 3, 3)
     truth = fp8_truth(aq[rows], bq, sa, sb)
@@ -348,7 +351,7 @@ def test_gated_projection_of_the_8b_shape_on_sampled_rows(be):
     """The gate/up projection of the 8B shape with the SiLU-gate epilogue (N = 2 x 14336, K = 4096) at M = 4096:
     int8 and FP8 through the persistent 256-wide kernel, a few hundred sampled rows against the oracle."""
     m, f, k = 4096, 14336, 4096
-    assert be.gemm_plan_info(m, 2 * f, k, gated=True, fused=True) ["persistent"] == 1
+    assert be.gemm_plan_info(m, 2 * f, k, gated=True, fused=True) ["persistent"] == 2
     rng = np.random.default_rng(77)
     rows = tile_rows(m, 8, 4)[:256]
     a, w = rand_i8(5, (m, k)), rand_i8(6, (2 * f, k))

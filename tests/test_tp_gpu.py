@@ -29,6 +29,20 @@ def test_two_rank_tensor_parallel_decode_matches_the_cpu_decoder(exchange):
     assert f"exchange={exchange}" in r.stdout, r.stdout[-3000:]
 
 
+def test_two_rank_exact_int8_gives_the_logits_of_one_gpu():
+    """tp_exact_int8 = 1: one per-token scale over the ranks (max all-reduce) and int32 partial sums (sum all-reduce):
+    ids and logits equal those of the kernel-order CPU decoder WITHOUT tensor parallelism, bit for bit."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200_TP_EXACT="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29733", str(ROOT / "tests" / "multi" / "tp_worker.py")]
+    r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_OK" in r.stdout, r.stdout[-3000:]
+
+
 def test_peer_wait_runs_out_with_an_error_status_and_the_device_stays_usable(fresh_be):
     """Failure detection without a fault: a finish kernel whose peer never raises its flag gives up after its
     bounded wait, the context reports the device error and is poisoned, and a new context works."""
