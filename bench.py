@@ -419,7 +419,7 @@ def run_gpu(args, cfg, rank, world, local_rank):
     plan = dec.plan_info()
     launches = dec.launches_per_step * args.steps
     weight_bytes = dec.weight_bytes
-    exchange = dec.tp_exchange
+    exchange = dec.tp_exchange_mode
     dec.close()
 
     if rank == 0:
@@ -458,6 +458,9 @@ def run_gpu(args, cfg, rank, world, local_rank):
                         "ms_per_step_median": ms / args.steps, "ms_per_step_q3": q3_ms / args.steps,
                         "e2e_q1": e2e_q1, "e2e_median": e2e_med, "e2e_q3": e2e_q3},
             "collective": ("none" if world == 1 else
+                           "row-parallel GEMMs store their partial rows into the owner rank's CUDA-IPC mapped block; one kernel "
+                           "per output sums them in rank order, residual + RMSNorm + int8, rows delivered to every rank"
+                           if exchange == 2 else
                            "row-parallel outputs finished over CUDA-IPC mapped peer blocks (one kernel: peer loads, "
                            "residual + RMSNorm + int8, rows delivered to every rank)" if exchange else
                            "ncclAllReduce of f32 partials"),

@@ -143,6 +143,7 @@ SIGNATURES = {
     "b200_decoder_tp_exchange": (_I32, [_P]),
     "b200_selftest_peer_wait": (_I32, [_P]),
     "b200_selftest_tp_finish": (_I32, [_P, _I32, _I32, _I32, _I32, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
+    "b200_selftest_tp_scatter": (_I32, [_P, _I32, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
     "b200_decoder_step_rows": (_I32, [_P, _P, _P, _P]),
     "b200_decoder_row_restart": (_I32, [_P, _I32, _I32]),
     "b200_scheduler_create": (_I32, [_P, _I32, _I32, _I32, _P]),

@@ -542,6 +542,13 @@ struct TpFinishArgs {
     unsigned int* arrived;     // CTAs of this launch that have delivered their row
     uint32_t* err;
     uint64_t timeout_ns;       // bound of every flag wait
+    // Scattered form: the GEMMs of all ranks have stored the partials of this rank's rows into the planes
+    // [tp][rows][d] of this rank's block (GemmPush) and count their launches in count[tp] at o_count; this kernel then
+    // sends no ready flag and loads nothing from a peer.  push_tiles = counts per GEMM launch (0: the pulled form),
+    // *push_target = counts consumed by the earlier calls.
+    size_t o_count;
+    uint32_t push_tiles;
+    uint32_t* push_target;
 };
 
 template <int VPT>
@@ -557,17 +564,23 @@ tp_finish_kernel(TpFinishArgs a) {
     pdl_wait();
     pdl_launch_dependents();
     const uint32_t epoch = *a.epoch + 1;
+    const bool scattered = a.push_tiles != 0u;
+    const uint32_t target = scattered ? *a.push_target + a.push_tiles : 0u;
     __syncthreads();
     uint8_t* mine = s_peer[a.rank];
     const uint32_t* ready = reinterpret_cast<const uint32_t*>(mine);
     // 1. this rank's partial is complete (the GEMM before this kernel has finished): tell every rank
-    if (blockIdx.x == 0 && threadIdx.x < a.tp) {
+    if (!scattered && blockIdx.x == 0 && threadIdx.x < a.tp) {
         __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t*>(s_peer[threadIdx.x]) + a.rank, epoch);
     }
-    // 2. wait for every rank's partial
+    // 2. wait for every rank's partial (scattered form: for every tile of every rank's GEMM; the ready word of a rank
+    //    then only carries its poison)
     if (threadIdx.x < a.tp) {
-        if (!wait_peer_flag(ready + threadIdx.x, epoch, a.err, a.timeout_ns)) s_ok = 0;
+        const bool got = scattered ? wait_peer_count(reinterpret_cast<const uint32_t*>(mine + a.o_count) + threadIdx.x, target,
+                                                     ready + threadIdx.x, a.err, a.timeout_ns)
+                                   : wait_peer_flag(ready + threadIdx.x, epoch, a.err, a.timeout_ns);
+        if (!got) s_ok = 0;
     }
     __syncthreads();
     const bool ok = s_ok != 0;
@@ -587,8 +600,12 @@ tp_finish_kernel(TpFinishArgs a) {
                     float4 x[8];
                     const float* src[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        src[i] = reinterpret_cast<const float*>(s_peer[p0 + i < a.tp ? p0 + i : 0] + a.o_part) + base + 4 * g;
+                    for (int i = 0; i < 8; ++i) {
+                        const int p = p0 + i < a.tp ? p0 + i : 0;
+                        src[i] = scattered ? reinterpret_cast<const float*>(mine + a.o_part) +
+                                                 (static_cast<size_t>(p) * a.rows + blockIdx.x) * a.d + 4 * g
+                                           : reinterpret_cast<const float*>(s_peer[p] + a.o_part) + base + 4 * g;
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         if (p0 + i < a.tp) x[i] = ld_relaxed_sys_f4(src[i]);
@@ -647,12 +664,17 @@ tp_finish_kernel(TpFinishArgs a) {
             if (threadIdx.x == 0) reinterpret_cast<float*>(s_peer[p] + a.o_sx)[row] = s;
         }
     }
-    __threadfence_system();
+    // The row stores above become visible to the other GPUs through one chain: a device-scope fence by every storing
+    // thread, the CTA barrier, the count of this CTA in this GPU's memory (device-scope fences around it), and the
+    // system-scope fence and release of the CTA that completes the launch.  Only that last CTA waits for the peers'
+    // acknowledgements.
+    __threadfence();
     __syncthreads();
     // 4. the last CTA of this launch tells every rank that this rank's rows are delivered (or, after a failed wait,
     //    that they never will be) and advances the call counter
     if (threadIdx.x == 0) {
         const unsigned int seen = atomicAdd(a.arrived, 1u);
+        __threadfence();
         s_last = seen == gridDim.x - 1 ? 1 : 0;
     }
     __syncthreads();
@@ -669,6 +691,7 @@ tp_finish_kernel(TpFinishArgs a) {
         if (threadIdx.x == 0) {
             *a.arrived = 0u;
             *a.epoch = epoch;
+            if (scattered) *a.push_target = target;
         }
     }
 }
@@ -824,11 +847,12 @@ bool tp_finish_supported(int d) {
 
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
-                      cudaStream_t s, uint64_t timeout_ns) {
+                      cudaStream_t s, uint64_t timeout_ns, size_t o_count, uint32_t push_tiles, uint32_t* push_target) {
     int vpt, threads;
     wide_shape(d, &vpt, &threads);
+    if (push_tiles != 0u && push_target == nullptr) return cudaErrorInvalidValue;
     TpFinishArgs a{peers, o_sx, o_xq, o_part, tp, rank, rows, d, norm_w, eps, h, epoch, arrived, err,
-                   timeout_ns ? timeout_ns : kPeerWaitNs};
+                   timeout_ns ? timeout_ns : kPeerWaitNs, o_count, push_tiles, push_target};
     if (vpt == 1) return launch_ex(tp_finish_kernel<1>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 2) return launch_ex(tp_finish_kernel<2>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 4) return launch_ex(tp_finish_kernel<4>, dim3(rows), dim3(threads), 0, s, 1, true, a);

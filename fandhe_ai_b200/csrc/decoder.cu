@@ -198,6 +198,10 @@ int64_t b200_block_table_batch(const b200_block_table* t) { return (t && t->has_
 // ------------------------------------------------------------------------------------ NCCL (dlopen)
 namespace {
 
+// Head of an exchange block: ready[tp] at +0, delivered[tp] at +256, count[tp] at +512 (32-bit words).
+constexpr size_t kTpCountOffset = 512;
+constexpr size_t kTpFlagBytes = 768;
+
 typedef struct ncclComm* ncclComm_t;
 struct NcclUniqueId { char internal[128]; };
 enum { kNcclInt8 = 0, kNcclInt32 = 2, kNcclFloat32 = 7 };
@@ -306,7 +310,11 @@ struct b200_decoder {
     size_t tp_o_sx = 0, tp_o_xq = 0, tp_o_part = 0;
     void* tp_peer_ptrs[16] = {};                // host copy of the mapped bases (own block at tp_rank)
     uint8_t** tp_peers_dev = nullptr;           // the same table on the device
-    uint32_t* tp_epoch = nullptr;               // [0] call counter, [1] CTA arrival counter of the finish kernel
+    uint32_t* tp_epoch = nullptr;               // [0] call counter, [1] CTA arrival counter of the finish kernel,
+                                                // [2] scattered outputs finished so far, [3] tile counter of the
+                                                // GEMM that scatters
+    bool tp_push = true;                        // row-parallel GEMMs scatter their rows over the owners' blocks
+    bool tp_push_all = true;                    // ... and every row-parallel GEMM of the last enqueued step could
     bool tp_exchange = false;                   // peers are mapped: use the finish kernel instead of ncclAllReduce
     uint64_t tp_timeout_ns = 0;                 // bound of every cross-GPU wait (0: the kernels' default of two seconds)
     // exact integer sums under tensor parallelism (cfg.tp_exact_int8): merged row maxima, f32 rows before the
@@ -624,6 +632,10 @@ int32_t enqueue_step(b200_decoder* d) {
             launches += 2;
             return B200_OK;
         }
+        // Peers mapped and the one-tile kernel with a fused epilogue: the GEMM stores every row straight into the block
+        // of the rank that owns it and counts its tiles there, and the finish kernel reads local memory only.
+        const bool push = exchange && d->tp_push && fused_ok && !p.persist;
+        if (exchange && !push) d->tp_push_all = false;
         if (fused_ok) {
             GemmEpilogue pe;
             pe.fused = 1;
@@ -632,6 +644,15 @@ int32_t enqueue_step(b200_decoder* d) {
             pe.b_scale = d->scales + s_off;
             pe.b_per_col = 1;
             pe.out = d->part;
+            if (push) {
+                pe.push.peers = d->tp_peers_dev;
+                pe.push.o_part = d->tp_o_part;
+                pe.push.o_count = kTpCountOffset;
+                pe.push.tp = c.tp_size;
+                pe.push.rank = c.tp_rank;
+                pe.push.rows = M / c.tp_size;
+                pe.push.arrived = d->tp_epoch + 3;
+            }
             CU_TRY(gemm_launch(p, pe, err, s));
             ++launches;
         } else {
@@ -641,7 +662,8 @@ int32_t enqueue_step(b200_decoder* d) {
         }
         if (exchange) {
             CU_TRY(tp_finish(d->tp_peers_dev, d->tp_o_sx, d->tp_o_xq, d->tp_o_part, c.tp_size, c.tp_rank, M / c.tp_size, dm, norm,
-                             c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s, d->tp_timeout_ns));
+                             c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s, d->tp_timeout_ns, kTpCountOffset,
+                             push ? 1u : 0u, d->tp_epoch + 2));
             ++launches;
             return B200_OK;
         }
@@ -803,7 +825,7 @@ int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_
     A(dmalloc(&d->next_ids_dev, M));
     A(dmalloc(&d->h, M * dm));
     if (tp > 1) {
-        size_t off = 512;                                        // ready[tp] at +0, done[tp] at +256
+        size_t off = kTpFlagBytes;                               // ready[tp] at +0, delivered[tp] at +256, count[tp] at +512
         d->tp_o_sx = off; off += align_up(M * sizeof(float), 256);
         d->tp_o_xq = off; off += align_up(M * widest, 256);
         d->tp_o_part = off; off += align_up(M * dm * sizeof(float), 256);
@@ -815,8 +837,9 @@ int32_t b200_decoder_create(b200_ctx* ctx, const b200_decoder_config* cfg, b200_
             d->xq = reinterpret_cast<int8_t*>(d->tp_block + d->tp_o_xq);
             d->part = reinterpret_cast<float*>(d->tp_block + d->tp_o_part);
         }
-        A(dmalloc(&d->tp_epoch, 2));
-        if (e == cudaSuccess) e = cudaMemset(d->tp_epoch, 0, 2 * sizeof(uint32_t));
+        A(dmalloc(&d->tp_epoch, 4));
+        if (e == cudaSuccess) e = cudaMemset(d->tp_epoch, 0, 4 * sizeof(uint32_t));
+        if (const char* v = std::getenv("B200_TP_PUSH")) d->tp_push = v[0] != '0';     // 0: the pulled form, for measurements
         A(cudaMalloc(reinterpret_cast<void**>(&d->tp_peers_dev), 16 * sizeof(uint8_t*)));
     } else {
         A(dmalloc(&d->xq, M * widest));
@@ -1124,7 +1147,10 @@ int32_t b200_decoder_init_tp(b200_decoder* d, const uint8_t* unique_id128) {
     return B200_OK;
 }
 
-int32_t b200_decoder_tp_exchange(const b200_decoder* d) { return d && d->tp_exchange ? 1 : 0; }
+int32_t b200_decoder_tp_exchange(const b200_decoder* d) {
+    if (!d || !d->tp_exchange) return 0;
+    return d->tp_push && d->tp_push_all ? 2 : 1;
+}
 
 // Failure-detection self-test of the cross-GPU finish kernel on one GPU: launches it as rank 0 of 2 over a scratch
 // exchange block in which nobody ever raises rank 1's flags.  The kernel's bounded wait (20 ms here) runs out, it
@@ -1237,6 +1263,100 @@ int32_t b200_selftest_tp_finish(b200_ctx* ctx, int32_t tp, int32_t rank, int32_t
     cudaFree(h);
     cudaFree(w);
     cudaFree(counters);
+    return st;
+}
+
+// Numerical self-test on one GPU of a row-parallel GEMM that scatters its rows (GemmPush) followed by the scattered
+// form of the finish kernel, with nothing to wait for: `tp` exchange blocks live on this device.  For every rank s the
+// GEMM [M = tp * rows, d] = a_q[s] [M, k] x w_q[s] [d, k]^T with the dequantising epilogue is launched as rank s
+// (splits / tile as in b200_set_tuning, 0 = heuristic); all ranks' GEMMs have completed when the finish kernel then
+// runs as rank 0, 1, ... .  Returns the residual rows [M, d], the int8 rows and scales as delivered into the first and
+// into the last block ([2][M][d], [2][M]) and the launch counts of every block ([tp][tp]: one per rank's GEMM).
+int32_t b200_selftest_tp_scatter(b200_ctx* ctx, int32_t tp, int32_t rows, int32_t d, int32_t k, int32_t splits, int32_t tile,
+                                 const int8_t* a_q, const float* a_scale, const int8_t* w_q, const float* w_scale,
+                                 const float* residual, const float* norm_w, float eps, float* h_out, int8_t* xq_out,
+                                 float* sx_out, uint32_t* counts_out) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (tp < 1 || tp > 16 || rows <= 0 || d <= 0 || k <= 0 || !a_q || !a_scale || !w_q || !w_scale || !residual || !norm_w ||
+        !h_out || !xq_out || !sx_out || !counts_out)
+        return fail(B200_INVALID_ARGUMENT, "selftest_tp_scatter: bad argument");
+    if (!tp_finish_supported(d)) return fail(B200_UNSUPPORTED, "selftest_tp_scatter: row width not supported by the finish kernel");
+    if (int32_t st = set_device(ctx)) return st;
+    const size_t M = size_t(tp) * rows;
+    const size_t o_sx = kTpFlagBytes;
+    const size_t o_xq = o_sx + (M * 4 + 255) / 256 * 256;
+    const size_t o_part = o_xq + (M * d + 255) / 256 * 256;
+    const size_t bytes = o_part + M * d * sizeof(float);
+    std::vector<uint8_t*> blocks(tp, nullptr);
+    std::vector<void*> owned;
+    cudaStream_t s = ctx->stream;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](size_t n) -> void* {
+        void* p = nullptr;
+        if (e == cudaSuccess) e = cudaMalloc(&p, n);
+        if (p) owned.push_back(p);
+        return p;
+    };
+    for (int p = 0; p < tp; ++p) {
+        blocks[p] = static_cast<uint8_t*>(alloc(bytes));
+        if (e == cudaSuccess) e = cudaMemsetAsync(blocks[p], 0, bytes, s);
+    }
+    uint8_t** peers = static_cast<uint8_t**>(alloc(tp * sizeof(uint8_t*)));
+    float* h = static_cast<float*>(alloc(M * d * sizeof(float)));
+    float* w = static_cast<float*>(alloc(d * sizeof(float)));
+    uint32_t* counters = static_cast<uint32_t*>(alloc((size_t(tp) * 4 + 1) * sizeof(uint32_t)));
+    int8_t* aq = static_cast<int8_t*>(alloc(size_t(tp) * M * k));
+    int8_t* wq = static_cast<int8_t*>(alloc(size_t(tp) * d * k));
+    float* as = static_cast<float*>(alloc(size_t(tp) * M * sizeof(float)));
+    float* ws = static_cast<float*>(alloc(size_t(tp) * d * sizeof(float)));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(peers, blocks.data(), tp * sizeof(uint8_t*), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h, residual, M * d * sizeof(float), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w, norm_w, d * sizeof(float), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(counters, 0, (size_t(tp) * 4 + 1) * sizeof(uint32_t), s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(aq, a_q, size_t(tp) * M * k, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(wq, w_q, size_t(tp) * d * k, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(as, a_scale, size_t(tp) * M * sizeof(float), cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ws, w_scale, size_t(tp) * d * sizeof(float), cudaMemcpyHostToDevice, s);
+    const char* why = "";
+    for (int r = 0; r < tp && e == cudaSuccess; ++r) {
+        GemmPlan plan;
+        e = gemm_make_plan(&plan, kGemmI8, aq + size_t(r) * M * k, wq + size_t(r) * d * k, int(M), d, k, 0, splits, tile, &why);
+        if (e != cudaSuccess) break;
+        if (!(plan.splits == 1 || plan.cluster)) {
+            for (void* p : owned) cudaFree(p);
+            return fail(B200_UNSUPPORTED, "selftest_tp_scatter: the plan has no fused epilogue");
+        }
+        GemmEpilogue pe;
+        pe.fused = 1;
+        pe.a_scale = as + size_t(r) * M;
+        pe.a_per_row = 1;
+        pe.b_scale = ws + size_t(r) * d;
+        pe.b_per_col = 1;
+        pe.out = h;                      // never written: every row goes to its owner's block
+        pe.push.peers = peers;
+        pe.push.o_part = o_part;
+        pe.push.o_count = kTpCountOffset;
+        pe.push.tp = tp;
+        pe.push.rank = r;
+        pe.push.rows = rows;
+        pe.push.arrived = counters + 4 * tp;
+        e = gemm_launch(plan, pe, ctx->err_dev, s);
+    }
+    for (int r = 0; r < tp && e == cudaSuccess; ++r)
+        e = tp_finish(peers, o_sx, o_xq, o_part, tp, r, rows, d, w, eps, h, counters + 4 * r, counters + 4 * r + 1, ctx->err_dev, s,
+                      50ull * 1000 * 1000, kTpCountOffset, 1u, counters + 4 * r + 2);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, h, M * d * sizeof(float), cudaMemcpyDeviceToHost, s);
+    for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+        const uint8_t* b = blocks[i == 0 ? 0 : tp - 1];
+        e = cudaMemcpyAsync(xq_out + size_t(i) * M * d, b + o_xq, M * d, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(sx_out + size_t(i) * M, b + o_sx, M * 4, cudaMemcpyDeviceToHost, s);
+    }
+    for (int p = 0; p < tp && e == cudaSuccess; ++p)
+        e = cudaMemcpyAsync(counts_out + size_t(p) * tp, blocks[p] + kTpCountOffset, size_t(tp) * 4, cudaMemcpyDeviceToHost, s);
+    int32_t st = B200_OK;
+    if (e != cudaSuccess) st = fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("selftest_tp_scatter: ") + why + " " + cudaGetErrorString(e));
+    else st = b200_synchronize(ctx);
+    for (void* p : owned) cudaFree(p);
     return st;
 }
 

@@ -66,8 +66,36 @@ __device__ __forceinline__ void store_out4(const GemmEpilogue& ep, size_t idx, f
 
 // Four finished accumulators of (row, columns n .. n + 3): raw store into the single output plane, or the
 // fused epilogue (not the gate form).
+// First element of output row `row` when the rows are scattered over the ranks' exchange blocks (GemmPush).
+__device__ __forceinline__ float* push_row(const GemmPush& ps, int row, int N) {
+    const int owner = row / ps.rows;
+    return reinterpret_cast<float*>(ps.peers[owner] + ps.o_part) +
+           (static_cast<size_t>(ps.rank) * ps.rows + (row - owner * ps.rows)) * N;
+}
+
+// Called by one warp of a tile's first CTA after a CTA or cluster barrier that follows the tile's stores (see
+// GemmPush): counts the tile; the warp that completes the launch tells every rank.  The barrier, the device-scope
+// fences around the local counter and the system-scope fence and release of the last warp order every store of the
+// launch before the count that the owners acquire.
+__device__ __forceinline__ void push_signal(const GemmPush& ps, int lane, unsigned int tiles) {
+    unsigned int last = 0;
+    if (lane == 0) {
+        __threadfence();
+        last = atomicAdd(ps.arrived, 1u) == tiles - 1u ? 1u : 0u;
+        if (last) {
+            __threadfence();
+            *ps.arrived = 0u;
+        }
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last && lane < ps.tp) {
+        __threadfence_system();
+        red_release_sys_add(reinterpret_cast<uint32_t*>(ps.peers[lane] + ps.o_count) + ps.rank, 1u);
+    }
+}
+
 template <bool kInt8>
-__device__ __forceinline__ void emit4(const KernelArgs& p, int row, int n, const uint32_t (&v)[4]) {
+__device__ __forceinline__ void emit4(const KernelArgs& p, int row, int n, const uint32_t (&v)[4], float* pushed = nullptr) {
     const GemmEpilogue& ep = p.ep;
     if (!ep.fused) {
         *reinterpret_cast<uint4*>(static_cast<uint32_t*>(ep.raw) + static_cast<size_t>(row) * p.N + n) =
@@ -85,6 +113,10 @@ __device__ __forceinline__ void emit4(const KernelArgs& p, int row, int n, const
         else if (ep.act == kActRelu) x = fmaxf(x, 0.0f);
         y[t] = x;
     }
+    if (pushed) {
+        *reinterpret_cast<float4*>(pushed + n) = make_float4(y[0], y[1], y[2], y[3]);
+        return;
+    }
     store_out4(ep, static_cast<size_t>(row) * p.N + n, y[0], y[1], y[2], y[3]);
 }
 
@@ -95,6 +127,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     constexpr int kStageBytes = kABytes + kBBytes;
     constexpr uint32_t kTmemCols = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;     // a power of two
     constexpr uint32_t kIdesc = kInt8 ? umma_idesc(1, 2, kBM, BN) : umma_idesc(0, 1, kBM, BN);
+    constexpr int kPartPitch = BN + 4;          // words per row of a partial tile parked for the cluster reduction
 
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -226,12 +259,25 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             // is idle by now (every MMA has completed), consecutive threads hold consecutive rows
             uint32_t* part = reinterpret_cast<uint32_t*>(smem_dyn + (smem_base - smem_u32(smem_dyn)));
             const int rl = q * 32 + lane;
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32(t_row + c0, v);
-                tmem_ld_wait();
+            if (ep.rope.enabled) {
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + c0, v);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) part[(c0 + j) * kBM + rl] = v[j];
+                    for (int j = 0; j < 32; ++j) part[(c0 + j) * kBM + rl] = v[j];
+                }
+            } else {
+                // row-major with a pitch of BN + 4 words: the 16-byte stores of eight neighbouring rows fall into
+                // different banks, and the reduction below reads (and then writes to global memory) whole row segments
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<uint4*>(part + rl * kPartPitch + c0 + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
             }
         } else if (ready) {
             if (!ep.fused) {
@@ -253,6 +299,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             } else if (!p.gate) {
                 const float sa = ep.a_scale[ep.a_per_row ? (row_ok ? row : 0) : 0];
                 const size_t row_off = static_cast<size_t>(row_ok ? row : 0) * p.N;
+                float* pushed = ep.push.peers != nullptr && row_ok ? push_row(ep.push, row, p.N) : nullptr;
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     if (n0 + c0 >= p.N) break;
                     uint32_t v[32];
@@ -273,7 +320,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                                 else if (ep.act == kActRelu) x = fmaxf(x, 0.0f);
                                 y[t] = x;
                             }
-                            store_out4(ep, row_off + n, y[0], y[1], y[2], y[3]);
+                            if (pushed) *reinterpret_cast<float4*>(pushed + n) = make_float4(y[0], y[1], y[2], y[3]);
+                            else store_out4(ep, row_off + n, y[0], y[1], y[2], y[3]);
                         }
                     }
                 }
@@ -396,28 +444,43 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                         *reinterpret_cast<uint2*>(dst + 64) = b;
                     }
                 }
-            } else
-            for (int cc = 0; cc < cpr; cc += 4) {
-                const int col = rank * cpr + cc;
-                uint32_t v[4] = {0u, 0u, 0u, 0u};
-                for (int peer = 0; peer < nsplit; ++peer) {
-                    const uint32_t* pp = cl.map_shared_rank(part, peer);
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        const uint32_t x = pp[(col + t) * kBM + rl];
-                        if constexpr (kInt8) v[t] += x;    // two's complement wrap = int32 addition
-                        else v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(x));
+            } else {
+                // CTA `rank` finishes the rows [rank * kBM / nsplit, (rank + 1) * kBM / nsplit) of the tile, all BN columns:
+                // sixteen bytes per thread, consecutive threads along a row, so that global memory (this GPU's or, with
+                // GemmPush, the owner's) receives whole row segments
+                const int rows_per = kBM / nsplit;
+                constexpr int kGroups = BN / 4;
+                const int total = rows_per * kGroups;
+                const bool push = p.ep.push.peers != nullptr && p.ep.fused;
+                for (int idx = (warp - 2) * 32 + lane; idx < total; idx += 128) {
+                    const int r_tile = rank * rows_per + idx / kGroups;     // row inside the tile
+                    const int col = 4 * (idx % kGroups);
+                    uint32_t v[4] = {0u, 0u, 0u, 0u};
+                    for (int peer = 0; peer < nsplit; ++peer) {
+                        const uint4 x = *reinterpret_cast<const uint4*>(cl.map_shared_rank(part, peer) + r_tile * kPartPitch + col);
+                        if constexpr (kInt8) {       // two's complement wrap = int32 addition
+                            v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+                        } else {
+                            v[0] = __float_as_uint(__uint_as_float(v[0]) + __uint_as_float(x.x));
+                            v[1] = __float_as_uint(__uint_as_float(v[1]) + __uint_as_float(x.y));
+                            v[2] = __float_as_uint(__uint_as_float(v[2]) + __uint_as_float(x.z));
+                            v[3] = __float_as_uint(__uint_as_float(v[3]) + __uint_as_float(x.w));
+                        }
                     }
+                    const int out_row = m0 + r_tile;
+                    const int n = n0 + col;
+                    if (out_row < p.M && n < p.N) emit4<kInt8>(p, out_row, n, v, push ? push_row(p.ep.push, out_row, p.N) : nullptr);
                 }
-                const int n = n0 + col;
-                if (row < p.M && n < p.N) emit4<kInt8>(p, row, n, v);
             }
         }
         cl.sync();
+        // every CTA of the cluster has stored its rows of the tile: the first one counts the tile
+        if (p.ep.push.peers != nullptr && warp == 2 && cl.block_rank() == 0) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
     }
 
     tc5_fence_before();
     __syncthreads();
+    if (p.ep.push.peers != nullptr && !p.cluster_reduce && warp == 2) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
     if (warp == 1) {
         __syncwarp();
         tc5_fence_after();
@@ -531,6 +594,21 @@ bool make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_
     return r == CUDA_SUCCESS;
 }
 
+// Tensor map of an output plane [rows, cols] of 4-byte (f32 / raw accumulators) or 2-byte (bf16) elements for TMA
+// stores of 32 x 32 boxes whose shared-memory rows (128 or 64 bytes) are swizzled over their own width.
+bool make_out_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, int elem_bytes) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, elem_bytes == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 template <int BN, bool kInt8>
 cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t stream) {
     const int stage_bytes = kABytes + BN * kBK;
@@ -547,13 +625,32 @@ cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t 
 constexpr int kMaxSmem = 232448;   // dynamic shared memory a CTA may ask for on sm_100
 
 template <int BN, bool kInt8, bool kPair>
-cudaError_t launch_persist_t(const GemmPlan& plan, const PersistArgs& args, cudaStream_t stream) {
+cudaError_t launch_persist_t(const GemmPlan& plan, PersistArgs args, cudaStream_t stream) {
     const int stage_bytes = kABytes + (kPair ? BN / 2 : BN) * kBK;
-    const int smem = plan.stages * stage_bytes + 1024 + 8 * (2 * plan.stages + 5) + 16;
+    // Output through shared memory and TMA stores when the plane allows it (16-byte aligned base and row pitch); the
+    // staging buffers may cost the operand ring a stage.
+    CUtensorMap tma_out = plan.tma_a;      // placeholder when the stores stay per thread
+    const GemmEpilogue& ep = args.ep;
+    void* out = ep.fused ? ep.out : ep.raw;
+    const int elem = ep.fused && ep.out_bf16 ? 2 : 4;
+    const int n_out = plan.gate ? plan.N / 2 : plan.N;
+    static const bool tma_store_allowed = [] {
+        const char* e = std::getenv("B200_GEMM_TMA_STORE");      // 0 keeps the per-thread stores, for measurements
+        return !(e && e[0] == '0');
+    }();
+    args.tma_store = 0;
+    if (tma_store_allowed && out != nullptr && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (static_cast<size_t>(n_out) * elem) % 16 == 0 &&
+        make_out_map(&tma_out, out, plan.M, n_out, elem)) {
+        args.tma_store = 1;
+        const int fit = (kMaxSmem - 1024 - 256 - kOutStageTotal) / stage_bytes;
+        if (args.stages > fit) args.stages = fit;
+        if (args.stages < 2) return cudaErrorInvalidValue;
+    }
+    const int smem = args.stages * stage_bytes + 1024 + 8 * (2 * args.stages + 5) + 16 + (args.tma_store ? kOutStageTotal : 0);
     static int configured[64] = {};
     if (cudaError_t e = ensure_dynamic_smem(gemm_tc5_persist_kernel<BN, kInt8, kPair>, smem, configured)) return e;
     return launch_ex(gemm_tc5_persist_kernel<BN, kInt8, kPair>, dim3(plan.grid), dim3(kPersistThreads), smem, stream, kPair ? 2 : 1,
-                     true, plan.tma_a, plan.tma_b, args);
+                     true, plan.tma_a, plan.tma_b, tma_out, args);
 }
 
 }  // namespace
@@ -586,6 +683,8 @@ void gemm_plan_make_persistent(GemmPlan* plan, int sm_count, bool fused_epilogue
     }();
     // (with at most one 128 x 256 tile per SM the one-CTA form has as many rounds and more streams in flight: measured)
     const bool pair = pair_allowed && bn == 256 && plan->M > kBM && sm_count >= 2 && tiles > sm_count;
+    // (256 x 128 tiles on pairs were tried for grids whose last round is half empty, 4096^3 = 3.46 rounds of 256 x 256
+    // tiles: 1944 TOPS against 2565, the narrower MMA does not keep the tensor pipe fed.)
     const int stage_bytes = kABytes + (pair ? bn / 2 : bn) * kBK;
     int stages = (kMaxSmem - 1024 - 256) / stage_bytes;
     if (stages > 8) stages = 8;
@@ -675,7 +774,7 @@ cudaError_t gemm_make_plan(GemmPlan* plan, int kind, const void* a, const void* 
     if (stages < 2) stages = 2;
     plan->stages = stages;
     // the parked partial tile (bn x 128 accumulators) reuses the operand ring
-    plan->cluster = (!gate && exact_pow2(splits) && stages * stage_bytes >= bn * kBM * 4) ? 1 : 0;
+    plan->cluster = (!gate && exact_pow2(splits) && stages * stage_bytes >= (bn + 4) * kBM * 4) ? 1 : 0;
     plan->out_planes = plan->cluster ? 1 : splits;
     if (!encode_maps) return cudaSuccess;      // shape decisions only (plan queries)
     if (!make_operand_map(&plan->tma_a, a, M, K, kBM)) return fail("gemm: cuTensorMapEncodeTiled failed for A");
@@ -701,6 +800,7 @@ cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* 
         pa.vec16 = ((reinterpret_cast<uintptr_t>(ep.b_scale) | reinterpret_cast<uintptr_t>(ep.bias)) & 15) == 0 ? 1 : 0;
         pa.ep = ep;
         pa.err = err;
+        if (ep.push.peers != nullptr) return cudaErrorInvalidValue;    // the scatter exists in the one-tile kernel only
         const bool i8p = plan.kind == kGemmI8;
         if (plan.pair) {
             if (plan.bn != 256 || ep.wait.flags != nullptr) return cudaErrorInvalidValue;
@@ -722,6 +822,10 @@ cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* 
     if (ep.fused && plan.splits != 1 && !plan.cluster) return cudaErrorInvalidValue;
     if (ep.rope.enabled && !gemm_plan_can_rope(plan, ep.rope.hq, ep.rope.hkv)) return cudaErrorInvalidValue;
     if (!ep.fused && plan.gate) return cudaErrorInvalidValue;   // raw planes always use the plain column layout
+    if (ep.push.peers != nullptr &&
+        (!ep.fused || plan.gate || ep.rope.enabled || ep.residual != nullptr || ep.out_bf16 || ep.push.rows <= 0 ||
+         ep.push.tp <= 0 || ep.push.tp > 32 || ep.push.arrived == nullptr || plan.M != ep.push.tp * ep.push.rows))
+        return cudaErrorInvalidValue;
     const bool i8 = plan.kind == kGemmI8;
     switch (plan.bn) {
         case 64: return i8 ? launch_t<64, true>(plan, args, stream) : launch_t<64, false>(plan, args, stream);
@@ -730,6 +834,12 @@ cudaError_t gemm_launch(const GemmPlan& plan, const GemmEpilogue& ep, uint32_t* 
         case 256: return i8 ? launch_t<256, true>(plan, args, stream) : launch_t<256, false>(plan, args, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+int gemm_plan_tiles(const GemmPlan& plan) {
+    const int n_out = plan.gate ? plan.N / 2 : plan.N;
+    const int out_cols = plan.gate ? plan.bn / 2 : plan.bn;
+    return ((n_out + out_cols - 1) / out_cols) * ((plan.M + kBM - 1) / kBM);
 }
 
 cudaError_t gemm_splitk_epilogue(int kind, int splits, int M, int N, int gate, const void* raw,

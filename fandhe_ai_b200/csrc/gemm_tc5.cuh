@@ -45,6 +45,22 @@ struct GemmPeerWait {
     uint64_t timeout_ns = 0;
 };
 
+// Optional scatter of a row-parallel output over the GPUs of a tensor-parallel group (a reduce-scatter fused into the
+// GEMM): the f32 rows of the fused epilogue are stored not into `out` but into the exchange block of the rank that
+// owns the row (rank = row / rows), plane `rank` of its receive area [tp][rows][N], through the peer mappings with
+// plain stores.  Every finished tile counts itself in *arrived (this GPU's memory); the tile that completes the launch
+// resets that counter and adds one to count[rank] in the block of every rank (system-scope release), and the owner's
+// finish kernel waits for the counts and sums its planes from local memory.
+// Needs fused = 1 with f32 output, no residual and no gate; one-tile kernel only.
+struct GemmPush {
+    uint8_t* const* peers = nullptr;   // device table [tp] of block bases (this rank's own included); null: off
+    size_t o_part = 0;                 // byte offset of the receive area in a block
+    size_t o_count = 0;                // byte offset of count[tp] in a block
+    int tp = 0, rank = 0;
+    int rows = 0;                      // rows per owner
+    unsigned int* arrived = nullptr;   // tiles of the running launch that have stored their rows (zero between launches)
+};
+
 struct GemmEpilogue {
     int fused = 0;                 // 0: write raw accumulators to `raw`; 1: fused epilogue to `out`
     void* raw = nullptr;           // [splits][M][N] int32 (i8) or f32 (fp8)
@@ -59,6 +75,7 @@ struct GemmEpilogue {
     int act = kActNone;              // kActSiluGate: B rows [0, N/2) are gate, [N/2, N) are up, N_out = N/2
     GemmRope rope;                   // see GemmRope; needs fused = 1 with per-row / per-column scales, no bias
     GemmPeerWait wait;               // see GemmPeerWait
+    GemmPush push;                   // see GemmPush
 };
 
 struct GemmPlan {
@@ -78,6 +95,9 @@ struct GemmPlan {
     int pair = 0;        // persistent form on CTA pairs (cta_group::2): 256-row tiles, each CTA loads half of the B rows
     const void* b_ptr = nullptr;   // operand B as given to gemm_make_plan (the pair form re-encodes its tensor map)
 };
+
+// Output tiles of a one-tile-kernel launch of the plan.
+int gemm_plan_tiles(const GemmPlan& plan);
 
 // Switches a plan to the persistent kernel when the problem has enough tiles for `sm_count` SMs: half a wave when
 // the launch will use a fused epilogue, two waves for raw accumulator output.  Afterwards splits == 1,

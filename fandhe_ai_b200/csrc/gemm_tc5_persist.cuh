@@ -18,6 +18,13 @@
 // the leader's commits arrive on both CTAs' empty / accumulator-full barriers, and both CTAs' epilogue threads arrive on
 // the leader's accumulator-empty barriers.
 //
+// Output (tma_store): every epilogue warp stages 32 rows x 32 columns of finished values (32 f32 / raw accumulators per row; 32 bf16 = 64 bytes) in
+// its own 4 KB of shared memory, in the swizzle pattern of the tensor map (128-byte rows: 16-byte piece t of row r at
+// piece t ^ (r & 7), so that the 32 lanes, one row each, write without bank conflicts), and one lane sends the box with
+// a TMA store, which also drops what lies beyond M or N.  The warp waits for the store to have read the buffer only
+// when it comes back to fill it again.  Output planes whose base or row pitch is not a multiple of 16 bytes keep the
+// per-thread 16-byte stores.
+//
 // The arithmetic per element is that of the one-tile kernel: y = act(fma(float(acc), sa * sb, bias)) (+ residual),
 // except that SiLU uses the fast exponential and reciprocal.
 
@@ -33,6 +40,7 @@ struct PersistArgs {
     int gate;              // B tile = BN/2 gate rows + BN/2 up rows
     int n_half;            // N / 2 in the gate form
     int vec16;             // the scale and bias vectors start on 16-byte boundaries (16-byte loads allowed)
+    int tma_store;         // the output goes through shared memory and TMA stores (tma_out is valid)
     GemmEpilogue ep;
     uint32_t* err;
 };
@@ -87,9 +95,72 @@ __device__ __forceinline__ void store32(const GemmEpilogue& ep, size_t idx, floa
     }
 }
 
+constexpr int kOutStageBytes = 4096;        // per epilogue warp: 32 rows x 128 bytes
+constexpr int kOutStageTotal = (kEpilogueThreads / 32) * kOutStageBytes;
+
+// Staging of one warp's finished values for TMA stores (see the file comment): 32 columns of the warp's 32 rows per
+// store.  `rows` = rows of the output (a warp whose rows all lie beyond it sends nothing).
+struct OutStage {
+    const CUtensorMap* map;
+    uint32_t buf;        // shared address of the warp's buffer (1024-byte aligned)
+    int lane;
+    int rows;
+
+    __device__ __forceinline__ void begin() {
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
+    }
+    __device__ __forceinline__ void st4(uint32_t dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+    }
+    __device__ __forceinline__ void send(int x, int y) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && y < rows) {
+            tma_store_2d(map, buf, x, y);
+            bulk_commit_group();
+        }
+    }
+    // 32 words (f32 values or raw accumulators) of columns n .. n + 31: 128-byte rows, 128-byte swizzle
+    __device__ __forceinline__ void put_words(const uint32_t (&w)[32], int n, int row0) {
+        begin();
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            st4(buf + static_cast<uint32_t>(lane * 128 + ((t ^ (lane & 7)) << 4)), w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
+        send(n, row0);
+    }
+    __device__ __forceinline__ void put_f32(const float (&y)[32], int n, int row0) {
+        begin();
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            st4(buf + static_cast<uint32_t>(lane * 128 + ((t ^ (lane & 7)) << 4)), __float_as_uint(y[4 * t]),
+                __float_as_uint(y[4 * t + 1]), __float_as_uint(y[4 * t + 2]), __float_as_uint(y[4 * t + 3]));
+        send(n, row0);
+    }
+    // 32 bf16 values per row: 64-byte rows, 64-byte swizzle (piece t of row r at piece t ^ ((r >> 1) & 3))
+    __device__ __forceinline__ void put_bf16(const float (&y)[32], int n, int row0) {
+        begin();
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            st4(buf + static_cast<uint32_t>(lane * 64 + ((t ^ ((lane >> 1) & 3)) << 4)), pack_bf16x2(y[8 * t], y[8 * t + 1]),
+                pack_bf16x2(y[8 * t + 2], y[8 * t + 3]), pack_bf16x2(y[8 * t + 4], y[8 * t + 5]), pack_bf16x2(y[8 * t + 6], y[8 * t + 7]));
+        send(n, row0);
+    }
+};
+
+// Adds the residual row segment to 32 finished values (columns n .. n + 31 of row `row`; the segment is whole).
+__device__ __forceinline__ void add_residual32(const GemmEpilogue& ep, size_t idx, float (&y)[32]) {
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        const float4 r = *reinterpret_cast<const float4*>(ep.residual + idx + 4 * t);
+        y[4 * t] += r.x; y[4 * t + 1] += r.y; y[4 * t + 2] += r.z; y[4 * t + 3] += r.w;
+    }
+}
+
 template <int BN, bool kInt8, bool kPair>
 __global__ void __launch_bounds__(kPersistThreads, 1)
-gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, PersistArgs p) {
+gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                        const __grid_constant__ CUtensorMap tma_out, PersistArgs p) {
     constexpr int kBRows = kPair ? BN / 2 : BN;      // B rows this CTA brings in per stage
     constexpr int kBBytes = kBRows * kBK;
     constexpr int kStageBytes = kABytes + kBBytes;
@@ -98,7 +169,9 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     constexpr uint32_t kIdesc = kInt8 ? umma_idesc(1, 2, kTileRows, BN) : umma_idesc(0, 1, kTileRows, BN);
 
     extern __shared__ uint8_t smem_dyn[];
-    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    // [output staging of the epilogue warps (tma_store)] [operand ring] [barriers]
+    const uint32_t out_stage_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t smem_base = out_stage_base + (p.tma_store ? static_cast<uint32_t>(kOutStageTotal) : 0u);
     const uint32_t bar_base = smem_base + p.stages * kStageBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (p.stages + s); };
@@ -117,6 +190,7 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tma_a);
         tma_prefetch_desc(&tma_b);
+        if (p.tma_store) tma_prefetch_desc(&tma_out);
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
@@ -271,6 +345,8 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
         const int half = (warp - 2) >> 2;
         const int rl = q * 32 + lane;                 // row inside the tile
         const GemmEpilogue& ep = p.ep;
+        OutStage st{&tma_out, out_stage_base + static_cast<uint32_t>((warp - 2) * kOutStageBytes), lane, p.M};
+        const bool staged = p.tma_store != 0;
         pdl_wait();      // scales, bias, residual and the output buffers belong to the surrounding kernels
         bool ok = true;
         int j = 0;
@@ -283,6 +359,7 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             tile_origin(p, tile, m_idx, n_idx);
             const int m0 = m_idx * kTileRows + static_cast<int>(rank) * kBM, n0 = n_idx * out_cols;
             const int row = m0 + rl;
+            const int row0 = m0 + q * 32;                 // first row of this warp
             const bool row_ok = row < p.M;
             const size_t row_c = static_cast<size_t>(row_ok ? row : 0);
             if (ok && !ep.fused) {
@@ -292,7 +369,8 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                     uint32_t v[32];
                     tmem_ld_32x32(t_row + c0, v);
                     tmem_ld_wait();
-                    if (row_ok) {
+                    if (staged) st.put_words(v, n0 + c0, row0);
+                    else if (row_ok) {
 #pragma unroll
                         for (int t = 0; t < 32; t += 4) {
                             const int n = n0 + c0 + t;
@@ -340,7 +418,17 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                         else if (ep.act == kActRelu) x = fmaxf(x, 0.0f);
                         y[t] = x;
                     }
-                    if (row_ok) {
+                    if (staged) {
+                        if (ep.residual && row_ok) {
+                            if (whole) add_residual32(ep, row_c * p.N + n, y);
+                            else {
+#pragma unroll
+                                for (int t = 0; t < 16; ++t) y[t] += ep.residual[row_c * p.N + n + t];
+                            }
+                        }
+                        if (ep.out_bf16) st.put_bf16(y, n, row0);
+                        else st.put_f32(y, n, row0);
+                    } else if (row_ok) {
                         if (whole) store32(ep, row_c * p.N + n, y);
                         else {
 #pragma unroll
@@ -377,7 +465,17 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                         const float uv = fmaf(acc_to_f32<kInt8>(u[t]), sa * su[t], bu);
                         y[t] = silu_fast(gv) * uv;
                     }
-                    if (row_ok) {
+                    if (staged) {
+                        if (ep.residual && row_ok) {
+                            if (whole) add_residual32(ep, row_c * p.n_half + n, y);
+                            else {
+#pragma unroll
+                                for (int t = 0; t < 16; ++t) y[t] += ep.residual[row_c * p.n_half + n + t];
+                            }
+                        }
+                        if (ep.out_bf16) st.put_bf16(y, n, row0);
+                        else st.put_f32(y, n, row0);
+                    } else if (row_ok) {
                         if (whole) store32(ep, row_c * p.n_half + n, y);
                         else {
 #pragma unroll
@@ -391,6 +489,7 @@ gemm_tc5_persist_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             if (kPair && rank != 0) mbar_arrive_cluster(mapa_shared(tmem_empty(buf), 0));
             else mbar_arrive(tmem_empty(buf));
         }
+        if (staged && lane == 0) bulk_wait_all();      // the staging buffers stay valid until the last store has read them
     }
 
     tc5_fence_before();

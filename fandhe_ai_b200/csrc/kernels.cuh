@@ -117,9 +117,14 @@ cudaError_t gate_rows_f32(const int* raw, int splits, int M, int F, const float*
 // bases; a block starts with 512 bytes of flags (ready[tp] at +0, delivered[tp] at +256).  The kernel waits for the
 // peers' partials but not for their rows: the consumer of the delivered rows waits for the delivered flags.
 // Needs one GPU per rank unless the flags are raised beforehand.
+// Scattered form (push_tiles != 0): the ranks' GEMMs have stored the partials of this rank's rows straight into its
+// block as planes [tp][rows][d] at o_part and count their launches in count[tp] at o_count (GemmPush); the kernel
+// waits until every count has grown by push_tiles (1: one count per launch) since the call before (*push_target
+// keeps the sum) and reads only its own memory.
 bool tp_finish_supported(int d);
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
-                      cudaStream_t s, uint64_t timeout_ns = 0);   // 0: the default bound of a cross-GPU wait
+                      cudaStream_t s, uint64_t timeout_ns = 0,    // 0: the default bound of a cross-GPU wait
+                      size_t o_count = 0, uint32_t push_tiles = 0, uint32_t* push_target = nullptr);
 
 }  // namespace b200

@@ -68,6 +68,18 @@ __device__ __forceinline__ void fence_proxy_async() {
 __device__ __forceinline__ void fence_proxy_async_all() {
     asm volatile("fence.proxy.async;" ::: "memory");
 }
+// TMA store of one box from shared memory (written by ordinary stores, then fence_proxy_async) to the tensor at
+// (x, y); parts of the box outside the tensor are dropped.  Stores are tracked in bulk groups of the issuing thread.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tmap), "r"(src_smem), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// every earlier bulk group of this thread has finished READING its shared memory (the buffer may be rewritten)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// every earlier bulk group of this thread is complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
@@ -349,6 +361,29 @@ __device__ __forceinline__ bool wait_peer_flag(const uint32_t* flag, uint32_t ep
             return false;
         }
         if (static_cast<int32_t>(v - epoch) >= 0) return true;
+        if ((it & 63u) == 63u && global_timer_ns() - t0 > timeout_ns) break;
+    }
+    atomicCAS(err, 0u, static_cast<uint32_t>(kErrPeerWait));
+    return false;
+}
+
+// A count that other GPUs raise in this GPU's memory with red_release_sys_add (one per finished piece of work): the
+// wait ends when it has reached `target` (difference modulo 2^32, so the count may wrap).  A count passes through
+// every value, so the poison travels in a word of its own: `poison` is a flag word of the same sender.
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ bool wait_peer_count(const uint32_t* count, uint32_t target, const uint32_t* poison, uint32_t* err,
+                                                uint64_t timeout_ns) {
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 0;; ++it) {
+        const uint32_t v = ld_acquire_sys(count);
+        if (static_cast<int32_t>(v - target) >= 0) return true;
+        if ((it & 15u) == 15u && ld_acquire_sys(poison) == kPeerPoison) {
+            atomicCAS(err, 0u, static_cast<uint32_t>(kErrPeerFailed));
+            return false;
+        }
         if ((it & 63u) == 63u && global_timer_ns() - t0 > timeout_ns) break;
     }
     atomicCAS(err, 0u, static_cast<uint32_t>(kErrPeerWait));

@@ -160,6 +160,12 @@ class Decoder:
         with peer loads and stores) instead of ncclAllReduce."""
         return bool(lib().b200_decoder_tp_exchange(self._h))
 
+    @property
+    def tp_exchange_mode(self) -> int:
+        """0: ncclAllReduce; 1: finish kernel that loads the peers' partials; 2: the GEMMs store their partial rows
+        into the owner's block and the finish kernel reads local memory only."""
+        return int(lib().b200_decoder_tp_exchange(self._h))
+
     def begin(self, batch: int, max_total_lens, start_lens=None) -> None:
         mt = np.ascontiguousarray(max_total_lens, dtype=np.int32)
         sl = np.ascontiguousarray(start_lens, dtype=np.int32) if start_lens is not None else None

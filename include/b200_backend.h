@@ -405,10 +405,14 @@ int32_t b200_decoder_init_random(b200_decoder* dec, uint64_t seed, float std);
 /* 128-byte NCCL unique id (rank 0 makes it, the launcher hands it to every rank) and communicator set-up. */
 int32_t b200_nccl_unique_id(uint8_t* out128);
 int32_t b200_decoder_init_tp(b200_decoder* dec, const uint8_t* unique_id128);
-/* 1 when init_tp mapped the other ranks' exchange blocks (CUDA IPC), so that the row-parallel outputs are
- * finished by one kernel that reads the peers' partial sums and delivers the quantised rows to every rank (the
- * GEMM that consumes those rows waits for the peers' delivered flags right before it loads its A operand);
- * 0 when the step uses ncclAllReduce instead (mapping failed, batch not divisible by the rank count, or
+/* Non-zero when init_tp mapped the other ranks' exchange blocks (CUDA IPC), so that a row-parallel output is finished
+ * by one kernel on the rank that owns the token row (rank-order sum of the ranks' partials, residual, RMSNorm, per-token
+ * int8) which delivers the quantised row to every rank; the GEMM that consumes those rows waits for the peers'
+ * delivered flags right before it loads its A operand.  2: the row-parallel GEMMs store their partial rows straight into
+ * the owner's block and count themselves there, the finish kernel reads local memory only (the default; as planned
+ * for the last enqueued step).  1: the GEMMs write local partials and the finish kernel loads them from the peers
+ * (B200_TP_PUSH=0 in the environment, or a GEMM plan without a fused epilogue in the one-tile kernel).
+ * 0: the step uses ncclAllReduce instead (mapping failed, batch not divisible by the rank count, or
  * B200_TP_EXCHANGE=0 in the environment).  No reference counterpart (the reference has no tensor parallelism). */
 int32_t b200_decoder_tp_exchange(const b200_decoder* dec);
 /* Failure-detection self-test on one GPU: runs the cross-GPU finish kernel as rank 0 of 2 with a peer whose flags
@@ -425,6 +429,17 @@ int32_t b200_selftest_peer_wait(b200_ctx* ctx);
 int32_t b200_selftest_tp_finish(b200_ctx* ctx, int32_t tp, int32_t rank, int32_t rows, int32_t d, const float* partials,
                                 const float* residual, const float* norm_w, float eps, float* h_out, int8_t* xq_out,
                                 float* sx_out, uint32_t* flags_out);
+/* Numerical self-test on one GPU of the scattered form of a row-parallel output: for every rank s the int8 GEMM
+ * a_q[s][tp * rows][k] x w_q[s][d][k]^T with scales a_scale[s][tp * rows], w_scale[s][d] is launched as rank s and
+ * stores each dequantised row into the exchange block of the rank that owns it (`tp` blocks on this device) and counts
+ * itself there when its last tile is stored; then the finish kernel runs as rank 0, 1, ... reading only its own block (rank-order sum, residual,
+ * RMSNorm, per-token int8) and delivers into every block.  splits / tile as in b200_set_tuning (0: heuristic).
+ * Outputs: h_out[tp * rows][d], xq_out[2][tp * rows][d] and sx_out[2][tp * rows] (first and last block),
+ * counts_out[tp][tp] (launches counted in every block, per source rank: 1 each).  No reference counterpart. */
+int32_t b200_selftest_tp_scatter(b200_ctx* ctx, int32_t tp, int32_t rows, int32_t d, int32_t k, int32_t splits, int32_t tile,
+                                 const int8_t* a_q, const float* a_scale, const int8_t* w_q, const float* w_scale,
+                                 const float* residual, const float* norm_w, float eps, float* h_out, int8_t* xq_out,
+                                 float* sx_out, uint32_t* counts_out);
 /* Starts a generation of `batch` rows: row b starts at start_lens[b] cached tokens (NULL: 0) and may grow
  * to max_total_lens[b]; blocks for the final length are reserved now and the tables uploaded once. */
 int32_t b200_decoder_begin(b200_decoder* dec, int32_t batch, const int32_t* start_lens, const int32_t* max_total_lens);

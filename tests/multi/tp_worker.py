@@ -36,7 +36,6 @@ def main():
     obj = [nccl_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(obj, src=0)
     dec.init_tp(obj[0])
-    exchange = dec.tp_exchange       # True: finish kernel over mapped peer blocks; False: ncclAllReduce
     dec.load_weights(weights)
     dec.begin(batch, [steps + 1] * batch)
     rng = np.random.default_rng(9)
@@ -45,6 +44,7 @@ def main():
     for t in range(steps):
         dec.step(all_ids[t])
         got.append(dec.logits())
+    exchange = dec.tp_exchange_mode   # 2: scattered by the GEMMs, 1: pulled by the finish kernel, 0: ncclAllReduce
     dec.close()
     ok, msg = True, ""
     if rank == 0:
