@@ -144,6 +144,9 @@ SIGNATURES = {
     "b200_selftest_peer_wait": (_I32, [_P]),
     "b200_selftest_tp_finish": (_I32, [_P, _I32, _I32, _I32, _I32, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
     "b200_selftest_tp_scatter": (_I32, [_P, _I32, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
+    "b200_decoder_batch": (_I32, [_P]),
+    "b200_sampling_weights": (_I32, [_P, C.c_int64, C.c_int64, _I32, _I32, C.c_float, _P]),
+    "b200_decoder_sampling_weights": (_I32, [_P, _I32, _I32, C.c_float, _P, C.c_uint64]),
     "b200_decoder_step_rows": (_I32, [_P, _P, _P, _P]),
     "b200_decoder_row_restart": (_I32, [_P, _I32, _I32]),
     "b200_scheduler_create": (_I32, [_P, _I32, _I32, _I32, _P]),

@@ -13,7 +13,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libb200backend.so"
-SOURCES = ["backend.cu", "backend_paged.cu", "decoder.cu", "gemm_tc5.cu", "gemm_block_scaled.cu", "quant.cu", "paged_kv.cu", "decode_kernels.cu", "decode_rows.cu", "scheduler.cu", "safetensors.cu"]
+SOURCES = ["backend.cu", "backend_paged.cu", "decoder.cu", "gemm_tc5.cu", "gemm_block_scaled.cu", "quant.cu", "paged_kv.cu", "decode_kernels.cu", "decode_rows.cu", "scheduler.cu", "safetensors.cu", "sampling.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

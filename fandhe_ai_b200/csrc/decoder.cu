@@ -1802,6 +1802,7 @@ int32_t b200_decoder_shard_plan(const b200_decoder_config* cfg, int32_t which, i
 }
 
 int32_t b200_decoder_vocab(const b200_decoder* d) { return d ? d->cfg.vocab : 0; }
+int32_t b200_decoder_batch(const b200_decoder* d) { return d ? d->batch : 0; }
 uint64_t b200_decoder_launches_per_step(const b200_decoder* d) { return d ? d->launches_per_step : 0; }
 uint64_t b200_decoder_weight_bytes(const b200_decoder* d) { return d ? d->payload_bytes : 0; }
 

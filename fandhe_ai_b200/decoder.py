@@ -66,6 +66,19 @@ class BlockTable:
         return None if b < 0 else b
 
 
+SAMPLE_GREEDY, SAMPLE_TEMPERATURE, SAMPLE_TOP_K = 0, 1, 2
+
+
+def sampling_weights(logits, strategy: int, k: int = 0, temperature: float = 1.0) -> np.ndarray:
+    """Host rows of logits [rows, vocab] -> the reference's sampling weights (see Decoder.sampling_weights)."""
+    x = np.ascontiguousarray(logits, dtype=np.float32)
+    rows, vocab = x.shape
+    out = np.empty((rows, vocab), np.float32)
+    check(lib().b200_sampling_weights(x.ctypes.data_as(C.c_void_p), rows, vocab, strategy, k, C.c_float(temperature),
+                                      out.ctypes.data_as(C.c_void_p)))
+    return out
+
+
 @dataclass
 class DecoderConfig:
     n_layers: int
@@ -196,6 +209,14 @@ class Decoder:
     def logits(self) -> np.ndarray:
         out = np.empty((self._batch, self.cfg.vocab), np.float32)
         check(lib().b200_decoder_logits(self._h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
+    def sampling_weights(self, strategy: int, k: int = 0, temperature: float = 1.0) -> np.ndarray:
+        """[batch, vocab] f32 weights of the last step's logits, as the reference's sample_step builds them before
+        it draws (crates/autodiff/src/generate/mod.rs:382-455); the draw stays with the caller's generator."""
+        out = np.empty((self._batch, self.cfg.vocab), np.float32)
+        check(lib().b200_decoder_sampling_weights(self._h, strategy, k, C.c_float(temperature),
+                                                  out.ctypes.data_as(C.c_void_p), out.size))
         return out
 
     def generate(self, prompt, max_length: int) -> np.ndarray:

@@ -462,6 +462,28 @@ int32_t b200_decoder_step_rows(b200_decoder* dec, const int32_t* ids, const uint
  * counterpart of the prefill forward of generate() (crates/autodiff/src/generate/mod.rs:500-560). */
 int32_t b200_decoder_prefill(b200_decoder* dec, int32_t row0, int32_t count, const int32_t* ids, int32_t l_new);
 int32_t b200_decoder_vocab(const b200_decoder* dec);
+/* Rows of the running generation (the batch given to b200_decoder_begin; 0 before). */
+int32_t b200_decoder_batch(const b200_decoder* dec);
+
+/* ---- sampling other than greedy ------------------------------------------------------------------------------
+ * generate() of the reference samples on the host: sample_step (crates/autodiff/src/generate/mod.rs:382-427) builds,
+ * per row, f32 weights from the logits in f64 - softmax_weights_f64 (:347-355), top_k_indices (:359-369, value
+ * descending then index ascending), sampling_weights_f32 (:433-455) - and draws one index per row from them with its
+ * own Generator::multinomial.  These entries produce exactly those weights; the draw stays with the caller's
+ * generator, and the drawn ids go back through b200_decoder_step(ids).  The argument rules are those of
+ * GenerateConfig::validate (:179-250): temperature finite and > 0; greedy with temperature 1 and k 0; temperature
+ * strategy with k 0; top-k with 1 <= k <= vocab.  A non-finite logit is InvalidArgument, as in sample_step. */
+enum b200_sampling_strategy {
+    B200_SAMPLE_GREEDY = 0,        /* one-hot at the first maximum (never drawn from by the reference) */
+    B200_SAMPLE_TEMPERATURE = 1,   /* softmax((x - max) / t) over the whole row */
+    B200_SAMPLE_TOP_K = 2          /* the same softmax over the k largest logits, 0 elsewhere */
+};
+/* logits[rows][vocab] (host) -> weights_out[rows][vocab] (host). */
+int32_t b200_sampling_weights(const float* logits, int64_t rows, int64_t vocab, int32_t strategy, int32_t k, float temperature,
+                              float* weights_out);
+/* The same for the logits of the decoder's last step: weights_out[batch][vocab] (host, capacity in elements). */
+int32_t b200_decoder_sampling_weights(b200_decoder* dec, int32_t strategy, int32_t k, float temperature, float* weights_out,
+                                      uint64_t capacity_elems);
 /* Between steps: empties row `row` (its blocks return to the free stack) and reserves blocks for a new sequence
  * of up to max_total_len tokens (at most the largest length given to b200_decoder_begin). */
 int32_t b200_decoder_row_restart(b200_decoder* dec, int32_t row, int32_t max_total_len);

@@ -380,3 +380,41 @@ def gemm_i8_block_scaled(a, da, w, dw):
     f.restype = C.c_int
     bad = f(_p(a), _p(_c(da, np.float32)), _p(w), _p(_c(dw, np.float32)), C.c_int64(m), C.c_int64(n), C.c_int64(k), _p(out))
     return out, bool(bad)
+
+
+# ---- sampling weights of generate() (crates/autodiff/src/generate/mod.rs:331-369, 433-455) ----------------------
+SAMPLE_GREEDY, SAMPLE_TEMPERATURE, SAMPLE_TOP_K = 0, 1, 2
+
+
+def top_k_indices(row, k: int):
+    """The k largest values by value descending, index ascending (mod.rs:359-369)."""
+    row = np.asarray(row, np.float32)
+    return sorted(range(len(row)), key=lambda i: (-float(row[i]), i))[:k]
+
+
+def softmax_weights_f64(row, temperature: float) -> np.ndarray:
+    """exp((x - max) / t) in f64, summed in index order, divided, narrowed to f32 (mod.rs:347-355)."""
+    import math
+
+    x = np.asarray(row, np.float32).astype(np.float64)
+    mx = float(x.max())
+    t = float(np.float32(temperature))
+    e = [math.exp((float(v) - mx) / t) for v in x]
+    total = 0.0
+    for v in e:
+        total += v
+    return np.array([v / total for v in e], np.float64).astype(np.float32)
+
+
+def sampling_weights(row, strategy: int, k: int = 0, temperature: float = 1.0) -> np.ndarray:
+    """sampling_weights_f32 (mod.rs:433-455) for one row of finite logits."""
+    row = np.asarray(row, np.float32)
+    if strategy == SAMPLE_TEMPERATURE:
+        return softmax_weights_f64(row, temperature)
+    w = np.zeros(len(row), np.float32)
+    if strategy == SAMPLE_GREEDY:
+        w[greedy_argmax(row)] = 1.0
+        return w
+    top = top_k_indices(row, k)
+    w[top] = softmax_weights_f64(row[top], temperature)
+    return w

@@ -383,3 +383,37 @@ def test_prefill_of_a_long_prompt_runs_in_chunks(be):
     finally:
         dec.close()
     assert np.array_equal(got, want), np.argwhere(got != want)[:4].tolist()
+
+
+@pytest.mark.parametrize("strategy,k,temperature", [(2, 8, 0.8), (1, 0, 1.5)])
+def test_sampled_generation_follows_the_cpu_decoder(be, strategy, k, temperature):
+    """Top-k / temperature sampling: at every step the library's weights for the device logits equal the oracle's
+    weights for the CPU decoder's logits (kernel-order decoder: the logits are bit-identical, so the supports are
+    too), and the ids a host generator draws from them - here numpy's, in the reference its own Generator - are fed
+    back through step(ids) on both sides."""
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=512, max_seq_len=32)
+    weights = make_weights(cfg, seed=41)
+    batch, steps = 3, 12
+    ref = DecoderRef(cfg, weights, exact=True)
+    ref.begin(batch)
+    dec = make_decoder(be, cfg, batch)
+    draw = np.random.default_rng(7)
+    try:
+        dec.load_weights(weights)
+        dec.begin(batch, [steps + 1] * batch)
+        ids = np.array([3, 77, 400], np.int32)
+        for t in range(steps):
+            want_logits, _ = ref.step(ids)
+            dec.step(ids)
+            assert np.array_equal(dec.logits(), want_logits), t
+            got = dec.sampling_weights(strategy, k, temperature)
+            nxt = np.empty(batch, np.int32)
+            for r in range(batch):
+                want = O.sampling_weights(want_logits[r], strategy, k, temperature)
+                assert np.array_equal(got[r] != 0, want != 0), (t, r)
+                assert np.allclose(got[r], want, rtol=2e-7, atol=0), (t, r)
+                p = got[r].astype(np.float64)
+                nxt[r] = draw.choice(cfg["vocab"], p=p / p.sum())
+            ids = nxt
+    finally:
+        dec.close()
