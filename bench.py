@@ -439,6 +439,29 @@ def run_gpu(args, cfg, rank, world, local_rank):
                                   "(the dense int8 / fp8 rate is twice the bf16 rate); frac_of_4500_nominal: against the "
                                   "vendor's dense figure",
                      "attention_c3": bk.measure_attention_config3(be, iters=20, warmup=5, host_call=False)}
+            # the same decode workload in the FP8 x FP8 form (E4M3 weights and activations, f32 accumulation): one block
+            # of K steps after the warm-up, device-resident loop
+            dc8 = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
+                                cfg["vocab"], max_batch=cfg["batch"], max_seq_len=max_seq, block_size=16,
+                                num_blocks=cfg["batch"] * blocks_per_seq, use_graph=1, act_fp8=1)
+            dec8 = Decoder(be, dc8)
+            dec8.init_random(seed=0, std=0.02)
+            dec8.fill_cache_random(seed=1, std=1.0)
+            dec8.begin(batch, (lens + total_steps).tolist(), start_lens=lens.tolist())
+            ids[:] = first_ids
+            dec8.step_raw(ids_p, None)
+            for _ in range(warmup - 1):
+                dec8.step_raw(None, None)
+            be.synchronize_device()
+            be.timer_start()
+            for _ in range(args.steps):
+                dec8.step_raw(None, None)
+            ms8 = be.timer_stop()
+            dec8.close()
+            extra["decode_fp8"] = {"value": batch * args.steps / (ms8 / 1e3), "unit": "tokens/s", "ms_per_step": ms8 / args.steps,
+                                   "steps": args.steps, "dtype": "fp8_e4m3 x fp8_e4m3, f32 accumulation",
+                                   "note": "same workload and caches as the headline line; weights re-encoded to E4M3 with "
+                                           "per-row scales, per-token E4M3 activations"}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             sample = CpuSample(cfg, args.cpu_layers, args.cpu_vocab, cpu_threads(args))

@@ -69,7 +69,7 @@ class DecoderConfigC(C.Structure):
                 ("head_dim", C.c_int32), ("d_ff", C.c_int32), ("vocab", C.c_int32), ("rms_eps", C.c_float),
                 ("rope_theta", C.c_float), ("max_batch", C.c_int32), ("max_seq_len", C.c_int32),
                 ("block_size", C.c_int32), ("num_blocks", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32),
-                ("use_graph", C.c_int32), ("tp_exact_int8", C.c_int32)]
+                ("use_graph", C.c_int32), ("tp_exact_int8", C.c_int32), ("act_fp8", C.c_int32)]
 
 
 _P = C.c_void_p

@@ -81,7 +81,7 @@ __device__ __forceinline__ float cluster_max(cg::cluster_group& cl, RowShared& s
 // `n` is the full row width.  Ends with a cluster barrier so that no CTA leaves while a peer still reads it.
 __device__ __forceinline__ void norm_quant_chunk(cg::cluster_group& cl, RowShared& sh, int n, int c0, int nc,
                                                  const float* __restrict__ norm_w, float eps, int8_t* __restrict__ q_row,
-                                                 float* __restrict__ scale_out) {
+                                                 float* __restrict__ scale_out, int fp8 = 0) {
     double acc = 0.0;
     for (int i = threadIdx.x; i < nc; i += kThreads) {
         const double v = static_cast<double>(sh.chunk[i]);
@@ -97,10 +97,14 @@ __device__ __forceinline__ void norm_quant_chunk(cg::cluster_group& cl, RowShare
         amax = fmaxf(amax, fabsf(v));
     }
     amax = cluster_max(cl, sh, block_max(amax, sh));
-    const float s = amax / 127.0f;
+    const float s = fp8 ? amax / kE4m3Max : amax / 127.0f;
     if (cl.block_rank() == 0 && threadIdx.x == 0) *scale_out = s;
     uint32_t* q4 = reinterpret_cast<uint32_t*>(q_row + c0);
     for (int i = threadIdx.x; i < nc / 4; i += kThreads) {
+        if (fp8) {
+            q4[i] = quant4_e4m3(sh.chunk[4 * i + 0], sh.chunk[4 * i + 1], sh.chunk[4 * i + 2], sh.chunk[4 * i + 3], s);
+            continue;
+        }
         const uint32_t b0 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 0], s)) & 0xFFu;
         const uint32_t b1 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 1], s)) & 0xFFu;
         const uint32_t b2 = static_cast<uint32_t>(quant_i8(sh.chunk[4 * i + 2], s)) & 0xFFu;
@@ -110,8 +114,17 @@ __device__ __forceinline__ void norm_quant_chunk(cg::cluster_group& cl, RowShare
     cl.sync();
 }
 
-// Sum of the split-K planes of four consecutive elements (16-byte loads).
-__device__ __forceinline__ int4 sum_planes4(const int* __restrict__ raw, int splits, size_t plane, size_t idx) {
+// Sum of the split-K planes of four consecutive elements (16-byte loads): int32 sums, or (fp8) f32 sums in plane
+// order whose bits are returned; acc_word_f32 turns either into the f32 value.
+__device__ __forceinline__ int4 sum_planes4(const int* __restrict__ raw, int splits, size_t plane, size_t idx, int fp8 = 0) {
+    if (fp8) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < splits; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(raw + s * plane + idx);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        return make_int4(__float_as_int(a.x), __float_as_int(a.y), __float_as_int(a.z), __float_as_int(a.w));
+    }
     int4 a = make_int4(0, 0, 0, 0);
     for (int s = 0; s < splits; ++s) {
         const int4 v = *reinterpret_cast<const int4*>(raw + s * plane + idx);
@@ -125,7 +138,7 @@ __device__ __forceinline__ int4 sum_planes4(const int* __restrict__ raw, int spl
 __global__ void __launch_bounds__(kThreads)
 embed_norm_quant_cl_kernel(const int* __restrict__ ids, const float* __restrict__ table, int vocab, int d, int nc,
                            const float* __restrict__ norm_w, float eps, float* __restrict__ h, int8_t* __restrict__ xq,
-                           float* __restrict__ sx, uint32_t* err) {
+                           float* __restrict__ sx, uint32_t* err, int fp8) {
     __shared__ RowShared sh;
     cg::cluster_group cl = cg::this_cluster();
     pdl_wait();
@@ -144,7 +157,7 @@ embed_norm_quant_cl_kernel(const int* __restrict__ ids, const float* __restrict_
         *reinterpret_cast<float4*>(&sh.chunk[4 * g]) = v;
     }
     __syncthreads();
-    norm_quant_chunk(cl, sh, d, c0, nc, norm_w, eps, xq + static_cast<size_t>(m) * d, sx + m);
+    norm_quant_chunk(cl, sh, d, c0, nc, norm_w, eps, xq + static_cast<size_t>(m) * d, sx + m, fp8);
 }
 
 // First index of the row maximum; chunk = columns per CTA (a multiple of 4).
@@ -208,7 +221,7 @@ qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int r
                            const uint32_t* __restrict__ positions, const uint32_t* __restrict__ active,
                            const uint32_t* __restrict__ block_tables,
                            int max_blocks_per_seq, int block_size, int num_blocks, float* __restrict__ q_out,
-                           uint16_t* __restrict__ k_pool, uint16_t* __restrict__ v_pool, uint32_t* err) {
+                           uint16_t* __restrict__ k_pool, uint16_t* __restrict__ v_pool, uint32_t* err, int fp8) {
     pdl_wait();
     pdl_launch_dependents();
     const int m = blockIdx.y;
@@ -238,12 +251,18 @@ qkv_rope_append_par_kernel(const int* __restrict__ raw, int splits, int M, int r
         if (head >= hq + 2 * hkv) break;
         const size_t idx = static_cast<size_t>(m) * n + head * dh + i;
         int a1 = 0, a2 = 0;
+        float f1 = 0.0f, f2 = 0.0f;
         for (int s = 0; s < splits; ++s) {
-            a1 += raw[s * plane + idx];
-            a2 += raw[s * plane + idx + half];
+            if (fp8) {
+                f1 += __int_as_float(raw[s * plane + idx]);
+                f2 += __int_as_float(raw[s * plane + idx + half]);
+            } else {
+                a1 += raw[s * plane + idx];
+                a2 += raw[s * plane + idx + half];
+            }
         }
-        const float x1 = fmaf(static_cast<float>(a1), sa * sw[head * dh + i], 0.0f);
-        const float x2 = fmaf(static_cast<float>(a2), sa * sw[head * dh + i + half], 0.0f);
+        const float x1 = fmaf(fp8 ? f1 : static_cast<float>(a1), sa * sw[head * dh + i], 0.0f);
+        const float x2 = fmaf(fp8 ? f2 : static_cast<float>(a2), sa * sw[head * dh + i + half], 0.0f);
         if (head < hq + hkv) {
             const float c = cr[i], s = sr[i];
             const float o1 = fmaf(x1, c, -__fmul_rn(x2, s));
@@ -304,33 +323,39 @@ __device__ __forceinline__ uint32_t quant4(const float4& v, float s) {
     const uint32_t b3 = static_cast<uint32_t>(quant_i8(v.w, s)) & 0xFFu;
     return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
 }
+// four codes of the row's activation format: int8 (scale amax / 127) or e4m3 (scale amax / 448)
+__device__ __forceinline__ uint32_t pack4(const float4& v, float s, int fp8) {
+    return fp8 ? quant4_e4m3(v.x, v.y, v.z, v.w, s) : quant4(v, s);
+}
+__device__ __forceinline__ float row_scale(float amax, int fp8) { return fp8 ? amax / kE4m3Max : amax / 127.0f; }
 __device__ __forceinline__ float amax4(const float4& v) {
     return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 }
 
-// |max| of the row, scale = amax / 127, int8 store.  v[k] holds group threadIdx.x + k * blockDim.x.
+// |max| of the row, scale = amax / 127 (int8) or amax / 448 (e4m3), code store.  v[k] holds group
+// threadIdx.x + k * blockDim.x.
 template <int VPT>
 __device__ __forceinline__ void wide_quant(const float4 (&v)[VPT], int groups, WideShared& sh, int8_t* __restrict__ q_row,
-                                           float* __restrict__ scale_out) {
+                                           float* __restrict__ scale_out, int fp8 = 0) {
     float amax = 0.0f;
 #pragma unroll
     for (int k = 0; k < VPT; ++k)
         if (int(threadIdx.x + k * blockDim.x) < groups) amax = fmaxf(amax, amax4(v[k]));
     amax = wide_max(amax, sh);
-    const float s = amax / 127.0f;
+    const float s = row_scale(amax, fp8);
     if (threadIdx.x == 0) *scale_out = s;
     uint32_t* q4 = reinterpret_cast<uint32_t*>(q_row);
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int g = threadIdx.x + k * blockDim.x;
-        if (g < groups) q4[g] = quant4(v[k], s);
+        if (g < groups) q4[g] = pack4(v[k], s, fp8);
     }
 }
 
 template <int VPT>
 __device__ __forceinline__ void wide_norm_quant(float4 (&v)[VPT], int groups, int n, WideShared& sh,
                                                 const float* __restrict__ norm_w, float eps, int8_t* __restrict__ q_row,
-                                                float* __restrict__ scale_out) {
+                                                float* __restrict__ scale_out, int fp8 = 0) {
     double acc = 0.0;
 #pragma unroll
     for (int k = 0; k < VPT; ++k)
@@ -352,14 +377,14 @@ __device__ __forceinline__ void wide_norm_quant(float4 (&v)[VPT], int groups, in
             v[k].w = __fmul_rn(__fmul_rn(v[k].w, rstd), w4.w);
         }
     }
-    wide_quant<VPT>(v, groups, sh, q_row, scale_out);
+    wide_quant<VPT>(v, groups, sh, q_row, scale_out, fp8);
 }
 
 template <int VPT>
 __global__ void __launch_bounds__(kWideThreads)
 resid_norm_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int d, const float* __restrict__ sx_in,
                              const float* __restrict__ sw, const float* __restrict__ pre, const float* __restrict__ norm_w,
-                             float eps, float* __restrict__ h, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+                             float eps, float* __restrict__ h, int8_t* __restrict__ xq, float* __restrict__ sx_out, int fp8) {
     __shared__ WideShared sh;
     pdl_wait();
     pdl_launch_dependents();
@@ -376,12 +401,12 @@ resid_norm_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int
             if (pre) {
                 y = *reinterpret_cast<const float4*>(pre + base + 4 * g);
             } else {
-                const int4 a = sum_planes4(raw, splits, plane, base + 4 * g);
+                const int4 a = sum_planes4(raw, splits, plane, base + 4 * g, fp8);
                 const float4 w4 = *reinterpret_cast<const float4*>(sw + 4 * g);
-                y.x = fmaf(static_cast<float>(a.x), sa * w4.x, 0.0f);
-                y.y = fmaf(static_cast<float>(a.y), sa * w4.y, 0.0f);
-                y.z = fmaf(static_cast<float>(a.z), sa * w4.z, 0.0f);
-                y.w = fmaf(static_cast<float>(a.w), sa * w4.w, 0.0f);
+                y.x = fmaf(acc_word_f32(a.x, fp8), sa * w4.x, 0.0f);
+                y.y = fmaf(acc_word_f32(a.y, fp8), sa * w4.y, 0.0f);
+                y.z = fmaf(acc_word_f32(a.z, fp8), sa * w4.z, 0.0f);
+                y.w = fmaf(acc_word_f32(a.w, fp8), sa * w4.w, 0.0f);
             }
             float4 hv = *reinterpret_cast<const float4*>(h + base + 4 * g);
             hv.x = y.x + hv.x; hv.y = y.y + hv.y; hv.z = y.z + hv.z; hv.w = y.w + hv.w;
@@ -389,13 +414,13 @@ resid_norm_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int
             v[k] = hv;
         }
     }
-    wide_norm_quant<VPT>(v, groups, d, sh, norm_w, eps, xq + base, sx_out + m);
+    wide_norm_quant<VPT>(v, groups, d, sh, norm_w, eps, xq + base, sx_out + m, fp8);
 }
 
 template <int VPT>
 __global__ void __launch_bounds__(kWideThreads)
 gate_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int F, const float* __restrict__ sx_in,
-                       const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+                       const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out, int fp8) {
     __shared__ WideShared sh;
     pdl_wait();
     pdl_launch_dependents();
@@ -408,22 +433,22 @@ gate_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int F, co
     for (int k = 0; k < VPT; ++k) {
         const int g = threadIdx.x + k * blockDim.x;
         if (g < groups) {
-            const int4 ag = sum_planes4(raw, splits, plane, base + 4 * g);
-            const int4 au = sum_planes4(raw, splits, plane, base + F + 4 * g);
+            const int4 ag = sum_planes4(raw, splits, plane, base + 4 * g, fp8);
+            const int4 au = sum_planes4(raw, splits, plane, base + F + 4 * g, fp8);
             const float4 wg = *reinterpret_cast<const float4*>(sw + 4 * g);
             const float4 wu = *reinterpret_cast<const float4*>(sw + F + 4 * g);
-            v[k].x = __fmul_rn(silu(fmaf(static_cast<float>(ag.x), sa * wg.x, 0.0f)), fmaf(static_cast<float>(au.x), sa * wu.x, 0.0f));
-            v[k].y = __fmul_rn(silu(fmaf(static_cast<float>(ag.y), sa * wg.y, 0.0f)), fmaf(static_cast<float>(au.y), sa * wu.y, 0.0f));
-            v[k].z = __fmul_rn(silu(fmaf(static_cast<float>(ag.z), sa * wg.z, 0.0f)), fmaf(static_cast<float>(au.z), sa * wu.z, 0.0f));
-            v[k].w = __fmul_rn(silu(fmaf(static_cast<float>(ag.w), sa * wg.w, 0.0f)), fmaf(static_cast<float>(au.w), sa * wu.w, 0.0f));
+            v[k].x = __fmul_rn(silu(fmaf(acc_word_f32(ag.x, fp8), sa * wg.x, 0.0f)), fmaf(acc_word_f32(au.x, fp8), sa * wu.x, 0.0f));
+            v[k].y = __fmul_rn(silu(fmaf(acc_word_f32(ag.y, fp8), sa * wg.y, 0.0f)), fmaf(acc_word_f32(au.y, fp8), sa * wu.y, 0.0f));
+            v[k].z = __fmul_rn(silu(fmaf(acc_word_f32(ag.z, fp8), sa * wg.z, 0.0f)), fmaf(acc_word_f32(au.z, fp8), sa * wu.z, 0.0f));
+            v[k].w = __fmul_rn(silu(fmaf(acc_word_f32(ag.w, fp8), sa * wg.w, 0.0f)), fmaf(acc_word_f32(au.w, fp8), sa * wu.w, 0.0f));
         }
     }
-    wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * F, sx_out + m);
+    wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * F, sx_out + m, fp8);
 }
 
 template <int VPT>
 __global__ void __launch_bounds__(kWideThreads)
-quant_rows_wide_kernel(const float* __restrict__ x, int n, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+quant_rows_wide_kernel(const float* __restrict__ x, int n, int8_t* __restrict__ xq, float* __restrict__ sx_out, int fp8) {
     __shared__ WideShared sh;
     pdl_wait();
     pdl_launch_dependents();
@@ -435,7 +460,7 @@ quant_rows_wide_kernel(const float* __restrict__ x, int n, int8_t* __restrict__ 
         const int g = threadIdx.x + k * blockDim.x;
         if (g < groups) v[k] = *reinterpret_cast<const float4*>(src + 4 * g);
     }
-    wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * n, sx_out + m);
+    wide_quant<VPT>(v, groups, sh, xq + static_cast<size_t>(m) * n, sx_out + m, fp8);
 }
 
 // ------------------------------------------------------------------------------------ rows under a global scale
@@ -549,6 +574,7 @@ struct TpFinishArgs {
     size_t o_count;
     uint32_t push_tiles;
     uint32_t* push_target;
+    int fp8;                   // the delivered rows are e4m3 codes under the scale amax / 448
 };
 
 template <int VPT>
@@ -651,7 +677,7 @@ tp_finish_kernel(TpFinishArgs a) {
         }
     }
     amax = wide_max(amax, sh);
-    const float s = amax / 127.0f;
+    const float s = row_scale(amax, a.fp8);
     // 3. deliver the row to every rank
     if (ok) {
         for (int p = 0; p < a.tp; ++p) {
@@ -659,7 +685,7 @@ tp_finish_kernel(TpFinishArgs a) {
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 const int g = threadIdx.x + k * blockDim.x;
-                if (g < groups) q4[g] = quant4(v[k], s);
+                if (g < groups) q4[g] = pack4(v[k], s, a.fp8);
             }
             if (threadIdx.x == 0) reinterpret_cast<float*>(s_peer[p] + a.o_sx)[row] = s;
         }
@@ -735,47 +761,50 @@ cudaError_t launch_cluster(void (*kernel)(KArgs...), int cl, int rows, cudaStrea
 
 // Dispatchers: the wide (or cluster) kernel when the row width allows it, else the one-CTA-per-row kernel.
 cudaError_t embed_norm_quant_auto(const int* ids, const float* table, int vocab, int M, int d, const float* norm_w,
-                                  float eps, float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s) {
+                                  float eps, float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s, int fp8) {
     const int cl = pick_cluster(d);
-    if (cl == 0) return embed_norm_quant(ids, table, vocab, M, d, norm_w, eps, h, xq, sx, err, s);
-    return launch_cluster(embed_norm_quant_cl_kernel, cl, M, s, ids, table, vocab, d, d / cl, norm_w, eps, h, xq, sx, err);
+    if (cl == 0) return fp8 ? cudaErrorInvalidValue : embed_norm_quant(ids, table, vocab, M, d, norm_w, eps, h, xq, sx, err, s);
+    return launch_cluster(embed_norm_quant_cl_kernel, cl, M, s, ids, table, vocab, d, d / cl, norm_w, eps, h, xq, sx, err, fp8);
 }
 
 cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, const float* sx_in, const float* sw,
                                   const float* pre, const float* norm_w, float eps, float* h, int8_t* xq, float* sx_out,
-                                  cudaStream_t s) {
+                                  cudaStream_t s, int fp8) {
     int vpt, threads;
     wide_shape(d, &vpt, &threads, M);
 #define B200_WIDE_RESID(V)                                                                                              \
     return launch_ex(resid_norm_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, d, sx_in, \
-                     sw, pre, norm_w, eps, h, xq, sx_out)
+                     sw, pre, norm_w, eps, h, xq, sx_out, fp8)
     if (vpt == 1) B200_WIDE_RESID(1);
     if (vpt == 2) B200_WIDE_RESID(2);
     if (vpt == 4) B200_WIDE_RESID(4);
 #undef B200_WIDE_RESID
+    if (fp8) return cudaErrorInvalidValue;      // the FP8 format exists in the wide kernels only
     return resid_norm_quant(raw, splits, M, d, sx_in, sw, pre, norm_w, eps, h, xq, sx_out, s);
 }
 
 cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
-                            float* sx_out, cudaStream_t s) {
+                            float* sx_out, cudaStream_t s, int fp8) {
     int vpt, threads;
     wide_shape(F, &vpt, &threads, M);
 #define B200_WIDE_GATE(V)                                                                                        \
     return launch_ex(gate_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, F, sx_in, \
-                     sw, xq, sx_out)
+                     sw, xq, sx_out, fp8)
     if (vpt == 1) B200_WIDE_GATE(1);
     if (vpt == 2) B200_WIDE_GATE(2);
     if (vpt == 4) B200_WIDE_GATE(4);
 #undef B200_WIDE_GATE
+    if (fp8) return cudaErrorInvalidValue;
     return gate_quant(raw, splits, M, F, sx_in, sw, xq, sx_out, s);
 }
 
-cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s) {
+cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s, int fp8) {
     int vpt, threads;
     wide_shape(n, &vpt, &threads, M);
-    if (vpt == 1) return launch_ex(quant_rows_wide_kernel<1>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
-    if (vpt == 2) return launch_ex(quant_rows_wide_kernel<2>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
-    if (vpt == 4) return launch_ex(quant_rows_wide_kernel<4>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out);
+    if (vpt == 1) return launch_ex(quant_rows_wide_kernel<1>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out, fp8);
+    if (vpt == 2) return launch_ex(quant_rows_wide_kernel<2>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out, fp8);
+    if (vpt == 4) return launch_ex(quant_rows_wide_kernel<4>, dim3(M), dim3(threads), 0, s, 1, true, x, n, xq, sx_out, fp8);
+    if (fp8) return cudaErrorInvalidValue;
     return quantize_i8_per_row(x, M, n, xq, sx_out, s);
 }
 
@@ -791,14 +820,14 @@ cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int 
                                  const float* sw, const float* cos_t, const float* sin_t, int max_pos,
                                  const uint32_t* positions, const uint32_t* active, const uint32_t* block_tables,
                                  int max_blocks_per_seq, int block_size, int num_blocks, float* q_out, uint16_t* k_pool,
-                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s, int rows_per_seq) {
+                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s, int rows_per_seq, int fp8) {
     const int heads = hq + 2 * hkv;
     int hpc = (2 * kThreads) / (dh / 2);      // two rotary pairs per thread
     if (hpc < 1) hpc = 1;
     dim3 grid((heads + hpc - 1) / hpc, M);
     return launch_ex(qkv_rope_append_par_kernel, grid, dim3(kThreads), 0, s, 1, true, raw, splits, M, rows_per_seq, hq, hkv, dh, hpc, sx_in,
                      sw, cos_t, sin_t, max_pos, positions, active, block_tables, max_blocks_per_seq, block_size, num_blocks,
-                     q_out, k_pool, v_pool, err);
+                     q_out, k_pool, v_pool, err, fp8);
 }
 
 cudaError_t rows_amax(const float* x, int M, int n, float* amax_out, cudaStream_t s) {
@@ -847,12 +876,12 @@ bool tp_finish_supported(int d) {
 
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
-                      cudaStream_t s, uint64_t timeout_ns, size_t o_count, uint32_t push_tiles, uint32_t* push_target) {
+                      cudaStream_t s, uint64_t timeout_ns, size_t o_count, uint32_t push_tiles, uint32_t* push_target, int fp8) {
     int vpt, threads;
     wide_shape(d, &vpt, &threads);
     if (push_tiles != 0u && push_target == nullptr) return cudaErrorInvalidValue;
     TpFinishArgs a{peers, o_sx, o_xq, o_part, tp, rank, rows, d, norm_w, eps, h, epoch, arrived, err,
-                   timeout_ns ? timeout_ns : kPeerWaitNs, o_count, push_tiles, push_target};
+                   timeout_ns ? timeout_ns : kPeerWaitNs, o_count, push_tiles, push_target, fp8};
     if (vpt == 1) return launch_ex(tp_finish_kernel<1>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 2) return launch_ex(tp_finish_kernel<2>, dim3(rows), dim3(threads), 0, s, 1, true, a);
     if (vpt == 4) return launch_ex(tp_finish_kernel<4>, dim3(rows), dim3(threads), 0, s, 1, true, a);

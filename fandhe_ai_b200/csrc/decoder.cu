@@ -378,6 +378,12 @@ int32_t check_config(const b200_decoder_config& c) {
     if (c.tp_exact_int8 && c.tp_size > 1 &&
         (!rows_scaled_supported(c.d_ff / c.tp_size) || !rows_scaled_supported(c.n_heads / c.tp_size * c.head_dim)))
         return fail(B200_UNSUPPORTED, "decoder config: tp_exact_int8 needs rows of at most 16384 columns per rank");
+    if (c.act_fp8) {
+        if (c.tp_exact_int8) return fail(B200_UNSUPPORTED, "decoder config: act_fp8 and tp_exact_int8 exclude each other");
+        if (!rows_scaled_supported(c.d_model) || !rows_scaled_supported(c.d_ff / c.tp_size) || !rows_scaled_supported(c.d_ff) ||
+            !rows_scaled_supported(c.n_heads / c.tp_size * c.head_dim) || !rows_scaled_supported(c.n_heads * c.head_dim))
+            return fail(B200_UNSUPPORTED, "decoder config: act_fp8 needs rows of at most 16384 columns, multiples of 4");
+    }
     if (c.block_size <= 0 || c.block_size > 256 || (c.block_size & (c.block_size - 1))) return bad("block_size must be a power of two <= 256");
     if (c.num_blocks <= 0) return bad("num_blocks must be positive");
     if (!(c.rms_eps >= 0.0f) || !std::isfinite(c.rms_eps)) return bad("rms_eps must be finite and non-negative");
@@ -427,7 +433,13 @@ int32_t store_weight(b200_decoder* d, const float* w_full, int64_t rows, int64_t
     float* s_full = nullptr;
     CU_TRY(dmalloc(&q_full, size_t(rows) * cols));
     CU_TRY(dmalloc(&s_full, size_t(rows)));
-    CU_TRY(quantize_i8_per_row(w_full, rows, cols, q_full, s_full, s));
+    if (d->cfg.act_fp8) {
+        // E4M3 codes under one scale per output row (amax / 448): the row quantiser of the activations, run over the weight rows
+        if (rows > 0x7FFFFFFF || cols > 0x7FFFFFFF) return fail(B200_UNSUPPORTED, "decoder: weight too large for the FP8 encoder");
+        CU_TRY(quantize_rows_auto(w_full, int(rows), int(cols), q_full, s_full, s, 1));
+    } else {
+        CU_TRY(quantize_i8_per_row(w_full, rows, cols, q_full, s_full, s));
+    }
     const int32_t st = store_weight_q(d, q_full, s_full, cols, row_ranges, c0, ccount, payload_off, scale_off);
     cudaFree(q_full);
     cudaFree(s_full);
@@ -570,6 +582,7 @@ int32_t enqueue_step(b200_decoder* d) {
     uint32_t* err = d->ctx->err_dev;
     const int M = d->batch, dm = c.d_model, dh = c.head_dim;
     const bool tp = c.tp_size > 1;
+    const int fp8 = c.act_fp8 ? 1 : 0;      // E4M3 activations and f32 accumulators instead of int8 / int32
     uint64_t launches = 0;
     GemmEpilogue ep;
     ep.raw = d->raw;
@@ -593,7 +606,7 @@ int32_t enqueue_step(b200_decoder* d) {
     CU_TRY(begin_step(d->seq_lens_dev, d->pos_dev, d->active_dev, M, s));
     ++launches;
     CU_TRY(embed_norm_quant_auto(d->ids_dev, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, d->h,
-                            d->xq, d->sx, err, s));
+                            d->xq, d->sx, err, s, fp8));
     ++launches;
     // A row-parallel projection and what follows it: residual add, RMSNorm with `norm`, per-token int8 rows in xq.
     // One rank: the row kernel reads the raw accumulators.  Several ranks: the GEMM writes its dequantised f32
@@ -611,7 +624,7 @@ int32_t enqueue_step(b200_decoder* d) {
             ++launches;
         }
         if (int32_t st = all_reduce_sum_i32(d, acc, size_t(M) * dm)) return st;
-        CU_TRY(resid_norm_quant_auto(acc, 1, M, dm, d->sx, d->scales + s_off, nullptr, norm, c.rms_eps, d->h, d->xq, d->sx, s));
+        CU_TRY(resid_norm_quant_auto(acc, 1, M, dm, d->sx, d->scales + s_off, nullptr, norm, c.rms_eps, d->h, d->xq, d->sx, s, fp8));
         launches += 3;
         return B200_OK;
     };
@@ -628,7 +641,7 @@ int32_t enqueue_step(b200_decoder* d) {
         if (!tp) {
             CU_TRY(gemm_launch(p, ep, err, s));
             CU_TRY(resid_norm_quant_auto(d->raw, p.out_planes, M, dm, d->sx, d->scales + s_off, nullptr, norm, c.rms_eps, d->h,
-                                         d->xq, d->sx, s));
+                                         d->xq, d->sx, s, fp8));
             launches += 2;
             return B200_OK;
         }
@@ -656,6 +669,7 @@ int32_t enqueue_step(b200_decoder* d) {
             CU_TRY(gemm_launch(p, pe, err, s));
             ++launches;
         } else {
+            if (fp8) return fail(B200_UNSUPPORTED, "decoder: this GEMM shape has no fused epilogue, which the FP8 form needs under tensor parallelism");
             CU_TRY(gemm_launch(p, ep, err, s));
             CU_TRY(dequant_planes(d->raw, p.out_planes, M, dm, d->sx, d->scales + s_off, d->part, s));
             launches += 2;
@@ -663,13 +677,13 @@ int32_t enqueue_step(b200_decoder* d) {
         if (exchange) {
             CU_TRY(tp_finish(d->tp_peers_dev, d->tp_o_sx, d->tp_o_xq, d->tp_o_part, c.tp_size, c.tp_rank, M / c.tp_size, dm, norm,
                              c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s, d->tp_timeout_ns, kTpCountOffset,
-                             push ? 1u : 0u, d->tp_epoch + 2));
+                             push ? 1u : 0u, d->tp_epoch + 2, fp8));
             ++launches;
             return B200_OK;
         }
         if (int32_t st = all_reduce_sum_f32(d, d->part, size_t(M) * dm)) return st;
         CU_TRY(resid_norm_quant_auto(d->raw, p.out_planes, M, dm, d->sx, d->scales + s_off, d->part, norm, c.rms_eps, d->h, d->xq,
-                                     d->sx, s));
+                                     d->sx, s, fp8));
         launches += 2;
         return B200_OK;
     };
@@ -706,7 +720,7 @@ int32_t enqueue_step(b200_decoder* d) {
             CU_TRY(qkv_rope_append_auto(d->raw, L.p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, d->sx, d->scales + L.s_qkv,
                                         d->cos_t, d->sin_t, c.max_seq_len, d->pos_dev, d->active_dev, d->tables_dev, d->max_blocks_per_seq,
                                         c.block_size, c.num_blocks, d->q, static_cast<uint16_t*>(L.k_pool),
-                                        static_cast<uint16_t*>(L.v_pool), err, s));
+                                        static_cast<uint16_t*>(L.v_pool), err, s, 1, fp8));
         }
         // attention over the cache (this rank's KV heads), then per-token quantisation
         if (exact_tp) {
@@ -717,11 +731,11 @@ int32_t enqueue_step(b200_decoder* d) {
             launches += 1 - (paged_attention_can_quantize(L.attn) ? 0 : 1);
         } else if (paged_attention_can_quantize(L.attn)) {
             CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, nullptr,
-                                          d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s, d->xq, d->sx));
+                                          d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s, d->xq, d->sx, fp8));
         } else {
             CU_TRY(paged_attention_launch(L.attn, d->q, L.k_pool, L.v_pool, d->tables_dev, d->seq_lens_dev, d->attn_out,
                                           d->attn_scratch, d->ctx->attn_counter, d->ctx->sm_count, err, s));
-            CU_TRY(quantize_rows_auto(d->attn_out, M, d->hq_l * dh, d->xq, d->sx, s));
+            CU_TRY(quantize_rows_auto(d->attn_out, M, d->hq_l * dh, d->xq, d->sx, s, fp8));
         }
         // O projection (row-parallel) -> residual -> norm -> quant
         launches += paged_attention_can_quantize(L.attn) ? 4 : 5;
@@ -732,7 +746,7 @@ int32_t enqueue_step(b200_decoder* d) {
             CU_TRY(gate_rows_f32(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->tp_rows_f32, d->tp_amax, s));
             if (int32_t st = quant_global(d->tp_rows_f32, d->f_l)) return st;
         } else
-        CU_TRY(gate_quant_auto(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s));
+        CU_TRY(gate_quant_auto(d->raw, L.p_gu.out_planes, M, d->f_l, d->sx, d->scales + L.s_gu, d->xq, d->sx, s, fp8));
         // down (row-parallel) -> residual -> next norm -> quant
         const float* next_norm = d->vectors + (l + 1 < c.n_layers ? d->layers[l + 1].attn_norm : d->final_norm);
         launches += 2;
@@ -981,7 +995,18 @@ int32_t b200_decoder_load_tensor_i8(b200_decoder* d, int32_t which, int32_t laye
     CU_TRY(dmalloc(&s_full, size_t(rows)));
     CU_TRY(cudaMemcpyAsync(q_full, q_host, size_t(rows) * cols, cudaMemcpyHostToDevice, s));
     CU_TRY(cudaMemcpyAsync(s_full, scale_host, size_t(rows) * 4, cudaMemcpyHostToDevice, s));
-    const int32_t st = store_weight_q(d, q_full, s_full, cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off);
+    int32_t st = B200_OK;
+    if (d->cfg.act_fp8) {
+        // the FP8 form re-encodes an int8 payload: dequantise to f32, then E4M3 codes under new per-row scales
+        float* w_full = nullptr;
+        CU_TRY(dmalloc(&w_full, size_t(rows) * cols));
+        cudaError_t e = dequantize_i8_per_row(q_full, s_full, rows, cols, w_full, s);
+        st = e == cudaSuccess ? store_weight(d, w_full, rows, cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off)
+                              : dec_fail(d, B200_KERNEL_LAUNCH_FAILED, cudaGetErrorString(e));
+        cudaFree(w_full);
+    } else {
+        st = store_weight_q(d, q_full, s_full, cols, t.row_ranges, t.c0, t.ccount, t.payload_off, t.scale_off);
+    }
     cudaFree(q_full);
     cudaFree(s_full);
     return st;
@@ -1408,8 +1433,9 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
     size_t raw_need = 0;
     // `fused`: the launch will use a fused epilogue (the row-parallel projections under tensor parallelism write
     // their dequantised partial), which moves the switch to the persistent kernel down to half a wave of tiles
+    const int kind = c.act_fp8 ? kGemmFp8 : kGemmI8;
     auto plan = [&](GemmPlan* p, size_t w_off, int N, int K, bool fused = false) -> cudaError_t {
-        cudaError_t e = gemm_make_plan(p, kGemmI8, d->xq, d->payload + w_off, M, N, K, 0, d->ctx->tune_splits, d->ctx->tune_bn, &why);
+        cudaError_t e = gemm_make_plan(p, kind, d->xq, d->payload + w_off, M, N, K, 0, d->ctx->tune_splits, d->ctx->tune_bn, &why);
         if (e == cudaSuccess && d->ctx->tune_splits == 0) gemm_plan_make_persistent(p, d->ctx->sm_count, fused);
         if (e == cudaSuccess) raw_need = std::max(raw_need, gemm_raw_elems(*p));
         return e;
@@ -1430,7 +1456,7 @@ int32_t b200_decoder_begin(b200_decoder* d, int32_t batch, const int32_t* start_
         attn_need = std::max(attn_need, paged_attention_scratch_bytes(L.attn));
     }
     {
-        cudaError_t e = gemm_make_plan(&d->p_lm, kGemmI8, d->xq, d->payload + d->w_lm, M, c.vocab, dm, 0, 1, d->ctx->tune_bn, &why);
+        cudaError_t e = gemm_make_plan(&d->p_lm, kind, d->xq, d->payload + d->w_lm, M, c.vocab, dm, 0, 1, d->ctx->tune_bn, &why);
         if (e != cudaSuccess) return fail(B200_UNSUPPORTED, std::string("decoder_begin: ") + why);
         if (d->ctx->tune_splits == 0) gemm_plan_make_persistent(&d->p_lm, d->ctx->sm_count, true);
     }
@@ -1563,6 +1589,7 @@ constexpr int kPrefillRowsCap = 2048;      // token rows per pass
 
 int32_t prefill_pass(b200_decoder* d, int row0, int count, int l_new, const int32_t* ids_host) {
     const auto& c = d->cfg;
+    const int fp8 = c.act_fp8 ? 1 : 0;
     cudaStream_t s = d->ctx->stream;
     uint32_t* err = d->ctx->err_dev;
     const int M = count * l_new, dm = c.d_model, dh = c.head_dim;
@@ -1590,7 +1617,7 @@ int32_t prefill_pass(b200_decoder* d, int row0, int count, int l_new, const int3
     GemmPlan p_qkv, p_o, p_gu, p_down;
     size_t raw_need = 0;
     auto plan = [&](GemmPlan* p, const int8_t* w, int N, int K, bool fused) -> cudaError_t {
-        cudaError_t e = gemm_make_plan(p, kGemmI8, pf.xq, w, M, N, K, 0, 0, 0, &why);
+        cudaError_t e = gemm_make_plan(p, c.act_fp8 ? kGemmFp8 : kGemmI8, pf.xq, w, M, N, K, 0, 0, 0, &why);
         if (e == cudaSuccess) gemm_plan_make_persistent(p, d->ctx->sm_count, fused);
         if (e == cudaSuccess && !(fused && (p->persist || p->splits == 1 || p->cluster))) raw_need = std::max(raw_need, gemm_raw_elems(*p));
         return e;
@@ -1601,7 +1628,7 @@ int32_t prefill_pass(b200_decoder* d, int row0, int count, int l_new, const int3
     uint32_t* lens = d->seq_lens_dev + row0;
     CU_TRY(prefill_positions(lens, pf.pos, count, l_new, s));
     CU_TRY(prefill_advance(lens, count, l_new, s));
-    CU_TRY(embed_norm_quant_auto(pf.ids, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, pf.h, pf.xq, pf.sx, err, s));
+    CU_TRY(embed_norm_quant_auto(pf.ids, d->embed, c.vocab, M, dm, d->vectors + d->layers[0].attn_norm, c.rms_eps, pf.h, pf.xq, pf.sx, err, s, fp8));
     for (int l = 0; l < c.n_layers; ++l) {
         LayerParams& L = d->layers[l];
         raw_need = 0;
@@ -1633,16 +1660,16 @@ int32_t prefill_pass(b200_decoder* d, int row0, int count, int l_new, const int3
         CU_TRY(gemm_launch(p_qkv, ep, err, s));
         CU_TRY(qkv_rope_append_auto(pf.raw, p_qkv.out_planes, M, d->hq_l, d->hkv_l, dh, pf.sx, d->scales + L.s_qkv, d->cos_t, d->sin_t,
                                     c.max_seq_len, pf.pos, nullptr, tables, d->max_blocks_per_seq, c.block_size, c.num_blocks, pf.q,
-                                    static_cast<uint16_t*>(L.k_pool), static_cast<uint16_t*>(L.v_pool), err, s, l_new));
+                                    static_cast<uint16_t*>(L.k_pool), static_cast<uint16_t*>(L.v_pool), err, s, l_new, fp8));
         // nothing is sampled from a prefill pass: once the last layer's K / V rows are in the cache the pass is complete
         if (l + 1 == c.n_layers) break;
         CU_TRY(paged_attention_launch(ap, pf.q, L.k_pool, L.v_pool, tables, lens, pf.attn, pf.attn_scratch, d->ctx->attn_counter,
                                       d->ctx->sm_count, err, s));
-        CU_TRY(quantize_rows_auto(pf.attn, M, d->hq_l * dh, pf.xq, pf.sx, s));
+        CU_TRY(quantize_rows_auto(pf.attn, M, d->hq_l * dh, pf.xq, pf.sx, s, fp8));
         auto row_parallel = [&](const GemmPlan& p, size_t s_off, const float* norm) -> int32_t {
             if (!tp) {
                 CU_TRY(gemm_launch(p, ep, err, s));
-                CU_TRY(resid_norm_quant_auto(pf.raw, p.out_planes, M, dm, pf.sx, d->scales + s_off, nullptr, norm, c.rms_eps, pf.h, pf.xq, pf.sx, s));
+                CU_TRY(resid_norm_quant_auto(pf.raw, p.out_planes, M, dm, pf.sx, d->scales + s_off, nullptr, norm, c.rms_eps, pf.h, pf.xq, pf.sx, s, fp8));
                 return B200_OK;
             }
             if (p.persist || p.splits == 1 || p.cluster) {
@@ -1655,16 +1682,17 @@ int32_t prefill_pass(b200_decoder* d, int row0, int count, int l_new, const int3
                 pe.out = pf.part;
                 CU_TRY(gemm_launch(p, pe, err, s));
             } else {
+                if (fp8) return fail(B200_UNSUPPORTED, "decoder_prefill: this GEMM shape has no fused epilogue, which the FP8 form needs under tensor parallelism");
                 CU_TRY(gemm_launch(p, ep, err, s));
                 CU_TRY(dequant_planes(pf.raw, p.out_planes, M, dm, pf.sx, d->scales + s_off, pf.part, s));
             }
             if (int32_t st = all_reduce_sum_f32(d, pf.part, size_t(M) * dm)) return st;
-            CU_TRY(resid_norm_quant_auto(pf.raw, 1, M, dm, pf.sx, d->scales + s_off, pf.part, norm, c.rms_eps, pf.h, pf.xq, pf.sx, s));
+            CU_TRY(resid_norm_quant_auto(pf.raw, 1, M, dm, pf.sx, d->scales + s_off, pf.part, norm, c.rms_eps, pf.h, pf.xq, pf.sx, s, fp8));
             return B200_OK;
         };
         if (int32_t st = row_parallel(p_o, L.s_o, d->vectors + L.mlp_norm)) return st;
         CU_TRY(gemm_launch(p_gu, ep, err, s));
-        CU_TRY(gate_quant_auto(pf.raw, p_gu.out_planes, M, d->f_l, pf.sx, d->scales + L.s_gu, pf.xq, pf.sx, s));
+        CU_TRY(gate_quant_auto(pf.raw, p_gu.out_planes, M, d->f_l, pf.sx, d->scales + L.s_gu, pf.xq, pf.sx, s, fp8));
         if (int32_t st = row_parallel(p_down, L.s_down, d->vectors + d->layers[l + 1].attn_norm)) return st;
     }
     return B200_OK;

@@ -403,21 +403,28 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const size_t slot = static_cast<size_t>(blk) * rp.block_size + pos % rp.block_size;
                 for (int cc = 0; cc < half_cpr; cc += 4) {
                     const int i0 = rank * half_cpr + cc;
-                    int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+                    // partial sums over the K slices in rank order: int32 (exact), or f32 for FP8 operands
+                    uint32_t lo[4] = {0u, 0u, 0u, 0u}, hi[4] = {0u, 0u, 0u, 0u};
                     for (int peer = 0; peer < nsplit; ++peer) {
                         const uint32_t* pp = cl.map_shared_rank(part, peer);
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
-                            lo[t] += static_cast<int>(pp[(i0 + t) * kBM + rl]);
-                            hi[t] += static_cast<int>(pp[(64 + i0 + t) * kBM + rl]);
+                            const uint32_t a = pp[(i0 + t) * kBM + rl], b = pp[(64 + i0 + t) * kBM + rl];
+                            if constexpr (kInt8) {
+                                lo[t] += a;
+                                hi[t] += b;
+                            } else {
+                                lo[t] = __float_as_uint(__uint_as_float(lo[t]) + __uint_as_float(a));
+                                hi[t] = __float_as_uint(__uint_as_float(hi[t]) + __uint_as_float(b));
+                            }
                         }
                     }
                     if (!ok) continue;
                     float o1[4], o2[4];
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
-                        const float x1 = fmaf(static_cast<float>(lo[t]), sa * p.ep.b_scale[head * BN + i0 + t], 0.0f);
-                        const float x2 = fmaf(static_cast<float>(hi[t]), sa * p.ep.b_scale[head * BN + 64 + i0 + t], 0.0f);
+                        const float x1 = fmaf(acc_to_f32<kInt8>(lo[t]), sa * p.ep.b_scale[head * BN + i0 + t], 0.0f);
+                        const float x2 = fmaf(acc_to_f32<kInt8>(hi[t]), sa * p.ep.b_scale[head * BN + 64 + i0 + t], 0.0f);
                         if (head < rp.hq + rp.hkv) {
                             const float c = cr[i0 + t], sn = sr[i0 + t];
                             o1[t] = fmaf(x1, c, -__fmul_rn(x2, sn));
@@ -660,7 +667,7 @@ bool gemm_make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, ui
 }
 
 bool gemm_plan_can_rope(const GemmPlan& plan, int hq, int hkv) {
-    return !plan.persist && plan.cluster && plan.bn == 128 && !plan.gate && plan.kind == kGemmI8 && plan.splits >= 2 &&
+    return !plan.persist && plan.cluster && plan.bn == 128 && !plan.gate && plan.splits >= 2 &&
            plan.splits <= 16 && (128 / plan.splits) % 8 == 0 && plan.N == (hq + 2 * hkv) * 128;
 }
 

@@ -47,9 +47,10 @@ size_t paged_attention_scratch_bytes(const PagedAttnPlan& plan);
 cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,
                                    const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
                                    unsigned int* work_counter, int sm_count, uint32_t* err, cudaStream_t stream,
-                                   int8_t* xq_out = nullptr, float* sx_out = nullptr);
-// True when the launch can also emit the per-token int8 quantisation of the output rows (xq_out / sx_out):
-// `out` may then be null.  The caller must also pass a 16-byte aligned q.
+                                   int8_t* xq_out = nullptr, float* sx_out = nullptr, int fp8 = 0);
+// True when the launch can also emit the per-token quantisation of the output rows (xq_out / sx_out; int8 under
+// amax / 127, or with fp8 != 0 E4M3 under amax / 448): `out` may then be null.  The caller must also pass a 16-byte
+// aligned q.
 bool paged_attention_can_quantize(const PagedAttnPlan& plan);
 
 // Device address (for the given, current device) and size of the file-scope static scratch array that
@@ -70,21 +71,24 @@ cudaError_t gate_quant(const int* raw, int splits, int M, int F, const float* sx
                        float* sx_out, cudaStream_t s);
 // ---- decode_rows.cu: the same operations with one wide CTA per row (or one cluster per row for the once-per-step
 // kernels); they fall back to the kernels above for rows wider than 16384 columns.
+// fp8 != 0 selects the FP8 form of the decoder: `raw` holds f32 accumulators (bit patterns, summed over the planes in
+// plane order) and the rows are emitted as E4M3 codes under the per-token scale amax / 448 instead of int8 under
+// amax / 127.  It exists in the wide / cluster kernels only (invalid-value error for other row widths).
 cudaError_t embed_norm_quant_auto(const int* ids, const float* table, int vocab, int M, int d, const float* norm_w,
-                                  float eps, float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s);
+                                  float eps, float* h, int8_t* xq, float* sx, uint32_t* err, cudaStream_t s, int fp8 = 0);
 cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, const float* sx_in, const float* sw,
                                   const float* pre, const float* norm_w, float eps, float* h, int8_t* xq, float* sx_out,
-                                  cudaStream_t s);
+                                  cudaStream_t s, int fp8 = 0);
 cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const float* sx_in, const float* sw, int8_t* xq,
-                            float* sx_out, cudaStream_t s);
-cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s);
+                            float* sx_out, cudaStream_t s, int fp8 = 0);
+cudaError_t quantize_rows_auto(const float* x, int M, int n, int8_t* xq, float* sx_out, cudaStream_t s, int fp8 = 0);
 cudaError_t argmax_rows_auto(const float* logits, int M, int vocab, int* out_ids, cudaStream_t s);
 // `active` (null: all rows) marks the rows whose K / V are appended; the others only get their q row.
 cudaError_t qkv_rope_append_auto(const int* raw, int splits, int M, int hq, int hkv, int dh, const float* sx_in,
                                  const float* sw, const float* cos_t, const float* sin_t, int max_pos,
                                  const uint32_t* positions, const uint32_t* active, const uint32_t* block_tables,
                                  int max_blocks_per_seq, int block_size, int num_blocks, float* q_out, uint16_t* k_pool,
-                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s, int rows_per_seq = 1);
+                                 uint16_t* v_pool, uint32_t* err, cudaStream_t s, int rows_per_seq = 1, int fp8 = 0);
 // Prefill: `rows_per_seq` consecutive token rows belong to one sequence (row m uses table row m / rows_per_seq).
 // positions[m] = seq_lens[m / l_new] + m % l_new for m < count * l_new ...
 cudaError_t prefill_positions(const uint32_t* seq_lens, uint32_t* positions, int count, int l_new, cudaStream_t s);
@@ -125,6 +129,6 @@ bool tp_finish_supported(int d);
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,
                       cudaStream_t s, uint64_t timeout_ns = 0,    // 0: the default bound of a cross-GPU wait
-                      size_t o_count = 0, uint32_t push_tiles = 0, uint32_t* push_target = nullptr);
+                      size_t o_count = 0, uint32_t push_tiles = 0, uint32_t* push_target = nullptr, int fp8 = 0);
 
 }  // namespace b200

@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(1024)
 paged_attention_combine_quant_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      const uint32_t* __restrict__ seq_lens, PagedAttnShape sh, int chunk_tokens,
                                      int max_chunks, float* __restrict__ out, int8_t* __restrict__ xq,
-                                     float* __restrict__ sx, unsigned int* __restrict__ work_counter, uint32_t* err) {
+                                     float* __restrict__ sx, unsigned int* __restrict__ work_counter, uint32_t* err, int fp8) {
     __shared__ float warp_max[32];
     pdl_wait();
     pdl_launch_dependents();
@@ -283,13 +283,14 @@ paged_attention_combine_quant_kernel(const float* __restrict__ part_o, const flo
     __syncthreads();
     amax = 0.0f;
     for (int w = 0; w < sh.num_q_heads; ++w) amax = fmaxf(amax, warp_max[w]);
-    const float scale = amax / 127.0f;
+    const float scale = fp8 ? amax / kE4m3Max : amax / 127.0f;
     if (threadIdx.x == 0) sx[row] = scale;
     const uint32_t b0 = static_cast<uint32_t>(quant_i8(v.x, scale)) & 0xFFu;
     const uint32_t b1 = static_cast<uint32_t>(quant_i8(v.y, scale)) & 0xFFu;
     const uint32_t b2 = static_cast<uint32_t>(quant_i8(v.z, scale)) & 0xFFu;
     const uint32_t b3 = static_cast<uint32_t>(quant_i8(v.w, scale)) & 0xFFu;
-    reinterpret_cast<uint32_t*>(xq + pair * kD)[lane] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    reinterpret_cast<uint32_t*>(xq + pair * kD)[lane] =
+        fp8 ? quant4_e4m3(v.x, v.y, v.z, v.w, scale) : (b0 | (b1 << 8) | (b2 << 16) | (b3 << 24));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -444,7 +445,7 @@ cudaError_t paged_attention_static_scratch(int device, void** out) {
 cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, const void* k_pool, const void* v_pool,
                                    const uint32_t* tables_dev, const uint32_t* seq_lens_dev, float* out, void* scratch,
                                    unsigned int* work_counter, int sm_count, uint32_t* err, cudaStream_t stream,
-                                   int8_t* xq_out, float* sx_out) {
+                                   int8_t* xq_out, float* sx_out, int fp8) {
     const PagedAttnShape& sh = plan.shape;
     const int64_t rows = int64_t(sh.batch) * sh.l_new;
     if (rows == 0) return cudaSuccess;
@@ -471,7 +472,7 @@ cudaError_t paged_attention_launch(const PagedAttnPlan& plan, const float* q, co
     if (xq_out)
         return launch_ex(paged_attention_combine_quant_kernel, dim3(static_cast<unsigned>(rows)), dim3(32 * sh.num_q_heads),
                          0, stream, 1, true, part_o, part_ml, seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks,
-                         out, xq_out, sx_out, work_counter, err);
+                         out, xq_out, sx_out, work_counter, err, fp8);
     const int blocks = static_cast<int>((pairs + 3) / 4);
     return launch_ex(paged_attention_combine_kernel, dim3(blocks), dim3(128), 0, stream, 1, true, part_o, part_ml,
                      seq_lens_dev, sh, plan.chunk_blocks * kBS, plan.max_chunks, out, work_counter, err);

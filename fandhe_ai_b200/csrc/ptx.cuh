@@ -399,4 +399,19 @@ __device__ __forceinline__ int quant_i8(float x, float scale) {
     return static_cast<int>(r);
 }
 
+// ---- FP8 (E4M3) activations: per-token scale amax / 448, codes = e4m3(x / scale) rounded to nearest even, saturating.
+constexpr float kE4m3Max = 448.0f;
+// Two f32 -> two e4m3 codes (first value in the low byte).
+__device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t quant4_e4m3(float x0, float x1, float x2, float x3, float scale) {
+    if (scale == 0.0f) return 0u;
+    return e4m3x2(x0 / scale, x1 / scale) | (e4m3x2(x2 / scale, x3 / scale) << 16);
+}
+// A finished accumulator word as f32: an int32 sum (INT8 operands) or the bits of an f32 sum (FP8 operands).
+__device__ __forceinline__ float acc_word_f32(int v, int fp8) { return fp8 ? __int_as_float(v) : static_cast<float>(v); }
+
 }  // namespace b200

@@ -98,12 +98,13 @@ class DecoderConfig:
     tp_size: int = 1
     use_graph: int = 1
     tp_exact_int8: int = 0       # tensor parallel: one global per-token scale + int32 all-reduce (results independent of tp_size)
+    act_fp8: int = 0             # 1: E4M3 weights and activations, f32 accumulation (the FP8 x FP8 form of the decoder)
 
     def to_c(self) -> DecoderConfigC:
         nb = self.num_blocks or self.max_batch * -(-self.max_seq_len // self.block_size)
         return DecoderConfigC(self.n_layers, self.d_model, self.n_heads, self.n_kv_heads, self.head_dim, self.d_ff,
                               self.vocab, self.rms_eps, self.rope_theta, self.max_batch, self.max_seq_len,
-                              self.block_size, nb, self.tp_rank, self.tp_size, self.use_graph, self.tp_exact_int8)
+                              self.block_size, nb, self.tp_rank, self.tp_size, self.use_graph, self.tp_exact_int8, self.act_fp8)
 
 
 def shard_plan(cfg: DecoderConfig, which: int) -> dict:

@@ -362,6 +362,12 @@ typedef struct b200_decoder_config {
                              * that logits and ids do not depend on tp_size (bit-identical to one GPU); costs two more
                              * collectives per layer and runs on ncclAllReduce.  0: every rank scales its slice of a row by
                              * itself and the ranks add dequantised f32 partials (the fast path). */
+    int32_t act_fp8;        /* 1: the FP8 x FP8 form of the decoder.  Weights are kept as E4M3 codes with one scale per output
+                             * row (amax / 448; f32 weights are encoded at load, int8 payloads are dequantised and re-encoded),
+                             * activations are quantised per token to E4M3 (amax / 448), the GEMMs run on the kind::f8f6f4 MMA
+                             * with f32 accumulation.  Everything else (RMSNorm, RoPE, attention, sampling) is unchanged.
+                             * Row widths must fit the one-CTA row kernels (multiples of 4, at most 16384 columns per rank);
+                             * not combinable with tp_exact_int8.  0: INT8 x INT8 (exact int32 accumulation). */
 } b200_decoder_config;
 
 typedef enum b200_weight {

@@ -70,15 +70,21 @@ class DecoderRef:
     logits and greedy ids can be compared bit for bit with the device (shapes that run on the general attention
     kernel only: head_dim other than 128, or blocks other than 16 tokens); the integer GEMMs go through BLAS."""
 
-    def __init__(self, cfg: dict, weights: dict, tp: int = 1, exact: bool = False, sm_count: int = 148):
+    def __init__(self, cfg: dict, weights: dict, tp: int = 1, exact: bool = False, sm_count: int = 148, fp8: bool = False):
+        """fp8=True: the FP8 x FP8 form - weights and activations as E4M3 codes under per-row scales amax / 448,
+        products accumulated in f32 (ascending k, one fma per product); everything else unchanged."""
         self.cfg = cfg
         self.tp = tp
         self.w = weights
         self.exact = exact
         self.sm_count = sm_count
-        self.q = {"lm_head": O.quantize_i8_per_row(weights["lm_head"]), "layers": []}
+        self.fp8 = fp8
+        self._qrow = O.quantize_fp8_per_row if fp8 else O.quantize_i8_per_row
+        if fp8 and exact:
+            raise ValueError("the tensor core's f32 accumulation order is not restated")
+        self.q = {"lm_head": self._qrow(weights["lm_head"]), "layers": []}
         for lw in weights["layers"]:
-            self.q["layers"].append({k: O.quantize_i8_per_row(lw[k]) for k in ("wqkv", "wo", "wgu", "wdown")})
+            self.q["layers"].append({k: self._qrow(lw[k]) for k in ("wqkv", "wo", "wgu", "wdown")})
         self.blas = None
         if exact:
             if tp != 1:
@@ -93,6 +99,8 @@ class DecoderRef:
         self.k = None
 
     def _acc(self, xq, lq_entry, blas_entry):
+        if self.fp8:
+            return O.gemm_fp8_f32(xq, lq_entry[0])
         return O.gemm_i8_s32_blas(xq, blas_entry) if blas_entry is not None else O.gemm_i8_s32(xq, lq_entry[0])
 
     def _norm(self, h, w, eps, first: bool):
@@ -125,8 +133,9 @@ class DecoderRef:
         k = x.shape[1] // tp
         total = None
         for r in range(tp):
-            xq, sx = O.quantize_i8_per_row(x[:, r * k:(r + 1) * k])
-            acc = O.gemm_i8_s32(xq, np.ascontiguousarray(wq[:, r * k:(r + 1) * k]))
+            xq, sx = self._qrow(x[:, r * k:(r + 1) * k])
+            wr = np.ascontiguousarray(wq[:, r * k:(r + 1) * k])
+            acc = O.gemm_fp8_f32(xq, wr) if self.fp8 else O.gemm_i8_s32(xq, wr)
             y = O.epilogue_scaled(acc, sx, True, ws, True)
             total = y if total is None else (total + y).astype(np.float32)
         return (total + h).astype(np.float32)
@@ -144,7 +153,7 @@ class DecoderRef:
         for l, (lw, lq) in enumerate(zip(self.w["layers"], self.q["layers"])):
             lb = self.blas["layers"][l] if self.blas else {}
             xn = self._norm(h, lw["attn_norm"], eps, first=(l == 0))
-            xq, sx = O.quantize_i8_per_row(xn)
+            xq, sx = self._qrow(xn)
             qkv = O.epilogue_scaled(self._acc(xq, lq["wqkv"], lb.get("wqkv")), sx, True, lq["wqkv"][1], True)
             q = np.empty((b, hq * dh), np.float32)
             k_new = np.empty((b, hkv * dh), np.float32)
@@ -159,23 +168,23 @@ class DecoderRef:
                           num_blocks=self.nblk, max_blocks_per_seq=self.mbps,
                           scale=float(np.float32(1.0) / np.sqrt(np.float32(dh))), kv_bf16=True).reshape(b, -1)
             if self.exact:
-                aq, sa = O.quantize_i8_per_row(a)
+                aq, sa = self._qrow(a)
                 h = (O.epilogue_scaled(self._acc(aq, lq["wo"], lb["wo"]), sa, True, lq["wo"][1], True) + h).astype(np.float32)
             else:
                 h = self._row_parallel(a, *lq["wo"], h)
             xn = self._norm(h, lw["mlp_norm"], eps, first=False)
-            xq, sx = O.quantize_i8_per_row(xn)
+            xq, sx = self._qrow(xn)
             acc = self._acc(xq, lq["wgu"], lb.get("wgu"))
             if self.exact:
                 act = O.epilogue_det(acc, sx, lq["wgu"][1], act=O.ACT_SILU_GATE)
-                fq, sf = O.quantize_i8_per_row(act)
+                fq, sf = self._qrow(act)
                 h = (O.epilogue_scaled(self._acc(fq, lq["wdown"], lb["wdown"]), sf, True, lq["wdown"][1], True) + h).astype(np.float32)
             else:
                 act = O.epilogue_scaled(acc, sx, True, lq["wgu"][1], True, act=O.ACT_SILU_GATE)
                 h = self._row_parallel(act, *lq["wdown"], h)
         self.seq += 1
         xn = self._norm(h, self.w["final_norm"], eps, first=False)
-        xq, sx = O.quantize_i8_per_row(xn)
+        xq, sx = self._qrow(xn)
         logits = O.epilogue_scaled(self._acc(xq, self.q["lm_head"], self.blas["lm_head"] if self.blas else None), sx, True,
                                    self.q["lm_head"][1], True)
         nxt = np.argmax(logits, axis=1).astype(np.int32) if self.exact else \
@@ -201,7 +210,7 @@ class DecoderRef:
         for l, (lw, lq) in enumerate(zip(self.w["layers"], self.q["layers"])):
             lb = self.blas["layers"][l] if self.blas else {}
             xn = self._norm(h, lw["attn_norm"], eps, first=(l == 0))
-            xq, sx = O.quantize_i8_per_row(xn)
+            xq, sx = self._qrow(xn)
             qkv = O.epilogue_scaled(self._acc(xq, lq["wqkv"], lb.get("wqkv")), sx, True, lq["wqkv"][1], True)
             q = np.empty((m, hq * dh), np.float32)
             k_new = np.empty((m, hkv * dh), np.float32)
@@ -217,16 +226,16 @@ class DecoderRef:
                           num_q_heads=hq, num_kv_heads=hkv, head_dim=dh, block_size=self.bs,
                           num_blocks=self.nblk, max_blocks_per_seq=self.mbps,
                           scale=float(np.float32(1.0) / np.sqrt(np.float32(dh))), kv_bf16=True).reshape(m, -1)
-            aq, sa = O.quantize_i8_per_row(a)
+            aq, sa = self._qrow(a)
             h = (O.epilogue_scaled(self._acc(aq, lq["wo"], lb.get("wo")), sa, True, lq["wo"][1], True) + h).astype(np.float32)
             xn = self._norm(h, lw["mlp_norm"], eps, first=False)
-            xq, sx = O.quantize_i8_per_row(xn)
+            xq, sx = self._qrow(xn)
             acc = self._acc(xq, lq["wgu"], lb.get("wgu"))
             if self.exact:
                 act = O.epilogue_det(acc, sx, lq["wgu"][1], act=O.ACT_SILU_GATE)
             else:
                 act = O.epilogue_scaled(acc, sx, True, lq["wgu"][1], True, act=O.ACT_SILU_GATE)
-            fq, sf = O.quantize_i8_per_row(act)
+            fq, sf = self._qrow(act)
             h = (O.epilogue_scaled(self._acc(fq, lq["wdown"], lb.get("wdown")), sf, True, lq["wdown"][1], True) + h).astype(np.float32)
         self.seq += L
 

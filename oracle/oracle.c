@@ -223,6 +223,19 @@ void orc_quantize_fp8_per_tensor(const float* x, int64_t n, uint8_t* q, float* s
     for (int64_t i = 0; i < n; ++i) q[i] = orc_f32_to_e4m3(s == 0.0f ? 0.0f : x[i] / s);
 }
 
+/* Per-row form (the FP8 decoder's activations and weights): scale[r] = amax(row r) / 448, q = e4m3(x / scale[r]). */
+void orc_quantize_fp8_per_row(const float* x, int64_t rows, int64_t cols, uint8_t* q, float* scale) {
+#pragma omp parallel for schedule(static) if (rows * cols > SMALL_WORK)
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* xr = x + r * cols;
+        float amax = 0.0f;
+        for (int64_t c = 0; c < cols; ++c) amax = fmaxf(amax, fabsf(xr[c]));
+        const float s = amax / 448.0f;
+        scale[r] = s;
+        for (int64_t c = 0; c < cols; ++c) q[r * cols + c] = orc_f32_to_e4m3(s == 0.0f ? 0.0f : xr[c] / s);
+    }
+}
+
 /* ------------------------------------------------------------------ activations
  * Two-branch sigmoid and SiLU = x * sigmoid(x) (crates/tensor-core/src/scalar_op.rs:355,666-673). */
 float orc_sigmoid_stable(float x) {

@@ -178,6 +178,16 @@ def quantize_fp8_per_tensor(x):
     return q, s
 
 
+def quantize_fp8_per_row(x):
+    """E4M3 codes [rows, cols] (uint8) and one scale per row (amax / 448): the FP8 decoder's quantiser."""
+    x = _c(x, np.float32)
+    rows, cols = x.shape
+    q = np.empty((rows, cols), np.uint8)
+    s = np.empty((rows,), np.float32)
+    lib().orc_quantize_fp8_per_row(_p(x), C.c_int64(rows), C.c_int64(cols), _p(q), _p(s))
+    return q, s
+
+
 ACT_NONE, ACT_RELU, ACT_SILU, ACT_SILU_GATE = 0, 1, 2, 3
 
 

@@ -417,3 +417,74 @@ def test_sampled_generation_follows_the_cpu_decoder(be, strategy, k, temperature
             ids = nxt
     finally:
         dec.close()
+
+
+def make_fp8_decoder(be, cfg: dict, batch: int) -> Decoder:
+    dc = DecoderConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["d_ff"],
+                       cfg["vocab"], cfg.get("rms_eps", 1e-5), cfg.get("rope_theta", 10000.0), max_batch=batch,
+                       max_seq_len=cfg["max_seq_len"], block_size=cfg.get("block_size", 16), act_fp8=1)
+    return Decoder(be, dc)
+
+
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_fp8_decoder_against_the_cpu_fp8_decoder(be, head_dim):
+    """The FP8 x FP8 form (E4M3 weights and activations under per-row scales amax / 448, f32 accumulation) against
+    the CPU decoder in the same format, teacher-forced.  The tensor core adds the products of a row in another order
+    than the CPU's fma chain, and one E4M3 code is a step of 1/8 .. 1/16 of a value, so a last-bit difference upstream
+    of a quantiser moves the result by far more than with int8: the bound is relative to the logit range and the
+    greedy choice must agree wherever the CPU decoder's margin exceeds twice that deviation.  head_dim 128 runs the
+    tensor-core attention and the QKV GEMM that finishes RoPE and the cache append itself (f32 partial sums over the
+    K slices), head_dim 64 the general kernels."""
+    cfg = dict(n_layers=2, d_model=512, n_heads=512 // head_dim, n_kv_heads=256 // head_dim, head_dim=head_dim, d_ff=1024,
+               vocab=2048, max_seq_len=40)
+    weights = make_weights(cfg, seed=51)
+    batch, steps = 6, 24
+    ref = DecoderRef(cfg, weights, fp8=True)
+    ref.begin(batch)
+    dec = make_fp8_decoder(be, cfg, batch)
+    rng = np.random.default_rng(52)
+    try:
+        dec.load_weights(weights)
+        dec.begin(batch, [steps + 1] * batch)
+        ids = rng.integers(0, cfg["vocab"], batch).astype(np.int32)
+        worst = 0.0
+        for t in range(steps):
+            want, want_next = ref.step(ids)
+            got_next = dec.step(ids)
+            got = dec.logits()
+            assert np.all(np.isfinite(got)), t
+            span = float(np.abs(want).max())
+            dev = float(np.abs(got - want).max())
+            worst = max(worst, dev / span)
+            for r in range(batch):
+                if got_next[r] != want_next[r]:
+                    assert want[r, want_next[r]] - want[r, got_next[r]] <= 2 * dev, (t, r)
+            ids = want_next
+        assert worst < 4e-2, worst
+        print(f"fp8 decoder head_dim={head_dim}: worst |dlogit| / max|logit| = {worst:.3e}")
+    finally:
+        dec.close()
+
+
+def test_fp8_decoder_is_not_the_int8_decoder(be):
+    """The two forms give different logits from the same f32 weights (E4M3 keeps 4 significant bits), both close to
+    their own CPU decoder: a silent fall-back of one form to the other would show here."""
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=512, max_seq_len=16)
+    weights = make_weights(cfg, seed=53)
+    ids = np.array([5, 400], np.int32)
+    out = {}
+    for name, mk in (("int8", make_decoder), ("fp8", make_fp8_decoder)):
+        dec = mk(be, cfg, 2)
+        try:
+            dec.load_weights(weights)
+            dec.begin(2, [4, 4])
+            dec.step(ids)
+            out[name] = dec.logits()
+        finally:
+            dec.close()
+    ref8 = DecoderRef(cfg, weights, fp8=True)
+    ref8.begin(2)
+    want8, _ = ref8.step(ids)
+    span = float(np.abs(want8).max())
+    assert float(np.abs(out["fp8"] - want8).max()) / span < 2e-2
+    assert float(np.abs(out["fp8"] - out["int8"]).max()) / span > 2e-2
