@@ -144,6 +144,7 @@ SIGNATURES = {
     "b200_selftest_peer_wait": (_I32, [_P]),
     "b200_selftest_tp_finish": (_I32, [_P, _I32, _I32, _I32, _I32, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
     "b200_selftest_tp_scatter": (_I32, [_P, _I32, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
+    "b200_gemm_phase_stamps": (_I32, [_P, C.c_int64, C.c_int64, C.c_int64, _I32, _I32, _P, _P, _P, _P]),
     "b200_decoder_batch": (_I32, [_P]),
     "b200_sampling_weights": (_I32, [_P, C.c_int64, C.c_int64, _I32, _I32, C.c_float, _P]),
     "b200_decoder_sampling_weights": (_I32, [_P, _I32, _I32, C.c_float, _P, C.c_uint64]),

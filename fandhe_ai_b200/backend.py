@@ -120,6 +120,17 @@ class Backend:
         check(lib().b200_gemm_plan_info(self._ctx, m, n, k, int(gated), int(fused), buf))
         return dict(zip(["tile", "splits", "cluster", "persistent", "ctas", "stages"], list(buf)))
 
+    def gemm_phase_stamps(self, m: int, n: int, k: int, fused: bool = False, iters: int = 50) -> dict:
+        """Profiling aid: where the time of one decode-shaped GEMM launch goes (see b200_gemm_phase_stamps)."""
+        stamps = (C.c_uint64 * 9)()
+        loop_us, alone_us = C.c_float(), C.c_float()
+        info = (C.c_int32 * 6)()
+        check(lib().b200_gemm_phase_stamps(self._ctx, m, n, k, int(fused), iters, stamps, C.byref(loop_us), C.byref(alone_us), info))
+        names = ["entry", "setup", "dep_wait", "loads_issued", "first_tile", "mma_issued", "acc_ready", "stored", "exit"]
+        return {"m": m, "n": n, "k": k, "fused": bool(fused), "tile": info[0], "splits": info[1], "cluster": info[2],
+                "stages": info[5], "loop_us_per_launch": round(float(loop_us.value), 2), "alone_us": round(float(alone_us.value), 2),
+                "stamps_ns": dict(zip(names, [int(x) for x in stamps]))}
+
     def memory_info(self):
         """(free, total) device memory in bytes."""
         free, total = C.c_size_t(), C.c_size_t()

@@ -168,9 +168,26 @@ def run_attention(args):
     be.close()
 
 
+def run_gemm_phases(args):
+    """Where the time of a decode-shaped GEMM launch goes: the M = 1 / 16 / 128 shapes of the weight sweep (or --shape),
+    raw accumulators and the dequantising epilogue, %globaltimer stamps of the launch's first CTA."""
+    be = Backend(0)
+    if args.shape:
+        shapes = [tuple(int(x) for x in args.shape.split(","))]
+    else:
+        shapes = [(m, n, n) for n in (4096, 8192, 14336) for m in (1, 16, 128)]
+    for m, n, k in shapes:
+        for fused in (False, True):
+            try:
+                print(json.dumps(be.gemm_phase_stamps(m, n, k, fused=fused, iters=max(args.iters, 20))), flush=True)
+            except Exception as exc:            # a shape without that form: say so and go on
+                print(json.dumps({"m": m, "n": n, "k": k, "fused": fused, "skipped": str(exc)[:120]}), flush=True)
+    be.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention"])
+    ap.add_argument("what", choices=["gemm", "attention", "gemm-phases"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--quick", action="store_true")
@@ -183,6 +200,8 @@ def main():
     args = ap.parse_args()
     if args.what == "gemm":
         run_gemm(args)
+    elif args.what == "gemm-phases":
+        run_gemm_phases(args)
     else:
         run_attention(args)
 

@@ -692,6 +692,86 @@ int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int3
     return B200_OK;
 }
 
+// Where the time of one decode-shaped GEMM launch goes: runs the int8 GEMM of the shape the way b200_gemm_i8_s32
+// (fused = 0) or the dequantising epilogue (fused = 1) would on the one-tile kernel, first `iters` launches back to
+// back between two events (what a launch costs inside a stream of dependent launches), then ONE launch alone whose
+// first CTA stamps %globaltimer at nine points of its life.  Operands are zero-filled device buffers.
+int32_t b200_gemm_phase_stamps(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t fused, int32_t iters, uint64_t* stamps_ns9,
+                               float* loop_us_per_launch, float* alone_us, int32_t* info6) {
+    if (int32_t st = check_ctx(ctx)) return st;
+    if (!stamps_ns9 || !loop_us_per_launch || !alone_us || !info6 || iters <= 0)
+        return fail(B200_INVALID_ARGUMENT, "gemm_phase_stamps: bad argument");
+    if (int32_t st = check_gemm_dims("gemm_phase_stamps", m, n, k)) return st;
+    if (m <= 0 || n <= 0 || k <= 0) return fail(B200_INVALID_ARGUMENT, "gemm_phase_stamps: m, n, k must be positive");
+    if (int32_t st = set_device(ctx)) return st;
+    cudaStream_t s = ctx->stream;
+    int8_t *a = nullptr, *b = nullptr;
+    float* scales = nullptr;
+    void* out = nullptr;
+    unsigned long long* stamps = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    GemmPlan plan;
+    const char* why = "";
+    int32_t st = B200_OK;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&a), size_t(m) * k);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b), size_t(n) * k);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&scales), size_t(m + n) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&stamps), kGemmStampCount * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemsetAsync(a, 0, size_t(m) * k, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(b, 0, size_t(n) * k, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(scales, 0, size_t(m + n) * sizeof(float), s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(stamps, 0, kGemmStampCount * sizeof(unsigned long long), s);
+    if (e == cudaSuccess) e = gemm_make_plan(&plan, kGemmI8, a, b, int(m), int(n), int(k), 0, ctx->tune_splits, ctx->tune_bn, &why);
+    if (e == cudaSuccess && fused && !(plan.splits == 1 || plan.cluster)) {
+        st = fail(B200_UNSUPPORTED, "gemm_phase_stamps: this shape has no fused epilogue in the one-tile kernel");
+    } else if (e == cudaSuccess) {
+        e = cudaMalloc(&out, gemm_raw_elems(plan) * 4);
+        GemmEpilogue ep;
+        ep.raw = out;
+        if (fused) {
+            ep.fused = 1;
+            ep.a_scale = scales;
+            ep.a_per_row = 1;
+            ep.b_scale = scales + m;
+            ep.b_per_col = 1;
+            ep.out = out;
+        }
+        if (e == cudaSuccess) e = cudaEventCreate(&e0);
+        if (e == cudaSuccess) e = cudaEventCreate(&e1);
+        for (int i = 0; i < 3 && e == cudaSuccess; ++i) e = gemm_launch(plan, ep, ctx->err_dev, s);
+        if (e == cudaSuccess) e = cudaEventRecord(e0, s);
+        for (int i = 0; i < iters && e == cudaSuccess; ++i) e = gemm_launch(plan, ep, ctx->err_dev, s);
+        if (e == cudaSuccess) e = cudaEventRecord(e1, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        float ms = 0.0f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+        *loop_us_per_launch = ms * 1000.0f / float(iters);
+        ep.stamps = stamps;
+        if (e == cudaSuccess) e = cudaEventRecord(e0, s);
+        if (e == cudaSuccess) e = gemm_launch(plan, ep, ctx->err_dev, s);
+        if (e == cudaSuccess) e = cudaEventRecord(e1, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+        *alone_us = ms * 1000.0f;
+        unsigned long long host[kGemmStampCount] = {};
+        if (e == cudaSuccess) e = cudaMemcpy(host, stamps, sizeof(host), cudaMemcpyDeviceToHost);
+        for (int i = 0; i < kGemmStampCount; ++i) stamps_ns9[i] = host[i] >= host[0] ? host[i] - host[0] : 0;
+        const int v[6] = {plan.bn, plan.splits, plan.cluster, 0, 0, plan.stages};
+        for (int i = 0; i < 6; ++i) info6[i] = v[i];
+    }
+    if (e != cudaSuccess && st == B200_OK)
+        st = fail_runtime(ctx, B200_KERNEL_LAUNCH_FAILED, std::string("gemm_phase_stamps: ") + why + " " + cudaGetErrorString(e));
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(a);
+    cudaFree(b);
+    cudaFree(scales);
+    cudaFree(out);
+    cudaFree(stamps);
+    if (st == B200_OK) st = b200_synchronize(ctx);
+    return st;
+}
+
 /* ------------------------------------------------------------------ block-scale contract (QuantOps of the reference) */
 
 static constexpr int64_t kBlockLen = 128;

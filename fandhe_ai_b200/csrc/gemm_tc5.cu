@@ -141,6 +141,11 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const bool stamping = p.ep.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    auto stamp = [&](int i) {
+        if (stamping) p.ep.stamps[i] = global_timer_ns();
+    };
+    if (threadIdx.x == 0) stamp(kGemmStampEntry);
 
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tma_a);
@@ -160,6 +165,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     __syncthreads();
     tc5_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    if (threadIdx.x == 0) stamp(kGemmStampSetup);
 
     const int out_cols = p.gate ? BN / 2 : BN;          // output columns per CTA
     const int n0 = blockIdx.x * out_cols;               // first output column
@@ -212,8 +218,10 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 }
                 pdl_wait();
             }
+            stamp(kGemmStampDepWait);
             pdl_launch_dependents();
             for (int i = 0; i < pre; ++i) load_a(i, i);
+            stamp(kGemmStampLoadsIssued);
             for (int i = pre; i < num_kb; ++i) {
                 const int s = i % p.stages;
                 const uint32_t ph = (i / p.stages) & 1;
@@ -231,6 +239,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const uint32_t ph = (i / p.stages) & 1;
                 ok = mbar_wait(full_bar(s), ph, p.err, kErrMmaWait);
                 if (!ok) break;
+                if (i == 0) stamp(kGemmStampFirstTile);
                 tc5_fence_after();
                 const uint32_t a_src = smem_base + s * kStageBytes;
                 const uint64_t adesc = umma_desc_k128(a_src);
@@ -243,6 +252,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 tc5_commit(empty_bar(s));
             }
             tc5_commit(tmem_full_bar);
+            stamp(kGemmStampMmaIssued);
         }
     } else {
         // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4
@@ -252,6 +262,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         pdl_wait();      // scales, bias, residual and the output buffers belong to the surrounding kernels
         bool ready = num_kb > 0 && mbar_wait(tmem_full_bar, 0, p.err, kErrEpilogueWait);
         tc5_fence_after();
+        if (warp == 2 && lane == 0) stamp(kGemmStampAccReady);
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         const GemmEpilogue& ep = p.ep;
         if (ready && p.cluster_reduce) {
@@ -487,11 +498,13 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
     tc5_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) stamp(kGemmStampStored);
     if (p.ep.push.peers != nullptr && !p.cluster_reduce && warp == 2) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
     if (warp == 1) {
         __syncwarp();
         tc5_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
+        if (lane == 0) stamp(kGemmStampExit);
     }
 }
 

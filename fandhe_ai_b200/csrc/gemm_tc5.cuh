@@ -76,6 +76,22 @@ struct GemmEpilogue {
     GemmRope rope;                   // see GemmRope; needs fused = 1 with per-row / per-column scales, no bias
     GemmPeerWait wait;               // see GemmPeerWait
     GemmPush push;                   // see GemmPush
+    // Profiling aid of the one-tile kernel: when not null, the first CTA of the launch writes %globaltimer (ns) at
+    // nine points of its life (kGemmStamp*); costs one predicated branch per point otherwise.
+    unsigned long long* stamps = nullptr;
+};
+
+enum GemmStamp : int {
+    kGemmStampEntry = 0,        // first instruction of the CTA
+    kGemmStampSetup = 1,        // barriers initialised, tensor memory allocated, CTA barrier passed
+    kGemmStampDepWait = 2,      // producer: the kernel before this one has completed (griddepcontrol.wait returned)
+    kGemmStampLoadsIssued = 3,  // producer: first pass over the ring issued (A and B tiles)
+    kGemmStampFirstTile = 4,    // MMA warp: first stage has landed in shared memory
+    kGemmStampMmaIssued = 5,    // MMA warp: last MMA issued and committed
+    kGemmStampAccReady = 6,     // epilogue: accumulator complete in tensor memory
+    kGemmStampStored = 7,       // epilogue: last store of the CTA issued (after the cluster reduction, if any)
+    kGemmStampExit = 8,         // tensor memory freed
+    kGemmStampCount = 9
 };
 
 struct GemmPlan {

@@ -199,6 +199,14 @@ int32_t b200_quant_check(b200_ctx* ctx);
  * 2: CTA pairs on 256-row tiles), resident CTAs of the persistent kernel, operand stages}.  The counterpart of asking the reference's kernel selection what it would run
  * (crates/backend-cuda/src/gemm_auto.rs:1829-1892); lets a test state which kernel it reached. */
 int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t gated, int32_t fused, int32_t* out6);
+/* Profiling aid for decode-shaped GEMMs (one-tile kernel): `iters` launches back to back between two CUDA events
+ * (loop_us_per_launch), then one launch alone (alone_us) whose first CTA records %globaltimer at nine points;
+ * stamps_ns9[i] = nanoseconds since the CTA's first instruction: 0 entry, 1 barriers + tensor memory set up, 2 the
+ * launch before has completed, 3 first pass of TMA loads issued, 4 first operand stage has landed, 5 last MMA issued,
+ * 6 accumulator complete, 7 all stores of the CTA issued, 8 tensor memory freed.  info6 as in b200_gemm_plan_info.
+ * fused = 0: raw accumulators; 1: the dequantising epilogue.  Operands are zero-filled.  No reference counterpart. */
+int32_t b200_gemm_phase_stamps(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t fused, int32_t iters, uint64_t* stamps_ns9,
+                               float* loop_us_per_launch, float* alone_us, int32_t* info6);
 
 /* ------------------------------------------------------------------ quantized linear
  * BackendOps::linear_forward_device_into_tracked (crates/tensor-core/src/backend_ops.rs:4296-4366)

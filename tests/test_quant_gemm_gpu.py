@@ -458,3 +458,19 @@ def test_committed_linear_and_fp8_cases(be):
         assert fails == 0, (key, max_abs, max_rel)
     q, s = be.quantize_fp8_e4m3_per_tensor(be.upload(g["fp8_x"]), g["fp8_x"].size)
     assert np.array_equal(q.numpy(), g["fp8_q"]) and np.array_equal(s.numpy(), g["fp8_scale"])
+
+
+@pytest.mark.parametrize("m,n,k,fused", [(128, 4096, 4096, False), (16, 4096, 4096, True), (1, 8192, 8192, False)])
+def test_gemm_phase_stamps_are_ordered(be, m, n, k, fused):
+    """The profiling aid of the one-tile kernel: the nine %globaltimer stamps of the first CTA follow the life of the
+    kernel (set-up, loads, first operands, MMAs, accumulator, stores, exit) and fit inside the event-timed launch."""
+    r = be.gemm_phase_stamps(m, n, k, fused=fused, iters=10)
+    st = r["stamps_ns"]
+    assert st["entry"] == 0
+    assert st["entry"] <= st["setup"] <= st["loads_issued"]
+    assert st["dep_wait"] <= st["loads_issued"]
+    assert st["setup"] <= st["first_tile"] <= st["mma_issued"]
+    assert st["first_tile"] <= st["acc_ready"] <= st["stored"] <= st["exit"]
+    assert 0 < st["exit"] < 1_000_000                       # under a millisecond
+    assert r["alone_us"] > 0 and r["loop_us_per_launch"] > 0
+    assert not be.poisoned
