@@ -380,11 +380,12 @@ __device__ __forceinline__ void wide_norm_quant(float4 (&v)[VPT], int groups, in
     wide_quant<VPT>(v, groups, sh, q_row, scale_out, fp8);
 }
 
-template <int VPT>
+template <int VPT, bool kF8>
 __global__ void __launch_bounds__(kWideThreads)
 resid_norm_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int d, const float* __restrict__ sx_in,
                              const float* __restrict__ sw, const float* __restrict__ pre, const float* __restrict__ norm_w,
-                             float eps, float* __restrict__ h, int8_t* __restrict__ xq, float* __restrict__ sx_out, int fp8) {
+                             float eps, float* __restrict__ h, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+    constexpr int fp8 = kF8 ? 1 : 0;
     __shared__ WideShared sh;
     pdl_wait();
     pdl_launch_dependents();
@@ -417,10 +418,13 @@ resid_norm_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int
     wide_norm_quant<VPT>(v, groups, d, sh, norm_w, eps, xq + base, sx_out + m, fp8);
 }
 
-template <int VPT>
+// kF8: the FP8 form (f32 accumulator words in, E4M3 codes out); a template parameter because the extra paths cost the
+// int8 instantiation registers it does not have (1024 threads: 64 per thread)
+template <int VPT, bool kF8>
 __global__ void __launch_bounds__(kWideThreads)
 gate_quant_wide_kernel(const int* __restrict__ raw, int splits, int M, int F, const float* __restrict__ sx_in,
-                       const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out, int fp8) {
+                       const float* __restrict__ sw, int8_t* __restrict__ xq, float* __restrict__ sx_out) {
+    constexpr int fp8 = kF8 ? 1 : 0;
     __shared__ WideShared sh;
     pdl_wait();
     pdl_launch_dependents();
@@ -577,7 +581,8 @@ struct TpFinishArgs {
     int fp8;                   // the delivered rows are e4m3 codes under the scale amax / 448
 };
 
-template <int VPT>
+// kScattered / kF8 are template parameters for the registers' sake (1024 threads: 64 per thread).
+template <int VPT, bool kScattered, bool kF8>
 __global__ void __launch_bounds__(kWideThreads)
 tp_finish_kernel(TpFinishArgs a) {
     __shared__ WideShared sh;
@@ -590,7 +595,8 @@ tp_finish_kernel(TpFinishArgs a) {
     pdl_wait();
     pdl_launch_dependents();
     const uint32_t epoch = *a.epoch + 1;
-    const bool scattered = a.push_tiles != 0u;
+    constexpr bool scattered = kScattered;
+    constexpr int fp8 = kF8 ? 1 : 0;
     const uint32_t target = scattered ? *a.push_target + a.push_tiles : 0u;
     __syncthreads();
     uint8_t* mine = s_peer[a.rank];
@@ -677,7 +683,7 @@ tp_finish_kernel(TpFinishArgs a) {
         }
     }
     amax = wide_max(amax, sh);
-    const float s = row_scale(amax, a.fp8);
+    const float s = row_scale(amax, fp8);
     // 3. deliver the row to every rank
     if (ok) {
         for (int p = 0; p < a.tp; ++p) {
@@ -685,7 +691,7 @@ tp_finish_kernel(TpFinishArgs a) {
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 const int g = threadIdx.x + k * blockDim.x;
-                if (g < groups) q4[g] = pack4(v[k], s, a.fp8);
+                if (g < groups) q4[g] = pack4(v[k], s, fp8);
             }
             if (threadIdx.x == 0) reinterpret_cast<float*>(s_peer[p] + a.o_sx)[row] = s;
         }
@@ -772,9 +778,11 @@ cudaError_t resid_norm_quant_auto(const int* raw, int splits, int M, int d, cons
                                   cudaStream_t s, int fp8) {
     int vpt, threads;
     wide_shape(d, &vpt, &threads, M);
-#define B200_WIDE_RESID(V)                                                                                              \
-    return launch_ex(resid_norm_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, d, sx_in, \
-                     sw, pre, norm_w, eps, h, xq, sx_out, fp8)
+#define B200_WIDE_RESID(V)                                                                                                     \
+    return fp8 ? launch_ex(resid_norm_quant_wide_kernel<V, true>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, d,   \
+                           sx_in, sw, pre, norm_w, eps, h, xq, sx_out)                                                          \
+               : launch_ex(resid_norm_quant_wide_kernel<V, false>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, d,  \
+                           sx_in, sw, pre, norm_w, eps, h, xq, sx_out)
     if (vpt == 1) B200_WIDE_RESID(1);
     if (vpt == 2) B200_WIDE_RESID(2);
     if (vpt == 4) B200_WIDE_RESID(4);
@@ -787,9 +795,11 @@ cudaError_t gate_quant_auto(const int* raw, int splits, int M, int F, const floa
                             float* sx_out, cudaStream_t s, int fp8) {
     int vpt, threads;
     wide_shape(F, &vpt, &threads, M);
-#define B200_WIDE_GATE(V)                                                                                        \
-    return launch_ex(gate_quant_wide_kernel<V>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, F, sx_in, \
-                     sw, xq, sx_out, fp8)
+#define B200_WIDE_GATE(V)                                                                                                 \
+    return fp8 ? launch_ex(gate_quant_wide_kernel<V, true>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, F, sx_in, \
+                           sw, xq, sx_out)                                                                                 \
+               : launch_ex(gate_quant_wide_kernel<V, false>, dim3(M), dim3(threads), 0, s, 1, true, raw, splits, M, F, sx_in, \
+                           sw, xq, sx_out)
     if (vpt == 1) B200_WIDE_GATE(1);
     if (vpt == 2) B200_WIDE_GATE(2);
     if (vpt == 4) B200_WIDE_GATE(4);
@@ -882,9 +892,18 @@ cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_
     if (push_tiles != 0u && push_target == nullptr) return cudaErrorInvalidValue;
     TpFinishArgs a{peers, o_sx, o_xq, o_part, tp, rank, rows, d, norm_w, eps, h, epoch, arrived, err,
                    timeout_ns ? timeout_ns : kPeerWaitNs, o_count, push_tiles, push_target, fp8};
-    if (vpt == 1) return launch_ex(tp_finish_kernel<1>, dim3(rows), dim3(threads), 0, s, 1, true, a);
-    if (vpt == 2) return launch_ex(tp_finish_kernel<2>, dim3(rows), dim3(threads), 0, s, 1, true, a);
-    if (vpt == 4) return launch_ex(tp_finish_kernel<4>, dim3(rows), dim3(threads), 0, s, 1, true, a);
+#define B200_TP_FINISH(V)                                                                                             \
+    do {                                                                                                              \
+        if (push_tiles != 0u)                                                                                         \
+            return fp8 ? launch_ex(tp_finish_kernel<V, true, true>, dim3(rows), dim3(threads), 0, s, 1, true, a)      \
+                       : launch_ex(tp_finish_kernel<V, true, false>, dim3(rows), dim3(threads), 0, s, 1, true, a);    \
+        return fp8 ? launch_ex(tp_finish_kernel<V, false, true>, dim3(rows), dim3(threads), 0, s, 1, true, a)         \
+                   : launch_ex(tp_finish_kernel<V, false, false>, dim3(rows), dim3(threads), 0, s, 1, true, a);       \
+    } while (0)
+    if (vpt == 1) B200_TP_FINISH(1);
+    if (vpt == 2) B200_TP_FINISH(2);
+    if (vpt == 4) B200_TP_FINISH(4);
+#undef B200_TP_FINISH
     return cudaErrorInvalidValue;
 }
 

@@ -120,7 +120,12 @@ __device__ __forceinline__ void emit4(const KernelArgs& p, int row, int n, const
     store_out4(ep, static_cast<size_t>(row) * p.N + n, y[0], y[1], y[2], y[3]);
 }
 
-template <int BN, bool kInt8>
+// kAux selects one of three instantiations: 0 the plain kernel; 1 the rows are scattered over the GPUs (GemmPush);
+// 2 the first CTA stamps %globaltimer (GemmEpilogue::stamps).  Template parameters, not run-time flags: the mere
+// presence of either path cost the plain decode GEMMs 0.09 + 0.04 ms per 8B-shape step (measured on one GPU).
+constexpr int kAuxNone = 0, kAuxPush = 1, kAuxStamps = 2;
+
+template <int BN, bool kInt8, int kAux>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, KernelArgs p) {
     constexpr int kBBytes = BN * kBK;
@@ -141,9 +146,12 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const bool stamping = p.ep.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    const bool stamping = kAux == kAuxStamps && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    constexpr bool pushing = kAux == kAuxPush;     // the rows go to their owner ranks (GemmPush)
     auto stamp = [&](int i) {
-        if (stamping) p.ep.stamps[i] = global_timer_ns();
+        if constexpr (kAux == kAuxStamps) {
+            if (stamping) p.ep.stamps[i] = global_timer_ns();
+        }
     };
     if (threadIdx.x == 0) stamp(kGemmStampEntry);
 
@@ -270,7 +278,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             // is idle by now (every MMA has completed), consecutive threads hold consecutive rows
             uint32_t* part = reinterpret_cast<uint32_t*>(smem_dyn + (smem_base - smem_u32(smem_dyn)));
             const int rl = q * 32 + lane;
-            if (ep.rope.enabled) {
+            if (!pushing) {
+                // column-major ([col][row]): consecutive threads hold consecutive rows, 4-byte accesses without bank conflicts
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld_32x32(t_row + c0, v);
@@ -279,8 +288,9 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     for (int j = 0; j < 32; ++j) part[(c0 + j) * kBM + rl] = v[j];
                 }
             } else {
-                // row-major with a pitch of BN + 4 words: the 16-byte stores of eight neighbouring rows fall into
-                // different banks, and the reduction below reads (and then writes to global memory) whole row segments
+                // the rows will be scattered over the GPUs: row-major with a pitch of BN + 4 words (the 16-byte stores of
+                // eight neighbouring rows fall into different banks), so that the reduction below reads and then stores
+                // whole row segments
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld_32x32(t_row + c0, v);
@@ -310,7 +320,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             } else if (!p.gate) {
                 const float sa = ep.a_scale[ep.a_per_row ? (row_ok ? row : 0) : 0];
                 const size_t row_off = static_cast<size_t>(row_ok ? row : 0) * p.N;
-                float* pushed = ep.push.peers != nullptr && row_ok ? push_row(ep.push, row, p.N) : nullptr;
+                float* pushed = pushing && row_ok ? push_row(ep.push, row, p.N) : nullptr;
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     if (n0 + c0 >= p.N) break;
                     uint32_t v[32];
@@ -462,14 +472,31 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                         *reinterpret_cast<uint2*>(dst + 64) = b;
                     }
                 }
+            } else if (!pushing) {
+                // CTA `rank` finishes a slice of BN / nsplit columns of all rows
+                for (int cc = 0; cc < cpr; cc += 4) {
+                    const int col = rank * cpr + cc;
+                    uint32_t v[4] = {0u, 0u, 0u, 0u};
+                    for (int peer = 0; peer < nsplit; ++peer) {
+                        const uint32_t* pp = cl.map_shared_rank(part, peer);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const uint32_t x = pp[(col + t) * kBM + rl];
+                            if constexpr (kInt8) v[t] += x;    // two's complement wrap = int32 addition
+                            else v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(x));
+                        }
+                    }
+                    const int n = n0 + col;
+                    if (row < p.M && n < p.N) emit4<kInt8>(p, row, n, v);
+                }
             } else {
-                // CTA `rank` finishes the rows [rank * kBM / nsplit, (rank + 1) * kBM / nsplit) of the tile, all BN columns:
-                // sixteen bytes per thread, consecutive threads along a row, so that global memory (this GPU's or, with
-                // GemmPush, the owner's) receives whole row segments
+                // Scattered output: CTA `rank` finishes the rows [rank * kBM / nsplit, (rank + 1) * kBM / nsplit) of the tile,
+                // all BN columns, sixteen bytes per thread and consecutive threads along a row, so that the owner's memory
+                // receives whole row segments (16-byte stores into 32 different rows per instruction cost 1.1 ms per
+                // 8B-shape decode step on two GPUs)
                 const int rows_per = kBM / nsplit;
                 constexpr int kGroups = BN / 4;
                 const int total = rows_per * kGroups;
-                const bool push = p.ep.push.peers != nullptr && p.ep.fused;
                 for (int idx = (warp - 2) * 32 + lane; idx < total; idx += 128) {
                     const int r_tile = rank * rows_per + idx / kGroups;     // row inside the tile
                     const int col = 4 * (idx % kGroups);
@@ -487,19 +514,19 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                     }
                     const int out_row = m0 + r_tile;
                     const int n = n0 + col;
-                    if (out_row < p.M && n < p.N) emit4<kInt8>(p, out_row, n, v, push ? push_row(p.ep.push, out_row, p.N) : nullptr);
+                    if (out_row < p.M && n < p.N) emit4<kInt8>(p, out_row, n, v, push_row(p.ep.push, out_row, p.N));
                 }
             }
         }
         cl.sync();
         // every CTA of the cluster has stored its rows of the tile: the first one counts the tile
-        if (p.ep.push.peers != nullptr && warp == 2 && cl.block_rank() == 0) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
+        if (pushing && warp == 2 && cl.block_rank() == 0) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
     }
 
     tc5_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) stamp(kGemmStampStored);
-    if (p.ep.push.peers != nullptr && !p.cluster_reduce && warp == 2) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
+    if (pushing && !p.cluster_reduce && warp == 2) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
     if (warp == 1) {
         __syncwarp();
         tc5_fence_after();
@@ -629,17 +656,30 @@ bool make_out_map(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, in
     return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool kInt8>
-cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t stream) {
+template <int BN, bool kInt8, int kAux>
+cudaError_t launch_aux_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t stream) {
     const int stage_bytes = kABytes + BN * kBK;
     const int smem = plan.stages * stage_bytes + 1024 + 8 * (2 * plan.stages + 2);
     static int configured[64] = {};
-    if (cudaError_t e = ensure_dynamic_smem(gemm_tc5_kernel<BN, kInt8>, smem, configured)) return e;
+    if (cudaError_t e = ensure_dynamic_smem(gemm_tc5_kernel<BN, kInt8, kAux>, smem, configured)) return e;
     const int out_cols = plan.gate ? BN / 2 : BN;
     const int n_out = plan.gate ? plan.N / 2 : plan.N;
     dim3 grid((n_out + out_cols - 1) / out_cols, (plan.M + kBM - 1) / kBM, plan.splits);
-    return launch_ex_z(gemm_tc5_kernel<BN, kInt8>, grid, dim3(kThreads), smem, stream, plan.cluster ? plan.splits : 1, true,
+    return launch_ex_z(gemm_tc5_kernel<BN, kInt8, kAux>, grid, dim3(kThreads), smem, stream, plan.cluster ? plan.splits : 1, true,
                        plan.tma_a, plan.tma_b, args);
+}
+
+template <int BN, bool kInt8>
+cudaError_t launch_t(const GemmPlan& plan, const KernelArgs& args, cudaStream_t stream) {
+    if (args.ep.push.peers != nullptr) {
+        if (args.ep.stamps != nullptr) return cudaErrorInvalidValue;
+        return launch_aux_t<BN, kInt8, kAuxPush>(plan, args, stream);
+    }
+    if (args.ep.stamps != nullptr) {
+        if constexpr (kInt8) return launch_aux_t<BN, true, kAuxStamps>(plan, args, stream);
+        else return cudaErrorInvalidValue;          // the stamping instantiation exists for int8 operands
+    }
+    return launch_aux_t<BN, kInt8, kAuxNone>(plan, args, stream);
 }
 
 constexpr int kMaxSmem = 232448;   // dynamic shared memory a CTA may ask for on sm_100
