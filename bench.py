@@ -11,7 +11,8 @@ contents are synthetic (seeded, generated on the device; the caches are random f
 ids are the model's own greedy samples.  The timed block of K steps is repeated (up to five times inside the
 256 decode steps the workload names); `value` is the median block, Q1 / Q3 go to `repeats`.  One JSON line
 is printed by rank 0.  At N = 1 the line also carries `extra`: the quantized GEMM (T(FL)OPS, fraction of
-peak) and the paged decode attention of the kernel configurations (GB/s), timed the same way.  At N > 1 a
+peak) and the paged decode attention of the kernel configurations (GB/s), timed the same way, and the same decode
+workload in the FP8 x FP8 form of the decoder (`decode_fp8`, one block of K steps).  At N > 1 a
 small tensor-parallel decoder is first checked against the CPU decoder on both collective paths
 (`tp_parity`); a failure ends the run with a non-zero exit code.
 """

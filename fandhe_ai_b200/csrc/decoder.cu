@@ -576,7 +576,7 @@ int32_t all_reduce_sum_f32(b200_decoder* d, float* buf, size_t n) {
 }
 
 // Enqueues one decode step for the current batch on the context's stream.
-int32_t enqueue_step(b200_decoder* d) {
+int32_t enqueue_step(b200_decoder* d, bool eager = false) {
     const auto& c = d->cfg;
     cudaStream_t s = d->ctx->stream;
     uint32_t* err = d->ctx->err_dev;
@@ -596,10 +596,15 @@ int32_t enqueue_step(b200_decoder* d) {
         delivered.epoch = d->tp_epoch;
         delivered.timeout_ns = 0;
     }
+    // Bound of the cross-GPU waits of this step.  A step that is launched kernel by kernel (the first one of a decoder)
+    // also waits for the other ranks' HOST work between their launches - first-use loading of every kernel - so it gets
+    // a longer bound than the replayed graph.
+    uint64_t wait_ns = d->tp_timeout_ns ? d->tp_timeout_ns : kCrossGpuWaitNs;
+    if (eager && wait_ns < 10 * kCrossGpuWaitNs) wait_ns = 10 * kCrossGpuWaitNs;
     auto after_exchange = [&](GemmEpilogue e) {
         if (exchange) {
             e.wait = delivered;
-            if (e.wait.timeout_ns == 0) e.wait.timeout_ns = d->tp_timeout_ns;
+            e.wait.timeout_ns = wait_ns;
         }
         return e;
     };
@@ -676,7 +681,7 @@ int32_t enqueue_step(b200_decoder* d) {
         }
         if (exchange) {
             CU_TRY(tp_finish(d->tp_peers_dev, d->tp_o_sx, d->tp_o_xq, d->tp_o_part, c.tp_size, c.tp_rank, M / c.tp_size, dm, norm,
-                             c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s, d->tp_timeout_ns, kTpCountOffset,
+                             c.rms_eps, d->h, d->tp_epoch, d->tp_epoch + 1, err, s, wait_ns, kTpCountOffset,
                              push ? 1u : 0u, d->tp_epoch + 2, fp8));
             ++launches;
             return B200_OK;
@@ -1542,7 +1547,7 @@ int32_t b200_decoder_step_rows(b200_decoder* d, const int32_t* ids_host, const u
         CU_TRY(cudaGraphLaunch(d->graph, s));
     } else if (d->eager_steps_done < 1 || d->cfg.use_graph == 0) {
         // the first step runs eagerly (it also sets the kernels' shared-memory attributes)
-        if (int32_t st = enqueue_step(d)) return st;
+        if (int32_t st = enqueue_step(d, true)) return st;
         d->eager_steps_done++;
     } else {
         cudaGraph_t g = nullptr;

@@ -125,6 +125,7 @@ cudaError_t gate_rows_f32(const int* raw, int splits, int M, int F, const float*
 // block as planes [tp][rows][d] at o_part and count their launches in count[tp] at o_count (GemmPush); the kernel
 // waits until every count has grown by push_tiles (1: one count per launch) since the call before (*push_target
 // keeps the sum) and reads only its own memory.
+constexpr uint64_t kCrossGpuWaitNs = 2000000000ull;      // default bound of a cross-GPU wait (two seconds)
 bool tp_finish_supported(int d);
 cudaError_t tp_finish(uint8_t* const* peers, size_t o_sx, size_t o_xq, size_t o_part, int tp, int rank, int rows, int d,
                       const float* norm_w, float eps, float* h, uint32_t* epoch, unsigned int* arrived, uint32_t* err,

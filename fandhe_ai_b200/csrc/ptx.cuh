@@ -353,6 +353,7 @@ constexpr uint32_t kPeerPoison = 0xFFFFFFFFu;
 constexpr uint64_t kPeerWaitNs = 2000000000ull;      // default bound of a cross-GPU wait: two seconds
 
 __device__ __forceinline__ bool wait_peer_flag(const uint32_t* flag, uint32_t epoch, uint32_t* err, uint64_t timeout_ns) {
+    if (timeout_ns == 0) timeout_ns = kPeerWaitNs;      // "no bound given" means the default bound, never "no patience"
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0;; ++it) {
         const uint32_t v = ld_acquire_sys(flag);
@@ -376,6 +377,7 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
 
 __device__ __forceinline__ bool wait_peer_count(const uint32_t* count, uint32_t target, const uint32_t* poison, uint32_t* err,
                                                 uint64_t timeout_ns) {
+    if (timeout_ns == 0) timeout_ns = kPeerWaitNs;
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0;; ++it) {
         const uint32_t v = ld_acquire_sys(count);
