@@ -166,6 +166,7 @@ class CpuSample:
                           vocab=vocab_rows, max_seq_len=max_len, block_size=16)
         ref = DecoderRef.__new__(DecoderRef)
         ref.cfg, ref.tp, ref.exact, ref.blas = sample_cfg, 1, False, None
+        ref.fp8, ref._qrow, ref.sm_count = False, O.quantize_i8_per_row, 148
         ref.w = {"embed": (rng.standard_normal((vocab_rows, d)) * 0.02).astype(np.float32),
                  "final_norm": np.ones(d, np.float32),
                  "layers": [{"attn_norm": np.ones(d, np.float32), "mlp_norm": np.ones(d, np.float32)}

@@ -523,9 +523,9 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         if (pushing && warp == 2 && cl.block_rank() == 0) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
     }
 
+    if (warp == 2 && lane == 0) stamp(kGemmStampStored);      // this warp's part of the tile is stored
     tc5_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) stamp(kGemmStampStored);
     if (pushing && !p.cluster_reduce && warp == 2) push_signal(p.ep.push, lane, gridDim.x * gridDim.y);
     if (warp == 1) {
         __syncwarp();

@@ -89,7 +89,7 @@ enum GemmStamp : int {
     kGemmStampFirstTile = 4,    // MMA warp: first stage has landed in shared memory
     kGemmStampMmaIssued = 5,    // MMA warp: last MMA issued and committed
     kGemmStampAccReady = 6,     // epilogue: accumulator complete in tensor memory
-    kGemmStampStored = 7,       // epilogue: last store of the CTA issued (after the cluster reduction, if any)
+    kGemmStampStored = 7,       // epilogue: the first epilogue warp has issued its stores (after the cluster reduction, if any)
     kGemmStampExit = 8,         // tensor memory freed
     kGemmStampCount = 9
 };

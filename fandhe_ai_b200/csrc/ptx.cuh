@@ -341,7 +341,7 @@ __device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* addr) {
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");      // not to be moved across barriers or memory accesses
     return t;
 }
 

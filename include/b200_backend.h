@@ -203,7 +203,7 @@ int32_t b200_gemm_plan_info(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int3
  * (loop_us_per_launch), then one launch alone (alone_us) whose first CTA records %globaltimer at nine points;
  * stamps_ns9[i] = nanoseconds since the CTA's first instruction: 0 entry, 1 barriers + tensor memory set up, 2 the
  * launch before has completed, 3 first pass of TMA loads issued, 4 first operand stage has landed, 5 last MMA issued,
- * 6 accumulator complete, 7 all stores of the CTA issued, 8 tensor memory freed.  info6 as in b200_gemm_plan_info.
+ * 6 accumulator complete, 7 the first epilogue warp has issued its stores, 8 tensor memory freed.  info6 as in b200_gemm_plan_info.
  * fused = 0: raw accumulators; 1: the dequantising epilogue.  Operands are zero-filled.  No reference counterpart. */
 int32_t b200_gemm_phase_stamps(b200_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t fused, int32_t iters, uint64_t* stamps_ns9,
                                float* loop_us_per_launch, float* alone_us, int32_t* info6);
