@@ -488,3 +488,42 @@ def test_fp8_decoder_is_not_the_int8_decoder(be):
     span = float(np.abs(want8).max())
     assert float(np.abs(out["fp8"] - want8).max()) / span < 2e-2
     assert float(np.abs(out["fp8"] - out["int8"]).max()) / span > 2e-2
+
+
+def test_fp8_decoder_re_encodes_int8_payloads(be, tmp_path):
+    """An int8 safetensors file loaded into the FP8 form: every payload is dequantised and re-encoded to E4M3 under
+    new per-row scales on the device.  The logits equal - within the FP8 tolerance - those of the CPU FP8 decoder
+    built from the dequantised weights."""
+    from fandhe_ai_b200.decoder import write_safetensors
+
+    cfg = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512, vocab=512, max_seq_len=16)
+    weights = make_weights(cfg, seed=61)
+    tensors = {"embed.weight": weights["embed"], "final_norm.weight": weights["final_norm"]}
+    deq = {"embed": weights["embed"], "final_norm": weights["final_norm"], "layers": []}
+    q, s = O.quantize_i8_per_row(weights["lm_head"])
+    tensors["lm_head.qweight"], tensors["lm_head.scale"] = q, s
+    deq["lm_head"] = O.dequantize_i8_per_row(q, s)
+    for l, lw in enumerate(weights["layers"]):
+        dl = {}
+        for norm in ("attn_norm", "mlp_norm"):
+            tensors[f"layers.{l}.{norm}.weight"] = lw[norm]
+            dl[norm] = lw[norm]
+        for m in ("wqkv", "wo", "wgu", "wdown"):
+            q, s = O.quantize_i8_per_row(lw[m])
+            tensors[f"layers.{l}.{m}.qweight"], tensors[f"layers.{l}.{m}.scale"] = q, s
+            dl[m] = O.dequantize_i8_per_row(q, s)
+        deq["layers"].append(dl)
+    write_safetensors(tmp_path / "i8.safetensors", tensors)
+    ids = np.array([7, 300, 41], np.int32)
+    ref = DecoderRef(cfg, deq, fp8=True)
+    ref.begin(3)
+    want, _ = ref.step(ids)
+    dec = make_fp8_decoder(be, cfg, 3)
+    try:
+        dec.load_safetensors(tmp_path / "i8.safetensors")
+        dec.begin(3, [4] * 3)
+        dec.step(ids)
+        got = dec.logits()
+    finally:
+        dec.close()
+    assert float(np.abs(got - want).max()) / float(np.abs(want).max()) < 2e-2
