@@ -304,11 +304,12 @@ __device__ __forceinline__ float exp_det(float x) {
     return __fmul_rn(y, __int_as_float((b + 127) << 23));
 }
 
-// Two-branch sigmoid: never exponentiates a positive argument.
+// Two-branch sigmoid (never exponentiates a positive argument): 1 / (1 + e^-x) for x >= 0, e^x / (1 + e^x) below.
+// Written without a branch - both forms exponentiate -|x| - so that a warp whose lanes differ in sign evaluates one
+// exponential and one division per value instead of both paths; the results are those of the two-branch form bit for bit.
 __device__ __forceinline__ float sigmoid_stable(float x) {
-    if (x >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_det(-x)));
-    const float e = exp_det(x);
-    return __fdiv_rn(e, __fadd_rn(1.0f, e));
+    const float e = exp_det(-fabsf(x));
+    return __fdiv_rn(x >= 0.0f ? 1.0f : e, __fadd_rn(1.0f, e));
 }
 __device__ __forceinline__ float silu(float x) { return __fmul_rn(x, sigmoid_stable(x)); }
 
