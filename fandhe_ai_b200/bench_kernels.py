@@ -172,6 +172,8 @@ def run_gemm_phases(args):
     """Where the time of a decode-shaped GEMM launch goes: the M = 1 / 16 / 128 shapes of the weight sweep (or --shape),
     raw accumulators and the dequantising epilogue, %globaltimer stamps of the launch's first CTA."""
     be = Backend(0)
+    if args.tile or args.splits:
+        be.gemm_tuning(args.tile, args.splits)
     if args.shape:
         shapes = [tuple(int(x) for x in args.shape.split(","))]
     else:
