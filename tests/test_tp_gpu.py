@@ -30,6 +30,23 @@ def test_two_rank_tensor_parallel_decode_matches_the_cpu_decoder(exchange):
     assert f"exchange={exchange}" in r.stdout, r.stdout[-3000:]
 
 
+@pytest.mark.parametrize("exchange", ["2", "0"])
+def test_two_rank_fp8_decoder_matches_the_cpu_fp8_decoder(exchange):
+    """The FP8 x FP8 form under tensor parallelism (E4M3 rows delivered by the finish kernel, f32 accumulators scattered
+    by the row-parallel GEMMs; or ncclAllReduce) against the CPU FP8 decoder with the same rank split."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200_TP_FP8="1", B200_TP_EXCHANGE="0" if exchange == "0" else "1",
+               B200_TP_PUSH="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29735", str(ROOT / "tests" / "multi" / "tp_worker.py")]
+    r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_OK" in r.stdout, r.stdout[-8000:]
+    assert f"exchange={exchange}" in r.stdout, r.stdout[-3000:]
+
+
 def test_two_rank_exact_int8_gives_the_logits_of_one_gpu():
     """tp_exact_int8 = 1: one per-token scale over the ranks (max all-reduce) and int32 partial sums (sum all-reduce):
     ids and logits equal those of the kernel-order CPU decoder WITHOUT tensor parallelism, bit for bit."""
